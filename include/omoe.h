@@ -1,0 +1,165 @@
+/*
+ * omoe.h — C ABI of libomoe.so: the mixture-of-experts FFN forward for
+ * Omega-AI, built for NVIDIA B200 (sm_100a).
+ *
+ * The library takes the place of the JCuda "load a CUfunction by name and
+ * cuLaunchKernel it" plumbing for this one layer.  A Java layer (or any other
+ * host) passes raw 64-bit device addresses and sizes; no C++ or torch types
+ * cross this boundary.  Every call returns OMOE_OK (0) or a negative
+ * OMOE_ERR_* code and never exits the process or throws.
+ *
+ * Conventions shared by all entry points
+ *   - Weights are row-major [out,in], as the engine's FullyLayer stores them
+ *     (src/main/java/com/omega/engine/nn/layer/FullyLayer.java:181), experts
+ *     contiguous on the leading dimension.
+ *   - Work is enqueued on the CUDA stream the caller passes; 0 means the legacy
+ *     default stream, which is what every reference kernel launch uses
+ *     (src/main/java/com/omega/engine/gpu/BaseKernel.java:66-72), so later
+ *     JCuda work is ordered after it without extra synchronisation.
+ *   - The library runs in the caller's current CUDA context and on its current
+ *     device; it never switches devices and never frees caller buffers.
+ *   - A handle is used by one host thread at a time.
+ */
+#ifndef OMOE_H
+#define OMOE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OMOE_VERSION 1
+
+#if defined(__GNUC__)
+#define OMOE_API __attribute__((visibility("default")))
+#else
+#define OMOE_API
+#endif
+
+/* element types for weights and activations */
+#define OMOE_F32 0
+#define OMOE_BF16 1
+
+/* status codes */
+#define OMOE_OK 0
+#define OMOE_ERR_INVALID (-1)      /* bad argument (null pointer, bad shape, bad dtype) */
+#define OMOE_ERR_CUDA (-2)         /* a CUDA runtime/driver call failed */
+#define OMOE_ERR_TOO_LARGE (-3)    /* T exceeds the handle's t_max (no hidden realloc) */
+#define OMOE_ERR_STATE (-4)        /* call order (e.g. forward before set_weights) */
+#define OMOE_ERR_UNSUPPORTED (-5)  /* shape not supported by the selected arithmetic */
+#define OMOE_ERR_DEVICE (-6)       /* a kernel reported a device-side error word */
+#define OMOE_ERR_COMM (-7)         /* expert-parallel transport failed */
+#define OMOE_ERR_NOMEM (-8)        /* device or host allocation failed */
+
+typedef struct omoe_handle omoe_handle;
+
+/*
+ * Layer description.  Mirrors the constructor arguments of the Java layer
+ * (embedDim, dff, numExperts, topK, bias, network) that sits where
+ * LlamaMLPLayer is built today
+ * (src/main/java/com/omega/engine/nn/layer/llama/LlamaTransformerBlock.java:97).
+ */
+typedef struct omoe_config {
+    int32_t t_max;           /* largest token count one forward may carry on this rank */
+    int32_t d_model;         /* multiple of 8 */
+    int32_t d_ff;            /* multiple of 8 */
+    int32_t n_experts;       /* global expert count E */
+    int32_t top_k;           /* 1..min(E,16) */
+    int32_t compute_dtype;   /* OMOE_F32: fp32 FMA everywhere; OMOE_BF16: bf16 tensor cores, fp32 accumulate */
+    int32_t renormalize;     /* 1: gate weights divided by the sum over the k picks */
+    int32_t has_router_bias; /* 1: a per-expert bias is added to the router logits */
+    int32_t world;           /* expert-parallel ranks (1 = single GPU) */
+    int32_t rank;            /* this rank; owns experts [rank*E/world, (rank+1)*E/world) */
+    int32_t recv_rows_max;   /* EP only: capacity (rows) of the buffer that receives dispatched
+                                tokens; 0 = t_max*top_k*world (worst case) */
+    int32_t reserved[5];     /* must be zero */
+} omoe_config;
+
+/* Replaces: constructing the layer's kernels (BaseKernel.java:38-56 loads the
+ * CUfunctions; FullyLayer.initKernel at FullyLayer.java:108-114).  Allocates
+ * the workspace (dispatch buffers, maps, bf16 weight copies) once. */
+OMOE_API int omoe_create(const omoe_config *cfg, omoe_handle **out);
+OMOE_API int omoe_destroy(omoe_handle *h);
+
+/* Message for the last error on this handle (or on the last failed create
+ * when h is NULL).  The pointer stays valid until the next call on the handle. */
+OMOE_API const char *omoe_last_error(const omoe_handle *h);
+
+/*
+ * Copies (and for compute_dtype=BF16 converts) the weights from DEVICE memory.
+ *   w_router [E, d]              always kept in fp32 for the router
+ *   router_bias [E] or NULL
+ *   w_gate, w_up [E_local, d_ff, d]   (linear1 and linear3 of LlamaMLPLayer,
+ *   w_down [E_local, d, d_ff]          linear2; LlamaMLPLayer.java:70-87)
+ * E_local = E/world experts owned by this rank, in global expert order.
+ * src_dtype is the element type of all five buffers.
+ * Replaces: the per-layer weight tensors handed to cublasSgemm
+ * (FullyLayer.java:235 -> GPUOP.java:405-417).
+ */
+OMOE_API int omoe_set_weights(omoe_handle *h, const void *w_router, const void *router_bias,
+                     const void *w_gate, const void *w_up, const void *w_down,
+                     int32_t src_dtype, void *cuda_stream);
+
+/*
+ * y[T, d] = MoE(x[T, d]) with x and y in DEVICE memory of element type
+ * io_dtype.  Replaces LlamaMLPLayer.output()
+ * (LlamaMLPLayer.java:117-130: linear1 -> SiLU -> linear3 -> mul -> linear2)
+ * with router -> top-k -> dispatch -> grouped SwiGLU -> combine.  Does not
+ * synchronise the host.  With world > 1 this is a collective call: every rank
+ * calls it with its own T tokens (T may differ per rank).
+ */
+OMOE_API int omoe_forward(omoe_handle *h, const void *x_dev, void *y_dev, int32_t T,
+                 int32_t io_dtype, void *cuda_stream);
+
+/*
+ * Same layer with x and y in HOST memory (pinned memory makes the copies
+ * asynchronous).  This is the call behind Layer.forward(Tensor) for a Tensor
+ * whose data lives in its float[] (Tensor.hostToDevice / syncHost,
+ * src/main/java/com/omega/engine/tensor/Tensor.java:559-579): H2D copy of x,
+ * forward, D2H copy of y, then a stream synchronise so y is readable on return.
+ */
+OMOE_API int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host, int32_t T,
+                      int32_t io_dtype, void *cuda_stream);
+
+/*
+ * Routing results of the last forward on this rank, copied to HOST buffers
+ * (any may be NULL).  Synchronises the stream of that forward.
+ *   topk_idx [T, k] int32, topk_w [T, k] fp32, counts [E] int32,
+ *   offsets [E+1] int32 (exclusive scan of counts),
+ *   perm [T*k] int32: perm[offsets[e]+r] = t*k+j, expert-major, stable in t*k+j.
+ * There is no reference counterpart; this exists so parity tests can compare
+ * indices, counts and the permutation bit for bit.
+ */
+OMOE_API int omoe_get_routing(omoe_handle *h, int32_t *topk_idx, float *topk_w, int32_t *counts,
+                     int32_t *offsets, int32_t *perm);
+
+/* Router logits [T, E] fp32 of the last forward, to a HOST buffer (debug/parity). */
+OMOE_API int omoe_get_logits(omoe_handle *h, float *logits);
+
+/* Kernels launched by the last forward on this handle (for accounting). */
+OMOE_API int omoe_last_launch_count(const omoe_handle *h);
+
+/* Per-stage device times of the last forward in milliseconds, when stage
+ * timing was enabled with omoe_set_profiling(h, 1).  Order: router, scan,
+ * permute, dispatch, up_gate, down, return, combine.  Synchronises. */
+#define OMOE_N_STAGES 8
+OMOE_API int omoe_set_profiling(omoe_handle *h, int32_t enabled);
+OMOE_API int omoe_get_stage_ms(omoe_handle *h, float *ms /* [OMOE_N_STAGES] */);
+
+/*
+ * Expert-parallel transport.  The reference's only multi-GPU mechanism is
+ * cudaMemcpyPeerAsync between Java threads
+ * (src/main/java/com/omega/engine/parallel/dp/NetworkRunnable.java:442-459);
+ * here ranks are processes and rows travel by NCCL all-to-all.
+ * omoe_ep_unique_id fills a 128-byte NCCL id on rank 0; the host shares it
+ * with every rank by any means, then each rank calls omoe_ep_init.
+ */
+#define OMOE_EP_ID_BYTES 128
+OMOE_API int omoe_ep_unique_id(void *id_out /* [OMOE_EP_ID_BYTES] */);
+OMOE_API int omoe_ep_init(omoe_handle *h, const void *id /* [OMOE_EP_ID_BYTES] */);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OMOE_H */

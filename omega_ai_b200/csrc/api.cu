@@ -1,0 +1,396 @@
+// C ABI of libomoe.so (declared in include/omoe.h): handle life cycle, weight
+// upload, the forward pass and the read-outs used by parity tests.
+#include <stdarg.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <new>
+
+#include "common.cuh"
+#include "ep.cuh"
+
+using namespace omoe;
+
+namespace {
+
+thread_local char g_create_err[512] = "";
+
+int fail(omoe_handle *h, int code, const char *fmt, ...) {
+    char *dst = h ? h->err : g_create_err;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(dst, 512, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define CU_TRY(h, expr)                                                                            \
+    do {                                                                                           \
+        cudaError_t _e = (expr);                                                                   \
+        if (_e != cudaSuccess)                                                                     \
+            return fail(h, _e == cudaErrorMemoryAllocation ? OMOE_ERR_NOMEM : OMOE_ERR_CUDA,       \
+                        "%s failed: %s", #expr, cudaGetErrorString(_e));                           \
+    } while (0)
+
+template <typename T>
+cudaError_t dev_alloc(T **p, size_t count) {
+    *p = nullptr;
+    if (count == 0) count = 1;
+    return cudaMalloc(reinterpret_cast<void **>(p), count * sizeof(T));
+}
+
+size_t elt_size(int dtype) { return dtype == OMOE_BF16 ? 2 : 4; }
+
+__global__ void f32_to_bf16_kernel(const float *__restrict__ src, __nv_bfloat16 *__restrict__ dst, int64_t n) {
+    int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x * 4;
+    for (; i + 3 < n; i += stride) {
+        float4 v = *reinterpret_cast<const float4 *>(src + i);
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t *>(&a);
+        o.y = *reinterpret_cast<uint32_t *>(&b);
+        *reinterpret_cast<uint2 *>(dst + i) = o;
+    }
+}
+
+__global__ void bf16_to_f32_kernel(const __nv_bfloat16 *__restrict__ src, float *__restrict__ dst, int64_t n) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) dst[i] = __bfloat162float(src[i]);
+}
+
+int check_dev_err(omoe_handle *h) {
+    int32_t v = 0;
+    CU_TRY(h, cudaMemcpy(&v, h->dev_err, sizeof(v), cudaMemcpyDeviceToHost));
+    if (v != 0) {
+        cudaMemset(h->dev_err, 0, sizeof(int32_t));
+        return fail(h, OMOE_ERR_DEVICE, "device error word = %d (%s%s)", v,
+                    (v & kDevErrTimeout) ? "a bounded wait ran out " : "",
+                    (v & kDevErrBounds) ? "an index check failed" : "");
+    }
+    return OMOE_OK;
+}
+
+}  // namespace
+
+namespace omoe {
+
+cudaError_t launch_convert_f32_to_bf16(const float *src, __nv_bfloat16 *dst, int64_t n, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    int64_t blocks = (n / 4 + 255) / 256;  // n is a multiple of 8 for every weight tensor
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    f32_to_bf16_kernel<<<(int)blocks, 256, 0, s>>>(src, dst, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_convert_bf16_to_f32(const __nv_bfloat16 *src, float *dst, int64_t n, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    bf16_to_f32_kernel<<<(int)blocks, 256, 0, s>>>(src, dst, n);
+    return cudaGetLastError();
+}
+
+}  // namespace omoe
+
+extern "C" {
+
+const char *omoe_last_error(const omoe_handle *h) { return h ? h->err : g_create_err; }
+
+int omoe_destroy(omoe_handle *h) {
+    if (!h) return OMOE_OK;
+    ep_destroy(h);
+    void *ptrs[] = {h->w_router, h->router_bias, h->w_gate, h->w_up, h->w_down, h->logits, h->topk_idx,
+                    h->topk_w, h->block_counts, h->counts, h->offsets, h->poffsets, h->tile_expert, h->pos,
+                    h->perm_out, h->dev_err, h->xp, h->hbuf, h->yp, h->x_stage, h->y_stage};
+    for (void *p : ptrs)
+        if (p) cudaFree(p);
+    for (int i = 0; i <= OMOE_N_STAGES; i++)
+        if (h->ev[i]) cudaEventDestroy(h->ev[i]);
+    delete h;
+    return OMOE_OK;
+}
+
+int omoe_create(const omoe_config *cfg, omoe_handle **out) {
+    if (!cfg || !out) return fail(nullptr, OMOE_ERR_INVALID, "omoe_create: null argument");
+    *out = nullptr;
+    const omoe_config &c = *cfg;
+    if (c.t_max <= 0 || c.d_model <= 0 || c.d_ff <= 0 || c.n_experts <= 0 || c.top_k <= 0)
+        return fail(nullptr, OMOE_ERR_INVALID, "omoe_create: sizes must be positive");
+    if (c.d_model % 8 || c.d_ff % 8)
+        return fail(nullptr, OMOE_ERR_INVALID, "omoe_create: d_model and d_ff must be multiples of 8");
+    if (c.n_experts > kMaxExperts)
+        return fail(nullptr, OMOE_ERR_UNSUPPORTED, "omoe_create: at most %d experts", kMaxExperts);
+    if (c.top_k > c.n_experts || c.top_k > kMaxTopK)
+        return fail(nullptr, OMOE_ERR_INVALID, "omoe_create: top_k must be <= min(n_experts, %d)", kMaxTopK);
+    if (c.compute_dtype != OMOE_F32 && c.compute_dtype != OMOE_BF16)
+        return fail(nullptr, OMOE_ERR_INVALID, "omoe_create: compute_dtype must be OMOE_F32 or OMOE_BF16");
+    if (c.world < 1 || c.rank < 0 || c.rank >= c.world || c.n_experts % c.world)
+        return fail(nullptr, OMOE_ERR_INVALID, "omoe_create: need 0 <= rank < world and world dividing n_experts");
+    if (c.compute_dtype == OMOE_BF16 && (c.d_model < 64 || c.d_ff < 64))
+        return fail(nullptr, OMOE_ERR_UNSUPPORTED, "omoe_create: the bf16 path needs d_model, d_ff >= 64");
+    for (int i = 0; i < 5; i++)
+        if (c.reserved[i] != 0) return fail(nullptr, OMOE_ERR_INVALID, "omoe_create: reserved fields must be zero");
+
+    int dev = 0, major = 0, sms = 0;
+    CU_TRY(nullptr, cudaGetDevice(&dev));
+    CU_TRY(nullptr, cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    CU_TRY(nullptr, cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (major != 10)
+        return fail(nullptr, OMOE_ERR_UNSUPPORTED,
+                    "omoe_create: this library is built for sm_100a only (device has compute capability %d.x)", major);
+
+    omoe_handle *h = new (std::nothrow) omoe_handle();
+    if (!h) return fail(nullptr, OMOE_ERR_NOMEM, "omoe_create: host allocation failed");
+    memset(h, 0, sizeof(*h));
+    h->cfg = c;
+    h->e_local = c.n_experts / c.world;
+    h->e_first = c.rank * h->e_local;
+    h->sm_count = sms;
+    h->tokens_per_block = router_tokens_per_block(c.n_experts);
+    h->n_blocks_max = ceil_div(c.t_max, h->tokens_per_block);
+
+    const int64_t E = c.n_experts, k = c.top_k, d = c.d_model, dff = c.d_ff, tm = c.t_max;
+    // Rows the expert kernels may see on this rank: its own picks on one GPU,
+    // or up to recv_rows_max rows arriving from all ranks.
+    int64_t rows_in = tm * k;
+    if (c.world > 1) rows_in = c.recv_rows_max > 0 ? (int64_t)c.recv_rows_max : tm * k * c.world;
+    // the send-side dispatch buffer is laid out over all E experts, the
+    // receive side over the local ones; one capacity covers both
+    int64_t pad_experts = c.world > 1 ? E : h->e_local;
+    int64_t rows_send = (ceil_div((int)(tm * k), kRowAlign) + E) * (int64_t)kRowAlign;
+    int64_t rows_recv = ((rows_in + kRowAlign - 1) / kRowAlign + pad_experts) * (int64_t)kRowAlign;
+    h->rows_cap = rows_send > rows_recv ? rows_send : rows_recv;
+    const size_t cs = elt_size(c.compute_dtype);
+
+#define ALLOC(field, count)                                                          \
+    do {                                                                             \
+        cudaError_t _e = dev_alloc(&h->field, (size_t)(count));                      \
+        if (_e != cudaSuccess) {                                                     \
+            int rc = fail(nullptr, OMOE_ERR_NOMEM, "omoe_create: cudaMalloc(%s, %lld) failed: %s", #field, \
+                          (long long)(count), cudaGetErrorString(_e));               \
+            omoe_destroy(h);                                                         \
+            return rc;                                                               \
+        }                                                                            \
+    } while (0)
+
+    ALLOC(w_router, E * d);
+    if (c.has_router_bias) ALLOC(router_bias, E);
+    {
+        struct { void **p; size_t bytes; } bufs[] = {
+            {&h->w_gate, (size_t)h->e_local * dff * d * cs}, {&h->w_up, (size_t)h->e_local * dff * d * cs},
+            {&h->w_down, (size_t)h->e_local * dff * d * cs}, {&h->xp, (size_t)h->rows_cap * d * cs},
+            {&h->hbuf, (size_t)h->rows_cap * dff * cs},      {&h->yp, (size_t)h->rows_cap * d * cs},
+            {&h->x_stage, (size_t)tm * d * 4},               {&h->y_stage, (size_t)tm * d * 4}};
+        h->stage_bytes = (size_t)tm * d * 4;
+        for (auto &b : bufs) {
+            cudaError_t e = cudaMalloc(b.p, b.bytes ? b.bytes : 1);
+            if (e != cudaSuccess) {
+                *b.p = nullptr;
+                int rc = fail(nullptr, OMOE_ERR_NOMEM, "omoe_create: cudaMalloc of %zu bytes failed: %s", b.bytes,
+                              cudaGetErrorString(e));
+                omoe_destroy(h);
+                return rc;
+            }
+        }
+    }
+    ALLOC(logits, tm * E);
+    ALLOC(topk_idx, tm * k);
+    ALLOC(topk_w, tm * k);
+    ALLOC(block_counts, (int64_t)h->n_blocks_max * E);
+    ALLOC(counts, E);
+    ALLOC(offsets, E + 1);
+    ALLOC(poffsets, E + 1);
+    ALLOC(tile_expert, h->rows_cap / kRowAlign);
+    ALLOC(pos, tm * k);
+    ALLOC(perm_out, tm * k);
+    ALLOC(dev_err, 1);
+#undef ALLOC
+    h->ex_counts = h->counts;
+    h->ex_poffsets = h->poffsets;
+    h->ex_tile_expert = h->tile_expert;
+    cudaMemset(h->dev_err, 0, sizeof(int32_t));
+    // padding rows of the dispatch buffers are never read back, but start them
+    // at zero so no stale NaN pattern ever enters a tensor-core tile
+    cudaMemset(h->xp, 0, (size_t)h->rows_cap * d * cs);
+    for (int i = 0; i <= OMOE_N_STAGES; i++)
+        if (cudaEventCreate(&h->ev[i]) != cudaSuccess) {
+            int rc = fail(nullptr, OMOE_ERR_CUDA, "omoe_create: cudaEventCreate failed");
+            omoe_destroy(h);
+            return rc;
+        }
+    if (c.compute_dtype == OMOE_BF16 && !build_tensor_maps(h)) {
+        int rc = fail(nullptr, OMOE_ERR_CUDA, "omoe_create: %s", h->err);
+        omoe_destroy(h);
+        return rc;
+    }
+    if (cudaDeviceSynchronize() != cudaSuccess) {
+        int rc = fail(nullptr, OMOE_ERR_CUDA, "omoe_create: device synchronise failed");
+        omoe_destroy(h);
+        return rc;
+    }
+    h->err[0] = 0;
+    *out = h;
+    return OMOE_OK;
+}
+
+int omoe_set_weights(omoe_handle *h, const void *w_router, const void *router_bias, const void *w_gate,
+                     const void *w_up, const void *w_down, int32_t src_dtype, void *cuda_stream) {
+    if (!h) return OMOE_ERR_INVALID;
+    if (!w_router || !w_gate || !w_up || !w_down) return fail(h, OMOE_ERR_INVALID, "omoe_set_weights: null weight pointer");
+    if (src_dtype != OMOE_F32 && src_dtype != OMOE_BF16) return fail(h, OMOE_ERR_INVALID, "omoe_set_weights: bad src_dtype");
+    if (h->cfg.has_router_bias && !router_bias)
+        return fail(h, OMOE_ERR_INVALID, "omoe_set_weights: the layer was created with a router bias but none was given");
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    const int64_t E = h->cfg.n_experts, d = h->cfg.d_model, dff = h->cfg.d_ff, El = h->e_local;
+    const int64_t n_exp = El * dff * d;
+    // router weights and bias are always held in fp32
+    if (src_dtype == OMOE_F32) {
+        CU_TRY(h, cudaMemcpyAsync(h->w_router, w_router, E * d * 4, cudaMemcpyDeviceToDevice, s));
+        if (h->cfg.has_router_bias)
+            CU_TRY(h, cudaMemcpyAsync(h->router_bias, router_bias, E * 4, cudaMemcpyDeviceToDevice, s));
+    } else {
+        CU_TRY(h, launch_convert_bf16_to_f32(static_cast<const __nv_bfloat16 *>(w_router), h->w_router, E * d, s));
+        if (h->cfg.has_router_bias)
+            CU_TRY(h, launch_convert_bf16_to_f32(static_cast<const __nv_bfloat16 *>(router_bias), h->router_bias, E, s));
+    }
+    const void *src[3] = {w_gate, w_up, w_down};
+    void *dst[3] = {h->w_gate, h->w_up, h->w_down};
+    for (int i = 0; i < 3; i++) {
+        if (h->cfg.compute_dtype == OMOE_BF16) {
+            if (src_dtype == OMOE_BF16)
+                CU_TRY(h, cudaMemcpyAsync(dst[i], src[i], n_exp * 2, cudaMemcpyDeviceToDevice, s));
+            else
+                CU_TRY(h, launch_convert_f32_to_bf16(static_cast<const float *>(src[i]),
+                                                     static_cast<__nv_bfloat16 *>(dst[i]), n_exp, s));
+        } else {
+            if (src_dtype == OMOE_F32)
+                CU_TRY(h, cudaMemcpyAsync(dst[i], src[i], n_exp * 4, cudaMemcpyDeviceToDevice, s));
+            else
+                CU_TRY(h, launch_convert_bf16_to_f32(static_cast<const __nv_bfloat16 *>(src[i]),
+                                                     static_cast<float *>(dst[i]), n_exp, s));
+        }
+    }
+    h->weights_set = true;
+    return OMOE_OK;
+}
+
+int omoe_forward(omoe_handle *h, const void *x_dev, void *y_dev, int32_t T, int32_t io_dtype, void *cuda_stream) {
+    if (!h) return OMOE_ERR_INVALID;
+    if (!h->weights_set) return fail(h, OMOE_ERR_STATE, "omoe_forward: call omoe_set_weights first");
+    if (T < 0) return fail(h, OMOE_ERR_INVALID, "omoe_forward: negative token count");
+    if (T > h->cfg.t_max) return fail(h, OMOE_ERR_TOO_LARGE, "omoe_forward: T=%d exceeds t_max=%d", T, h->cfg.t_max);
+    if (io_dtype != OMOE_F32 && io_dtype != OMOE_BF16) return fail(h, OMOE_ERR_INVALID, "omoe_forward: bad io_dtype");
+    if (h->cfg.compute_dtype == OMOE_F32 && io_dtype != OMOE_F32)
+        return fail(h, OMOE_ERR_UNSUPPORTED, "omoe_forward: an fp32 layer takes fp32 rows");
+    if (T > 0 && (!x_dev || !y_dev)) return fail(h, OMOE_ERR_INVALID, "omoe_forward: null buffer");
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    h->last_T = T;
+    h->last_io_dtype = io_dtype;
+    h->last_stream = s;
+    h->last_launches = 0;
+    h->ev_valid = false;
+    if (h->cfg.world > 1) return ep_forward(h, x_dev, y_dev, T, io_dtype, s);
+    if (T == 0) return OMOE_OK;
+
+    int n = 0;
+    const bool prof = h->profiling;
+#define MARK(i) do { if (prof) cudaEventRecord(h->ev[i], s); } while (0)
+    MARK(0);
+    CU_TRY(h, launch_router(h, x_dev, io_dtype, T, s, &n));
+    MARK(1);
+    CU_TRY(h, launch_scan(h, T, s, &n));
+    MARK(2);
+    CU_TRY(h, launch_permute(h, x_dev, io_dtype, T, s, &n));
+    MARK(3);
+    MARK(4);
+    if (h->cfg.compute_dtype == OMOE_BF16) {
+        CU_TRY(h, launch_experts_bf16(h, s, &n, prof ? h->ev[5] : nullptr));
+    } else {
+        CU_TRY(h, launch_experts_f32(h, s, &n));
+        MARK(5);
+    }
+    MARK(6);
+    MARK(7);
+    CU_TRY(h, launch_combine(h, y_dev, io_dtype, T, s, &n));
+    MARK(8);
+#undef MARK
+    h->ev_valid = prof;
+    h->last_launches = n;
+    return OMOE_OK;
+}
+
+int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host, int32_t T, int32_t io_dtype,
+                      void *cuda_stream) {
+    if (!h) return OMOE_ERR_INVALID;
+    if (T < 0 || T > h->cfg.t_max)
+        return fail(h, T < 0 ? OMOE_ERR_INVALID : OMOE_ERR_TOO_LARGE, "omoe_forward_host: T=%d outside [0, %d]", T,
+                    h->cfg.t_max);
+    if (io_dtype != OMOE_F32 && io_dtype != OMOE_BF16) return fail(h, OMOE_ERR_INVALID, "omoe_forward_host: bad io_dtype");
+    if (T > 0 && (!x_host || !y_host)) return fail(h, OMOE_ERR_INVALID, "omoe_forward_host: null buffer");
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    const size_t bytes = (size_t)T * h->cfg.d_model * elt_size(io_dtype);
+    if (bytes) CU_TRY(h, cudaMemcpyAsync(h->x_stage, x_host, bytes, cudaMemcpyHostToDevice, s));
+    int rc = omoe_forward(h, h->x_stage, h->y_stage, T, io_dtype, s);
+    if (rc != OMOE_OK) return rc;
+    if (bytes) CU_TRY(h, cudaMemcpyAsync(y_host, h->y_stage, bytes, cudaMemcpyDeviceToHost, s));
+    CU_TRY(h, cudaStreamSynchronize(s));
+    return check_dev_err(h);
+}
+
+int omoe_get_routing(omoe_handle *h, int32_t *topk_idx, float *topk_w, int32_t *counts, int32_t *offsets,
+                     int32_t *perm) {
+    if (!h) return OMOE_ERR_INVALID;
+    const int T = h->last_T, k = h->cfg.top_k, E = h->cfg.n_experts;
+    cudaStream_t s = h->last_stream;
+    if (perm && T > 0) CU_TRY(h, launch_perm_readout(h, T, s));
+    CU_TRY(h, cudaStreamSynchronize(s));
+    int rc = check_dev_err(h);
+    if (rc != OMOE_OK) return rc;
+    const size_t n = (size_t)T * k;
+    if (topk_idx && n) CU_TRY(h, cudaMemcpy(topk_idx, h->topk_idx, n * 4, cudaMemcpyDeviceToHost));
+    if (topk_w && n) CU_TRY(h, cudaMemcpy(topk_w, h->topk_w, n * 4, cudaMemcpyDeviceToHost));
+    if (T == 0) {
+        if (counts) memset(counts, 0, sizeof(int32_t) * E);
+        if (offsets) memset(offsets, 0, sizeof(int32_t) * (E + 1));
+        return OMOE_OK;
+    }
+    if (counts) CU_TRY(h, cudaMemcpy(counts, h->counts, sizeof(int32_t) * E, cudaMemcpyDeviceToHost));
+    if (offsets) CU_TRY(h, cudaMemcpy(offsets, h->offsets, sizeof(int32_t) * (E + 1), cudaMemcpyDeviceToHost));
+    if (perm && n) CU_TRY(h, cudaMemcpy(perm, h->perm_out, n * 4, cudaMemcpyDeviceToHost));
+    return OMOE_OK;
+}
+
+int omoe_get_logits(omoe_handle *h, float *logits) {
+    if (!h || !logits) return OMOE_ERR_INVALID;
+    CU_TRY(h, cudaStreamSynchronize(h->last_stream));
+    const size_t n = (size_t)h->last_T * h->cfg.n_experts;
+    if (n) CU_TRY(h, cudaMemcpy(logits, h->logits, n * 4, cudaMemcpyDeviceToHost));
+    return OMOE_OK;
+}
+
+int omoe_last_launch_count(const omoe_handle *h) { return h ? h->last_launches : 0; }
+
+int omoe_set_profiling(omoe_handle *h, int32_t enabled) {
+    if (!h) return OMOE_ERR_INVALID;
+    h->profiling = enabled != 0;
+    return OMOE_OK;
+}
+
+int omoe_get_stage_ms(omoe_handle *h, float *ms) {
+    if (!h || !ms) return OMOE_ERR_INVALID;
+    if (!h->ev_valid) return fail(h, OMOE_ERR_STATE, "omoe_get_stage_ms: profiling was off for the last forward");
+    CU_TRY(h, cudaEventSynchronize(h->ev[OMOE_N_STAGES]));
+    for (int i = 0; i < OMOE_N_STAGES; i++) CU_TRY(h, cudaEventElapsedTime(&ms[i], h->ev[i], h->ev[i + 1]));
+    return check_dev_err(h);
+}
+
+int omoe_ep_unique_id(void *id_out) { return ep_unique_id(id_out); }
+
+int omoe_ep_init(omoe_handle *h, const void *id) {
+    if (!h || !id) return OMOE_ERR_INVALID;
+    return ep_init(h, id);
+}
+
+}  // extern "C"

@@ -1,0 +1,121 @@
+// Gate-weighted combine: y[t,:] = ((w0*yp[p0,:]) + w1*yp[p1,:]) + ... in pick
+// order with fp32 accumulation, reading every expert output row exactly once
+// and holding the k gate weights and row positions in registers.
+//
+// No reference kernel exists for this stage; the nearest idiom is the
+// accumulate kernel axpy_kernel (src/main/java/com/omega/engine/gpu/BaseKernel.java:306-329)
+// and the residual add at LlamaTransformerBlock.java:136.
+#include "common.cuh"
+
+namespace omoe {
+
+namespace {
+
+__device__ __forceinline__ void unpack8(const uint4 &r, float (&v)[8]) {
+    uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// One warp per token, 8 columns per lane per step (16 bytes of bf16 / 32 bytes of fp32).
+template <typename YT, typename OT, int K>
+__global__ void __launch_bounds__(256)
+combine_kernel(const YT *__restrict__ yp, OT *__restrict__ y, const int32_t *__restrict__ pos,
+               const float *__restrict__ topk_w, int T, int d, int k_rt) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T) return;
+    const int k = (K > 0) ? K : k_rt;
+    constexpr int KR = (K > 0) ? K : kMaxTopK;
+    int row[KR];
+    float w[KR];
+    {
+        int r = 0;
+        float g = 0.f;
+        if (lane < k) {
+            r = pos[(size_t)t * k + lane];
+            g = topk_w[(size_t)t * k + lane];
+        }
+#pragma unroll
+        for (int j = 0; j < KR; j++) {
+            row[j] = __shfl_sync(0xffffffffu, r, j);
+            w[j] = __shfl_sync(0xffffffffu, g, j);
+        }
+    }
+    for (int c = lane * 8; c < d; c += 256) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < KR; j++) {
+            if (j < k) {
+                float v[8];
+                if constexpr (sizeof(YT) == 2) {
+                    uint4 r = __ldcs(reinterpret_cast<const uint4 *>(yp + (size_t)row[j] * d + c));
+                    unpack8(r, v);
+                } else {
+                    float4 a = __ldcs(reinterpret_cast<const float4 *>(yp + (size_t)row[j] * d + c));
+                    float4 b = __ldcs(reinterpret_cast<const float4 *>(yp + (size_t)row[j] * d + c) + 1);
+                    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+                    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc[i] = (j == 0) ? w[0] * v[i] : fmaf(w[j], v[i], acc[i]);
+            }
+        }
+        if constexpr (sizeof(OT) == 2) {
+            uint4 o;
+            o.x = pack2(acc[0], acc[1]);
+            o.y = pack2(acc[2], acc[3]);
+            o.z = pack2(acc[4], acc[5]);
+            o.w = pack2(acc[6], acc[7]);
+            *reinterpret_cast<uint4 *>(y + (size_t)t * d + c) = o;
+        } else {
+            float4 *o = reinterpret_cast<float4 *>(y + (size_t)t * d + c);
+            o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        }
+    }
+}
+
+template <typename YT, typename OT>
+cudaError_t launch_k(omoe_handle *h, void *y, int T, cudaStream_t s) {
+    const int d = h->cfg.d_model, k = h->cfg.top_k;
+    dim3 grid(ceil_div(T, 8)), block(256);
+    const YT *yp = static_cast<const YT *>(h->yp);
+    OT *out = static_cast<OT *>(y);
+    switch (k) {
+        case 1: combine_kernel<YT, OT, 1><<<grid, block, 0, s>>>(yp, out, h->pos, h->topk_w, T, d, k); break;
+        case 2: combine_kernel<YT, OT, 2><<<grid, block, 0, s>>>(yp, out, h->pos, h->topk_w, T, d, k); break;
+        case 4: combine_kernel<YT, OT, 4><<<grid, block, 0, s>>>(yp, out, h->pos, h->topk_w, T, d, k); break;
+        case 6: combine_kernel<YT, OT, 6><<<grid, block, 0, s>>>(yp, out, h->pos, h->topk_w, T, d, k); break;
+        case 8: combine_kernel<YT, OT, 8><<<grid, block, 0, s>>>(yp, out, h->pos, h->topk_w, T, d, k); break;
+        default: combine_kernel<YT, OT, 0><<<grid, block, 0, s>>>(yp, out, h->pos, h->topk_w, T, d, k); break;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_combine(omoe_handle *h, void *y, int io_dtype, int T, cudaStream_t s, int *n) {
+    const bool cbf = h->cfg.compute_dtype == OMOE_BF16;
+    cudaError_t e;
+    if (cbf && io_dtype == OMOE_BF16)
+        e = launch_k<__nv_bfloat16, __nv_bfloat16>(h, y, T, s);
+    else if (cbf && io_dtype == OMOE_F32)
+        e = launch_k<__nv_bfloat16, float>(h, y, T, s);
+    else if (!cbf && io_dtype == OMOE_F32)
+        e = launch_k<float, float>(h, y, T, s);
+    else
+        return cudaErrorInvalidValue;
+    if (e == cudaSuccess) (*n)++;
+    return e;
+}
+
+}  // namespace omoe

@@ -1,0 +1,442 @@
+// Grouped expert products on Blackwell tensor cores (compute_dtype = OMOE_BF16).
+//
+// Replaces, per expert, the three cublasSgemm calls plus the silu_forward and
+// mul_kernel passes of LlamaMLPLayer.output()
+// (src/main/java/com/omega/engine/nn/layer/llama/LlamaMLPLayer.java:117-123;
+// FullyLayer.java:235; src/main/resources/cu/activeFunction.cu:172-180;
+// src/main/resources/cu/OPKernel.cu:1040) with two persistent kernels:
+//   up/gate:  h  = silu(xp * Wg^T) * (xp * Wu^T)      (SiLU and product in the epilogue)
+//   down:     yp = h * Wd^T
+// Both are the same mainloop: one CTA per SM walks a list of 128 x 256 output
+// tiles; a producer thread feeds a 4-stage shared-memory ring with TMA
+// (128-byte swizzle), one thread issues tcgen05.mma (M=128, N=256, K=16, bf16
+// in, fp32 accumulate in tensor memory), and four epilogue warps read the
+// accumulator with tcgen05.ld while the next tile's mainloop already runs in
+// the other half of tensor memory.
+//
+// Every wait on an mbarrier is bounded: when it runs out the kernel raises a
+// flag in the device error word, lets outstanding copies land, frees its tensor
+// memory and returns, so the context stays usable.
+#include "common.cuh"
+
+namespace omoe {
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_N = 256;   // accumulator columns per tile (gate 128 + up 128, or 256 of down)
+constexpr int BLOCK_K = 64;    // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kAccStages = 2;
+constexpr int kTmemCols = 512;
+constexpr int kABytes = BLOCK_M * BLOCK_K * 2;      // 16 KB
+constexpr int kBHalfBytes = 128 * BLOCK_K * 2;      // 16 KB (one 128-row TMA box)
+constexpr int kStageBytes = kABytes + 2 * kBHalfBytes;  // 48 KB
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int kThreads = 192;  // warp 0 producer, warp 1 MMA, warps 2-5 epilogue
+constexpr int kBand = 16;      // m-tiles per band of the tile order (L2 reuse of A rows)
+constexpr unsigned long long kWaitNs = 2000000000ull;  // 2 s bound on any single wait
+
+// ---- PTX wrappers ---------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait.  Returns false when the wait ran out or another role already
+// gave up (abort flag in shared memory); the caller then leaves its loop.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          int32_t *dev_err) {
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0 = 0;
+    for (uint32_t spin = 1;; spin++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 0xffu) == 0) {
+            if (*abort_flag) return false;
+            unsigned long long now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitNs) {
+                *abort_flag = 1;
+                atomicOr(dev_err, kDevErrTimeout);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]^T
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// 32 lanes x 32 columns of fp32: thread i of the warp gets row (lane base + i).
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128
+// bytes apart, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
+    uint64_t desc = 0;
+    desc |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);  // start address, 16-byte units
+    desc |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle)
+    desc |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row groups
+    desc |= (uint64_t)1 << 46;                        // descriptor version of this architecture
+    desc |= (uint64_t)2 << 61;                        // 128-byte swizzle
+    return desc;
+}
+
+// Instruction descriptor: fp32 accumulator, bf16 A and B, both K-major, N=256, M=128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_N >> 3) << 17) |
+                            ((uint32_t)(BLOCK_M >> 4) << 24);
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+struct TileCoord {
+    int mt, nt;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m_tiles, int n_tiles) {
+    int per_band = kBand * n_tiles;
+    int band = tile / per_band, r = tile % per_band;
+    int m0 = band * kBand;
+    int bm = min(kBand, num_m_tiles - m0);
+    TileCoord c;
+    c.mt = m0 + r % bm;
+    c.nt = r / bm;
+    return c;
+}
+
+// SWIGLU = true : B0 = W_gate, B1 = W_up, tile nt covers output columns [128 nt, 128 nt + 128)
+// SWIGLU = false: B0 = B1 = W_down,     tile nt covers output columns [256 nt, 256 nt + 256)
+// n_out: output features per expert (d_ff or d_model); K: reduction length.
+template <bool SWIGLU>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
+                    const __grid_constant__ CUtensorMap map_b1, __nv_bfloat16 *__restrict__ out, int n_out,
+                    int K, const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ poffsets,
+                    int E, int32_t *dev_err) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;  // stages need 1024-byte alignment for the swizzle
+    unsigned char *base_ptr = smem_raw + (base - raw);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(base_ptr + kStages * kStageBytes);
+    const uint32_t bar0 = base + kStages * kStageBytes;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
+    auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * kStages + s); };
+    auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * kStages + kAccStages + s); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 2 * kAccStages);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int s = 0; s < kAccStages; s++) {
+            mbar_init(tfull_bar(s), 1);
+            mbar_init(tempty_bar(s), 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_m_tiles = poffsets[E] / kRowAlign;
+    const int n_tile_w = SWIGLU ? 128 : 256;
+    const int n_tiles = (n_out + n_tile_w - 1) / n_tile_w;
+    const int total = num_m_tiles * n_tiles;
+    const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+
+    if (warp == 0) {
+        // ---------------- producer: TMA loads into the ring ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+                TileCoord tc = tile_coord(tile, num_m_tiles, n_tiles);
+                const int e = tile_expert[tc.mt];
+                const int row_a = tc.mt * BLOCK_M;
+                const int row_b0 = e * n_out + tc.nt * n_tile_w;
+                const int row_b1 = SWIGLU ? row_b0 : row_b0 + 128;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, dev_err)) { ok = false; break; }
+                    const uint32_t sa = base + stage * kStageBytes;
+                    mbar_expect_tx(full_bar(stage), kStageBytes);
+                    tma_load_2d(sa, &map_a, full_bar(stage), kb * BLOCK_K, row_a);
+                    tma_load_2d(sa + kABytes, &map_b0, full_bar(stage), kb * BLOCK_K, row_b0);
+                    tma_load_2d(sa + kABytes + kBHalfBytes, &map_b1, full_bar(stage), kb * BLOCK_K, row_b1);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // let copies that were already issued land before the CTA retires
+                unsigned long long t0 = globaltimer_ns();
+                while (globaltimer_ns() - t0 < 2000000ull) { }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int stage = 0, as = 0;
+            uint32_t phase = 0, aphase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+                if (!mbar_wait(tempty_bar(as), aphase ^ 1u, abort_flag, dev_err)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + as * BLOCK_N;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, dev_err)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = base + stage * kStageBytes;
+                    const uint64_t adesc = make_sw128_desc(sa);
+                    const uint64_t bdesc = make_sw128_desc(sa + kABytes);
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
+                        // advance 32 bytes (16 bf16) inside the swizzled row: +2 in 16-byte units
+                        tc_mma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                tc_commit(tfull_bar(as));  // accumulator complete
+                if (++as == kAccStages) { as = 0; aphase ^= 1u; }
+            }
+        }
+    } else {
+        // ---------------- epilogue: TMEM -> registers -> global ----------------
+        const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter+32)
+        int as = 0;
+        uint32_t aphase = 0;
+        for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+            TileCoord tc = tile_coord(tile, num_m_tiles, n_tiles);
+            bool ok = mbar_wait(tfull_bar(as), aphase, abort_flag, dev_err);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_acc = tmem_base + as * BLOCK_N + ((uint32_t)(quarter * 32) << 16);
+            const size_t row = (size_t)tc.mt * BLOCK_M + quarter * 32 + lane;
+            __nv_bfloat16 *orow = out + row * n_out;
+            if constexpr (SWIGLU) {
+                const int col0 = tc.nt * 128;
+#pragma unroll 1
+                for (int c = 0; c < 128; c += 32) {
+                    uint32_t g[32], u[32];
+                    tc_ld32(t_acc + c, g);
+                    tc_ld32(t_acc + 128 + c, u);
+                    tc_wait_ld();
+                    uint32_t o[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
+                        float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
+                        o[i] = pack_bf16(silu_f(g0) * u0, silu_f(g1) * u1);
+                    }
+                    const int col = col0 + c;
+                    if (col + 32 <= n_out) {
+#pragma unroll
+                        for (int v = 0; v < 4; v++)
+                            *reinterpret_cast<uint4 *>(orow + col + 8 * v) =
+                                make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                    } else {
+                        for (int v = 0; v < 4; v++)
+                            if (col + 8 * v < n_out)  // n_out is a multiple of 8
+                                *reinterpret_cast<uint4 *>(orow + col + 8 * v) =
+                                    make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                    }
+                }
+            } else {
+                const int col0 = tc.nt * 256;
+#pragma unroll 1
+                for (int c = 0; c < 256; c += 32) {
+                    uint32_t a[32];
+                    tc_ld32(t_acc + c, a);
+                    tc_wait_ld();
+                    uint32_t o[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++)
+                        o[i] = pack_bf16(__uint_as_float(a[2 * i]), __uint_as_float(a[2 * i + 1]));
+                    const int col = col0 + c;
+                    if (col + 32 <= n_out) {
+#pragma unroll
+                        for (int v = 0; v < 4; v++)
+                            *reinterpret_cast<uint4 *>(orow + col + 8 * v) =
+                                make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                    } else {
+                        for (int v = 0; v < 4; v++)
+                            if (col + 8 * v < n_out)
+                                *reinterpret_cast<uint4 *>(orow + col + 8 * v) =
+                                    make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(as));
+            if (++as == kAccStages) { as = 0; aphase ^= 1u; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+    return fn;
+}
+
+// 2-D bf16 tensor [rows, cols] row-major, box 128 rows x 64 columns, 128-byte swizzle.
+bool encode_map(EncodeTiledFn fn, CUtensorMap *m, void *ptr, uint64_t rows, uint64_t cols) {
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {BLOCK_K, 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool build_tensor_maps(omoe_handle *h) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) {
+        snprintf(h->err, sizeof(h->err), "cuTensorMapEncodeTiled is not available from this driver");
+        return false;
+    }
+    const uint64_t d = h->cfg.d_model, dff = h->cfg.d_ff, El = h->e_local, rows = h->rows_cap;
+    bool ok = encode_map(fn, &h->maps.a_x, h->xp, rows, d) && encode_map(fn, &h->maps.a_h, h->hbuf, rows, dff) &&
+              encode_map(fn, &h->maps.b_gate, h->w_gate, El * dff, d) &&
+              encode_map(fn, &h->maps.b_up, h->w_up, El * dff, d) &&
+              encode_map(fn, &h->maps.b_down, h->w_down, El * d, dff);
+    if (!ok) snprintf(h->err, sizeof(h->err), "cuTensorMapEncodeTiled failed (d=%d, d_ff=%d)", (int)d, (int)dff);
+    h->maps_ready = ok;
+    return ok;
+}
+
+cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid) {
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kSmemBytes);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        attr_done = true;
+    }
+    const int d = h->cfg.d_model, dff = h->cfg.d_ff;
+    dim3 grid(h->sm_count), block(kThreads);
+    grouped_gemm_kernel<true><<<grid, block, kSmemBytes, s>>>(
+        h->maps.a_x, h->maps.b_gate, h->maps.b_up, static_cast<__nv_bfloat16 *>(h->hbuf), dff, d,
+        h->ex_tile_expert, h->ex_poffsets, h->e_local, h->dev_err);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    (*n)++;
+    if (mid) cudaEventRecord(mid, s);
+    grouped_gemm_kernel<false><<<grid, block, kSmemBytes, s>>>(
+        h->maps.a_h, h->maps.b_down, h->maps.b_down, static_cast<__nv_bfloat16 *>(h->yp), d, dff,
+        h->ex_tile_expert, h->ex_poffsets, h->e_local, h->dev_err);
+    e = cudaGetLastError();
+    if (e == cudaSuccess) (*n)++;
+    return e;
+}
+
+}  // namespace omoe

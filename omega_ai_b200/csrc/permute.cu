@@ -1,0 +1,186 @@
+// Prefix sums over the per-block expert histograms and the dispatch copy of
+// token rows into per-expert contiguous buffers.
+//
+// No reference kernel exists for this stage; the nearest precedent is the row
+// gather EmbeddingFW (src/main/resources/cu/EmbeddingKernel.cu:13-33), which
+// carries indices as floats — here every index is int32.
+//
+// Layout produced: rows of expert e start at poffsets[e], a multiple of 128, so
+// a 128-row tensor-core tile belongs to exactly one expert; inside an expert
+// rows keep the order of the flat pick index t*k+j (stable), which is what
+// makes the permutation reproducible bit for bit.
+#include "common.cuh"
+
+namespace omoe {
+
+namespace {
+
+// One block.  Warp w walks experts w, w+32, ...: turns block_counts[b][e] into
+// the exclusive prefix over blocks b and leaves the total in counts[e].  Then
+// offsets (exact) and poffsets (each expert rounded up to kRowAlign) and the
+// expert of every 128-row tile.
+__global__ void __launch_bounds__(1024)
+scan_kernel(int32_t *__restrict__ block_counts, int n_blocks, int E,
+            int32_t *__restrict__ counts, int32_t *__restrict__ offsets,
+            int32_t *__restrict__ poffsets, int32_t *__restrict__ tile_expert, int max_tiles) {
+    __shared__ int32_t s_cnt[kMaxExperts];
+    __shared__ int32_t s_poff[kMaxExperts + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int e = warp; e < E; e += nwarps) {
+        int run = 0;
+        for (int b0 = 0; b0 < n_blocks; b0 += 32) {
+            int b = b0 + lane;
+            int c = (b < n_blocks) ? block_counts[(size_t)b * E + e] : 0;
+            int inc = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                int v = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += v;
+            }
+            if (b < n_blocks) block_counts[(size_t)b * E + e] = run + inc - c;
+            run += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) s_cnt[e] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int off = 0, poff = 0;
+        for (int e = 0; e < E; e++) {
+            int c = s_cnt[e];
+            counts[e] = c;
+            offsets[e] = off;
+            poffsets[e] = poff;
+            s_poff[e] = poff;
+            off += c;
+            poff += (c + kRowAlign - 1) / kRowAlign * kRowAlign;
+        }
+        offsets[E] = off;
+        poffsets[E] = poff;
+        s_poff[E] = poff;
+    }
+    __syncthreads();
+    const int n_tiles = s_poff[E] / kRowAlign;
+    for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) {
+        int ex = -1;
+        if (i < n_tiles) {
+            int row = i * kRowAlign;
+            ex = 0;
+            while (ex + 1 < E && s_poff[ex + 1] <= row) ex++;
+        }
+        tile_expert[i] = ex;
+    }
+}
+
+template <typename T>
+struct Vec16 {};
+template <>
+struct Vec16<float> { static constexpr int n = 4; };
+template <>
+struct Vec16<__nv_bfloat16> { static constexpr int n = 8; };
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// One warp per token: finalise the k row positions, read the token's row once
+// and write it to its k places with 16-byte stores.
+template <typename XT, typename OT>
+__global__ void __launch_bounds__(256)
+permute_kernel(const XT *__restrict__ x, OT *__restrict__ xp, const int32_t *__restrict__ topk_idx,
+               int32_t *__restrict__ pos, const int32_t *__restrict__ block_base,
+               const int32_t *__restrict__ poffsets, int T, int d, int E, int k, int tokens_per_block) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T) return;
+    int my = 0;
+    if (lane < k) {
+        int f = t * k + lane;
+        int e = topk_idx[f];
+        int b = t / tokens_per_block;
+        my = poffsets[e] + block_base[(size_t)b * E + e] + pos[f];
+        pos[f] = my;
+    }
+    int rows[kMaxTopK];
+#pragma unroll
+    for (int j = 0; j < kMaxTopK; j++) rows[j] = __shfl_sync(0xffffffffu, my, j);
+
+    const XT *src = x + (size_t)t * d;
+    if constexpr (sizeof(XT) == sizeof(OT)) {
+        constexpr int V = 16 / sizeof(XT);
+        for (int c = lane * V; c < d; c += 32 * V) {
+            uint4 v = __ldg(reinterpret_cast<const uint4 *>(src + c));
+#pragma unroll
+            for (int j = 0; j < kMaxTopK; j++)
+                if (j < k) *reinterpret_cast<uint4 *>(xp + (size_t)rows[j] * d + c) = v;
+        }
+    } else {
+        // fp32 rows in, bf16 rows out: 8 elements per lane per step
+        for (int c = lane * 8; c < d; c += 32 * 8) {
+            float4 a = __ldg(reinterpret_cast<const float4 *>(src + c));
+            float4 b = __ldg(reinterpret_cast<const float4 *>(src + c) + 1);
+            uint4 v;
+            v.x = pack_bf16(a.x, a.y);
+            v.y = pack_bf16(a.z, a.w);
+            v.z = pack_bf16(b.x, b.y);
+            v.w = pack_bf16(b.z, b.w);
+#pragma unroll
+            for (int j = 0; j < kMaxTopK; j++)
+                if (j < k) *reinterpret_cast<uint4 *>(xp + (size_t)rows[j] * d + c) = v;
+        }
+    }
+}
+
+// perm[offsets[e] + (pos[f] - poffsets[e])] = f : the unpadded permutation.
+__global__ void perm_readout_kernel(const int32_t *__restrict__ topk_idx, const int32_t *__restrict__ pos,
+                                    const int32_t *__restrict__ offsets, const int32_t *__restrict__ poffsets,
+                                    int32_t *__restrict__ perm, int n) {
+    int f = blockIdx.x * blockDim.x + threadIdx.x;
+    if (f >= n) return;
+    int e = topk_idx[f];
+    perm[offsets[e] + (pos[f] - poffsets[e])] = f;
+}
+
+}  // namespace
+
+cudaError_t launch_scan(omoe_handle *h, int T, cudaStream_t s, int *n) {
+    int n_blocks = ceil_div(T, h->tokens_per_block);
+    int max_tiles = (int)(h->rows_cap / kRowAlign);
+    scan_kernel<<<1, 1024, 0, s>>>(h->block_counts, n_blocks, h->cfg.n_experts, h->counts, h->offsets,
+                                   h->poffsets, h->tile_expert, max_tiles);
+    (*n)++;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_permute(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n) {
+    const int d = h->cfg.d_model, E = h->cfg.n_experts, k = h->cfg.top_k;
+    const int wpb = 8;
+    dim3 grid(ceil_div(T, wpb)), block(wpb * 32);
+    const bool cbf = h->cfg.compute_dtype == OMOE_BF16;
+    if (io_dtype == OMOE_F32 && !cbf)
+        permute_kernel<float, float><<<grid, block, 0, s>>>(
+            static_cast<const float *>(x), static_cast<float *>(h->xp), h->topk_idx, h->pos,
+            h->block_counts, h->poffsets, T, d, E, k, h->tokens_per_block);
+    else if (io_dtype == OMOE_F32 && cbf)
+        permute_kernel<float, __nv_bfloat16><<<grid, block, 0, s>>>(
+            static_cast<const float *>(x), static_cast<__nv_bfloat16 *>(h->xp), h->topk_idx, h->pos,
+            h->block_counts, h->poffsets, T, d, E, k, h->tokens_per_block);
+    else if (io_dtype == OMOE_BF16 && cbf)
+        permute_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, block, 0, s>>>(
+            static_cast<const __nv_bfloat16 *>(x), static_cast<__nv_bfloat16 *>(h->xp), h->topk_idx,
+            h->pos, h->block_counts, h->poffsets, T, d, E, k, h->tokens_per_block);
+    else
+        return cudaErrorInvalidValue;  // bf16 rows into an fp32 layer are rejected by the API
+    (*n)++;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_perm_readout(omoe_handle *h, int T, cudaStream_t s) {
+    int n = T * h->cfg.top_k;
+    if (n == 0) return cudaSuccess;
+    perm_readout_kernel<<<ceil_div(n, 256), 256, 0, s>>>(h->topk_idx, h->pos, h->offsets, h->poffsets,
+                                                         h->perm_out, n);
+    return cudaGetLastError();
+}
+
+}  // namespace omoe

@@ -1,0 +1,226 @@
+// Fused router: logits = x * W_r^T (+bias), softmax, top-k, gate weights,
+// per-block expert histogram and the stable in-block rank of every pick.
+//
+// No reference kernel exists for this stage.  The dense semantics are those of
+// FullyLayer (Y = X * W^T, W [out,in];
+// src/main/java/com/omega/engine/nn/layer/FullyLayer.java:181,235) and the
+// softmax arithmetic is that of src/main/resources/cu/SoftmaxKernel.cu:5-24
+// (max, expf(x-max) summed in index order, divide).
+//
+// Bit-exact routing needs a fixed summation order for the logits.  The order
+// is: lane l of a warp owns the elements i with (i/8)%32 == l and folds them in
+// ascending i with one fmaf chain; the 32 partial sums are then combined by an
+// xor butterfly over distances 16,8,4,2,1; the bias is added last.  One warp
+// computes several tokens at once so every router weight read from shared
+// memory is used for TPW tokens.
+#include "common.cuh"
+
+namespace omoe {
+
+namespace {
+
+constexpr int kSub = 256;  // elements one warp covers per step (32 lanes x 8)
+
+__device__ __forceinline__ void load8(const float *p, float (&v)[8]) {
+    float4 a = __ldg(reinterpret_cast<const float4 *>(p));
+    float4 b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+__device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&v)[8]) {
+    uint4 r = __ldg(reinterpret_cast<const uint4 *>(p));
+    uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+// EMAX: experts held in registers per token (>= E); TPW: tokens per warp;
+// DCG: 256-element sub-chunks of W_r staged in shared memory per chunk.
+template <int EMAX, int TPW, int DCG, typename XT>
+__global__ void __launch_bounds__(kRouterWarps * 32)
+router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const float *__restrict__ bias,
+              int T, int d, int E, int k, int renorm,
+              float *__restrict__ logits, int32_t *__restrict__ topk_idx, float *__restrict__ topk_w,
+              int32_t *__restrict__ block_counts, int32_t *__restrict__ local_rank) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float *ws = reinterpret_cast<float *>(smem_raw);                    // [EMAX][DCG][256] (lane-split layout)
+    float *sl = ws + EMAX * DCG * kSub;                                  // [warps][TPW][EMAX] logits
+    int32_t *sidx = reinterpret_cast<int32_t *>(sl + kRouterWarps * TPW * EMAX);  // [warps*TPW][k]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int TB = kRouterWarps * TPW;
+    const int t0 = blockIdx.x * TB;
+    const int tw = t0 + warp * TPW;  // first token of this warp
+
+    float acc[TPW][EMAX];
+#pragma unroll
+    for (int i = 0; i < TPW; i++)
+#pragma unroll
+        for (int e = 0; e < EMAX; e++) acc[i][e] = 0.0f;
+
+    constexpr int DC = DCG * kSub;
+    for (int c0 = 0; c0 < d; c0 += DC) {
+        __syncthreads();
+        // stage W_r[:, c0:c0+DC) — float4 units, zero beyond d or E
+        for (int u = tid; u < EMAX * (DC / 4); u += blockDim.x) {
+            int e = u / (DC / 4), q = u % (DC / 4);
+            int i = c0 + 4 * q;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (e < E && i < d) v = __ldg(reinterpret_cast<const float4 *>(w_r + (size_t)e * d + i));
+            int sub = (4 * q) / kSub, within = (4 * q) % kSub;
+            int ln = within >> 3, half = (within & 7) >> 2;
+            *reinterpret_cast<float4 *>(ws + (e * DCG + sub) * kSub + half * 128 + ln * 4) = v;
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int sub = 0; sub < DCG; sub++) {
+            int i0 = c0 + sub * kSub + lane * 8;
+            if (i0 >= d) continue;  // d is a multiple of 8: a lane's group is whole or absent
+            float xv[TPW][8];
+#pragma unroll
+            for (int i = 0; i < TPW; i++) {
+                if (tw + i < T) {
+                    load8(x + (size_t)(tw + i) * d + i0, xv[i]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) xv[i][j] = 0.f;
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < EMAX; e++) {
+                const float *wp = ws + (e * DCG + sub) * kSub + lane * 4;
+                float4 wa = *reinterpret_cast<const float4 *>(wp);
+                float4 wb = *reinterpret_cast<const float4 *>(wp + 128);
+                float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                for (int i = 0; i < TPW; i++)
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc[i][e] = fmaf(xv[i][j], wv[j], acc[i][e]);
+            }
+        }
+    }
+
+    // xor butterfly, then lane (e % 32) publishes logit e
+#pragma unroll
+    for (int i = 0; i < TPW; i++)
+#pragma unroll
+        for (int e = 0; e < EMAX; e++) {
+            float a = acc[i][e];
+#pragma unroll
+            for (int m = 16; m >= 1; m >>= 1) a = a + __shfl_xor_sync(0xffffffffu, a, m);
+            if (lane == (e & 31) && e < E) {
+                float v = a;
+                if (bias != nullptr) v = v + __ldg(bias + e);
+                sl[(warp * TPW + i) * EMAX + e] = v;
+                if (tw + i < T) logits[(size_t)(tw + i) * E + e] = v;
+            }
+        }
+    __syncwarp();
+
+    // one lane per token: softmax statistics, top-k on the logits, gate weights
+    if (lane < TPW) {
+        const int t = tw + lane;
+        const float *lv = sl + (warp * TPW + lane) * EMAX;
+        int32_t *my_idx = sidx + (warp * TPW + lane) * k;
+        if (t < T) {
+            float mx = -3.402823466e+38F;
+            for (int e = 0; e < E; e++)
+                if (mx <= lv[e]) mx = lv[e];
+            float sum = 0.f;
+            for (int e = 0; e < E; e++) sum += expf(lv[e] - mx);
+            uint32_t used[kMaxExperts / 32];
+#pragma unroll
+            for (int i = 0; i < kMaxExperts / 32; i++) used[i] = 0u;
+            float wk[kMaxTopK];
+            float wsum = 0.f;
+#pragma unroll 1
+            for (int j = 0; j < k; j++) {
+                int best = -1;
+                float bv = 0.f;
+                for (int e = 0; e < E; e++) {
+                    if ((used[e >> 5] >> (e & 31)) & 1u) continue;
+                    float v = lv[e];
+                    if (best < 0 || v > bv) { best = e; bv = v; }
+                }
+                used[best >> 5] |= 1u << (best & 31);
+                float p = expf(bv - mx) / sum;
+                wk[j] = p;
+                wsum += p;
+                my_idx[j] = best;
+                topk_idx[(size_t)t * k + j] = best;
+            }
+#pragma unroll 1
+            for (int j = 0; j < k; j++) topk_w[(size_t)t * k + j] = renorm ? wk[j] / wsum : wk[j];
+        } else {
+            for (int j = 0; j < k; j++) my_idx[j] = -1;
+        }
+    }
+    __syncthreads();
+
+    // Stable rank of every pick among the block's picks of the same expert, in
+    // order of the flat index t*k+j; the last running count is the histogram.
+    const int n_entries = TB * k;
+    for (int e = warp; e < E; e += kRouterWarps) {
+        int base = 0;
+        for (int c = 0; c < n_entries; c += 32) {
+            int f = c + lane;
+            int v = (f < n_entries) ? sidx[f] : -1;
+            uint32_t m = __ballot_sync(0xffffffffu, v == e);
+            if (v == e) local_rank[(size_t)t0 * k + f] = base + __popc(m & ((1u << lane) - 1u));
+            base += __popc(m);
+        }
+        if (lane == 0) block_counts[(size_t)blockIdx.x * E + e] = base;
+    }
+}
+
+template <int EMAX, int TPW, int DCG, typename XT>
+cudaError_t launch_one(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
+    constexpr int TB = kRouterWarps * TPW;
+    const int k = h->cfg.top_k;
+    size_t smem = sizeof(float) * (EMAX * DCG * kSub + kRouterWarps * TPW * EMAX) + sizeof(int32_t) * TB * k;
+    auto kern = router_kernel<EMAX, TPW, DCG, XT>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    int blocks = ceil_div(T, TB);
+    kern<<<blocks, kRouterWarps * 32, smem, s>>>(x, h->w_router, h->router_bias, T, h->cfg.d_model,
+                                                  h->cfg.n_experts, k, h->cfg.renormalize, h->logits,
+                                                  h->topk_idx, h->topk_w, h->block_counts, h->pos);
+    return cudaGetLastError();
+}
+
+template <typename XT>
+cudaError_t launch_typed(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
+    const int E = h->cfg.n_experts;
+    if (E <= 8) return launch_one<8, 8, 8, XT>(h, x, T, s);
+    if (E <= 16) return launch_one<16, 4, 4, XT>(h, x, T, s);
+    if (E <= 32) return launch_one<32, 4, 2, XT>(h, x, T, s);
+    if (E <= 64) return launch_one<64, 2, 1, XT>(h, x, T, s);
+    return launch_one<128, 1, 1, XT>(h, x, T, s);
+}
+
+}  // namespace
+
+// Tokens one router block covers for E experts (also the granularity of the
+// per-block histogram the scan kernel walks).
+int router_tokens_per_block(int E) {
+    if (E <= 8) return kRouterWarps * 8;
+    if (E <= 32) return kRouterWarps * 4;
+    if (E <= 64) return kRouterWarps * 2;
+    return kRouterWarps;
+}
+
+cudaError_t launch_router(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n) {
+    cudaError_t e;
+    if (io_dtype == OMOE_F32)
+        e = launch_typed<float>(h, static_cast<const float *>(x), T, s);
+    else
+        e = launch_typed<__nv_bfloat16>(h, static_cast<const __nv_bfloat16 *>(x), T, s);
+    if (e == cudaSuccess) (*n)++;
+    return e;
+}
+
+}  // namespace omoe

@@ -1,0 +1,250 @@
+"""Host-side mirror of the engine's operator surface for the MoE layer.
+
+The reference is a Java engine: a layer is built with ``(dims..., network)``,
+driven with ``forward(Tensor)`` (``setInput; init(); output()``) and read with
+``getOutput()`` (src/main/java/com/omega/engine/nn/layer/Layer.java:66-104;
+LlamaMLPLayer.java:199-217).  No JDK exists in this build environment, so the
+same surface is mirrored here in Python over the identical C ABI; the Java
+sources that bind the ABI are under ``omega_ai_b200/java``.  torch is used only
+to own device memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import native
+from .native import OMOE_BF16, OMOE_F32, Config, OmoeError, check
+
+
+class Tensor:
+    """4-D NCHW tensor with a host array and a device buffer, as
+    src/main/java/com/omega/engine/tensor/Tensor.java:23-47.  ``data`` is the
+    host ``float[]``; ``gpu`` is the device buffer (fp32 like the reference, or
+    bf16 for the benchmark configurations)."""
+
+    def __init__(self, number, channel, height, width, data=None, hasGPU=True, dtype=torch.float32,
+                 device="cuda"):
+        self.number, self.channel, self.height, self.width = number, channel, height, width
+        self.dataLength = number * channel * height * width
+        self.dtype = dtype
+        if data is None:
+            self.data = np.zeros(self.dataLength, np.float32)
+        else:
+            self.data = np.ascontiguousarray(data, np.float32).reshape(-1)
+            assert self.data.size == self.dataLength
+        self.gpu = None
+        if hasGPU:
+            self.gpu = torch.empty(self.dataLength, dtype=dtype, device=device)
+            if data is not None:
+                self.hostToDevice()
+
+    @classmethod
+    def from_device(cls, t: torch.Tensor):
+        """Wrap an existing [N, W] device tensor without copying."""
+        obj = cls.__new__(cls)
+        obj.number, obj.channel, obj.height, obj.width = t.shape[0], 1, 1, t.shape[1]
+        obj.dataLength = t.numel()
+        obj.dtype = t.dtype
+        obj.data = None
+        obj.gpu = t.contiguous().view(-1)
+        return obj
+
+    def getGpuData(self) -> int:
+        """Raw device address (what a JCuda Pointer wraps)."""
+        return self.gpu.data_ptr()
+
+    def hostToDevice(self):  # Tensor.java:571-579
+        self.gpu.copy_(torch.from_numpy(self.data).to(self.dtype))
+        torch.cuda.synchronize()
+
+    def syncHost(self):  # Tensor.java:559-565
+        self.data = self.gpu.float().cpu().numpy().reshape(-1)
+        return self.data
+
+    def view2d(self) -> torch.Tensor:
+        return self.gpu.view(self.number, -1)
+
+
+class Layer:
+    """Subset of the abstract operator surface (Layer.java:66-104) this path uses."""
+
+    def __init__(self, network=None):
+        self.network = network
+        self.input = None
+        self.output_t = None
+        self.number = 0
+
+    def init(self):
+        raise NotImplementedError
+
+    def initParam(self):
+        raise NotImplementedError
+
+    def output(self):
+        raise NotImplementedError
+
+    def getOutput(self) -> Tensor:
+        return self.output_t
+
+    def setInput(self, input: Tensor):
+        self.input = input
+
+    def forward(self, input: Tensor) -> Tensor:  # LlamaMLPLayer.java:199-207
+        self.setInput(input)
+        self.init()
+        self.output()
+        return self.output_t
+
+
+def _dt(t: torch.dtype) -> int:
+    if t == torch.float32:
+        return OMOE_F32
+    if t == torch.bfloat16:
+        return OMOE_BF16
+    raise OmoeError(-1, f"unsupported dtype {t}")
+
+
+class MoELayer(Layer):
+    """Mixture-of-experts FFN that takes the slot of ``LlamaMLPLayer``
+    (LlamaTransformerBlock.java:97,135).  Constructor arguments follow the Java
+    layer: ``(embedDim, dff, numExperts, topK, bias, network)``.
+
+    ``compute_dtype`` selects the arithmetic: ``torch.float32`` (the
+    reference's precision) or ``torch.bfloat16`` (tensor cores, fp32
+    accumulate).  ``t_max`` bounds the tokens of one forward.
+    """
+
+    def __init__(self, embedDim, dff, numExperts, topK, bias=False, network=None, *, t_max=4096,
+                 compute_dtype=torch.bfloat16, renormalize=True, world=1, rank=0, recv_rows_max=0):
+        super().__init__(network)
+        self.embedDim, self.dff, self.numExperts, self.topK = embedDim, dff, numExperts, topK
+        self.hasBias = bool(bias)
+        self.compute_dtype = compute_dtype
+        self.t_max = t_max
+        self.world, self.rank = world, rank
+        self._h = C.c_void_p()
+        cfg = Config(t_max=t_max, d_model=embedDim, d_ff=dff, n_experts=numExperts, top_k=topK,
+                     compute_dtype=_dt(compute_dtype), renormalize=int(renormalize),
+                     has_router_bias=int(self.hasBias), world=world, rank=rank, recv_rows_max=recv_rows_max)
+        self._lib = native.lib()
+        rc = self._lib.omoe_create(C.byref(cfg), C.byref(self._h))
+        if rc != 0:
+            raise OmoeError(rc, self._lib.omoe_last_error(None).decode())
+        self._weights = None
+
+    # ---- parameters ------------------------------------------------------
+    def initParam(self, seed: int = 0, std: float = 0.02, device="cuda"):
+        """Random N(0, std) weights, the convention of the benchmark configs
+        (the reference initialises FullyLayer weights with RandomUtils.normal_,
+        RandomUtils.java:697-703)."""
+        g = torch.Generator(device=device).manual_seed(seed)
+        E, El, d, dff = self.numExperts, self.numExperts // self.world, self.embedDim, self.dff
+        dt = self.compute_dtype
+
+        def rn(*shape):
+            return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * std).to(dt)
+
+        w_router = rn(E, d)
+        bias = rn(E) if self.hasBias else None
+        self.setWeights(w_router, rn(El, dff, d), rn(El, dff, d), rn(El, d, dff), bias)
+
+    def setWeights(self, w_router, w_gate, w_up, w_down, router_bias=None, stream=None):
+        """All tensors on the device, same dtype, [out,in] row-major
+        (FullyLayer.java:181): router [E,d]; gate/up [E_local,dff,d]
+        (linear1/linear3); down [E_local,d,dff] (linear2)."""
+        ts = [w_router, w_gate, w_up, w_down] + ([router_bias] if router_bias is not None else [])
+        dt = w_router.dtype
+        El = self.numExperts // self.world
+        assert all(t.is_cuda and t.dtype == dt and t.is_contiguous() for t in ts)
+        assert tuple(w_router.shape) == (self.numExperts, self.embedDim)
+        assert tuple(w_gate.shape) == (El, self.dff, self.embedDim) == tuple(w_up.shape)
+        assert tuple(w_down.shape) == (El, self.embedDim, self.dff)
+        s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        check(self._h, self._lib.omoe_set_weights(
+            self._h, w_router.data_ptr(), router_bias.data_ptr() if router_bias is not None else None,
+            w_gate.data_ptr(), w_up.data_ptr(), w_down.data_ptr(), _dt(dt), s))
+        torch.cuda.current_stream().synchronize()
+        self._weights = True
+
+    # ---- forward ---------------------------------------------------------
+    def init(self):
+        self.number = self.input.number
+        if self.output_t is None or self.output_t.number != self.number or self.output_t.dtype != self.input.dtype:
+            self.output_t = Tensor(self.number, 1, 1, self.embedDim, dtype=self.input.dtype,
+                                   device=self.input.gpu.device)
+
+    def output(self, stream=None):
+        s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        check(self._h, self._lib.omoe_forward(self._h, self.input.getGpuData(), self.output_t.getGpuData(),
+                                              self.number, _dt(self.input.dtype), s))
+
+    def forward_device(self, x: torch.Tensor, y: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+        """Raw-pointer call on [T, d] device tensors (no Tensor wrapper)."""
+        assert x.is_cuda and x.is_contiguous() and x.shape[1] == self.embedDim
+        if y is None:
+            y = torch.empty_like(x)
+        s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        check(self._h, self._lib.omoe_forward(self._h, x.data_ptr(), y.data_ptr(), x.shape[0], _dt(x.dtype), s))
+        return y
+
+    def forward_host(self, x: torch.Tensor, y: torch.Tensor, stream=None) -> torch.Tensor:
+        """Host buffers in and out (pinned for asynchronous copies): H2D, forward, D2H, sync."""
+        assert not x.is_cuda and not y.is_cuda and x.is_contiguous() and y.is_contiguous()
+        s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        check(self._h, self._lib.omoe_forward_host(self._h, x.data_ptr(), y.data_ptr(), x.shape[0], _dt(x.dtype), s))
+        return y
+
+    # ---- read-outs -------------------------------------------------------
+    def routing(self, T: int):
+        """(topk_idx [T,k], topk_w [T,k], counts [E], offsets [E+1], perm [T*k]) of the last forward."""
+        k, E = self.topK, self.numExperts
+        idx = np.empty((T, k), np.int32)
+        w = np.empty((T, k), np.float32)
+        counts = np.empty(E, np.int32)
+        offsets = np.empty(E + 1, np.int32)
+        perm = np.empty(T * k, np.int32)
+        p = lambda a: a.ctypes.data_as(C.c_void_p)
+        check(self._h, self._lib.omoe_get_routing(self._h, p(idx), p(w), p(counts), p(offsets), p(perm)))
+        return idx, w, counts, offsets, perm
+
+    def logits(self, T: int) -> np.ndarray:
+        out = np.empty((T, self.numExperts), np.float32)
+        check(self._h, self._lib.omoe_get_logits(self._h, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def launch_count(self) -> int:
+        return int(self._lib.omoe_last_launch_count(self._h))
+
+    def set_profiling(self, on: bool):
+        check(self._h, self._lib.omoe_set_profiling(self._h, int(on)))
+
+    def stage_ms(self) -> dict:
+        ms = (C.c_float * native.N_STAGES)()
+        check(self._h, self._lib.omoe_get_stage_ms(self._h, ms))
+        return dict(zip(native.STAGE_NAMES, [float(v) for v in ms]))
+
+    def ep_init(self, unique_id: bytes):
+        buf = C.create_string_buffer(unique_id, native.EP_ID_BYTES)
+        check(self._h, self._lib.omoe_ep_init(self._h, buf))
+
+    @staticmethod
+    def ep_unique_id() -> bytes:
+        buf = C.create_string_buffer(native.EP_ID_BYTES)
+        rc = native.lib().omoe_ep_unique_id(buf)
+        if rc != 0:
+            raise OmoeError(rc, "omoe_ep_unique_id failed")
+        return buf.raw
+
+    def close(self):
+        if self._h:
+            self._lib.omoe_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

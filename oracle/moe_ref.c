@@ -1,0 +1,380 @@
+/*
+ * moe_ref.c — CPU oracle for the mixture-of-experts FFN forward path.
+ *
+ * TEST INFRASTRUCTURE ONLY (see moe_ref.h).  PARITY UNPINNED: the reference has
+ * no MoE layer and no golden vectors for this path; each function below cites
+ * the reference primitive whose arithmetic it restates, and the routing rules
+ * that have no reference counterpart are stated where they are implemented.
+ *
+ * Build with -ffp-contract=off: the reference's host code is Java, which never
+ * fuses a multiply and an add, so every `a*b + c` here must stay two roundings.
+ * The one place a fused multiply-add is wanted (router logits) calls fmaf().
+ */
+#include "moe_ref.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+int ref_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* ---- bf16 rounding ------------------------------------------------------ */
+
+float ref_bf16_round(float v) {
+    uint32_t u;
+    memcpy(&u, &v, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) { /* NaN: keep quiet NaN */
+        u = (u | 0x00400000u) & 0xffff0000u;
+    } else {
+        uint32_t lsb = (u >> 16) & 1u;
+        u += 0x7fffu + lsb; /* round to nearest, ties to even */
+        u &= 0xffff0000u;
+    }
+    memcpy(&v, &u, 4);
+    return v;
+}
+
+void ref_bf16_round_array(float *v, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; i++) v[i] = ref_bf16_round(v[i]);
+}
+
+/* ---- dense primitives --------------------------------------------------- */
+
+/* src/main/resources/cu/activeFunction.cu:172-180 (silu_forward):
+ * output[i] = x[i] / (1.0f + expf(-x[i])). */
+static inline float silu1(float x) { return x / (1.0f + expf(-x)); }
+
+void ref_silu(const float *x, float *out, int64_t n) {
+    for (int64_t i = 0; i < n; i++) out[i] = silu1(x[i]);
+}
+
+/* Y = X * W^T with W stored [out,in] row-major:
+ * src/main/java/com/omega/engine/nn/layer/FullyLayer.java:181 (weight shape),
+ * :235 (CUBLAS_OP_N, CUBLAS_OP_T call).  Accumulation order follows the
+ * engine's host SGEMM, src/main/java/com/omega/engine/cpu/
+ * SimplePerfCpuBlasBatchSgemmJdk8.java:106-131: the reduction index p is an
+ * outer loop and each output does `C += a*b` once per p, i.e. one sequential
+ * chain per output with a separately rounded product.  This small version is
+ * the literal form; the blocked one below keeps the same per-output order. */
+void ref_linear_nt(const float *X, const float *W, float *Y, int64_t m, int64_t n, int64_t k) {
+    for (int64_t i = 0; i < m; i++)
+        for (int64_t j = 0; j < n; j++) {
+            float acc = 0.0f;
+            for (int64_t p = 0; p < k; p++) {
+                float prod = X[i * k + p] * W[j * k + p];
+                acc = acc + prod;
+            }
+            Y[i * n + j] = acc;
+        }
+}
+
+/* src/main/resources/cu/SoftmaxKernel.cu:5-24 (softmax) and its host twin
+ * src/main/java/com/omega/engine/gpu/SoftmaxKernel.java:69-87
+ * (safeSoftmax_3pass): max with `<=`, e = expf(x - max) summed in index
+ * order, then divide. */
+void ref_softmax_rows(const float *in, float *out, int64_t rows, int64_t n) {
+    for (int64_t r = 0; r < rows; r++) {
+        const float *x = in + r * n;
+        float *o = out + r * n;
+        float mx = -3.402823466e+38F;
+        float sum = 0.0f;
+        for (int64_t i = 0; i < n; i++)
+            if (mx <= x[i]) mx = x[i];
+        for (int64_t i = 0; i < n; i++) {
+            float e = expf(x[i] - mx);
+            sum += e;
+            o[i] = e;
+        }
+        for (int64_t i = 0; i < n; i++) o[i] /= sum;
+    }
+}
+
+/* ---- routing (no reference counterpart; rules fixed here) ---------------- */
+
+/* Router logits = x * W_r^T (+ bias), FullyLayer semantics as above, but with a
+ * FIXED reduction tree so that a 32-lane GPU warp can reproduce every bit:
+ *   lane l in [0,32) owns the elements i with (i / 8) % 32 == l and folds them
+ *   in ascending i with acc = fmaf(x[i], w[i], acc), acc starting at +0;
+ *   the 32 partials are then combined by an xor butterfly over lane distances
+ *   16, 8, 4, 2, 1, every lane computing a[l] = a[l] + a[l ^ m] at once (IEEE
+ *   addition commutes, so all lanes agree); lane 0 is the result.
+ *   The bias, when present, is added last. */
+void ref_router_logits(const float *x, const float *w_r, const float *bias,
+                       int64_t T, int64_t d, int64_t E, float *logits) {
+#pragma omp parallel for schedule(static)
+    for (int64_t t = 0; t < T; t++) {
+        const float *xr = x + t * d;
+        for (int64_t e = 0; e < E; e++) {
+            const float *w = w_r + e * d;
+            float lane[32];
+            for (int l = 0; l < 32; l++) lane[l] = 0.0f;
+            for (int64_t i = 0; i < d; i++) {
+                int l = (int)((i >> 3) & 31);
+                lane[l] = fmaf(xr[i], w[i], lane[l]);
+            }
+            for (int m = 16; m >= 1; m >>= 1) {
+                float nxt[32];
+                for (int l = 0; l < 32; l++) nxt[l] = lane[l] + lane[l ^ m];
+                for (int l = 0; l < 32; l++) lane[l] = nxt[l];
+            }
+            float v = lane[0];
+            if (bias) v = v + bias[e];
+            logits[t * E + e] = v;
+        }
+    }
+}
+
+/* Top-k and gate weights.  The k picks are taken on the LOGITS: pick j is the
+ * largest logit not picked before, a tie going to the lower expert index (the
+ * reference's only arg-max, MatrixOperation.maxIndex at
+ * src/main/java/com/omega/common/utils/MatrixOperation.java:2008-2020, lets
+ * the last maximum win; with no reference top-k to match, the lower index was
+ * chosen here and is what the CUDA path implements).  Gate weights are the
+ * three-pass softmax over all E logits (ref_softmax_rows arithmetic) read at
+ * the picks, and with renorm divided by their sum taken in pick order. */
+void ref_topk_gate(const float *logits, int64_t T, int64_t E, int64_t k, int renorm,
+                   int32_t *topk_idx, float *topk_w) {
+#pragma omp parallel
+    {
+        float *p = (float *)malloc(sizeof(float) * (size_t)E);
+        unsigned char *used = (unsigned char *)malloc((size_t)E);
+#pragma omp for schedule(static)
+        for (int64_t t = 0; t < T; t++) {
+            const float *x = logits + t * E;
+            ref_softmax_rows(x, p, 1, E);
+            memset(used, 0, (size_t)E);
+            float wsum = 0.0f;
+            for (int64_t j = 0; j < k; j++) {
+                int64_t best = -1;
+                for (int64_t e = 0; e < E; e++) {
+                    if (used[e]) continue;
+                    if (best < 0 || x[e] > x[best]) best = e;
+                }
+                used[best] = 1;
+                topk_idx[t * k + j] = (int32_t)best;
+                topk_w[t * k + j] = p[best];
+                wsum += p[best];
+            }
+            if (renorm)
+                for (int64_t j = 0; j < k; j++) topk_w[t * k + j] = topk_w[t * k + j] / wsum;
+        }
+        free(p);
+        free(used);
+    }
+}
+
+/* Histogram, exclusive scan and the dispatch permutation.  Rows are grouped
+ * expert-major; inside one expert they keep the order of the flat pick index
+ * f = t*k + j (a stable counting sort). */
+void ref_histogram_permute(const int32_t *topk_idx, int64_t T, int64_t E, int64_t k,
+                           int32_t *counts, int32_t *offsets, int32_t *perm, int32_t *pos) {
+    for (int64_t e = 0; e < E; e++) counts[e] = 0;
+    for (int64_t f = 0; f < T * k; f++) counts[topk_idx[f]]++;
+    offsets[0] = 0;
+    for (int64_t e = 0; e < E; e++) offsets[e + 1] = offsets[e] + counts[e];
+    if (!perm && !pos) return;
+    int32_t *cur = (int32_t *)malloc(sizeof(int32_t) * (size_t)E);
+    for (int64_t e = 0; e < E; e++) cur[e] = offsets[e];
+    for (int64_t f = 0; f < T * k; f++) {
+        int32_t e = topk_idx[f];
+        int32_t r = cur[e]++;
+        if (perm) perm[r] = (int32_t)f;
+        if (pos) pos[f] = r;
+    }
+    free(cur);
+}
+
+/* ---- expert products ---------------------------------------------------- */
+
+/* Y[m,n] (+)= X[m,kk] * Wt[kk,n] where Wt is W transposed to [in,out].  For
+ * every output the products are added in ascending reduction index, each
+ * product rounded on its own — the same per-output chain as ref_linear_nt and
+ * as the engine's tiledSgemm (p outer, `C += a*b`).  Blocking over rows and
+ * output columns only changes which outputs are worked on together. */
+static void linear_t_block(const float *X, int64_t ldx, const float *Wt, int64_t n,
+                           float *Yb, int64_t ldy, int64_t ycol0, int64_t m, int64_t kk,
+                           int64_t c0, int64_t c1) {
+    /* output column c is stored at Yb[r*ldy + c - ycol0] */
+    float *Y = Yb - ycol0;
+    for (int64_t r = 0; r < m; r++)
+        for (int64_t c = c0; c < c1; c++) Y[r * ldy + c] = 0.0f;
+    int64_t r = 0;
+    for (; r + 4 <= m; r += 4) {
+        float *y0 = Y + (r + 0) * ldy, *y1 = Y + (r + 1) * ldy;
+        float *y2 = Y + (r + 2) * ldy, *y3 = Y + (r + 3) * ldy;
+        for (int64_t p = 0; p < kk; p++) {
+            const float *w = Wt + p * n;
+            float a0 = X[(r + 0) * ldx + p], a1 = X[(r + 1) * ldx + p];
+            float a2 = X[(r + 2) * ldx + p], a3 = X[(r + 3) * ldx + p];
+            for (int64_t c = c0; c < c1; c++) {
+                float wv = w[c];
+                y0[c] += a0 * wv;
+                y1[c] += a1 * wv;
+                y2[c] += a2 * wv;
+                y3[c] += a3 * wv;
+            }
+        }
+    }
+    for (; r < m; r++) {
+        float *y0 = Y + r * ldy;
+        for (int64_t p = 0; p < kk; p++) {
+            const float *w = Wt + p * n;
+            float a0 = X[r * ldx + p];
+            for (int64_t c = c0; c < c1; c++) y0[c] += a0 * w[c];
+        }
+    }
+}
+
+static void transpose(const float *W, float *Wt, int64_t rows, int64_t cols) {
+    /* W [rows, cols] -> Wt [cols, rows] */
+    const int64_t B = 32;
+#pragma omp parallel for schedule(static) collapse(2)
+    for (int64_t r0 = 0; r0 < rows; r0 += B)
+        for (int64_t c0 = 0; c0 < cols; c0 += B) {
+            int64_t r1 = r0 + B < rows ? r0 + B : rows;
+            int64_t c1 = c0 + B < cols ? c0 + B : cols;
+            for (int64_t r = r0; r < r1; r++)
+                for (int64_t c = c0; c < c1; c++) Wt[c * rows + r] = W[r * cols + c];
+        }
+}
+
+/* One expert's SwiGLU FFN over m gathered rows.  Order of operations follows
+ * src/main/java/com/omega/engine/nn/layer/llama/LlamaMLPLayer.java:117-123:
+ * linear1 (gate) -> SiLU -> linear3 (up) -> element-wise multiply
+ * (src/main/resources/cu/OPKernel.cu:1040, R = X*Y) -> linear2 (down).
+ * bf16 mode inserts the roundings the tensor-core path has: h and yp. */
+static void expert_ffn(const float *Xe, int64_t m, int64_t d, int64_t dff,
+                       const float *WgT, const float *WuT, const float *WdT,
+                       int bf16, float *H, float *Yp) {
+    const int64_t CB = 512, RB = 16;
+    int64_t nrb = (m + RB - 1) / RB;
+    int64_t ncb1 = (dff + CB - 1) / CB, ncb2 = (d + CB - 1) / CB;
+#pragma omp parallel
+    {
+        float *tmp = (float *)malloc(sizeof(float) * (size_t)(RB * CB * 2));
+#pragma omp for schedule(dynamic) collapse(2)
+        for (int64_t rb = 0; rb < nrb; rb++)
+            for (int64_t cb = 0; cb < ncb1; cb++) {
+                int64_t r0 = rb * RB, r1 = r0 + RB < m ? r0 + RB : m;
+                int64_t c0 = cb * CB, c1 = c0 + CB < dff ? c0 + CB : dff;
+                int64_t mm = r1 - r0, w = c1 - c0;
+                float *g = tmp, *u = tmp + RB * CB;
+                linear_t_block(Xe + r0 * d, d, WgT, dff, g, CB, c0, mm, d, c0, c1);
+                linear_t_block(Xe + r0 * d, d, WuT, dff, u, CB, c0, mm, d, c0, c1);
+                for (int64_t r = 0; r < mm; r++)
+                    for (int64_t c = 0; c < w; c++) {
+                        float hv = silu1(g[r * CB + c]) * u[r * CB + c];
+                        H[(r0 + r) * dff + c0 + c] = bf16 ? ref_bf16_round(hv) : hv;
+                    }
+            }
+#pragma omp for schedule(dynamic) collapse(2)
+        for (int64_t rb = 0; rb < nrb; rb++)
+            for (int64_t cb = 0; cb < ncb2; cb++) {
+                int64_t r0 = rb * RB, r1 = r0 + RB < m ? r0 + RB : m;
+                int64_t c0 = cb * CB, c1 = c0 + CB < d ? c0 + CB : d;
+                linear_t_block(H + r0 * dff, dff, WdT, d, Yp + r0 * d, d, 0, r1 - r0, dff, c0, c1);
+                if (bf16)
+                    for (int64_t r = r0; r < r1; r++)
+                        for (int64_t c = c0; c < c1; c++) Yp[r * d + c] = ref_bf16_round(Yp[r * d + c]);
+            }
+        free(tmp);
+    }
+}
+
+/* ---- whole layer -------------------------------------------------------- */
+
+void ref_moe_forward(const ref_moe_shape *s,
+                     const float *x, const float *w_r, const float *bias,
+                     const float *w_gate, const float *w_up, const float *w_down,
+                     float *logits, int32_t *topk_idx, float *topk_w,
+                     int32_t *counts, int32_t *offsets, int32_t *perm,
+                     const int32_t *sel, int64_t n_sel, float *y, int nthreads) {
+    const int64_t T = s->T, d = s->d, dff = s->dff, E = s->E, k = s->k;
+#ifdef _OPENMP
+    int saved = omp_get_max_threads();
+    if (nthreads > 0) omp_set_num_threads(nthreads);
+#else
+    (void)nthreads;
+#endif
+    float *lg = logits ? logits : (float *)malloc(sizeof(float) * (size_t)(T * E));
+    ref_router_logits(x, w_r, bias, T, d, E, lg);
+    ref_topk_gate(lg, T, E, k, s->renorm, topk_idx, topk_w);
+    ref_histogram_permute(topk_idx, T, E, k, counts, offsets, perm, NULL);
+    if (!logits) free(lg);
+
+    if (y && (sel ? n_sel : T) > 0) {
+        int64_t ns = sel ? n_sel : T;
+        /* dispatch of the selected tokens only: expert-major, stable */
+        int64_t R = ns * k;
+        int32_t *scount = (int32_t *)calloc((size_t)E + 1, sizeof(int32_t));
+        int32_t *soff = (int32_t *)calloc((size_t)E + 1, sizeof(int32_t));
+        int32_t *spos = (int32_t *)malloc(sizeof(int32_t) * (size_t)R);
+        for (int64_t i = 0; i < ns; i++) {
+            int64_t t = sel ? sel[i] : i;
+            for (int64_t j = 0; j < k; j++) scount[topk_idx[t * k + j]]++;
+        }
+        for (int64_t e = 0; e < E; e++) soff[e + 1] = soff[e] + scount[e];
+        int32_t *cur = (int32_t *)malloc(sizeof(int32_t) * (size_t)E);
+        for (int64_t e = 0; e < E; e++) cur[e] = soff[e];
+        float *Xp = (float *)malloc(sizeof(float) * (size_t)(R * d));
+        for (int64_t i = 0; i < ns; i++) {
+            int64_t t = sel ? sel[i] : i;
+            for (int64_t j = 0; j < k; j++) {
+                int32_t e = topk_idx[t * k + j];
+                int32_t r = cur[e]++;
+                spos[i * k + j] = r;
+                for (int64_t c = 0; c < d; c++) {
+                    float v = x[t * d + c];
+                    Xp[(int64_t)r * d + c] = s->bf16 ? ref_bf16_round(v) : v;
+                }
+            }
+        }
+        int64_t mmax = 0;
+        for (int64_t e = 0; e < E; e++)
+            if (scount[e] > mmax) mmax = scount[e];
+        float *H = (float *)malloc(sizeof(float) * (size_t)(mmax * dff + 1));
+        float *Yp = (float *)malloc(sizeof(float) * (size_t)(R * d + 1));
+        float *WgT = (float *)malloc(sizeof(float) * (size_t)(d * dff));
+        float *WuT = (float *)malloc(sizeof(float) * (size_t)(d * dff));
+        float *WdT = (float *)malloc(sizeof(float) * (size_t)(d * dff));
+        for (int64_t e = 0; e < E; e++) {
+            int64_t m = scount[e];
+            if (m == 0) continue;
+            transpose(w_gate + e * dff * d, WgT, dff, d); /* [dff,d] -> [d,dff] */
+            transpose(w_up + e * dff * d, WuT, dff, d);
+            transpose(w_down + e * d * dff, WdT, d, dff); /* [d,dff] -> [dff,d] */
+            expert_ffn(Xp + (int64_t)soff[e] * d, m, d, dff, WgT, WuT, WdT, s->bf16, H,
+                       Yp + (int64_t)soff[e] * d);
+        }
+        /* Combine: y[t,:] = ((w0*yp0) + w1*yp1) + ... in pick order, fp32,
+         * each product rounded before it is added. */
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < ns; i++) {
+            int64_t t = sel ? sel[i] : i;
+            for (int64_t c = 0; c < d; c++) {
+                float acc = 0.0f;
+                for (int64_t j = 0; j < k; j++) {
+                    float prod = topk_w[t * k + j] * Yp[(int64_t)spos[i * k + j] * d + c];
+                    acc = (j == 0) ? prod : acc + prod;
+                }
+                y[i * d + c] = s->out_bf16 ? ref_bf16_round(acc) : acc;
+            }
+        }
+        free(WgT); free(WuT); free(WdT);
+        free(H); free(Yp); free(Xp);
+        free(cur); free(spos); free(soff); free(scount);
+    }
+#ifdef _OPENMP
+    omp_set_num_threads(saved);
+#endif
+}

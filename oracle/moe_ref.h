@@ -1,0 +1,89 @@
+/*
+ * moe_ref.h — CPU oracle for the mixture-of-experts FFN forward path.
+ *
+ * TEST INFRASTRUCTURE ONLY.  Nothing in the shipped library links, loads or
+ * calls this code; it exists so tests and the benchmark's CPU-baseline leg can
+ * check the CUDA path against a plain-C restatement of the arithmetic.
+ *
+ * PARITY UNPINNED: the reference engine (dromara/Omega-AI) has no
+ * mixture-of-experts layer, router, top-k or permutation code and ships no
+ * golden vectors for the dense pieces either, so this oracle is assembled from
+ * the reference's dense primitives (cited per function in moe_ref.c) plus
+ * routing/permutation/combine rules fixed by this project.  The only reference
+ * values it can be pinned to are the SiLU demo inputs and the all-ones GEMM
+ * check (see ref_silu / ref_linear_nt).
+ */
+#ifndef OMOE_ORACLE_MOE_REF_H
+#define OMOE_ORACLE_MOE_REF_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* rows padded to this many per expert in the library's internal dispatch
+ * buffer; the oracle reports UNPADDED positions, the constant is exported so
+ * tests can convert. */
+#define REF_ROW_ALIGN 128
+
+typedef struct ref_moe_shape {
+    int32_t T;        /* tokens */
+    int32_t d;        /* d_model */
+    int32_t dff;      /* expert hidden size */
+    int32_t E;        /* experts */
+    int32_t k;        /* picks per token */
+    int32_t renorm;   /* 1: gate weights renormalised over the k picks */
+    int32_t bf16;     /* 1: bf16 rounding points (weights, x, h, yp) */
+    int32_t out_bf16; /* 1: y rounded to bf16 */
+} ref_moe_shape;
+
+/* round-to-nearest-even to bf16 precision, result kept in a float */
+float ref_bf16_round(float v);
+void ref_bf16_round_array(float *v, int64_t n);
+
+/* silu(x) = x / (1 + expf(-x)) */
+void ref_silu(const float *x, float *out, int64_t n);
+
+/* Y[m,n] = X[m,k] * W[n,k]^T, W row-major [out,in]; per-output accumulation
+ * sequential in k with separate multiply and add. */
+void ref_linear_nt(const float *X, const float *W, float *Y, int64_t m, int64_t n, int64_t k);
+
+/* row softmax, three passes */
+void ref_softmax_rows(const float *in, float *out, int64_t rows, int64_t n);
+
+/* router logits with the fixed 32-lane reduction tree; bias may be NULL */
+void ref_router_logits(const float *x, const float *w_r, const float *bias,
+                       int64_t T, int64_t d, int64_t E, float *logits);
+
+/* top-k on logits (descending, ties -> lower expert), gate weights from the
+ * softmax over all E logits, optionally renormalised over the picks. */
+void ref_topk_gate(const float *logits, int64_t T, int64_t E, int64_t k, int renorm,
+                   int32_t *topk_idx, float *topk_w);
+
+/* per-expert counts, exclusive offsets[E+1], expert-major stable permutation:
+ * perm[offsets[e]+r] = t*k+j, pos[t*k+j] = offsets[e]+r. */
+void ref_histogram_permute(const int32_t *topk_idx, int64_t T, int64_t E, int64_t k,
+                           int32_t *counts, int32_t *offsets, int32_t *perm, int32_t *pos);
+
+/* Whole layer.  x [T,d]; w_r [E,d]; bias [E] or NULL; w_gate,w_up [E,dff,d];
+ * w_down [E,d,dff] (all row-major [out,in]).  Outputs for ALL tokens: logits
+ * (nullable), topk_idx, topk_w, counts, offsets, perm (nullable).  y is
+ * computed only for the n_sel tokens listed in sel (sel==NULL: all tokens, in
+ * order) and written as y[i,:] for the i-th selected token.  Weights must
+ * already hold bf16-representable values when shape.bf16 is set (call
+ * ref_bf16_round_array first); x is rounded internally for the expert path.
+ * nthreads <= 0: all cores. */
+void ref_moe_forward(const ref_moe_shape *shape,
+                     const float *x, const float *w_r, const float *bias,
+                     const float *w_gate, const float *w_up, const float *w_down,
+                     float *logits, int32_t *topk_idx, float *topk_w,
+                     int32_t *counts, int32_t *offsets, int32_t *perm,
+                     const int32_t *sel, int64_t n_sel, float *y, int nthreads);
+
+int ref_num_threads(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
