@@ -344,16 +344,23 @@ void ref_moe_forward(const ref_moe_shape *s,
             if (scount[e] > mmax) mmax = scount[e];
         float *H = (float *)malloc(sizeof(float) * (size_t)(mmax * dff + 1));
         float *Yp = (float *)malloc(sizeof(float) * (size_t)(R * d + 1));
-        float *WgT = (float *)malloc(sizeof(float) * (size_t)(d * dff));
-        float *WuT = (float *)malloc(sizeof(float) * (size_t)(d * dff));
-        float *WdT = (float *)malloc(sizeof(float) * (size_t)(d * dff));
+        float *WgT = NULL, *WuT = NULL, *WdT = NULL;
+        if (!s->pretransposed) {
+            WgT = (float *)malloc(sizeof(float) * (size_t)(d * dff));
+            WuT = (float *)malloc(sizeof(float) * (size_t)(d * dff));
+            WdT = (float *)malloc(sizeof(float) * (size_t)(d * dff));
+        }
         for (int64_t e = 0; e < E; e++) {
             int64_t m = scount[e];
             if (m == 0) continue;
-            transpose(w_gate + e * dff * d, WgT, dff, d); /* [dff,d] -> [d,dff] */
-            transpose(w_up + e * dff * d, WuT, dff, d);
-            transpose(w_down + e * d * dff, WdT, d, dff); /* [d,dff] -> [dff,d] */
-            expert_ffn(Xp + (int64_t)soff[e] * d, m, d, dff, WgT, WuT, WdT, s->bf16, H,
+            const float *g = w_gate + e * dff * d, *u = w_up + e * dff * d, *dn = w_down + e * d * dff;
+            if (!s->pretransposed) {
+                transpose(g, WgT, dff, d); /* [dff,d] -> [d,dff] */
+                transpose(u, WuT, dff, d);
+                transpose(dn, WdT, d, dff); /* [d,dff] -> [dff,d] */
+                g = WgT; u = WuT; dn = WdT;
+            }
+            expert_ffn(Xp + (int64_t)soff[e] * d, m, d, dff, g, u, dn, s->bf16, H,
                        Yp + (int64_t)soff[e] * d);
         }
         /* Combine: y[t,:] = ((w0*yp0) + w1*yp1) + ... in pick order, fp32,

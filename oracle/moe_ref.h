@@ -36,6 +36,8 @@ typedef struct ref_moe_shape {
     int32_t renorm;   /* 1: gate weights renormalised over the k picks */
     int32_t bf16;     /* 1: bf16 rounding points (weights, x, h, yp) */
     int32_t out_bf16; /* 1: y rounded to bf16 */
+    int32_t pretransposed; /* 1: w_gate,w_up given as [E,d,dff] and w_down as [E,dff,d]
+                              ([in,out]); skips the per-call transposition */
 } ref_moe_shape;
 
 /* round-to-nearest-even to bf16 precision, result kept in a float */

@@ -31,7 +31,7 @@ def build(force: bool = False) -> str:
 
 
 class _Shape(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in ("T", "d", "dff", "E", "k", "renorm", "bf16", "out_bf16")]
+    _fields_ = [(n, C.c_int32) for n in ("T", "d", "dff", "E", "k", "renorm", "bf16", "out_bf16", "pretransposed")]
 
 
 def lib():
@@ -145,7 +145,8 @@ class MoEResult:
 
 
 def moe_forward(x, w_r, w_gate, w_up, w_down, k: int, *, bias=None, renorm=True, bf16=False,
-                out_bf16=None, sel=None, compute_y=True, nthreads: int = 0) -> MoEResult:
+                out_bf16=None, sel=None, compute_y=True, nthreads: int = 0,
+                pretransposed=False) -> MoEResult:
     """Whole layer on the CPU.
 
     ``w_r`` [E,d]; ``w_gate``/``w_up`` [E,dff,d]; ``w_down`` [E,d,dff] — all
@@ -160,11 +161,15 @@ def moe_forward(x, w_r, w_gate, w_up, w_down, k: int, *, bias=None, renorm=True,
         w_gate, w_up, w_down = bf16_round(w_gate), bf16_round(w_up), bf16_round(w_down)
     bias = None if bias is None else _cf(bias)
     T, d = x.shape
-    E, dff, _ = w_gate.shape
-    assert w_r.shape == (E, d) and w_up.shape == (E, dff, d) and w_down.shape == (E, d, dff)
+    if pretransposed:  # [in,out] layouts: gate/up [E,d,dff], down [E,dff,d]
+        E, _, dff = w_gate.shape
+        assert w_r.shape == (E, d) and w_up.shape == (E, d, dff) and w_down.shape == (E, dff, d)
+    else:
+        E, dff, _ = w_gate.shape
+        assert w_r.shape == (E, d) and w_up.shape == (E, dff, d) and w_down.shape == (E, d, dff)
     if out_bf16 is None:
         out_bf16 = bf16
-    shp = _Shape(T, d, dff, E, k, int(renorm), int(bf16), int(out_bf16))
+    shp = _Shape(T, d, dff, E, k, int(renorm), int(bf16), int(out_bf16), int(pretransposed))
     logits = np.empty((T, E), np.float32)
     idx = np.empty((T, k), np.int32)
     w = np.empty((T, k), np.float32)
