@@ -32,6 +32,7 @@ struct TensorMaps {
     CUtensorMap b_gate;  // [E_local*dff, d]
     CUtensorMap b_up;    // [E_local*dff, d]
     CUtensorMap b_down;  // [E_local*d, dff]
+    CUtensorMap c_y;     // expert outputs yp [rows_cap, d] (store target)
 };
 
 }  // namespace omoe

@@ -33,8 +33,10 @@ constexpr int kTmemCols = 512;
 constexpr int kABytes = BLOCK_M * BLOCK_K * 2;      // 16 KB
 constexpr int kBHalfBytes = 128 * BLOCK_K * 2;      // 16 KB (one 128-row TMA box)
 constexpr int kStageBytes = kABytes + 2 * kBHalfBytes;  // 48 KB
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
-constexpr int kThreads = 192;  // warp 0 producer, warp 1 MMA, warps 2-5 epilogue
+constexpr int kOutSubBytes = 128 * 64 * 2;          // one [128 x 64] bf16 sub-tile of the output staging
+constexpr int kOutBytes = 2 * kOutSubBytes;         // 32 KB: 128 output columns per pass
+constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int kThreads = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 epilogue
 constexpr int kBand = 16;      // m-tiles per band of the tile order (L2 reuse of A rows)
 constexpr unsigned long long kWaitNs = 2000000000ull;  // 2 s bound on any single wait
 
@@ -102,6 +104,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         : "memory");
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src),
+                 "r"(x), "r"(y)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -157,7 +165,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+// x / (1 + exp(-x)) with the fast exponential and reciprocal (the result is rounded to bf16 next)
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+#ifdef OMOE_TRACE
+// Debug build only: per-CTA, per-tile timestamps (ns) of the MMA and epilogue
+// roles, written to a caller-provided buffer [ctas][kTraceTiles][4].
+constexpr int kTraceTiles = 256;
+__device__ unsigned long long *g_trace = nullptr;
+__device__ int g_trace_swiglu = 1;  // which of the two kernels records
+__device__ __forceinline__ void trace(int tile_i, int slot) {
+    if (g_trace && tile_i < kTraceTiles)
+        g_trace[((size_t)blockIdx.x * kTraceTiles + tile_i) * 4 + slot] = globaltimer_ns();
+}
+#define TRACE(i, s) do { if (SWIGLU == (g_trace_swiglu != 0)) trace(i, s); } while (0)
+#else
+#define TRACE(i, s) ((void)0)
+#endif
 
 struct TileCoord {
     int mt, nt;
@@ -180,15 +204,15 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m_tiles, int n
 template <bool SWIGLU>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
-                    const __grid_constant__ CUtensorMap map_b1, __nv_bfloat16 *__restrict__ out, int n_out,
+                    const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_out, int n_out,
                     int K, const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ poffsets,
                     int E, int32_t *dev_err) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;  // stages need 1024-byte alignment for the swizzle
     unsigned char *base_ptr = smem_raw + (base - raw);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(base_ptr + kStages * kStageBytes);
-    const uint32_t bar0 = base + kStages * kStageBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(base_ptr + kStages * kStageBytes + kOutBytes);
+    const uint32_t bar0 = base + kStages * kStageBytes + kOutBytes;
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
     auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * kStages + s); };
@@ -205,7 +229,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         for (int s = 0; s < kAccStages; s++) {
             mbar_init(tfull_bar(s), 1);
-            mbar_init(tempty_bar(s), 4);  // one arrival per epilogue warp
+            mbar_init(tempty_bar(s), 8);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -233,9 +257,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            // the expert of the next tile is fetched while the current tile streams
+            int e_next = (int)blockIdx.x < total ? tile_expert[tile_coord(blockIdx.x, num_m_tiles, n_tiles).mt] : 0;
             for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
                 TileCoord tc = tile_coord(tile, num_m_tiles, n_tiles);
-                const int e = tile_expert[tc.mt];
+                const int e = e_next;
+                if (tile + (int)gridDim.x < total)
+                    e_next = tile_expert[tile_coord(tile + gridDim.x, num_m_tiles, n_tiles).mt];
                 const int row_a = tc.mt * BLOCK_M;
                 const int row_b0 = e * n_out + tc.nt * n_tile_w;
                 const int row_b1 = SWIGLU ? row_b0 : row_b0 + 128;
@@ -261,9 +289,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int stage = 0, as = 0;
             uint32_t phase = 0, aphase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+            int ti = 0;
+            for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x, ti++) {
                 if (!mbar_wait(tempty_bar(as), aphase ^ 1u, abort_flag, dev_err)) { ok = false; break; }
                 tc_fence_after();
+                TRACE(ti, 0);
                 const uint32_t d_tmem = tmem_base + as * BLOCK_N;
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag, dev_err)) { ok = false; break; }
@@ -281,81 +311,96 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
                 if (!ok) break;
                 tc_commit(tfull_bar(as));  // accumulator complete
+                TRACE(ti, 1);
                 if (++as == kAccStages) { as = 0; aphase ^= 1u; }
             }
         }
     } else {
-        // ---------------- epilogue: TMEM -> registers -> global ----------------
-        const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter+32)
+        // ---------------- epilogue: TMEM -> registers -> shared -> TMA store ----------------
+        // Eight warps: warp%4 selects the 32 TMEM lanes (rows) the hardware lets it
+        // read, (warp-2)/4 the 64-column half of a 128-column pass.  Each pass is
+        // staged in shared memory as two [128 rows x 64 cols] sub-tiles in the
+        // 128-byte-swizzled layout the output tensor map expects.
+        const int ew = warp - 2;
+        const int quarter = warp & 3;
+        const int half = ew >> 2;
+        const int r = quarter * 32 + lane;
+        const uint32_t out_stage = base + kStages * kStageBytes;
+        const uint32_t my_row = out_stage + half * kOutSubBytes + r * 128;
+        constexpr int kPasses = SWIGLU ? 1 : 2;
         int as = 0;
         uint32_t aphase = 0;
-        for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+        int ti = 0;
+        for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ti++) {
             TileCoord tc = tile_coord(tile, num_m_tiles, n_tiles);
             bool ok = mbar_wait(tfull_bar(as), aphase, abort_flag, dev_err);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+            if (warp == 2 && lane == 0) TRACE(ti, 2);
             const uint32_t t_acc = tmem_base + as * BLOCK_N + ((uint32_t)(quarter * 32) << 16);
-            const size_t row = (size_t)tc.mt * BLOCK_M + quarter * 32 + lane;
-            __nv_bfloat16 *orow = out + row * n_out;
-            if constexpr (SWIGLU) {
-                const int col0 = tc.nt * 128;
-#pragma unroll 1
-                for (int c = 0; c < 128; c += 32) {
-                    uint32_t g[32], u[32];
-                    tc_ld32(t_acc + c, g);
-                    tc_ld32(t_acc + 128 + c, u);
-                    tc_wait_ld();
+#pragma unroll
+            for (int p = 0; p < kPasses; p++) {
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    const int col = p * 128 + half * 64 + c * 32;  // accumulator column of this chunk
                     uint32_t o[16];
+                    if constexpr (SWIGLU) {
+                        uint32_t g[32], u[32];
+                        tc_ld32(t_acc + col, g);
+                        tc_ld32(t_acc + 128 + col, u);
+                        tc_wait_ld();
+                        if (c == 1) {  // all of this warp's accumulator reads are done
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(tempty_bar(as));
+                        }
 #pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
-                        float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
-                        o[i] = pack_bf16(silu_f(g0) * u0, silu_f(g1) * u1);
-                    }
-                    const int col = col0 + c;
-                    if (col + 32 <= n_out) {
-#pragma unroll
-                        for (int v = 0; v < 4; v++)
-                            *reinterpret_cast<uint4 *>(orow + col + 8 * v) =
-                                make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                        for (int i = 0; i < 16; i++) {
+                            float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
+                            float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
+                            o[i] = pack_bf16(silu_f(g0) * u0, silu_f(g1) * u1);
+                        }
                     } else {
-                        for (int v = 0; v < 4; v++)
-                            if (col + 8 * v < n_out)  // n_out is a multiple of 8
-                                *reinterpret_cast<uint4 *>(orow + col + 8 * v) =
-                                    make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                        uint32_t a[32];
+                        tc_ld32(t_acc + col, a);
+                        tc_wait_ld();
+                        if (p == kPasses - 1 && c == 1) {
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(tempty_bar(as));
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; i++)
+                            o[i] = pack_bf16(__uint_as_float(a[2 * i]), __uint_as_float(a[2 * i + 1]));
+                    }
+                    if (c == 0) {
+                        // the previous pass's TMA store must have finished reading the staging tile
+                        if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                        asm volatile("bar.sync 1, 256;" ::: "memory");
+                    }
+#pragma unroll
+                    for (int v = 0; v < 4; v++) {
+                        const int chunk = (c * 4 + v) ^ (r & 7);  // 128-byte swizzle: 16-byte chunk ^ (row % 8)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + chunk * 16),
+                                     "r"(o[4 * v]), "r"(o[4 * v + 1]), "r"(o[4 * v + 2]), "r"(o[4 * v + 3])
+                                     : "memory");
                     }
                 }
-            } else {
-                const int col0 = tc.nt * 256;
-#pragma unroll 1
-                for (int c = 0; c < 256; c += 32) {
-                    uint32_t a[32];
-                    tc_ld32(t_acc + c, a);
-                    tc_wait_ld();
-                    uint32_t o[16];
-#pragma unroll
-                    for (int i = 0; i < 16; i++)
-                        o[i] = pack_bf16(__uint_as_float(a[2 * i]), __uint_as_float(a[2 * i + 1]));
-                    const int col = col0 + c;
-                    if (col + 32 <= n_out) {
-#pragma unroll
-                        for (int v = 0; v < 4; v++)
-                            *reinterpret_cast<uint4 *>(orow + col + 8 * v) =
-                                make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
-                    } else {
-                        for (int v = 0; v < 4; v++)
-                            if (col + 8 * v < n_out)
-                                *reinterpret_cast<uint4 *>(orow + col + 8 * v) =
-                                    make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
-                    }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    const int x0 = tc.nt * (SWIGLU ? 128 : 256) + p * 128;
+                    const int y0 = tc.mt * BLOCK_M;
+                    if (x0 < n_out) tma_store_2d(&map_out, out_stage, x0, y0);
+                    if (x0 + 64 < n_out) tma_store_2d(&map_out, out_stage + kOutSubBytes, x0 + 64, y0);
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(as));
+            if (warp == 2 && lane == 0) TRACE(ti, 3);
             if (++as == kAccStages) { as = 0; aphase ^= 1u; }
         }
+        if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     tc_fence_before();
@@ -396,6 +441,14 @@ bool encode_map(EncodeTiledFn fn, CUtensorMap *m, void *ptr, uint64_t rows, uint
 
 }  // namespace
 
+#ifdef OMOE_TRACE
+extern "C" __attribute__((visibility("default"))) int omoe_debug_set_trace(void *dev_buf, int swiglu) {
+    unsigned long long *p = static_cast<unsigned long long *>(dev_buf);
+    if (cudaMemcpyToSymbol(g_trace_swiglu, &swiglu, sizeof(int)) != cudaSuccess) return -2;
+    return cudaMemcpyToSymbol(g_trace, &p, sizeof(p)) == cudaSuccess ? 0 : -2;
+}
+#endif
+
 bool build_tensor_maps(omoe_handle *h) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) {
@@ -406,7 +459,7 @@ bool build_tensor_maps(omoe_handle *h) {
     bool ok = encode_map(fn, &h->maps.a_x, h->xp, rows, d) && encode_map(fn, &h->maps.a_h, h->hbuf, rows, dff) &&
               encode_map(fn, &h->maps.b_gate, h->w_gate, El * dff, d) &&
               encode_map(fn, &h->maps.b_up, h->w_up, El * dff, d) &&
-              encode_map(fn, &h->maps.b_down, h->w_down, El * d, dff);
+              encode_map(fn, &h->maps.b_down, h->w_down, El * d, dff) && encode_map(fn, &h->maps.c_y, h->yp, rows, d);
     if (!ok) snprintf(h->err, sizeof(h->err), "cuTensorMapEncodeTiled failed (d=%d, d_ff=%d)", (int)d, (int)dff);
     h->maps_ready = ok;
     return ok;
@@ -425,14 +478,14 @@ cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEven
     const int d = h->cfg.d_model, dff = h->cfg.d_ff;
     dim3 grid(h->sm_count), block(kThreads);
     grouped_gemm_kernel<true><<<grid, block, kSmemBytes, s>>>(
-        h->maps.a_x, h->maps.b_gate, h->maps.b_up, static_cast<__nv_bfloat16 *>(h->hbuf), dff, d,
+        h->maps.a_x, h->maps.b_gate, h->maps.b_up, h->maps.a_h, dff, d,
         h->ex_tile_expert, h->ex_poffsets, h->e_local, h->dev_err);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     (*n)++;
     if (mid) cudaEventRecord(mid, s);
     grouped_gemm_kernel<false><<<grid, block, kSmemBytes, s>>>(
-        h->maps.a_h, h->maps.b_down, h->maps.b_down, static_cast<__nv_bfloat16 *>(h->yp), d, dff,
+        h->maps.a_h, h->maps.b_down, h->maps.b_down, h->maps.c_y, d, dff,
         h->ex_tile_expert, h->ex_poffsets, h->e_local, h->dev_err);
     e = cudaGetLastError();
     if (e == cudaSuccess) (*n)++;
