@@ -159,6 +159,38 @@ OMOE_API int omoe_get_stage_ms(omoe_handle *h, float *ms /* [OMOE_N_STAGES] */);
 OMOE_API int omoe_ep_unique_id(void *id_out /* [OMOE_EP_ID_BYTES] */);
 OMOE_API int omoe_ep_init(omoe_handle *h, const void *id /* [OMOE_EP_ID_BYTES] */);
 
+/*
+ * Routing only, with NO allocation.  This entry point has no counterpart in
+ * the reference.  It exists for hosts that may not call cudaMalloc where they
+ * need a routing decision (a serving loop whose memory pool owns all free
+ * device memory and bans allocation on the request path, or any caller that
+ * must avoid the device-wide synchronisation an allocation implies).  It runs
+ * the same fused router kernel as omoe_forward; the kernel's scratch lives in
+ * a fixed array inside the library image (about 2.5 MiB per GPU that loads
+ * the library, held until the process exits) and nothing is allocated or
+ * freed, by this call or by anything it calls.
+ *
+ *   x_dev [T, d_model] of io_dtype; w_router_dev [n_experts, d_model] fp32;
+ *   router_bias_dev [n_experts] fp32 or NULL.
+ *   Outputs (caller's DEVICE buffers): topk_idx_dev [T, top_k] int32,
+ *   topk_w_dev [T, top_k] fp32, counts_dev [n_experts] int32.
+ *
+ * Limits: T <= OMOE_NOALLOC_MAX_TOKENS, n_experts <= 128, top_k <= 16; a call
+ * beyond them returns OMOE_ERR_TOO_LARGE and launches nothing.
+ * The first call on each device looks up the array's device address; make that
+ * first call before any stream capture begins on that device.
+ * All calls on one device share the array: it keeps the previous call's
+ * contents (nothing in it needs clearing between calls), and two calls whose
+ * kernels overlap on the GPU (different streams, no ordering) race on it.
+ * Error text: omoe_route_noalloc_error().
+ */
+#define OMOE_NOALLOC_MAX_TOKENS 4096
+OMOE_API int omoe_route_noalloc(const void *x_dev, const float *w_router_dev, const float *router_bias_dev,
+                                int32_t T, int32_t d_model, int32_t n_experts, int32_t top_k,
+                                int32_t renormalize, int32_t io_dtype, int32_t *topk_idx_dev,
+                                float *topk_w_dev, int32_t *counts_dev, void *cuda_stream);
+OMOE_API const char *omoe_route_noalloc_error(void);
+
 #ifdef __cplusplus
 }
 #endif

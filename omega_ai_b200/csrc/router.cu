@@ -13,6 +13,8 @@
 // xor butterfly over distances 16,8,4,2,1; the bias is added last.  One warp
 // computes several tokens at once so every router weight read from shared
 // memory is used for TPW tokens.
+#include <string.h>
+
 #include "common.cuh"
 
 namespace omoe {
@@ -224,3 +226,125 @@ cudaError_t launch_router(omoe_handle *h, const void *x, int io_dtype, int T, cu
 }
 
 }  // namespace omoe
+
+// ---------------------------------------------------------------------------
+// Routing without any allocation.
+//
+// Some hosts of this library may not allocate device memory at the moment they
+// need a routing decision: a serving loop that has handed all free memory to
+// its own pool and forbids cudaMalloc on the request path (it would synchronise
+// the device and may fail), or a caller inside a region where allocation calls
+// are not permitted.  For them omoe_route_noalloc runs the same fused router
+// kernel as omoe_forward, but keeps the kernel's scratch (logits, per-block
+// histograms, in-block ranks) in a fixed array that is part of the library
+// image instead of a cudaMalloc'd workspace.  Inputs and outputs are still the
+// caller's buffers.
+//
+// The array is a host-side stand-in when named from host code; its device
+// address is looked up once per device with cudaGetSymbolAddress, on the first
+// call made while that device is current.
+// ---------------------------------------------------------------------------
+
+namespace omoe {
+namespace {
+
+constexpr int kNaMaxTokens = OMOE_NOALLOC_MAX_TOKENS;
+constexpr size_t kNaLogitsBytes = sizeof(float) * (size_t)kNaMaxTokens * kMaxExperts;      // 2 MiB
+constexpr size_t kNaBlocksBytes = sizeof(int32_t) * (size_t)(kNaMaxTokens / kRouterWarps) * kMaxExperts;  // 256 KiB
+constexpr size_t kNaRankBytes = sizeof(int32_t) * (size_t)kNaMaxTokens * kMaxTopK;         // 256 KiB
+constexpr size_t kNaScratchBytes = kNaLogitsBytes + kNaBlocksBytes + kNaRankBytes;
+
+// Scratch shared by every omoe_route_noalloc call on a device (about 2.5 MiB,
+// held by each GPU that loads the library until the process exits).
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNaScratchBytes];
+
+constexpr int kNaMaxDevices = 64;
+unsigned char *g_na_ptr[kNaMaxDevices] = {};  // device address of the array, per device ordinal
+
+// counts[e] = sum over router blocks of block_counts[b][e]; one warp per expert.
+__global__ void noalloc_counts_kernel(const int32_t *__restrict__ block_counts, int n_blocks, int E,
+                                      int32_t *__restrict__ counts) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int e = warp; e < E; e += nwarps) {
+        int sum = 0;
+        for (int b = lane; b < n_blocks; b += 32) sum += block_counts[(size_t)b * E + e];
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) counts[e] = sum;
+    }
+}
+
+thread_local char g_na_err[256] = "";
+
+int na_fail(int code, const char *msg, const char *detail = "") {
+    snprintf(g_na_err, sizeof(g_na_err), "omoe_route_noalloc: %s%s", msg, detail);
+    return code;
+}
+
+}  // namespace
+}  // namespace omoe
+
+extern "C" {
+
+const char *omoe_route_noalloc_error(void) { return omoe::g_na_err; }
+
+int omoe_route_noalloc(const void *x_dev, const float *w_router_dev, const float *router_bias_dev, int32_t T,
+                       int32_t d_model, int32_t n_experts, int32_t top_k, int32_t renormalize, int32_t io_dtype,
+                       int32_t *topk_idx_dev, float *topk_w_dev, int32_t *counts_dev, void *cuda_stream) {
+    using namespace omoe;
+    if (T < 0 || d_model <= 0 || n_experts <= 0 || top_k <= 0) return na_fail(OMOE_ERR_INVALID, "sizes must be positive");
+    if (T > kNaMaxTokens || n_experts > kMaxExperts || top_k > kMaxTopK || top_k > n_experts) {
+        char lim[128];
+        snprintf(lim, sizeof(lim), " (limits: T <= %d, n_experts <= %d, top_k <= min(n_experts, %d))", kNaMaxTokens,
+                 kMaxExperts, kMaxTopK);
+        return na_fail(OMOE_ERR_TOO_LARGE, "the fixed scratch array is too small for this call", lim);
+    }
+    if (d_model % 8) return na_fail(OMOE_ERR_INVALID, "d_model must be a multiple of 8");
+    if (io_dtype != OMOE_F32 && io_dtype != OMOE_BF16) return na_fail(OMOE_ERR_INVALID, "bad io_dtype");
+    if (!counts_dev || (T > 0 && (!x_dev || !w_router_dev || !topk_idx_dev || !topk_w_dev)))
+        return na_fail(OMOE_ERR_INVALID, "null buffer");
+
+    // set-up, once per device, with that device current
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNaMaxDevices)
+        return na_fail(OMOE_ERR_CUDA, "cudaGetDevice failed or device ordinal out of range");
+    if (g_na_ptr[dev] == nullptr) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) return na_fail(OMOE_ERR_CUDA, "cudaGetSymbolAddress failed: ", cudaGetErrorString(e));
+        g_na_ptr[dev] = static_cast<unsigned char *>(p);
+    }
+    unsigned char *scratch = g_na_ptr[dev];
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+
+    // A stack handle that only carries what the router launcher reads; every
+    // workspace pointer lands in the fixed array, every output in caller memory.
+    omoe_handle hd;
+    memset(&hd, 0, sizeof(hd));
+    hd.cfg.d_model = d_model;
+    hd.cfg.n_experts = n_experts;
+    hd.cfg.top_k = top_k;
+    hd.cfg.renormalize = renormalize;
+    hd.w_router = const_cast<float *>(w_router_dev);
+    hd.router_bias = const_cast<float *>(router_bias_dev);
+    hd.logits = reinterpret_cast<float *>(scratch);
+    hd.block_counts = reinterpret_cast<int32_t *>(scratch + kNaLogitsBytes);
+    hd.pos = reinterpret_cast<int32_t *>(scratch + kNaLogitsBytes + kNaBlocksBytes);
+    hd.topk_idx = topk_idx_dev;
+    hd.topk_w = topk_w_dev;
+    const int n_blocks = T > 0 ? ceil_div(T, router_tokens_per_block(n_experts)) : 0;
+    if (T > 0) {
+        int n = 0;
+        cudaError_t e = launch_router(&hd, x_dev, io_dtype, T, s, &n);
+        if (e != cudaSuccess) return na_fail(OMOE_ERR_CUDA, "router launch failed: ", cudaGetErrorString(e));
+    }
+    // Nothing in the array has to start at zero: every router block writes all
+    // n_experts entries of its histogram row, and only rows [0, n_blocks) are read.
+    noalloc_counts_kernel<<<1, 256, 0, s>>>(hd.block_counts, n_blocks, n_experts, counts_dev);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return na_fail(OMOE_ERR_CUDA, "counts launch failed: ", cudaGetErrorString(e));
+    g_na_err[0] = 0;
+    return OMOE_OK;
+}
+
+}  // extern "C"

@@ -31,7 +31,9 @@ SYMBOLS = (
     "omoe_create", "omoe_destroy", "omoe_last_error", "omoe_set_weights", "omoe_forward",
     "omoe_forward_host", "omoe_get_routing", "omoe_get_logits", "omoe_last_launch_count",
     "omoe_set_profiling", "omoe_get_stage_ms", "omoe_ep_unique_id", "omoe_ep_init",
+    "omoe_route_noalloc", "omoe_route_noalloc_error",
 )
+NOALLOC_MAX_TOKENS = 4096
 
 
 class OmoeError(RuntimeError):
@@ -96,8 +98,11 @@ def lib():
     L.omoe_get_stage_ms.argtypes = [vp, vp]
     L.omoe_ep_unique_id.argtypes = [vp]
     L.omoe_ep_init.argtypes = [vp, vp]
+    L.omoe_route_noalloc.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]
+    L.omoe_route_noalloc_error.argtypes = []
+    L.omoe_route_noalloc_error.restype = C.c_char_p
     for name in SYMBOLS:
-        if name != "omoe_last_error":
+        if name not in ("omoe_last_error", "omoe_route_noalloc_error"):
             getattr(L, name).restype = C.c_int
     _lib = L
     return L
