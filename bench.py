@@ -217,9 +217,7 @@ def run_ours(args, cfg):
     layer = MoELayer(d, dff, E, k, bias=bias is not None, t_max=T_local, compute_dtype=cdt, world=world, rank=rank)
     layer.setWeights(w_r, w_g, w_u, w_d, bias)
     if world > 1:
-        idb = [layer.ep_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(idb, src=0)
-        layer.ep_init(idb[0])
+        layer.ep_connect()
     del w_g, w_u, w_d
     torch.cuda.synchronize()
 

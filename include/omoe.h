@@ -69,7 +69,7 @@ typedef struct omoe_config {
     int32_t compute_dtype;   /* OMOE_F32: fp32 FMA everywhere; OMOE_BF16: bf16 tensor cores, fp32 accumulate */
     int32_t renormalize;     /* 1: gate weights divided by the sum over the k picks */
     int32_t has_router_bias; /* 1: a per-expert bias is added to the router logits */
-    int32_t world;           /* expert-parallel ranks (1 = single GPU) */
+    int32_t world;           /* expert-parallel ranks (1 = single GPU, at most 8) */
     int32_t rank;            /* this rank; owns experts [rank*E/world, (rank+1)*E/world) */
     int32_t recv_rows_max;   /* EP only: capacity (rows) of the buffer that receives dispatched
                                 tokens; 0 = t_max*top_k*world (worst case) */
@@ -149,15 +149,26 @@ OMOE_API int omoe_get_stage_ms(omoe_handle *h, float *ms /* [OMOE_N_STAGES] */);
 
 /*
  * Expert-parallel transport.  The reference's only multi-GPU mechanism is
- * cudaMemcpyPeerAsync between Java threads
- * (src/main/java/com/omega/engine/parallel/dp/NetworkRunnable.java:442-459);
- * here ranks are processes and rows travel by NCCL all-to-all.
- * omoe_ep_unique_id fills a 128-byte NCCL id on rank 0; the host shares it
- * with every rank by any means, then each rank calls omoe_ep_init.
+ * cudaMemcpyPeerAsync between Java threads, driven from the host
+ * (src/main/java/com/omega/engine/parallel/dp/NetworkRunnable.java:442-459).
+ * Here every rank is one process on one GPU of an NVLink/NVSwitch node, and
+ * the kernels move the rows themselves: the dispatch kernel stores each token
+ * row into the buffer of the rank that owns the expert, the combine kernel
+ * loads expert outputs back from the owners, both over peer-mapped memory.
+ *
+ * Set-up, once: every rank calls omoe_ep_export, the host gathers the blobs
+ * of all ranks in rank order (any transport: a file, sockets,
+ * torch.distributed), every rank calls omoe_ep_import with the gathered
+ * array, and a host barrier follows before the first forward.  After that
+ * omoe_forward is a collective: every rank calls it the same number of
+ * times, each with its own T (0 is allowed).  A rank that does not show up
+ * makes the others' bounded waits (10 s, or OMOE_EP_WAIT_MS) run out:
+ * they return normally and the next synchronising call reports
+ * OMOE_ERR_DEVICE.
  */
-#define OMOE_EP_ID_BYTES 128
-OMOE_API int omoe_ep_unique_id(void *id_out /* [OMOE_EP_ID_BYTES] */);
-OMOE_API int omoe_ep_init(omoe_handle *h, const void *id /* [OMOE_EP_ID_BYTES] */);
+#define OMOE_EP_BLOB_BYTES 192
+OMOE_API int omoe_ep_export(omoe_handle *h, void *blob /* [OMOE_EP_BLOB_BYTES] */);
+OMOE_API int omoe_ep_import(omoe_handle *h, const void *all_blobs /* [world][OMOE_EP_BLOB_BYTES] */);
 
 /*
  * Routing only, with NO allocation.  This entry point has no counterpart in

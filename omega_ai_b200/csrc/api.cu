@@ -103,7 +103,8 @@ int omoe_destroy(omoe_handle *h) {
     ep_destroy(h);
     void *ptrs[] = {h->w_router, h->router_bias, h->w_gate, h->w_up, h->w_down, h->logits, h->topk_idx,
                     h->topk_w, h->block_counts, h->counts, h->offsets, h->poffsets, h->tile_expert, h->pos,
-                    h->perm_out, h->dev_err, h->xp, h->hbuf, h->yp, h->x_stage, h->y_stage};
+                    h->perm_out, h->dev_err, h->xp, h->hbuf, h->yp, h->x_stage, h->y_stage, h->d_row_table,
+                    h->d_out_table, h->ticket, h->dst_base != h->poffsets ? h->dst_base : nullptr};
     for (void *p : ptrs)
         if (p) cudaFree(p);
     for (int i = 0; i <= OMOE_N_STAGES; i++)
@@ -126,8 +127,9 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
         return fail(nullptr, OMOE_ERR_INVALID, "omoe_create: top_k must be <= min(n_experts, %d)", kMaxTopK);
     if (c.compute_dtype != OMOE_F32 && c.compute_dtype != OMOE_BF16)
         return fail(nullptr, OMOE_ERR_INVALID, "omoe_create: compute_dtype must be OMOE_F32 or OMOE_BF16");
-    if (c.world < 1 || c.rank < 0 || c.rank >= c.world || c.n_experts % c.world)
-        return fail(nullptr, OMOE_ERR_INVALID, "omoe_create: need 0 <= rank < world and world dividing n_experts");
+    if (c.world < 1 || c.world > kMaxWorld || c.rank < 0 || c.rank >= c.world || c.n_experts % c.world)
+        return fail(nullptr, OMOE_ERR_INVALID, "omoe_create: need 0 <= rank < world <= %d and world dividing n_experts",
+                    kMaxWorld);
     if (c.compute_dtype == OMOE_BF16 && (c.d_model < 64 || c.d_ff < 64))
         return fail(nullptr, OMOE_ERR_UNSUPPORTED, "omoe_create: the bf16 path needs d_model, d_ff >= 64");
     for (int i = 0; i < 5; i++)
@@ -153,15 +155,11 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
 
     const int64_t E = c.n_experts, k = c.top_k, d = c.d_model, dff = c.d_ff, tm = c.t_max;
     // Rows the expert kernels may see on this rank: its own picks on one GPU,
-    // or up to recv_rows_max rows arriving from all ranks.
+    // or up to recv_rows_max rows arriving from all ranks; every local expert's
+    // segment is rounded up to kRowAlign.
     int64_t rows_in = tm * k;
     if (c.world > 1) rows_in = c.recv_rows_max > 0 ? (int64_t)c.recv_rows_max : tm * k * c.world;
-    // the send-side dispatch buffer is laid out over all E experts, the
-    // receive side over the local ones; one capacity covers both
-    int64_t pad_experts = c.world > 1 ? E : h->e_local;
-    int64_t rows_send = (ceil_div((int)(tm * k), kRowAlign) + E) * (int64_t)kRowAlign;
-    int64_t rows_recv = ((rows_in + kRowAlign - 1) / kRowAlign + pad_experts) * (int64_t)kRowAlign;
-    h->rows_cap = rows_send > rows_recv ? rows_send : rows_recv;
+    h->rows_cap = ((rows_in + kRowAlign - 1) / kRowAlign + h->e_local) * (int64_t)kRowAlign;
     const size_t cs = elt_size(c.compute_dtype);
 
 #define ALLOC(field, count)                                                          \
@@ -206,10 +204,26 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
     ALLOC(pos, tm * k);
     ALLOC(perm_out, tm * k);
     ALLOC(dev_err, 1);
+    ALLOC(ticket, 1);
+    ALLOC(d_row_table, c.world);
+    ALLOC(d_out_table, c.world);
+    if (c.world > 1) ALLOC(dst_base, E);
 #undef ALLOC
     h->ex_counts = h->counts;
     h->ex_poffsets = h->poffsets;
     h->ex_tile_expert = h->tile_expert;
+    if (c.world == 1) {
+        h->dst_base = h->poffsets;
+        cudaMemcpy(h->d_row_table, &h->xp, sizeof(void *), cudaMemcpyHostToDevice);
+        cudaMemcpy(h->d_out_table, &h->yp, sizeof(void *), cudaMemcpyHostToDevice);
+    } else {
+        int rc = ep_create(h);
+        if (rc != OMOE_OK) {
+            fail(nullptr, rc, "omoe_create: %s", h->err);
+            omoe_destroy(h);
+            return rc;
+        }
+    }
     cudaMemset(h->dev_err, 0, sizeof(int32_t));
     // padding rows of the dispatch buffers are never read back, but start them
     // at zero so no stale NaN pattern ever enters a tensor-core tile
@@ -302,7 +316,7 @@ int omoe_forward(omoe_handle *h, const void *x_dev, void *y_dev, int32_t T, int3
     MARK(1);
     CU_TRY(h, launch_scan(h, T, s, &n));
     MARK(2);
-    CU_TRY(h, launch_permute(h, x_dev, io_dtype, T, s, &n));
+    CU_TRY(h, launch_permute(h, x_dev, io_dtype, T, s, &n, nullptr));
     MARK(3);
     MARK(4);
     if (h->cfg.compute_dtype == OMOE_BF16) {
@@ -313,7 +327,7 @@ int omoe_forward(omoe_handle *h, const void *x_dev, void *y_dev, int32_t T, int3
     }
     MARK(6);
     MARK(7);
-    CU_TRY(h, launch_combine(h, y_dev, io_dtype, T, s, &n));
+    CU_TRY(h, launch_combine(h, y_dev, io_dtype, T, s, &n, nullptr));
     MARK(8);
 #undef MARK
     h->ev_valid = prof;
@@ -386,11 +400,14 @@ int omoe_get_stage_ms(omoe_handle *h, float *ms) {
     return check_dev_err(h);
 }
 
-int omoe_ep_unique_id(void *id_out) { return ep_unique_id(id_out); }
+int omoe_ep_export(omoe_handle *h, void *blob) {
+    if (!h || !blob) return OMOE_ERR_INVALID;
+    return ep_export(h, blob);
+}
 
-int omoe_ep_init(omoe_handle *h, const void *id) {
-    if (!h || !id) return OMOE_ERR_INVALID;
-    return ep_init(h, id);
+int omoe_ep_import(omoe_handle *h, const void *all_blobs) {
+    if (!h || !all_blobs) return OMOE_ERR_INVALID;
+    return ep_import(h, all_blobs);
 }
 
 }  // extern "C"

@@ -28,26 +28,36 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 // One warp per token, 8 columns per lane per step (16 bytes of bf16 / 32 bytes of fp32).
 template <typename YT, typename OT, int K>
 __global__ void __launch_bounds__(256)
-combine_kernel(const YT *__restrict__ yp, OT *__restrict__ y, const int32_t *__restrict__ pos,
-               const float *__restrict__ topk_w, int T, int d, int k_rt) {
+combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const int32_t *__restrict__ pos,
+               const int32_t *__restrict__ topk_idx, const float *__restrict__ topk_w, int T, int d, int k_rt,
+               int e_local, EpWait wait, int32_t *dev_err) {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wait.flags != nullptr) {
+        // expert-parallel return: rows are read from the owners' output buffers
+        // over NVLink once every rank has published them
+        if ((int)threadIdx.x < wait.world) ep_wait_flag(wait.flags + threadIdx.x, wait.seq, wait.timeout_ns, dev_err);
+        __syncthreads();
+    }
     if (t >= T) return;
     const int k = (K > 0) ? K : k_rt;
     constexpr int KR = (K > 0) ? K : kMaxTopK;
-    int row[KR];
+    const YT *src[KR];
     float w[KR];
     {
-        int r = 0;
+        int r = 0, q = 0;
         float g = 0.f;
         if (lane < k) {
             r = pos[(size_t)t * k + lane];
+            q = topk_idx[(size_t)t * k + lane] / e_local;
             g = topk_w[(size_t)t * k + lane];
         }
 #pragma unroll
         for (int j = 0; j < KR; j++) {
-            row[j] = __shfl_sync(0xffffffffu, r, j);
+            int rj = __shfl_sync(0xffffffffu, r, j);
+            int qj = __shfl_sync(0xffffffffu, q, j);
             w[j] = __shfl_sync(0xffffffffu, g, j);
+            src[j] = (j < k) ? static_cast<const YT *>(out_table[qj]) + (size_t)rj * d : nullptr;
         }
     }
     for (int c = lane * 8; c < d; c += 256) {
@@ -57,11 +67,11 @@ combine_kernel(const YT *__restrict__ yp, OT *__restrict__ y, const int32_t *__r
             if (j < k) {
                 float v[8];
                 if constexpr (sizeof(YT) == 2) {
-                    uint4 r = __ldcs(reinterpret_cast<const uint4 *>(yp + (size_t)row[j] * d + c));
+                    uint4 r = __ldcs(reinterpret_cast<const uint4 *>(src[j] + c));
                     unpack8(r, v);
                 } else {
-                    float4 a = __ldcs(reinterpret_cast<const float4 *>(yp + (size_t)row[j] * d + c));
-                    float4 b = __ldcs(reinterpret_cast<const float4 *>(yp + (size_t)row[j] * d + c) + 1);
+                    float4 a = __ldcs(reinterpret_cast<const float4 *>(src[j] + c));
+                    float4 b = __ldcs(reinterpret_cast<const float4 *>(src[j] + c) + 1);
                     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
                     v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
                 }
@@ -85,33 +95,37 @@ combine_kernel(const YT *__restrict__ yp, OT *__restrict__ y, const int32_t *__r
 }
 
 template <typename YT, typename OT>
-cudaError_t launch_k(omoe_handle *h, void *y, int T, cudaStream_t s) {
-    const int d = h->cfg.d_model, k = h->cfg.top_k;
+cudaError_t launch_k(omoe_handle *h, void *y, int T, cudaStream_t s, const EpWait *wait) {
+    const int d = h->cfg.d_model, k = h->cfg.top_k, El = h->e_local;
     dim3 grid(ceil_div(T, 8)), block(256);
-    const YT *yp = static_cast<const YT *>(h->yp);
     OT *out = static_cast<OT *>(y);
+    EpWait wt = wait ? *wait : EpWait{nullptr, 1, 0, 0};
+#define OMOE_COMBINE(KK)                                                                                         \
+    combine_kernel<YT, OT, KK><<<grid, block, 0, s>>>(h->d_out_table, out, h->pos, h->topk_idx, h->topk_w, T, d, k, \
+                                                      El, wt, h->dev_err)
     switch (k) {
-        case 1: combine_kernel<YT, OT, 1><<<grid, block, 0, s>>>(yp, out, h->pos, h->topk_w, T, d, k); break;
-        case 2: combine_kernel<YT, OT, 2><<<grid, block, 0, s>>>(yp, out, h->pos, h->topk_w, T, d, k); break;
-        case 4: combine_kernel<YT, OT, 4><<<grid, block, 0, s>>>(yp, out, h->pos, h->topk_w, T, d, k); break;
-        case 6: combine_kernel<YT, OT, 6><<<grid, block, 0, s>>>(yp, out, h->pos, h->topk_w, T, d, k); break;
-        case 8: combine_kernel<YT, OT, 8><<<grid, block, 0, s>>>(yp, out, h->pos, h->topk_w, T, d, k); break;
-        default: combine_kernel<YT, OT, 0><<<grid, block, 0, s>>>(yp, out, h->pos, h->topk_w, T, d, k); break;
+        case 1: OMOE_COMBINE(1); break;
+        case 2: OMOE_COMBINE(2); break;
+        case 4: OMOE_COMBINE(4); break;
+        case 6: OMOE_COMBINE(6); break;
+        case 8: OMOE_COMBINE(8); break;
+        default: OMOE_COMBINE(0); break;
     }
+#undef OMOE_COMBINE
     return cudaGetLastError();
 }
 
 }  // namespace
 
-cudaError_t launch_combine(omoe_handle *h, void *y, int io_dtype, int T, cudaStream_t s, int *n) {
+cudaError_t launch_combine(omoe_handle *h, void *y, int io_dtype, int T, cudaStream_t s, int *n, const EpWait *wait) {
     const bool cbf = h->cfg.compute_dtype == OMOE_BF16;
     cudaError_t e;
     if (cbf && io_dtype == OMOE_BF16)
-        e = launch_k<__nv_bfloat16, __nv_bfloat16>(h, y, T, s);
+        e = launch_k<__nv_bfloat16, __nv_bfloat16>(h, y, T, s, wait);
     else if (cbf && io_dtype == OMOE_F32)
-        e = launch_k<__nv_bfloat16, float>(h, y, T, s);
+        e = launch_k<__nv_bfloat16, float>(h, y, T, s, wait);
     else if (!cbf && io_dtype == OMOE_F32)
-        e = launch_k<float, float>(h, y, T, s);
+        e = launch_k<float, float>(h, y, T, s, wait);
     else
         return cudaErrorInvalidValue;
     if (e == cudaSuccess) (*n)++;

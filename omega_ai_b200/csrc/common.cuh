@@ -18,6 +18,7 @@ constexpr int kRowAlign = 128;
 constexpr int kMaxTopK = 16;
 constexpr int kMaxExperts = 128;
 constexpr int kRouterWarps = 8;  // warps per router block
+constexpr int kMaxWorld = 8;     // expert-parallel ranks (GPUs of one NVSwitch node)
 
 // Device-side error word bits (set by kernels instead of trapping).
 constexpr int kDevErrTimeout = 1;   // a bounded wait ran out
@@ -65,7 +66,15 @@ struct omoe_handle {
     // Views the expert kernels read.  On one GPU they alias the arrays above;
     // with expert parallelism they describe the rows received from all ranks.
     int32_t *ex_counts, *ex_poffsets, *ex_tile_expert;
-    int32_t *pos;         // [t_max*k] row of each pick in the padded dispatch buffer
+    int32_t *pos;         // [t_max*k] row of each pick in its owner's padded dispatch buffer
+    // Where this rank's picks of expert e start in the dispatch buffer of the
+    // rank that owns e.  On one GPU this is poffsets; with expert parallelism
+    // it is computed from the all-ranks count matrix.
+    int32_t *dst_base;    // [E]
+    // Device tables [world]: base address of every rank's dispatch buffer (xp)
+    // and expert-output buffer (yp); entry `rank` is this GPU's own buffer.
+    void **d_row_table, **d_out_table;
+    int32_t *ticket;      // blocks of the dispatch kernel that have finished (EP)
     int32_t *perm_out;    // [t_max*k] scratch for omoe_get_routing
     int32_t *dev_err;     // device error word
 
@@ -99,9 +108,16 @@ namespace omoe {
 
 cudaError_t launch_router(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n);
 cudaError_t launch_scan(omoe_handle *h, int T, cudaStream_t s, int *n);
-cudaError_t launch_permute(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n);
+// sig != nullptr: after the last block has written its rows, raise the
+// "rows have landed" flag on every rank (expert-parallel dispatch).
+struct EpSignal;
+cudaError_t launch_permute(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n,
+                           const EpSignal *sig);
 cudaError_t launch_perm_readout(omoe_handle *h, int T, cudaStream_t s);
-cudaError_t launch_combine(omoe_handle *h, void *y, int io_dtype, int T, cudaStream_t s, int *n);
+// wait != nullptr: every block first waits (bounded) until all ranks have
+// published their expert outputs (expert-parallel return).
+struct EpWait;
+cudaError_t launch_combine(omoe_handle *h, void *y, int io_dtype, int T, cudaStream_t s, int *n, const EpWait *wait);
 cudaError_t launch_experts_f32(omoe_handle *h, cudaStream_t s, int *n);
 cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid);
 cudaError_t launch_convert_f32_to_bf16(const float *src, __nv_bfloat16 *dst, int64_t n, cudaStream_t s);
@@ -112,5 +128,40 @@ cudaError_t launch_convert_bf16_to_f32(const __nv_bfloat16 *src, float *dst, int
 bool build_tensor_maps(omoe_handle *h);
 
 int router_tokens_per_block(int E);
+
+// Flag words the expert-parallel kernels exchange through peer-mapped memory.
+struct EpSignal {
+    uint32_t *const *flags;  // device table [world]: address of flag_rows[0] on every rank
+    int world, rank;
+    uint32_t seq;
+};
+struct EpWait {
+    const uint32_t *flags;   // this rank's flag_yp[world]
+    int world;
+    uint32_t seq;
+    unsigned long long timeout_ns;
+};
+
+// Bounded spin until *flag >= seq (acquire, system scope).  Returns false on
+// time-out or when the device error word is already set.
+__device__ __forceinline__ bool ep_wait_flag(const uint32_t *flag, uint32_t seq, unsigned long long timeout_ns,
+                                             int32_t *dev_err) {
+    unsigned long long t0 = 0;
+    for (uint32_t spin = 0;; spin++) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if ((int32_t)(v - seq) >= 0) return true;
+        if ((spin & 63u) == 63u) {
+            if (*(volatile int32_t *)dev_err != 0) return false;
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > timeout_ns) {
+                atomicOr(dev_err, kDevErrTimeout);
+                return false;
+            }
+        }
+    }
+}
 
 }  // namespace omoe

@@ -1,17 +1,329 @@
-// Expert-parallel transport (placeholder until the NCCL path lands).
+// Expert-parallel transport over NVLink peer memory.
+//
+// The reference's only multi-GPU mechanism is cudaMemcpyPeerAsync between Java
+// threads, driven from the host (src/main/java/com/omega/engine/parallel/dp/
+// NetworkRunnable.java:442-459).  Here each rank is a process on one GPU and
+// the kernels themselves move the rows: the dispatch kernel stores every token
+// row straight into the dispatch buffer of the rank that owns the expert, and
+// the combine kernel loads the expert outputs back from the owners' buffers.
+// Buffers are shared between processes with CUDA IPC handles; no host
+// synchronisation happens inside a forward, and no collective library is used.
+//
+// One forward (sequence number seq) on every rank:
+//   1. router, scan                          (local)
+//   2. exchange kernel: publish my per-expert counts to every rank, wait for
+//      all rows of the count matrix, derive where my picks go on each owner
+//      (dst_base) and how the rows I receive are laid out (ex_* arrays)
+//   3. dispatch: rows -> owners' buffers, then "rows landed" flag to every rank
+//   4. wait kernel: all ranks' rows have landed here
+//   5. grouped expert products                (local)
+//   6. signal kernel: "outputs ready" flag to every rank
+//   7. combine: wait for all owners' flags, gather rows over NVLink
+// Flags carry the sequence number, so nothing is reset between forwards; the
+// count matrix is double-buffered by the parity of seq.  Every wait is bounded
+// and reports through the device error word instead of hanging.
+#include <stdlib.h>
+#include <string.h>
+
 #include "ep.cuh"
 
 namespace omoe {
 
-int ep_unique_id(void *) { return OMOE_ERR_UNSUPPORTED; }
-int ep_init(omoe_handle *h, const void *) {
-    snprintf(h->err, sizeof(h->err), "expert parallelism is not built yet");
-    return OMOE_ERR_UNSUPPORTED;
+namespace {
+
+// Control block of one rank, written by its peers.  Lives in IPC-shared memory.
+struct EpCtl {
+    int32_t cnt[2][kMaxWorld][kMaxExperts];  // [parity][source rank][expert]
+    uint32_t flag_cnt[2][kMaxWorld];         // seq once source's count row is complete
+    uint32_t flag_rows[kMaxWorld];           // seq once source's rows have landed in my dispatch buffer
+    uint32_t flag_out[kMaxWorld];            // seq once owner's expert outputs are readable
+};
+
+struct EpState {
+    EpCtl *ctl;                 // this rank's control block (device)
+    EpCtl **d_ctl_table;        // device [world]
+    uint32_t **d_rows_flags;    // device [world]: &peer_ctl[q]->flag_rows[0]
+    uint32_t **d_out_flags;     // device [world]: &peer_ctl[q]->flag_out[0]
+    int32_t *ex_counts, *ex_poffsets, *ex_tile_expert;  // layout of the rows this rank receives
+    void *peer_ptrs[kMaxWorld][3];  // opened IPC mappings (ctl, xp, yp), null for self
+    bool imported;
+    uint32_t seq;
+    unsigned long long timeout_ns;
+};
+
+struct IpcBlob {
+    cudaIpcMemHandle_t ctl, xp, yp;
+};
+static_assert(sizeof(IpcBlob) == OMOE_EP_BLOB_BYTES, "blob size is part of the ABI");
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-int ep_forward(omoe_handle *h, const void *, void *, int, int, cudaStream_t) {
-    snprintf(h->err, sizeof(h->err), "expert parallelism is not built yet");
-    return OMOE_ERR_UNSUPPORTED;
+
+// One block of 256 threads.
+__global__ void __launch_bounds__(256)
+ep_exchange_kernel(EpCtl *self, EpCtl *const *__restrict__ peers, const int32_t *__restrict__ counts, int W, int r,
+                   int E, int El, uint32_t seq, int rows_cap, int32_t *__restrict__ dst_base,
+                   int32_t *__restrict__ ex_counts, int32_t *__restrict__ ex_poffsets,
+                   int32_t *__restrict__ ex_tile_expert, int max_tiles, int32_t *ticket, int32_t *dev_err,
+                   unsigned long long timeout_ns) {
+    __shared__ int32_t s_cnt[kMaxWorld][kMaxExperts];
+    __shared__ int32_t s_tot[kMaxExperts];
+    __shared__ int32_t s_rpoff[kMaxExperts + kMaxWorld];  // padded start of expert e in its owner's buffer
+    __shared__ int32_t s_mypoff[kMaxExperts + 1];
+    __shared__ int s_bad;
+    const int tid = threadIdx.x, par = seq & 1u;
+    if (tid == 0) { *ticket = 0; s_bad = 0; }
+    // publish my counts to every rank (my own included)
+    for (int i = tid; i < W * E; i += blockDim.x) {
+        int q = i / E, e = i % E;
+        peers[q]->cnt[par][r][e] = counts[e];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < W) st_release_sys(&peers[tid]->flag_cnt[par][r], seq);
+    // wait for every source's row
+    if (tid < W) {
+        if (!ep_wait_flag(&self->flag_cnt[par][tid], seq, timeout_ns, dev_err)) s_bad = 1;
+    }
+    __syncthreads();
+    __threadfence_system();
+    for (int i = tid; i < W * E; i += blockDim.x) {
+        int s = i / E, e = i % E;
+        s_cnt[s][e] = *(volatile int32_t *)&self->cnt[par][s][e];
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x) {
+        int t = 0;
+        for (int s = 0; s < W; s++) t += s_cnt[s][e];
+        s_tot[e] = t;
+    }
+    __syncthreads();
+    if (tid < W) {  // thread q lays out owner q's buffer
+        int q = tid, off = 0;
+        for (int le = 0; le < El; le++) {
+            int e = q * El + le;
+            s_rpoff[e] = off;
+            off += (s_tot[e] + kRowAlign - 1) / kRowAlign * kRowAlign;
+        }
+        if (off > rows_cap) s_bad = 1;  // every rank sees the same matrix, so all of them refuse together
+        if (q == r) {
+            for (int le = 0; le < El; le++) s_mypoff[le] = s_rpoff[q * El + le];
+            s_mypoff[El] = off;
+        }
+    }
+    __syncthreads();
+    const bool bad = s_bad != 0;
+    if (bad && tid == 0) atomicOr(dev_err, kDevErrBounds);
+    for (int e = tid; e < E; e += blockDim.x) {
+        int before = 0;
+        for (int s = 0; s < r; s++) before += s_cnt[s][e];
+        // a refused step parks every row in row 0 of the owner's buffer: harmless, and nothing is read back
+        dst_base[e] = bad ? 0 : s_rpoff[e] + before;
+    }
+    for (int le = tid; le < El; le += blockDim.x) {
+        ex_counts[le] = bad ? 0 : s_tot[r * El + le];
+        ex_poffsets[le] = bad ? 0 : s_mypoff[le];
+    }
+    if (tid == 0) ex_poffsets[El] = bad ? 0 : s_mypoff[El];
+    const int n_tiles = bad ? 0 : s_mypoff[El] / kRowAlign;
+    for (int i = tid; i < max_tiles; i += blockDim.x) {
+        int ex = -1;
+        if (i < n_tiles) {
+            int row = i * kRowAlign;
+            ex = 0;
+            while (ex + 1 < El && s_mypoff[ex + 1] <= row) ex++;
+        }
+        ex_tile_expert[i] = ex;
+    }
 }
-void ep_destroy(omoe_handle *) {}
+
+__global__ void ep_wait_kernel(const uint32_t *flags, int W, uint32_t seq, int32_t *dev_err,
+                               unsigned long long timeout_ns) {
+    if ((int)threadIdx.x < W) ep_wait_flag(flags + threadIdx.x, seq, timeout_ns, dev_err);
+}
+
+// flags[q] points at the flag array on rank q; slot `r` there belongs to this rank.
+__global__ void ep_signal_kernel(uint32_t *const *flags, int W, int r, uint32_t seq) {
+    __threadfence_system();
+    if ((int)threadIdx.x < W) st_release_sys(flags[threadIdx.x] + r, seq);
+}
+
+int ep_fail(omoe_handle *h, int code, const char *what, cudaError_t e) {
+    snprintf(h->err, sizeof(h->err), "%s: %s", what, cudaGetErrorString(e));
+    return code;
+}
+
+}  // namespace
+
+int ep_create(omoe_handle *h) {
+    EpState *st = static_cast<EpState *>(calloc(1, sizeof(EpState)));
+    if (!st) return OMOE_ERR_NOMEM;
+    h->ep = st;
+    const int W = h->cfg.world, El = h->e_local;
+    cudaError_t e;
+    if ((e = cudaMalloc(&st->ctl, sizeof(EpCtl))) != cudaSuccess) return ep_fail(h, OMOE_ERR_NOMEM, "cudaMalloc(ctl)", e);
+    cudaMemset(st->ctl, 0, sizeof(EpCtl));
+    if ((e = cudaMalloc(&st->d_ctl_table, sizeof(void *) * W)) != cudaSuccess ||
+        (e = cudaMalloc(&st->d_rows_flags, sizeof(void *) * W)) != cudaSuccess ||
+        (e = cudaMalloc(&st->d_out_flags, sizeof(void *) * W)) != cudaSuccess ||
+        (e = cudaMalloc(&st->ex_counts, sizeof(int32_t) * El)) != cudaSuccess ||
+        (e = cudaMalloc(&st->ex_poffsets, sizeof(int32_t) * (El + 1))) != cudaSuccess ||
+        (e = cudaMalloc(&st->ex_tile_expert, sizeof(int32_t) * (h->rows_cap / kRowAlign))) != cudaSuccess)
+        return ep_fail(h, OMOE_ERR_NOMEM, "cudaMalloc(expert-parallel state)", e);
+    h->ex_counts = st->ex_counts;
+    h->ex_poffsets = st->ex_poffsets;
+    h->ex_tile_expert = st->ex_tile_expert;
+    st->seq = 0;
+    st->timeout_ns = 10ull * 1000 * 1000 * 1000;
+    if (const char *v = getenv("OMOE_EP_WAIT_MS")) {
+        long ms = atol(v);
+        if (ms > 0) st->timeout_ns = (unsigned long long)ms * 1000000ull;
+    }
+    return OMOE_OK;
+}
+
+void ep_destroy(omoe_handle *h) {
+    EpState *st = static_cast<EpState *>(h->ep);
+    if (!st) return;
+    for (int q = 0; q < kMaxWorld; q++)
+        for (int i = 0; i < 3; i++)
+            if (st->peer_ptrs[q][i]) cudaIpcCloseMemHandle(st->peer_ptrs[q][i]);
+    void *ptrs[] = {st->ctl, st->d_ctl_table, st->d_rows_flags, st->d_out_flags, st->ex_counts, st->ex_poffsets,
+                    st->ex_tile_expert};
+    for (void *p : ptrs)
+        if (p) cudaFree(p);
+    free(st);
+    h->ep = nullptr;
+}
+
+int ep_export(omoe_handle *h, void *blob) {
+    EpState *st = static_cast<EpState *>(h->ep);
+    if (!st) {
+        snprintf(h->err, sizeof(h->err), "omoe_ep_export: the layer was created with world == 1");
+        return OMOE_ERR_STATE;
+    }
+    IpcBlob b;
+    cudaError_t e;
+    if ((e = cudaIpcGetMemHandle(&b.ctl, st->ctl)) != cudaSuccess || (e = cudaIpcGetMemHandle(&b.xp, h->xp)) != cudaSuccess ||
+        (e = cudaIpcGetMemHandle(&b.yp, h->yp)) != cudaSuccess)
+        return ep_fail(h, OMOE_ERR_COMM, "cudaIpcGetMemHandle", e);
+    memcpy(blob, &b, sizeof(b));
+    return OMOE_OK;
+}
+
+int ep_import(omoe_handle *h, const void *all_blobs) {
+    EpState *st = static_cast<EpState *>(h->ep);
+    if (!st) {
+        snprintf(h->err, sizeof(h->err), "omoe_ep_import: the layer was created with world == 1");
+        return OMOE_ERR_STATE;
+    }
+    if (st->imported) {
+        snprintf(h->err, sizeof(h->err), "omoe_ep_import: already imported");
+        return OMOE_ERR_STATE;
+    }
+    const int W = h->cfg.world, r = h->cfg.rank;
+    const IpcBlob *blobs = static_cast<const IpcBlob *>(all_blobs);
+    void *ctl[kMaxWorld], *xp[kMaxWorld], *yp[kMaxWorld];
+    uint32_t *rows_flags[kMaxWorld], *out_flags[kMaxWorld];
+    for (int q = 0; q < W; q++) {
+        if (q == r) {
+            ctl[q] = st->ctl;
+            xp[q] = h->xp;
+            yp[q] = h->yp;
+        } else {
+            const cudaIpcMemHandle_t *hs[3] = {&blobs[q].ctl, &blobs[q].xp, &blobs[q].yp};
+            for (int i = 0; i < 3; i++) {
+                cudaError_t e = cudaIpcOpenMemHandle(&st->peer_ptrs[q][i], *hs[i], cudaIpcMemLazyEnablePeerAccess);
+                if (e != cudaSuccess) return ep_fail(h, OMOE_ERR_COMM, "cudaIpcOpenMemHandle (is peer access available?)", e);
+            }
+            ctl[q] = st->peer_ptrs[q][0];
+            xp[q] = st->peer_ptrs[q][1];
+            yp[q] = st->peer_ptrs[q][2];
+        }
+        rows_flags[q] = static_cast<EpCtl *>(ctl[q])->flag_rows;  // address arithmetic only
+        out_flags[q] = static_cast<EpCtl *>(ctl[q])->flag_out;
+    }
+    cudaError_t e;
+    if ((e = cudaMemcpy(st->d_ctl_table, ctl, sizeof(void *) * W, cudaMemcpyHostToDevice)) != cudaSuccess ||
+        (e = cudaMemcpy(st->d_rows_flags, rows_flags, sizeof(void *) * W, cudaMemcpyHostToDevice)) != cudaSuccess ||
+        (e = cudaMemcpy(st->d_out_flags, out_flags, sizeof(void *) * W, cudaMemcpyHostToDevice)) != cudaSuccess ||
+        (e = cudaMemcpy(h->d_row_table, xp, sizeof(void *) * W, cudaMemcpyHostToDevice)) != cudaSuccess ||
+        (e = cudaMemcpy(h->d_out_table, yp, sizeof(void *) * W, cudaMemcpyHostToDevice)) != cudaSuccess)
+        return ep_fail(h, OMOE_ERR_CUDA, "cudaMemcpy(peer tables)", e);
+    st->imported = true;
+    return OMOE_OK;
+}
+
+int ep_forward(omoe_handle *h, const void *x, void *y, int T, int io_dtype, cudaStream_t s) {
+    EpState *st = static_cast<EpState *>(h->ep);
+    if (!st || !st->imported) {
+        snprintf(h->err, sizeof(h->err), "omoe_forward: call omoe_ep_export / omoe_ep_import on every rank first");
+        return OMOE_ERR_STATE;
+    }
+    const int W = h->cfg.world, r = h->cfg.rank, E = h->cfg.n_experts, El = h->e_local;
+    const uint32_t seq = ++st->seq;
+    int n = 0;
+    cudaError_t e = cudaSuccess;
+    const bool prof = h->profiling;
+#define MARK(i) do { if (prof) cudaEventRecord(h->ev[i], s); } while (0)
+#define TRY(expr)                                                                      \
+    do {                                                                               \
+        e = (expr);                                                                    \
+        if (e != cudaSuccess) return ep_fail(h, OMOE_ERR_CUDA, #expr, e);              \
+    } while (0)
+    MARK(0);
+    if (T > 0) {
+        TRY(launch_router(h, x, io_dtype, T, s, &n));
+    }
+    MARK(1);
+    TRY(launch_scan(h, T, s, &n));  // T == 0: zero blocks, all counts zero
+    MARK(2);
+    ep_exchange_kernel<<<1, 256, 0, s>>>(st->ctl, st->d_ctl_table, h->counts, W, r, E, El, seq, (int)h->rows_cap,
+                                         h->dst_base, st->ex_counts, st->ex_poffsets, st->ex_tile_expert,
+                                         (int)(h->rows_cap / kRowAlign), h->ticket, h->dev_err, st->timeout_ns);
+    TRY(cudaGetLastError());
+    n++;
+    EpSignal sig{st->d_rows_flags, W, r, seq};
+    if (T > 0) {
+        TRY(launch_permute(h, x, io_dtype, T, s, &n, &sig));
+    } else {
+        ep_signal_kernel<<<1, 32, 0, s>>>(st->d_rows_flags, W, r, seq);
+        TRY(cudaGetLastError());
+        n++;
+    }
+    MARK(3);
+    ep_wait_kernel<<<1, 32, 0, s>>>(st->ctl->flag_rows, W, seq, h->dev_err, st->timeout_ns);
+    TRY(cudaGetLastError());
+    n++;
+    MARK(4);
+    if (h->cfg.compute_dtype == OMOE_BF16) {
+        TRY(launch_experts_bf16(h, s, &n, prof ? h->ev[5] : nullptr));
+    } else {
+        TRY(launch_experts_f32(h, s, &n));
+        MARK(5);
+    }
+    MARK(6);
+    ep_signal_kernel<<<1, 32, 0, s>>>(st->d_out_flags, W, r, seq);
+    TRY(cudaGetLastError());
+    n++;
+    MARK(7);
+    EpWait wt{st->ctl->flag_out, W, seq, st->timeout_ns};
+    if (T > 0) {
+        TRY(launch_combine(h, y, io_dtype, T, s, &n, &wt));
+    } else {
+        // still wait: the owners' outputs of this step must not be overwritten
+        // by a later step before every rank has passed this point
+        ep_wait_kernel<<<1, 32, 0, s>>>(st->ctl->flag_out, W, seq, h->dev_err, st->timeout_ns);
+        TRY(cudaGetLastError());
+        n++;
+    }
+    MARK(8);
+#undef MARK
+#undef TRY
+    h->ev_valid = prof;
+    h->last_launches = n;
+    return OMOE_OK;
+}
 
 }  // namespace omoe

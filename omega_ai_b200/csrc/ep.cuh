@@ -5,8 +5,9 @@
 
 namespace omoe {
 
-int ep_unique_id(void *id_out);
-int ep_init(omoe_handle *h, const void *id);
+int ep_create(omoe_handle *h);   // allocates the control block and receive-side layout arrays
+int ep_export(omoe_handle *h, void *blob);
+int ep_import(omoe_handle *h, const void *all_blobs);
 int ep_forward(omoe_handle *h, const void *x, void *y, int T, int io_dtype, cudaStream_t s);
 void ep_destroy(omoe_handle *h);
 

@@ -85,25 +85,35 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 
 // One warp per token: finalise the k row positions, read the token's row once
 // and write it to its k places with 16-byte stores.
+// Rows go to the dispatch buffer of the rank that owns the expert: row_table[q]
+// is that buffer's base (this GPU's own for q == rank, a peer-mapped NVLink
+// address otherwise), dst_base[e] the first row reserved there for this rank's
+// picks of expert e.
 template <typename XT, typename OT>
 __global__ void __launch_bounds__(256)
-permute_kernel(const XT *__restrict__ x, OT *__restrict__ xp, const int32_t *__restrict__ topk_idx,
+permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, const int32_t *__restrict__ topk_idx,
                int32_t *__restrict__ pos, const int32_t *__restrict__ block_base,
-               const int32_t *__restrict__ poffsets, int T, int d, int E, int k, int tokens_per_block) {
+               const int32_t *__restrict__ dst_base, int T, int d, int E, int e_local, int k, int tokens_per_block,
+               EpSignal sig, int32_t *ticket) {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (t >= T) return;
-    int my = 0;
-    if (lane < k) {
+    int my = 0, owner = 0;
+    if (t < T && lane < k) {
         int f = t * k + lane;
         int e = topk_idx[f];
         int b = t / tokens_per_block;
-        my = poffsets[e] + block_base[(size_t)b * E + e] + pos[f];
+        my = dst_base[e] + block_base[(size_t)b * E + e] + pos[f];
+        owner = e / e_local;
         pos[f] = my;
     }
-    int rows[kMaxTopK];
+    if (t < T) {
+    OT *dst[kMaxTopK];
 #pragma unroll
-    for (int j = 0; j < kMaxTopK; j++) rows[j] = __shfl_sync(0xffffffffu, my, j);
+    for (int j = 0; j < kMaxTopK; j++) {
+        int row = __shfl_sync(0xffffffffu, my, j);
+        int q = __shfl_sync(0xffffffffu, owner, j);
+        dst[j] = (j < k) ? static_cast<OT *>(row_table[q]) + (size_t)row * d : nullptr;
+    }
 
     const XT *src = x + (size_t)t * d;
     if constexpr (sizeof(XT) == sizeof(OT)) {
@@ -112,7 +122,7 @@ permute_kernel(const XT *__restrict__ x, OT *__restrict__ xp, const int32_t *__r
             uint4 v = __ldg(reinterpret_cast<const uint4 *>(src + c));
 #pragma unroll
             for (int j = 0; j < kMaxTopK; j++)
-                if (j < k) *reinterpret_cast<uint4 *>(xp + (size_t)rows[j] * d + c) = v;
+                if (j < k) *reinterpret_cast<uint4 *>(dst[j] + c) = v;
         }
     } else {
         // fp32 rows in, bf16 rows out: 8 elements per lane per step
@@ -126,14 +136,29 @@ permute_kernel(const XT *__restrict__ x, OT *__restrict__ xp, const int32_t *__r
             v.w = pack_bf16(b.z, b.w);
 #pragma unroll
             for (int j = 0; j < kMaxTopK; j++)
-                if (j < k) *reinterpret_cast<uint4 *>(xp + (size_t)rows[j] * d + c) = v;
+                if (j < k) *reinterpret_cast<uint4 *>(dst[j] + c) = v;
+        }
+    }
+    }
+    if (sig.flags != nullptr) {
+        // Expert parallel: make this block's rows visible system-wide, take a
+        // ticket, and let the last block raise "rows have landed" on every rank.
+        __threadfence_system();
+        __syncthreads();
+        __shared__ int s_last;
+        if (threadIdx.x == 0) s_last = (atomicAdd(ticket, 1) == (int)gridDim.x - 1);
+        __syncthreads();
+        if (s_last && (int)threadIdx.x < sig.world) {
+            __threadfence_system();
+            uint32_t *f = sig.flags[threadIdx.x] + sig.rank;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(sig.seq) : "memory");
         }
     }
 }
 
-// perm[offsets[e] + (pos[f] - poffsets[e])] = f : the unpadded permutation.
+// perm[offsets[e] + (pos[f] - dst_base[e])] = f : the unpadded permutation of this rank's picks.
 __global__ void perm_readout_kernel(const int32_t *__restrict__ topk_idx, const int32_t *__restrict__ pos,
-                                    const int32_t *__restrict__ offsets, const int32_t *__restrict__ poffsets,
+                                    const int32_t *__restrict__ offsets, const int32_t *__restrict__ poffsets /* dst_base */,
                                     int32_t *__restrict__ perm, int n) {
     int f = blockIdx.x * blockDim.x + threadIdx.x;
     if (f >= n) return;
@@ -152,23 +177,25 @@ cudaError_t launch_scan(omoe_handle *h, int T, cudaStream_t s, int *n) {
     return cudaGetLastError();
 }
 
-cudaError_t launch_permute(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n) {
-    const int d = h->cfg.d_model, E = h->cfg.n_experts, k = h->cfg.top_k;
+cudaError_t launch_permute(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n,
+                           const EpSignal *sig) {
+    const int d = h->cfg.d_model, E = h->cfg.n_experts, k = h->cfg.top_k, El = h->e_local;
     const int wpb = 8;
     dim3 grid(ceil_div(T, wpb)), block(wpb * 32);
     const bool cbf = h->cfg.compute_dtype == OMOE_BF16;
+    EpSignal sg = sig ? *sig : EpSignal{nullptr, 1, 0, 0};
     if (io_dtype == OMOE_F32 && !cbf)
         permute_kernel<float, float><<<grid, block, 0, s>>>(
-            static_cast<const float *>(x), static_cast<float *>(h->xp), h->topk_idx, h->pos,
-            h->block_counts, h->poffsets, T, d, E, k, h->tokens_per_block);
+            static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->pos, h->block_counts, h->dst_base, T, d,
+            E, El, k, h->tokens_per_block, sg, h->ticket);
     else if (io_dtype == OMOE_F32 && cbf)
         permute_kernel<float, __nv_bfloat16><<<grid, block, 0, s>>>(
-            static_cast<const float *>(x), static_cast<__nv_bfloat16 *>(h->xp), h->topk_idx, h->pos,
-            h->block_counts, h->poffsets, T, d, E, k, h->tokens_per_block);
+            static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->pos, h->block_counts, h->dst_base, T, d,
+            E, El, k, h->tokens_per_block, sg, h->ticket);
     else if (io_dtype == OMOE_BF16 && cbf)
         permute_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, block, 0, s>>>(
-            static_cast<const __nv_bfloat16 *>(x), static_cast<__nv_bfloat16 *>(h->xp), h->topk_idx,
-            h->pos, h->block_counts, h->poffsets, T, d, E, k, h->tokens_per_block);
+            static_cast<const __nv_bfloat16 *>(x), h->d_row_table, h->topk_idx, h->pos, h->block_counts,
+            h->dst_base, T, d, E, El, k, h->tokens_per_block, sg, h->ticket);
     else
         return cudaErrorInvalidValue;  // bf16 rows into an fp32 layer are rejected by the API
     (*n)++;
@@ -178,7 +205,7 @@ cudaError_t launch_permute(omoe_handle *h, const void *x, int io_dtype, int T, c
 cudaError_t launch_perm_readout(omoe_handle *h, int T, cudaStream_t s) {
     int n = T * h->cfg.top_k;
     if (n == 0) return cudaSuccess;
-    perm_readout_kernel<<<ceil_div(n, 256), 256, 0, s>>>(h->topk_idx, h->pos, h->offsets, h->poffsets,
+    perm_readout_kernel<<<ceil_div(n, 256), 256, 0, s>>>(h->topk_idx, h->pos, h->offsets, h->dst_base,
                                                          h->perm_out, n);
     return cudaGetLastError();
 }

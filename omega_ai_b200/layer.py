@@ -226,17 +226,27 @@ class MoELayer(Layer):
         check(self._h, self._lib.omoe_get_stage_ms(self._h, ms))
         return dict(zip(native.STAGE_NAMES, [float(v) for v in ms]))
 
-    def ep_init(self, unique_id: bytes):
-        buf = C.create_string_buffer(unique_id, native.EP_ID_BYTES)
-        check(self._h, self._lib.omoe_ep_init(self._h, buf))
-
-    @staticmethod
-    def ep_unique_id() -> bytes:
-        buf = C.create_string_buffer(native.EP_ID_BYTES)
-        rc = native.lib().omoe_ep_unique_id(buf)
-        if rc != 0:
-            raise OmoeError(rc, "omoe_ep_unique_id failed")
+    def ep_export(self) -> bytes:
+        """This rank's IPC handles (control block, dispatch buffer, expert outputs)."""
+        buf = C.create_string_buffer(native.EP_BLOB_BYTES)
+        check(self._h, self._lib.omoe_ep_export(self._h, buf))
         return buf.raw
+
+    def ep_import(self, blobs):
+        """``blobs``: the exported handles of all ranks, in rank order."""
+        assert len(blobs) == self.world and all(len(b) == native.EP_BLOB_BYTES for b in blobs)
+        check(self._h, self._lib.omoe_ep_import(self._h, b"".join(blobs)))
+
+    def ep_connect(self, group=None):
+        """Exchange the handles over torch.distributed and open the peers' buffers.
+        Ends with a barrier, after which forward may be called (collectively)."""
+        import torch.distributed as dist
+
+        blobs = [None] * self.world
+        dist.all_gather_object(blobs, self.ep_export(), group=group)
+        self.ep_import(blobs)
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
 
     def close(self):
         if self._h:

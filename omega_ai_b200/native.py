@@ -18,7 +18,7 @@ OMOE_F32 = 0
 OMOE_BF16 = 1
 N_STAGES = 8
 STAGE_NAMES = ("router", "scan", "permute", "dispatch", "up_gate", "down", "return", "combine")
-EP_ID_BYTES = 128
+EP_BLOB_BYTES = 192
 
 ERRORS = {
     0: "OMOE_OK", -1: "OMOE_ERR_INVALID", -2: "OMOE_ERR_CUDA", -3: "OMOE_ERR_TOO_LARGE",
@@ -30,7 +30,7 @@ ERRORS = {
 SYMBOLS = (
     "omoe_create", "omoe_destroy", "omoe_last_error", "omoe_set_weights", "omoe_forward",
     "omoe_forward_host", "omoe_get_routing", "omoe_get_logits", "omoe_last_launch_count",
-    "omoe_set_profiling", "omoe_get_stage_ms", "omoe_ep_unique_id", "omoe_ep_init",
+    "omoe_set_profiling", "omoe_get_stage_ms", "omoe_ep_export", "omoe_ep_import",
     "omoe_route_noalloc", "omoe_route_noalloc_error",
 )
 NOALLOC_MAX_TOKENS = 4096
@@ -96,8 +96,8 @@ def lib():
     L.omoe_last_launch_count.argtypes = [vp]
     L.omoe_set_profiling.argtypes = [vp, i32]
     L.omoe_get_stage_ms.argtypes = [vp, vp]
-    L.omoe_ep_unique_id.argtypes = [vp]
-    L.omoe_ep_init.argtypes = [vp, vp]
+    L.omoe_ep_export.argtypes = [vp, vp]
+    L.omoe_ep_import.argtypes = [vp, vp]
     L.omoe_route_noalloc.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]
     L.omoe_route_noalloc_error.argtypes = []
     L.omoe_route_noalloc_error.restype = C.c_char_p

@@ -1,0 +1,74 @@
+"""Worker of the expert-parallel parity test: one process per GPU (torchrun).
+
+Every rank holds E/world experts and its own tokens; the layer's output and
+routing on each rank are compared with the CPU oracle run on that rank's tokens
+with ALL experts.  Exits non-zero on any mismatch.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+from helpers import assert_close_bf16, assert_close_f32, make_layer  # noqa: E402
+from omega_ai_b200 import MoELayer  # noqa: E402
+from oracle import ref  # noqa: E402
+
+
+def run_case(rank, world, tokens, d, dff, E, k, compute, zipf, steps=2):
+    El = E // world
+    t_max = max(max(tokens), 1)
+    _, w_r, w_g, w_u, w_d, bias = make_layer(1, d, dff, E, k, seed=77, zipf=zipf)
+    bf = compute == torch.bfloat16
+    if bf:
+        w_r = ref.bf16_round(w_r)
+        bias = None if bias is None else ref.bf16_round(bias)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda().to(compute).contiguous()
+    layer = MoELayer(d, dff, E, k, bias=bias is not None, t_max=t_max, compute_dtype=compute, world=world, rank=rank)
+    sl = slice(rank * El, (rank + 1) * El)
+    layer.setWeights(dev(w_r), dev(w_g[sl]), dev(w_u[sl]), dev(w_d[sl]), None if bias is None else dev(bias))
+    layer.ep_connect()
+    for step in range(steps):
+        T = tokens[(rank + step) % len(tokens)]
+        rng = np.random.Generator(np.random.Philox(key=1000 + 10 * step + rank))
+        x = rng.standard_normal((T, d), dtype=np.float32)
+        if bf:
+            x = ref.bf16_round(x)
+        xd = dev(x) if T > 0 else torch.empty(0, d, device="cuda", dtype=compute)
+        y = layer.forward_device(xd).float().cpu().numpy()
+        idx, w, counts, offsets, perm = layer.routing(T)
+        if T == 0:
+            assert counts.sum() == 0
+            continue
+        r = ref.moe_forward(x, w_r, w_g, w_u, w_d, k, bias=bias, bf16=bf)
+        np.testing.assert_array_equal(idx, r.topk_idx)
+        np.testing.assert_array_equal(counts, r.counts)
+        np.testing.assert_array_equal(offsets, r.offsets)
+        np.testing.assert_array_equal(perm, r.perm)
+        np.testing.assert_allclose(w, r.topk_w, rtol=1e-5, atol=1e-7)
+        (assert_close_bf16 if bf else assert_close_f32)(y, r.y)
+    torch.cuda.synchronize()
+    dist.barrier()
+    layer.close()
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    # uneven token counts per rank, one rank with no tokens in some steps
+    run_case(rank, world, [300, 171, 0, 64], 256, 384, 8, 2, torch.bfloat16, False, steps=3)
+    run_case(rank, world, [256, 128], 256, 256, 64, 6, torch.bfloat16, True, steps=2)
+    run_case(rank, world, [64, 40], 128, 256, 8, 2, torch.float32, False, steps=2)
+    dist.destroy_process_group()
+    if rank == 0:
+        print("ep parity ok")
+
+
+if __name__ == "__main__":
+    main()
