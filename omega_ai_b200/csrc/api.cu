@@ -102,7 +102,7 @@ int omoe_destroy(omoe_handle *h) {
     if (!h) return OMOE_OK;
     ep_destroy(h);
     void *ptrs[] = {h->w_router, h->router_bias, h->w_gate, h->w_up, h->w_down, h->logits, h->topk_idx,
-                    h->topk_w, h->block_counts, h->counts, h->offsets, h->poffsets, h->tile_expert, h->pos,
+                    h->topk_w, h->block_counts, h->block_base, h->counts, h->offsets, h->poffsets, h->tile_expert, h->pos,
                     h->perm_out, h->dev_err, h->xp, h->hbuf, h->yp, h->x_stage, h->y_stage, h->d_row_table,
                     h->d_out_table, h->ticket, h->dst_base != h->poffsets ? h->dst_base : nullptr};
     for (void *p : ptrs)
@@ -197,6 +197,7 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
     ALLOC(topk_idx, tm * k);
     ALLOC(topk_w, tm * k);
     ALLOC(block_counts, (int64_t)h->n_blocks_max * E);
+    ALLOC(block_base, (int64_t)h->n_blocks_max * E);
     ALLOC(counts, E);
     ALLOC(offsets, E + 1);
     ALLOC(poffsets, E + 1);

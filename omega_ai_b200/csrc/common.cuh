@@ -58,7 +58,8 @@ struct omoe_handle {
     float *logits;        // [t_max, E]
     int32_t *topk_idx;    // [t_max, k]
     float *topk_w;        // [t_max, k]
-    int32_t *block_counts;  // [n_blocks_max, E] counts, overwritten by per-block bases
+    int32_t *block_counts;  // [E][n_blocks] per-router-block histograms (expert-major)
+    int32_t *block_base;    // [E][n_blocks] exclusive prefix of block_counts over blocks
     int32_t *counts;      // [E]
     int32_t *offsets;     // [E+1] exclusive scan of counts (unpadded)
     int32_t *poffsets;    // [E+1] exclusive scan of counts rounded up to kRowAlign

@@ -15,29 +15,33 @@ namespace omoe {
 
 namespace {
 
-// One block.  Warp w walks experts w, w+32, ...: turns block_counts[b][e] into
-// the exclusive prefix over blocks b and leaves the total in counts[e].  Then
-// offsets (exact) and poffsets (each expert rounded up to kRowAlign) and the
-// expert of every 128-row tile.
+// One block.  Histograms are stored expert-major, block_counts[e][b], so a warp
+// reads one expert's row with coalesced loads.  Warp w walks experts w, w+32,
+// ...: block_base[e][b] becomes the exclusive prefix over blocks b and the
+// total goes to counts[e].  Then offsets (exact), poffsets (each expert rounded
+// up to kRowAlign) and the expert of every 128-row tile.
 __global__ void __launch_bounds__(1024)
-scan_kernel(int32_t *__restrict__ block_counts, int n_blocks, int E,
+scan_kernel(const int32_t *__restrict__ block_counts, int32_t *__restrict__ block_base, int n_blocks, int E,
             int32_t *__restrict__ counts, int32_t *__restrict__ offsets,
             int32_t *__restrict__ poffsets, int32_t *__restrict__ tile_expert, int max_tiles) {
     __shared__ int32_t s_cnt[kMaxExperts];
     __shared__ int32_t s_poff[kMaxExperts + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     for (int e = warp; e < E; e += nwarps) {
+        const int32_t *row = block_counts + (size_t)e * n_blocks;
+        int32_t *out = block_base + (size_t)e * n_blocks;
         int run = 0;
+#pragma unroll 4
         for (int b0 = 0; b0 < n_blocks; b0 += 32) {
             int b = b0 + lane;
-            int c = (b < n_blocks) ? block_counts[(size_t)b * E + e] : 0;
+            int c = (b < n_blocks) ? row[b] : 0;
             int inc = c;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 int v = __shfl_up_sync(0xffffffffu, inc, o);
                 if (lane >= o) inc += v;
             }
-            if (b < n_blocks) block_counts[(size_t)b * E + e] = run + inc - c;
+            if (b < n_blocks) out[b] = run + inc - c;
             run += __shfl_sync(0xffffffffu, inc, 31);
         }
         if (lane == 0) s_cnt[e] = run;
@@ -93,7 +97,7 @@ template <typename XT, typename OT>
 __global__ void __launch_bounds__(256)
 permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, const int32_t *__restrict__ topk_idx,
                int32_t *__restrict__ pos, const int32_t *__restrict__ block_base,
-               const int32_t *__restrict__ dst_base, int T, int d, int E, int e_local, int k, int tokens_per_block,
+               const int32_t *__restrict__ dst_base, int T, int d, int n_blocks, int e_local, int k, int tokens_per_block,
                EpSignal sig, int32_t *ticket) {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -102,7 +106,7 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
         int f = t * k + lane;
         int e = topk_idx[f];
         int b = t / tokens_per_block;
-        my = dst_base[e] + block_base[(size_t)b * E + e] + pos[f];
+        my = dst_base[e] + block_base[(size_t)e * n_blocks + b] + pos[f];
         owner = e / e_local;
         pos[f] = my;
     }
@@ -171,7 +175,7 @@ __global__ void perm_readout_kernel(const int32_t *__restrict__ topk_idx, const 
 cudaError_t launch_scan(omoe_handle *h, int T, cudaStream_t s, int *n) {
     int n_blocks = ceil_div(T, h->tokens_per_block);
     int max_tiles = (int)(h->rows_cap / kRowAlign);
-    scan_kernel<<<1, 1024, 0, s>>>(h->block_counts, n_blocks, h->cfg.n_experts, h->counts, h->offsets,
+    scan_kernel<<<1, 1024, 0, s>>>(h->block_counts, h->block_base, n_blocks, h->cfg.n_experts, h->counts, h->offsets,
                                    h->poffsets, h->tile_expert, max_tiles);
     (*n)++;
     return cudaGetLastError();
@@ -179,23 +183,24 @@ cudaError_t launch_scan(omoe_handle *h, int T, cudaStream_t s, int *n) {
 
 cudaError_t launch_permute(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n,
                            const EpSignal *sig) {
-    const int d = h->cfg.d_model, E = h->cfg.n_experts, k = h->cfg.top_k, El = h->e_local;
+    const int d = h->cfg.d_model, k = h->cfg.top_k, El = h->e_local;
+    const int nb = ceil_div(T, h->tokens_per_block);
     const int wpb = 8;
     dim3 grid(ceil_div(T, wpb)), block(wpb * 32);
     const bool cbf = h->cfg.compute_dtype == OMOE_BF16;
     EpSignal sg = sig ? *sig : EpSignal{nullptr, 1, 0, 0};
     if (io_dtype == OMOE_F32 && !cbf)
         permute_kernel<float, float><<<grid, block, 0, s>>>(
-            static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->pos, h->block_counts, h->dst_base, T, d,
-            E, El, k, h->tokens_per_block, sg, h->ticket);
+            static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->pos, h->block_base, h->dst_base, T, d,
+            nb, El, k, h->tokens_per_block, sg, h->ticket);
     else if (io_dtype == OMOE_F32 && cbf)
         permute_kernel<float, __nv_bfloat16><<<grid, block, 0, s>>>(
-            static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->pos, h->block_counts, h->dst_base, T, d,
-            E, El, k, h->tokens_per_block, sg, h->ticket);
+            static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->pos, h->block_base, h->dst_base, T, d,
+            nb, El, k, h->tokens_per_block, sg, h->ticket);
     else if (io_dtype == OMOE_BF16 && cbf)
         permute_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, block, 0, s>>>(
-            static_cast<const __nv_bfloat16 *>(x), h->d_row_table, h->topk_idx, h->pos, h->block_counts,
-            h->dst_base, T, d, E, El, k, h->tokens_per_block, sg, h->ticket);
+            static_cast<const __nv_bfloat16 *>(x), h->d_row_table, h->topk_idx, h->pos, h->block_base,
+            h->dst_base, T, d, nb, El, k, h->tokens_per_block, sg, h->ticket);
     else
         return cudaErrorInvalidValue;  // bf16 rows into an fp32 layer are rejected by the API
     (*n)++;

@@ -43,7 +43,7 @@ __device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&v)[8]) {
 // EMAX: experts held in registers per token (>= E); TPW: tokens per warp;
 // DCG: 256-element sub-chunks of W_r staged in shared memory per chunk.
 template <int EMAX, int TPW, int DCG, typename XT>
-__global__ void __launch_bounds__(kRouterWarps * 32)
+__global__ void __launch_bounds__(kRouterWarps * 32, (EMAX <= 32) ? 2 : 1)
 router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const float *__restrict__ bias,
               int T, int d, int E, int k, int renorm,
               float *__restrict__ logits, int32_t *__restrict__ topk_idx, float *__restrict__ topk_w,
@@ -64,6 +64,21 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
 #pragma unroll
         for (int e = 0; e < EMAX; e++) acc[i][e] = 0.0f;
 
+    // this lane's 8 elements of one 256-element step, for the warp's TPW tokens
+    auto load_x = [&](int i0, float (&dst)[TPW][8]) {
+#pragma unroll
+        for (int i = 0; i < TPW; i++) {
+            if (i0 < d && tw + i < T) {
+                load8(x + (size_t)(tw + i) * d + i0, dst[i]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++) dst[i][j] = 0.f;
+            }
+        }
+    };
+
+    float xc[TPW][8], xn[TPW][8];
+    load_x(lane * 8, xc);
     constexpr int DC = DCG * kSub;
     for (int c0 = 0; c0 < d; c0 += DC) {
         __syncthreads();
@@ -80,29 +95,26 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
         __syncthreads();
 #pragma unroll 1
         for (int sub = 0; sub < DCG; sub++) {
-            int i0 = c0 + sub * kSub + lane * 8;
-            if (i0 >= d) continue;  // d is a multiple of 8: a lane's group is whole or absent
-            float xv[TPW][8];
+            const int i0 = c0 + sub * kSub + lane * 8;
+            if (c0 + sub * kSub >= d) break;
+            load_x(i0 + kSub, xn);  // next step's rows are in flight while this step is folded in
+            if (i0 < d) {           // d is a multiple of 8: a lane's group is whole or absent
 #pragma unroll
-            for (int i = 0; i < TPW; i++) {
-                if (tw + i < T) {
-                    load8(x + (size_t)(tw + i) * d + i0, xv[i]);
-                } else {
+                for (int e = 0; e < EMAX; e++) {
+                    const float *wp = ws + (e * DCG + sub) * kSub + lane * 4;
+                    float4 wa = *reinterpret_cast<const float4 *>(wp);
+                    float4 wb = *reinterpret_cast<const float4 *>(wp + 128);
+                    float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
-                    for (int j = 0; j < 8; j++) xv[i][j] = 0.f;
+                    for (int i = 0; i < TPW; i++)
+#pragma unroll
+                        for (int j = 0; j < 8; j++) acc[i][e] = fmaf(xc[i][j], wv[j], acc[i][e]);
                 }
             }
 #pragma unroll
-            for (int e = 0; e < EMAX; e++) {
-                const float *wp = ws + (e * DCG + sub) * kSub + lane * 4;
-                float4 wa = *reinterpret_cast<const float4 *>(wp);
-                float4 wb = *reinterpret_cast<const float4 *>(wp + 128);
-                float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+            for (int i = 0; i < TPW; i++)
 #pragma unroll
-                for (int i = 0; i < TPW; i++)
-#pragma unroll
-                    for (int j = 0; j < 8; j++) acc[i][e] = fmaf(xv[i][j], wv[j], acc[i][e]);
-            }
+                for (int j = 0; j < 8; j++) xc[i][j] = xn[i][j];
         }
     }
 
@@ -175,7 +187,7 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
             if (v == e) local_rank[(size_t)t0 * k + f] = base + __popc(m & ((1u << lane) - 1u));
             base += __popc(m);
         }
-        if (lane == 0) block_counts[(size_t)blockIdx.x * E + e] = base;
+        if (lane == 0) block_counts[(size_t)e * gridDim.x + blockIdx.x] = base;  // expert-major
     }
 }
 
@@ -187,6 +199,7 @@ cudaError_t launch_one(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
     auto kern = router_kernel<EMAX, TPW, DCG, XT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
+    h->tokens_per_block = TB;  // the scan and dispatch kernels walk the histogram with this granularity
     int blocks = ceil_div(T, TB);
     kern<<<blocks, kRouterWarps * 32, smem, s>>>(x, h->w_router, h->router_bias, T, h->cfg.d_model,
                                                   h->cfg.n_experts, k, h->cfg.renormalize, h->logits,
@@ -194,26 +207,32 @@ cudaError_t launch_one(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
     return cudaGetLastError();
 }
 
+// More tokens per warp reuse every router weight read from shared memory more
+// often; fewer give more blocks.  Take the largest that still fills the GPU twice.
+template <int EMAX, int DCG, int TPW_MAX, typename XT>
+cudaError_t launch_tpw(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
+    const int want_blocks = 2 * (h->sm_count > 0 ? h->sm_count : 148);
+    if constexpr (TPW_MAX >= 4)
+        if (ceil_div(T, kRouterWarps * 4) >= want_blocks) return launch_one<EMAX, 4, DCG, XT>(h, x, T, s);
+    if constexpr (TPW_MAX >= 2)
+        if (ceil_div(T, kRouterWarps * 2) >= want_blocks) return launch_one<EMAX, 2, DCG, XT>(h, x, T, s);
+    return launch_one<EMAX, 1, DCG, XT>(h, x, T, s);
+}
+
 template <typename XT>
 cudaError_t launch_typed(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
     const int E = h->cfg.n_experts;
-    if (E <= 8) return launch_one<8, 8, 8, XT>(h, x, T, s);
-    if (E <= 16) return launch_one<16, 4, 4, XT>(h, x, T, s);
-    if (E <= 32) return launch_one<32, 4, 2, XT>(h, x, T, s);
-    if (E <= 64) return launch_one<64, 2, 1, XT>(h, x, T, s);
-    return launch_one<128, 1, 1, XT>(h, x, T, s);
+    if (E <= 8) return launch_tpw<8, 8, 4, XT>(h, x, T, s);
+    if (E <= 16) return launch_tpw<16, 4, 2, XT>(h, x, T, s);
+    if (E <= 32) return launch_tpw<32, 2, 2, XT>(h, x, T, s);
+    if (E <= 64) return launch_tpw<64, 1, 2, XT>(h, x, T, s);
+    return launch_tpw<128, 1, 1, XT>(h, x, T, s);
 }
 
 }  // namespace
 
-// Tokens one router block covers for E experts (also the granularity of the
-// per-block histogram the scan kernel walks).
-int router_tokens_per_block(int E) {
-    if (E <= 8) return kRouterWarps * 8;
-    if (E <= 32) return kRouterWarps * 4;
-    if (E <= 64) return kRouterWarps * 2;
-    return kRouterWarps;
-}
+// Smallest number of tokens one router block may cover (sizes the per-block histogram array).
+int router_tokens_per_block(int) { return kRouterWarps; }
 
 cudaError_t launch_router(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n) {
     cudaError_t e;
@@ -267,7 +286,7 @@ __global__ void noalloc_counts_kernel(const int32_t *__restrict__ block_counts, 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     for (int e = warp; e < E; e += nwarps) {
         int sum = 0;
-        for (int b = lane; b < n_blocks; b += 32) sum += block_counts[(size_t)b * E + e];
+        for (int b = lane; b < n_blocks; b += 32) sum += block_counts[(size_t)e * n_blocks + b];
 #pragma unroll
         for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         if (lane == 0) counts[e] = sum;
@@ -332,12 +351,12 @@ int omoe_route_noalloc(const void *x_dev, const float *w_router_dev, const float
     hd.pos = reinterpret_cast<int32_t *>(scratch + kNaLogitsBytes + kNaBlocksBytes);
     hd.topk_idx = topk_idx_dev;
     hd.topk_w = topk_w_dev;
-    const int n_blocks = T > 0 ? ceil_div(T, router_tokens_per_block(n_experts)) : 0;
     if (T > 0) {
         int n = 0;
         cudaError_t e = launch_router(&hd, x_dev, io_dtype, T, s, &n);
         if (e != cudaSuccess) return na_fail(OMOE_ERR_CUDA, "router launch failed: ", cudaGetErrorString(e));
     }
+    const int n_blocks = T > 0 ? ceil_div(T, hd.tokens_per_block) : 0;
     // Nothing in the array has to start at zero: every router block writes all
     // n_experts entries of its histogram row, and only rows [0, n_blocks) are read.
     noalloc_counts_kernel<<<1, 256, 0, s>>>(hd.block_counts, n_blocks, n_experts, counts_dev);
