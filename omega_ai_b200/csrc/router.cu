@@ -10,9 +10,15 @@
 // Bit-exact routing needs a fixed summation order for the logits.  The order
 // is: lane l of a warp owns the elements i with (i/8)%32 == l and folds them in
 // ascending i with one fmaf chain; the 32 partial sums are then combined by an
-// xor butterfly over distances 16,8,4,2,1; the bias is added last.  One warp
-// computes several tokens at once so every router weight read from shared
-// memory is used for TPW tokens.
+// xor butterfly over distances 16,8,4,2,1; the bias is added last.
+//
+// Data movement: a block covers TB tokens and walks d_model in steps of 256
+// columns.  Each step's token rows [TB x 256] and router weights [E x 256] are
+// brought into a ring of shared-memory stages with 16-byte cp.async copies, so
+// several steps of HBM traffic are in flight while one is being folded in.  A
+// warp holds TPW tokens x EPW experts of accumulators; with many experts ES
+// warps share one token group and split the experts, so every weight read from
+// shared memory feeds TPW tokens.
 #include <string.h>
 
 #include "common.cuh"
@@ -21,17 +27,26 @@ namespace omoe {
 
 namespace {
 
-constexpr int kSub = 256;  // elements one warp covers per step (32 lanes x 8)
+constexpr int kSub = 256;  // columns per step (32 lanes x 8)
 
-__device__ __forceinline__ void load8(const float *p, float (&v)[8]) {
-    float4 a = __ldg(reinterpret_cast<const float4 *>(p));
-    float4 b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void lds8(const float *p, float (&v)[8]) {
+    float4 a = *reinterpret_cast<const float4 *>(p);
+    float4 b = *reinterpret_cast<const float4 *>(p + 4);
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
     v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
-__device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&v)[8]) {
-    uint4 r = __ldg(reinterpret_cast<const uint4 *>(p));
+__device__ __forceinline__ void lds8(const __nv_bfloat16 *p, float (&v)[8]) {
+    uint4 r = *reinterpret_cast<const uint4 *>(p);
     uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -40,137 +55,191 @@ __device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&v)[8]) {
     }
 }
 
-// EMAX: experts held in registers per token (>= E); TPW: tokens per warp;
-// DCG: 256-element sub-chunks of W_r staged in shared memory per chunk.
-template <int EMAX, int TPW, int DCG, typename XT>
-__global__ void __launch_bounds__(kRouterWarps * 32, (EMAX <= 32) ? 2 : 1)
+template <int EMAX, int ES, int TPW, typename XT>
+struct RouterCfg {
+    static constexpr int EPW = EMAX / ES;                 // experts per warp
+    static constexpr int NG = kRouterWarps / ES;          // token groups per block
+    static constexpr int TB = NG * TPW;                   // tokens per block
+    // 256-column steps per stage: a stage reads NSUB*256 contiguous columns of every token row
+    static constexpr int NSUB = 1;
+    static constexpr int CS = NSUB * kSub;                // columns per stage
+    static constexpr int XBYTES = TB * CS * (int)sizeof(XT);
+    static constexpr int WBYTES = EMAX * CS * 4;
+    static constexpr int STAGE = XBYTES + WBYTES;
+    static constexpr int BUDGET = (EMAX <= 16) ? 100 * 1024 : 200 * 1024;  // two blocks per SM for few experts
+    static constexpr int S0 = BUDGET / STAGE;
+    static constexpr int S = S0 >= 4 ? 4 : (S0 < 1 ? 1 : S0);             // ring depth
+    static constexpr int MINB = (S * STAGE <= 100 * 1024 && EPW * TPW <= 64) ? 2 : 1;
+};
+
+// EMAX: experts padded to a power of two (>= E); ES: warps sharing a token
+// group; TPW: tokens per warp.
+template <int EMAX, int ES, int TPW, typename XT>
+__global__ void __launch_bounds__(kRouterWarps * 32, RouterCfg<EMAX, ES, TPW, XT>::MINB)
 router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const float *__restrict__ bias,
               int T, int d, int E, int k, int renorm,
               float *__restrict__ logits, int32_t *__restrict__ topk_idx, float *__restrict__ topk_w,
               int32_t *__restrict__ block_counts, int32_t *__restrict__ local_rank) {
+    using C = RouterCfg<EMAX, ES, TPW, XT>;
+    constexpr int EPW = C::EPW, TB = C::TB, S = C::S, NSUB = C::NSUB, CS = C::CS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    float *ws = reinterpret_cast<float *>(smem_raw);                    // [EMAX][DCG][256] (lane-split layout)
-    float *sl = ws + EMAX * DCG * kSub;                                  // [warps][TPW][EMAX] logits
-    int32_t *sidx = reinterpret_cast<int32_t *>(sl + kRouterWarps * TPW * EMAX);  // [warps*TPW][k]
+    // stage layout: x rows [TB][CS] XT, then weights [NSUB][2 halves][EMAX][32 lanes][4] fp32
+    float *sl = reinterpret_cast<float *>(smem_raw + S * C::STAGE);  // [TB][EMAX] logits, later exp values
+    int32_t *sidx = reinterpret_cast<int32_t *>(sl + TB * EMAX);      // [TB][k]
+    const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw));
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    constexpr int TB = kRouterWarps * TPW;
+    const int grp = warp / ES, es = warp % ES;
     const int t0 = blockIdx.x * TB;
-    const int tw = t0 + warp * TPW;  // first token of this warp
+    const int nsub = (d + CS - 1) / CS;  // stages to walk
 
-    float acc[TPW][EMAX];
-#pragma unroll
-    for (int i = 0; i < TPW; i++)
-#pragma unroll
-        for (int e = 0; e < EMAX; e++) acc[i][e] = 0.0f;
-
-    // this lane's 8 elements of one 256-element step, for the warp's TPW tokens
-    auto load_x = [&](int i0, float (&dst)[TPW][8]) {
-#pragma unroll
-        for (int i = 0; i < TPW; i++) {
-            if (i0 < d && tw + i < T) {
-                load8(x + (size_t)(tw + i) * d + i0, dst[i]);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 8; j++) dst[i][j] = 0.f;
-            }
+    auto issue_stage = [&](int su) {
+        const uint32_t st = smem_base + (su % S) * C::STAGE;
+        const int c0 = su * CS;
+        constexpr int PPR = CS * (int)sizeof(XT) / 16;  // 16-byte pieces per token row
+        for (int p = tid; p < TB * PPR; p += kRouterWarps * 32) {
+            const int row = p / PPR, piece = p % PPR;
+            const int col = c0 + piece * (16 / (int)sizeof(XT));
+            const bool ok = (t0 + row < T) && (col < d);  // d is a multiple of 8: a piece is whole or absent
+            const XT *src = ok ? x + (size_t)(t0 + row) * d + col : x;
+            cp_async16(st + p * 16, src, ok ? 16 : 0);
+        }
+        const uint32_t sw = st + C::XBYTES;
+        for (int p = tid; p < EMAX * 64 * NSUB; p += kRouterWarps * 32) {
+            const int e = p / (64 * NSUB), r = p % (64 * NSUB);
+            const int sub = r >> 6, q = r & 63;  // q: float4 index inside the 256-column step
+            const int col = c0 + sub * kSub + 4 * q;
+            const bool ok = (e < E) && (col < d);
+            const float *src = ok ? w_r + (size_t)e * d + col : w_r;
+            const int ln = q >> 1, half = q & 1;  // lane owns floats 8*ln .. 8*ln+7: two float4 halves
+            cp_async16(sw + (((sub * 2 + half) * EMAX + e) * 32 + ln) * 16, src, ok ? 16 : 0);
         }
     };
 
-    float xc[TPW][8], xn[TPW][8];
-    load_x(lane * 8, xc);
-    constexpr int DC = DCG * kSub;
-    for (int c0 = 0; c0 < d; c0 += DC) {
-        __syncthreads();
-        // stage W_r[:, c0:c0+DC) — float4 units, zero beyond d or E
-        for (int u = tid; u < EMAX * (DC / 4); u += blockDim.x) {
-            int e = u / (DC / 4), q = u % (DC / 4);
-            int i = c0 + 4 * q;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (e < E && i < d) v = __ldg(reinterpret_cast<const float4 *>(w_r + (size_t)e * d + i));
-            int sub = (4 * q) / kSub, within = (4 * q) % kSub;
-            int ln = within >> 3, half = (within & 7) >> 2;
-            *reinterpret_cast<float4 *>(ws + (e * DCG + sub) * kSub + half * 128 + ln * 4) = v;
-        }
-        __syncthreads();
+    float acc[TPW][EPW];
+#pragma unroll
+    for (int i = 0; i < TPW; i++)
+#pragma unroll
+        for (int e = 0; e < EPW; e++) acc[i][e] = 0.0f;
+
+#pragma unroll
+    for (int su = 0; su < S - 1; su++) {
+        if (su < nsub) issue_stage(su);
+        cp_async_commit();
+    }
 #pragma unroll 1
-        for (int sub = 0; sub < DCG; sub++) {
-            const int i0 = c0 + sub * kSub + lane * 8;
-            if (c0 + sub * kSub >= d) break;
-            load_x(i0 + kSub, xn);  // next step's rows are in flight while this step is folded in
-            if (i0 < d) {           // d is a multiple of 8: a lane's group is whole or absent
-#pragma unroll
-                for (int e = 0; e < EMAX; e++) {
-                    const float *wp = ws + (e * DCG + sub) * kSub + lane * 4;
-                    float4 wa = *reinterpret_cast<const float4 *>(wp);
-                    float4 wb = *reinterpret_cast<const float4 *>(wp + 128);
-                    float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
-#pragma unroll
-                    for (int i = 0; i < TPW; i++)
-#pragma unroll
-                        for (int j = 0; j < 8; j++) acc[i][e] = fmaf(xc[i][j], wv[j], acc[i][e]);
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < TPW; i++)
-#pragma unroll
-                for (int j = 0; j < 8; j++) xc[i][j] = xn[i][j];
+    for (int su = 0; su < nsub; su++) {
+        if constexpr (S == 1) {
+            issue_stage(su);
+            cp_async_commit();
+            cp_async_wait<0>();
+        } else {
+            cp_async_wait<S - 2>();  // this step's stage has landed (for this thread's copies)
         }
+        __syncthreads();             // ... and for everyone's; all warps are done with the previous step
+        if constexpr (S > 1) {
+            if (su + S - 1 < nsub) issue_stage(su + S - 1);  // refill the stage consumed one step ago
+            cp_async_commit();
+        }
+        const unsigned char *st = smem_raw + (su % S) * C::STAGE;
+        const XT *xs = reinterpret_cast<const XT *>(st);
+        const float *wst = reinterpret_cast<const float *>(st + C::XBYTES);
+#pragma unroll 1
+        for (int sub = 0; sub < NSUB; sub++) {
+            if (su * CS + sub * kSub + lane * 8 >= d) break;  // ascending: later steps are absent too
+            const float *ws = wst + sub * 2 * EMAX * 128;
+            float xv[TPW][8];
+#pragma unroll
+            for (int i = 0; i < TPW; i++) lds8(xs + (grp * TPW + i) * CS + sub * kSub + lane * 8, xv[i]);
+#pragma unroll
+            for (int e = 0; e < EPW; e++) {
+                const int eg = es * EPW + e;
+                float4 wa = *reinterpret_cast<const float4 *>(ws + (eg * 32 + lane) * 4);
+                float4 wb = *reinterpret_cast<const float4 *>(ws + ((EMAX + eg) * 32 + lane) * 4);
+                float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                for (int i = 0; i < TPW; i++)
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc[i][e] = fmaf(xv[i][j], wv[j], acc[i][e]);
+            }
+        }
+        if constexpr (S == 1) __syncthreads();
     }
 
     // xor butterfly, then lane (e % 32) publishes logit e
 #pragma unroll
     for (int i = 0; i < TPW; i++)
 #pragma unroll
-        for (int e = 0; e < EMAX; e++) {
+        for (int e = 0; e < EPW; e++) {
             float a = acc[i][e];
 #pragma unroll
             for (int m = 16; m >= 1; m >>= 1) a = a + __shfl_xor_sync(0xffffffffu, a, m);
-            if (lane == (e & 31) && e < E) {
+            const int eg = es * EPW + e, tt = grp * TPW + i;
+            if (lane == (e & 31) && eg < E) {
                 float v = a;
-                if (bias != nullptr) v = v + __ldg(bias + e);
-                sl[(warp * TPW + i) * EMAX + e] = v;
-                if (tw + i < T) logits[(size_t)(tw + i) * E + e] = v;
+                if (bias != nullptr) v = v + __ldg(bias + eg);
+                sl[tt * EMAX + eg] = v;
+                if (t0 + tt < T) logits[(size_t)(t0 + tt) * E + eg] = v;
             }
         }
-    __syncwarp();
+    __syncthreads();
 
-    // one lane per token: softmax statistics, top-k on the logits, gate weights
-    if (lane < TPW) {
-        const int t = tw + lane;
-        const float *lv = sl + (warp * TPW + lane) * EMAX;
-        int32_t *my_idx = sidx + (warp * TPW + lane) * k;
-        if (t < T) {
-            float mx = -3.402823466e+38F;
-            for (int e = 0; e < E; e++)
-                if (mx <= lv[e]) mx = lv[e];
-            float sum = 0.f;
-            for (int e = 0; e < E; e++) sum += expf(lv[e] - mx);
-            uint32_t used[kMaxExperts / 32];
+    // One warp per token: softmax statistics, top-k on the logits, gate weights.
+    constexpr int PL = (EMAX + 31) / 32;  // logits per lane
+    for (int tt = warp; tt < TB; tt += kRouterWarps) {
+        const int t = t0 + tt;
+        float *lv = sl + tt * EMAX;
+        if (t >= T) {
+            if (lane < k) sidx[tt * k + lane] = -1;
+            continue;
+        }
+        float v[PL];
+        float mx = -3.402823466e+38F;
 #pragma unroll
-            for (int i = 0; i < kMaxExperts / 32; i++) used[i] = 0u;
-            float wk[kMaxTopK];
-            float wsum = 0.f;
+        for (int m = 0; m < PL; m++) {
+            const int e = lane + 32 * m;
+            v[m] = (e < E) ? lv[e] : -INFINITY;
+            mx = fmaxf(mx, v[m]);
+        }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        __syncwarp();
+#pragma unroll
+        for (int m = 0; m < PL; m++) {
+            const int e = lane + 32 * m;
+            if (e < E) lv[e] = expf(v[m] - mx);  // the row now holds the exponentials
+        }
+        __syncwarp();
+        float sum = 0.f;
+        for (int e = 0; e < E; e++) sum += lv[e];  // index order, every lane redundantly (broadcast reads)
+        float my_w = 0.f, wsum = 0.f;
+        int my_e = 0;
 #pragma unroll 1
-            for (int j = 0; j < k; j++) {
-                int best = -1;
-                float bv = 0.f;
-                for (int e = 0; e < E; e++) {
-                    if ((used[e >> 5] >> (e & 31)) & 1u) continue;
-                    float v = lv[e];
-                    if (best < 0 || v > bv) { best = e; bv = v; }
-                }
-                used[best >> 5] |= 1u << (best & 31);
-                float p = expf(bv - mx) / sum;
-                wk[j] = p;
-                wsum += p;
-                my_idx[j] = best;
-                topk_idx[(size_t)t * k + j] = best;
+        for (int j = 0; j < k; j++) {
+            float bv = -INFINITY;
+            int be = 0x7fffffff;
+#pragma unroll
+            for (int m = 0; m < PL; m++) {
+                const int e = lane + 32 * m;
+                if (v[m] > bv || (v[m] == bv && e < be)) { bv = v[m]; be = e; }  // NaN never wins
             }
-#pragma unroll 1
-            for (int j = 0; j < k; j++) topk_w[(size_t)t * k + j] = renorm ? wk[j] / wsum : wk[j];
-        } else {
-            for (int j = 0; j < k; j++) my_idx[j] = -1;
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) {
+                float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                int oe = __shfl_xor_sync(0xffffffffu, be, o);
+                if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+            }
+#pragma unroll
+            for (int m = 0; m < PL; m++)
+                if (lane + 32 * m == be) v[m] = -INFINITY;  // taken
+            const float p = lv[be] / sum;
+            wsum += p;
+            if (lane == j) { my_w = p; my_e = be; }
+        }
+        if (lane < k) {
+            sidx[tt * k + lane] = my_e;
+            topk_idx[(size_t)t * k + lane] = my_e;
+            topk_w[(size_t)t * k + lane] = renorm ? my_w / wsum : my_w;
         }
     }
     __syncthreads();
@@ -191,16 +260,16 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
     }
 }
 
-template <int EMAX, int TPW, int DCG, typename XT>
+template <int EMAX, int ES, int TPW, typename XT>
 cudaError_t launch_one(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
-    constexpr int TB = kRouterWarps * TPW;
+    using C = RouterCfg<EMAX, ES, TPW, XT>;
     const int k = h->cfg.top_k;
-    size_t smem = sizeof(float) * (EMAX * DCG * kSub + kRouterWarps * TPW * EMAX) + sizeof(int32_t) * TB * k;
-    auto kern = router_kernel<EMAX, TPW, DCG, XT>;
+    size_t smem = (size_t)C::S * C::STAGE + sizeof(float) * C::TB * EMAX + sizeof(int32_t) * C::TB * k;
+    auto kern = router_kernel<EMAX, ES, TPW, XT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    h->tokens_per_block = TB;  // the scan and dispatch kernels walk the histogram with this granularity
-    int blocks = ceil_div(T, TB);
+    h->tokens_per_block = C::TB;  // the scan and dispatch kernels walk the histogram with this granularity
+    int blocks = ceil_div(T, C::TB);
     kern<<<blocks, kRouterWarps * 32, smem, s>>>(x, h->w_router, h->router_bias, T, h->cfg.d_model,
                                                   h->cfg.n_experts, k, h->cfg.renormalize, h->logits,
                                                   h->topk_idx, h->topk_w, h->block_counts, h->pos);
@@ -209,32 +278,32 @@ cudaError_t launch_one(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
 
 // More tokens per warp reuse every router weight read from shared memory more
 // often; fewer give more blocks.  Take the largest that still fills the GPU twice.
-template <int EMAX, int DCG, int TPW_MAX, typename XT>
+template <int EMAX, int ES, typename XT>
 cudaError_t launch_tpw(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
     const int want_blocks = 2 * (h->sm_count > 0 ? h->sm_count : 148);
-    if constexpr (TPW_MAX >= 4)
-        if (ceil_div(T, kRouterWarps * 4) >= want_blocks) return launch_one<EMAX, 4, DCG, XT>(h, x, T, s);
-    if constexpr (TPW_MAX >= 2)
-        if (ceil_div(T, kRouterWarps * 2) >= want_blocks) return launch_one<EMAX, 2, DCG, XT>(h, x, T, s);
-    return launch_one<EMAX, 1, DCG, XT>(h, x, T, s);
+    constexpr int NG = kRouterWarps / ES;
+    if (ceil_div(T, NG * 4) >= want_blocks) return launch_one<EMAX, ES, 4, XT>(h, x, T, s);
+    if (ceil_div(T, NG * 2) >= want_blocks) return launch_one<EMAX, ES, 2, XT>(h, x, T, s);
+    return launch_one<EMAX, ES, 1, XT>(h, x, T, s);
 }
 
 template <typename XT>
 cudaError_t launch_typed(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
     const int E = h->cfg.n_experts;
-    if (E <= 8) return launch_tpw<8, 8, 4, XT>(h, x, T, s);
-    if (E <= 16) return launch_tpw<16, 4, 2, XT>(h, x, T, s);
-    if (E <= 32) return launch_tpw<32, 2, 2, XT>(h, x, T, s);
-    if (E <= 64) return launch_tpw<64, 1, 2, XT>(h, x, T, s);
-    return launch_tpw<128, 1, 1, XT>(h, x, T, s);
+    if (E <= 8) return launch_tpw<8, 1, XT>(h, x, T, s);
+    if (E <= 16) return launch_tpw<16, 1, XT>(h, x, T, s);
+    if (E <= 32) return launch_tpw<32, 2, XT>(h, x, T, s);
+    if (E <= 64) return launch_tpw<64, 2, XT>(h, x, T, s);
+    return launch_tpw<128, 4, XT>(h, x, T, s);
 }
 
 }  // namespace
 
-// Smallest number of tokens one router block may cover (sizes the per-block histogram array).
-int router_tokens_per_block(int) { return kRouterWarps; }
+// Smallest number of tokens one router block may cover (sizes the per-block histogram arrays).
+int router_tokens_per_block(int E) { return E <= 16 ? kRouterWarps : (E <= 64 ? kRouterWarps / 2 : kRouterWarps / 4); }
 
 cudaError_t launch_router(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n) {
+    if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0) return cudaErrorMisalignedAddress;  // 16-byte copies
     cudaError_t e;
     if (io_dtype == OMOE_F32)
         e = launch_typed<float>(h, static_cast<const float *>(x), T, s);
@@ -269,11 +338,12 @@ namespace {
 
 constexpr int kNaMaxTokens = OMOE_NOALLOC_MAX_TOKENS;
 constexpr size_t kNaLogitsBytes = sizeof(float) * (size_t)kNaMaxTokens * kMaxExperts;      // 2 MiB
-constexpr size_t kNaBlocksBytes = sizeof(int32_t) * (size_t)(kNaMaxTokens / kRouterWarps) * kMaxExperts;  // 256 KiB
+// a router block covers at least 2 tokens (128 experts), 4 (64) or 8 (16 and fewer)
+constexpr size_t kNaBlocksBytes = sizeof(int32_t) * (size_t)(kNaMaxTokens / 2) * kMaxExperts;  // 1 MiB
 constexpr size_t kNaRankBytes = sizeof(int32_t) * (size_t)kNaMaxTokens * kMaxTopK;         // 256 KiB
 constexpr size_t kNaScratchBytes = kNaLogitsBytes + kNaBlocksBytes + kNaRankBytes;
 
-// Scratch shared by every omoe_route_noalloc call on a device (about 2.5 MiB,
+// Scratch shared by every omoe_route_noalloc call on a device (about 3.3 MiB,
 // held by each GPU that loads the library until the process exits).
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNaScratchBytes];
 
