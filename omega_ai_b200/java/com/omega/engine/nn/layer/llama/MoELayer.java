@@ -1,0 +1,222 @@
+package com.omega.engine.nn.layer.llama;
+
+import com.omega.engine.gpu.CUDAMemoryManager;
+import com.omega.engine.nn.layer.FullyLayer;
+import com.omega.engine.nn.layer.Layer;
+import com.omega.engine.nn.layer.LayerType;
+import com.omega.engine.nn.network.Network;
+import com.omega.engine.tensor.Tensor;
+import jcuda.Pointer;
+
+import java.io.IOException;
+import java.io.RandomAccessFile;
+
+/**
+ * Mixture-of-experts feed-forward layer: router -> top-k -> dispatch -> grouped
+ * SwiGLU experts -> gate-weighted combine, executed by libomoe.so on sm_100a.
+ *
+ * Takes the slot of LlamaMLPLayer in LlamaTransformerBlock (constructed at
+ * LlamaTransformerBlock.java:97, called at :135) and keeps its surface:
+ * forward(Tensor) = setInput; init(); output(), result via getOutput().
+ *
+ * Weights live in FullyLayer objects so the engine's bookkeeping (paramLayers,
+ * updaters, save/load, gradient clipping) keeps working: router [E,d] and per
+ * expert gate=linear1 [dff,d], up=linear3 [dff,d], down=linear2 [d,dff], the
+ * [out,in] layout of FullyLayer.  The native library keeps its own bf16 copies;
+ * call syncWeights() after the weights change.
+ *
+ * Forward only: diff()/back() throw.  Not compiled in the repository that ships
+ * it (no JDK in that build image).
+ */
+public class MoELayer extends Layer {
+
+    private final int embedDim;
+    private final int dff;
+    private final int numExperts;
+    private final int topK;
+    private final boolean bias;
+    private final int tMax;
+    private final int computeDtype;
+
+    private FullyLayer router;
+    private FullyLayer[] gate;   // linear1 of each expert
+    private FullyLayer[] up;     // linear3
+    private FullyLayer[] down;   // linear2
+
+    private long handle;
+    // experts packed contiguously for omoe_set_weights: [E,dff,d], [E,dff,d], [E,d,dff]
+    private Tensor packedGate, packedUp, packedDown;
+
+    public MoELayer(int embedDim, int dff, int numExperts, int topK, boolean bias, Network network) {
+        this(embedDim, dff, numExperts, topK, bias, network, 16384, OmoeNative.BF16);
+    }
+
+    public MoELayer(int embedDim, int dff, int numExperts, int topK, boolean bias, Network network, int tMax,
+                    int computeDtype) {
+        this.network = network;
+        this.embedDim = embedDim;
+        this.dff = dff;
+        this.numExperts = numExperts;
+        this.topK = topK;
+        this.bias = bias;
+        this.tMax = tMax;
+        this.computeDtype = computeDtype;
+        this.oChannel = 1;
+        this.oHeight = 1;
+        this.oWidth = embedDim;
+        this.router = new FullyLayer(embedDim, numExperts, bias, network);
+        this.gate = new FullyLayer[numExperts];
+        this.up = new FullyLayer[numExperts];
+        this.down = new FullyLayer[numExperts];
+        for (int e = 0; e < numExperts; e++) {
+            gate[e] = new FullyLayer(embedDim, dff, false, network);
+            up[e] = new FullyLayer(embedDim, dff, false, network);
+            down[e] = new FullyLayer(dff, embedDim, false, network);
+        }
+        this.handle = OmoeNative.create(tMax, embedDim, dff, numExperts, topK, computeDtype, 1, bias ? 1 : 0, 1, 0, 0);
+        if (handle == 0) {
+            throw new RuntimeException("omoe_create: " + OmoeNative.lastError(0));
+        }
+        this.packedGate = new Tensor(numExperts, 1, dff, embedDim, true, true);
+        this.packedUp = new Tensor(numExperts, 1, dff, embedDim, true, true);
+        this.packedDown = new Tensor(numExperts, 1, embedDim, dff, true, true);
+        syncWeights();
+    }
+
+    private static long addr(Pointer p) {
+        // the accessor the engine itself uses in SerializablePointer.getHexString()
+        return new com.omega.engine.parallel.ddp.distributed.SerializablePointer(p).address();
+    }
+
+    /** Packs the experts' FullyLayer weights and hands them to the native library. */
+    public void syncWeights() {
+        for (int e = 0; e < numExperts; e++) {
+            Tensor_OP().copyGPU(gate[e].weight, packedGate, e * dff * embedDim);
+            Tensor_OP().copyGPU(up[e].weight, packedUp, e * dff * embedDim);
+            Tensor_OP().copyGPU(down[e].weight, packedDown, e * embedDim * dff);
+        }
+        check(OmoeNative.setWeights(handle, addr(router.weight.getGpuData()),
+                bias ? addr(router.bias.getGpuData()) : 0L, addr(packedGate.getGpuData()),
+                addr(packedUp.getGpuData()), addr(packedDown.getGpuData()), OmoeNative.F32));
+    }
+
+    private void check(int rc) {
+        if (rc != 0) {
+            throw new RuntimeException("libomoe: " + OmoeNative.lastError(handle));
+        }
+    }
+
+    @Override
+    public void init() {
+        this.number = this.input.number;
+        if (this.output == null || this.number != this.output.number) {
+            this.output = Tensor.createGPUTensor(this.output, number, oChannel, oHeight, oWidth, true);
+        }
+    }
+
+    @Override
+    public void output() {
+        // one native call; it enqueues on the legacy default stream and does not synchronise
+        check(OmoeNative.forward(handle, addr(input.getGpuData()), addr(output.getGpuData()), number, OmoeNative.F32));
+    }
+
+    @Override
+    public void forward(Tensor input) {
+        this.setInput(input);
+        this.init();
+        this.output();
+    }
+
+    @Override
+    public void forward() {
+        this.setInput();
+        this.init();
+        this.output();
+    }
+
+    @Override
+    public Tensor getOutput() {
+        return output;
+    }
+
+    @Override
+    public LayerType getLayerType() {
+        return LayerType.feed_forward;
+    }
+
+    public void saveModel(RandomAccessFile outputStream) throws IOException {
+        // router first, then per expert gate, up, down — the order LlamaMLPLayer uses for linear1, linear3, linear2
+        router.saveModel(outputStream);
+        for (int e = 0; e < numExperts; e++) {
+            gate[e].saveModel(outputStream);
+            up[e].saveModel(outputStream);
+            down[e].saveModel(outputStream);
+        }
+    }
+
+    public void loadModel(RandomAccessFile inputStream) throws IOException {
+        router.loadModel(inputStream);
+        for (int e = 0; e < numExperts; e++) {
+            gate[e].loadModel(inputStream);
+            up[e].loadModel(inputStream);
+            down[e].loadModel(inputStream);
+        }
+        syncWeights();
+    }
+
+    public void close() {
+        if (handle != 0) {
+            OmoeNative.destroy(handle);
+            handle = 0;
+        }
+    }
+
+    // ---- training surface: this layer is forward-only ----
+    @Override
+    public void initBack() {
+    }
+
+    @Override
+    public void initParam() {
+    }
+
+    @Override
+    public void diff() {
+        throw new UnsupportedOperationException("MoELayer: backward is not implemented");
+    }
+
+    @Override
+    public void back() {
+        diff();
+    }
+
+    @Override
+    public void back(Tensor delta) {
+        diff();
+    }
+
+    @Override
+    public void backTemp() {
+    }
+
+    @Override
+    public void update() {
+    }
+
+    @Override
+    public void accGrad(float scale) {
+    }
+
+    @Override
+    public void showDiff() {
+    }
+
+    @Override
+    public float[][][][] output(float[][][][] input) {
+        return null;
+    }
+
+    @Override
+    public void initCache() {
+    }
+}

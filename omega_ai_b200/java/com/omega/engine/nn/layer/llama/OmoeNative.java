@@ -1,0 +1,49 @@
+package com.omega.engine.nn.layer.llama;
+
+import com.omega.common.lib.LibPaths;
+
+/**
+ * JNI binding of libomoe.so (C ABI in include/omoe.h).  Device buffers cross the
+ * boundary as raw 64-bit addresses; every call returns 0 or a negative
+ * OMOE_ERR_* code.  The shim library (jni/omoe_jni.c) only forwards to the C ABI.
+ *
+ * Not compiled in the repository that ships it: that build image has no JDK.
+ */
+public final class OmoeNative {
+
+    public static final int F32 = 0;
+    public static final int BF16 = 1;
+
+    static {
+        // same loading idiom as com.omega.engine.gpu.JNITest: an absolute path next to the kernels
+        System.load(LibPaths.getLibPath() + "libomoe_jni.so");
+    }
+
+    private OmoeNative() {
+    }
+
+    /** @return handle, or 0 on failure (see lastError(0)) */
+    public static native long create(int tMax, int dModel, int dFf, int nExperts, int topK, int computeDtype,
+                                     int renormalize, int hasRouterBias, int world, int rank, int recvRowsMax);
+
+    public static native int destroy(long handle);
+
+    public static native String lastError(long handle);
+
+    /** All pointers are device addresses; routerBias may be 0. */
+    public static native int setWeights(long handle, long wRouter, long routerBias, long wGate, long wUp,
+                                        long wDown, int srcDtype);
+
+    /** Enqueues on the legacy default stream, like every kernel launch of the engine. */
+    public static native int forward(long handle, long xDev, long yDev, int tokens, int ioDtype);
+
+    /** Host arrays in and out: H2D, forward, D2H, synchronise. */
+    public static native int forwardHost(long handle, float[] x, float[] y, int tokens);
+
+    public static native int getRouting(long handle, int[] topkIdx, float[] topkW, int[] counts, int[] offsets,
+                                        int[] perm);
+
+    public static native int epExport(long handle, byte[] blob192);
+
+    public static native int epImport(long handle, byte[] allBlobs);
+}
