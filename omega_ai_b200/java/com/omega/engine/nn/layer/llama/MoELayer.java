@@ -1,12 +1,14 @@
 package com.omega.engine.nn.layer.llama;
 
-import com.omega.engine.gpu.CUDAMemoryManager;
 import com.omega.engine.nn.layer.FullyLayer;
 import com.omega.engine.nn.layer.Layer;
 import com.omega.engine.nn.layer.LayerType;
 import com.omega.engine.nn.network.Network;
 import com.omega.engine.tensor.Tensor;
 import jcuda.Pointer;
+import jcuda.Sizeof;
+import jcuda.runtime.JCuda;
+import jcuda.runtime.cudaMemcpyKind;
 
 import java.io.IOException;
 import java.io.RandomAccessFile;
@@ -83,17 +85,33 @@ public class MoELayer extends Layer {
         syncWeights();
     }
 
+    /** Exposes the raw device address of a JCuda pointer (getNativePointer is protected), the way the
+     *  engine's own SerializablePointer does (parallel/ddp/distributed/SerializablePointer.java:26-28). */
+    private static final class RawPointer extends Pointer {
+        RawPointer(Pointer p) {
+            super(p);
+        }
+
+        long address() {
+            return getNativePointer();
+        }
+    }
+
     private static long addr(Pointer p) {
-        // the accessor the engine itself uses in SerializablePointer.getHexString()
-        return new com.omega.engine.parallel.ddp.distributed.SerializablePointer(p).address();
+        return new RawPointer(p).address();
+    }
+
+    private static void copyInto(Tensor dst, long floatOffset, Tensor src) {
+        JCuda.cudaMemcpy(dst.getGpuData().withByteOffset(floatOffset * Sizeof.FLOAT), src.getGpuData(),
+                (long) src.dataLength * Sizeof.FLOAT, cudaMemcpyKind.cudaMemcpyDeviceToDevice);
     }
 
     /** Packs the experts' FullyLayer weights and hands them to the native library. */
     public void syncWeights() {
         for (int e = 0; e < numExperts; e++) {
-            Tensor_OP().copyGPU(gate[e].weight, packedGate, e * dff * embedDim);
-            Tensor_OP().copyGPU(up[e].weight, packedUp, e * dff * embedDim);
-            Tensor_OP().copyGPU(down[e].weight, packedDown, e * embedDim * dff);
+            copyInto(packedGate, (long) e * dff * embedDim, gate[e].weight);
+            copyInto(packedUp, (long) e * dff * embedDim, up[e].weight);
+            copyInto(packedDown, (long) e * embedDim * dff, down[e].weight);
         }
         check(OmoeNative.setWeights(handle, addr(router.weight.getGpuData()),
                 bias ? addr(router.bias.getGpuData()) : 0L, addr(packedGate.getGpuData()),
