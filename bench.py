@@ -297,7 +297,9 @@ def run_ours(args, cfg):
         roof = {"bound": "hbm", "kernel": "grouped_gemm_kernel (up/gate + down)",
                 "achieved": wbytes / dur / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
                 "frac": wbytes / dur / 1e9 / peaks["hbm"], "traffic": None, "peak_source": peaks["src"],
-                "active_experts": n_active}
+                "active_experts": n_active, "weight_bytes": wbytes,
+                # the same bytes over the whole step (router, dispatch, combine and launch gaps included)
+                "whole_step_frac": wbytes / (ms_per_step * 1e-3) / 1e9 / peaks["hbm"]}
     elif cfg["dtype"] == "bf16":
         dur = stage_ms["up_gate"] * 1e-3
         ach = alg["up_gate_flops"] / dur / 1e12
@@ -306,7 +308,7 @@ def run_ours(args, cfg):
         roof = {"bound": "tensor", "kernel": "grouped_gemm_kernel<SWIGLU> (up/gate)", "achieved": ach,
                 "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
                 "peak_source": peaks["src"] + (" sustained" if timed_s >= 1.0 else " burst"),
-                "frac_of_burst": ach / peaks["tf_burst"],
+                "frac_of_burst": ach / peaks["tf_burst"], "frac_of_sustained": ach / peaks["tf_sust"],
                 "down_tflops": alg["down_flops"] / (stage_ms["down"] * 1e-3) / 1e12}
     else:
         dur = (stage_ms["up_gate"] + stage_ms["down"]) * 1e-3

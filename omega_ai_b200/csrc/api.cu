@@ -65,6 +65,7 @@ int check_dev_err(omoe_handle *h) {
     CU_TRY(h, cudaMemcpy(&v, h->dev_err, sizeof(v), cudaMemcpyDeviceToHost));
     if (v != 0) {
         cudaMemset(h->dev_err, 0, sizeof(int32_t));
+    cudaMemset(h->ticket, 0, sizeof(int32_t));
         return fail(h, OMOE_ERR_DEVICE, "device error word = %d (%s%s)", v,
                     (v & kDevErrTimeout) ? "a bounded wait ran out " : "",
                     (v & kDevErrBounds) ? "an index check failed" : "");
@@ -226,6 +227,7 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
         }
     }
     cudaMemset(h->dev_err, 0, sizeof(int32_t));
+    cudaMemset(h->ticket, 0, sizeof(int32_t));
     // padding rows of the dispatch buffers are never read back, but start them
     // at zero so no stale NaN pattern ever enters a tensor-core tile
     cudaMemset(h->xp, 0, (size_t)h->rows_cap * d * cs);
@@ -313,14 +315,22 @@ int omoe_forward(omoe_handle *h, const void *x_dev, void *y_dev, int32_t T, int3
     const bool prof = h->profiling;
 #define MARK(i) do { if (prof) cudaEventRecord(h->ev[i], s); } while (0)
     MARK(0);
-    CU_TRY(h, launch_router(h, x_dev, io_dtype, T, s, &n));
-    MARK(1);
-    CU_TRY(h, launch_scan(h, T, s, &n));
-    MARK(2);
-    CU_TRY(h, launch_permute(h, x_dev, io_dtype, T, s, &n, nullptr));
+    if (h->cfg.compute_dtype == OMOE_BF16 && T <= route_small_max_tokens()) {
+        CU_TRY(h, launch_route_small(h, x_dev, io_dtype, T, s, &n));
+        MARK(1);
+        MARK(2);
+    } else {
+        CU_TRY(h, launch_router(h, x_dev, io_dtype, T, s, &n));
+        MARK(1);
+        CU_TRY(h, launch_scan(h, T, s, &n));
+        MARK(2);
+        CU_TRY(h, launch_permute(h, x_dev, io_dtype, T, s, &n, nullptr));
+    }
     MARK(3);
     MARK(4);
-    if (h->cfg.compute_dtype == OMOE_BF16) {
+    if (h->cfg.compute_dtype == OMOE_BF16 && T <= decode_tokens_threshold()) {
+        CU_TRY(h, launch_experts_decode(h, T, s, &n, prof ? h->ev[5] : nullptr));
+    } else if (h->cfg.compute_dtype == OMOE_BF16) {
         CU_TRY(h, launch_experts_bf16(h, s, &n, prof ? h->ev[5] : nullptr));
     } else {
         CU_TRY(h, launch_experts_f32(h, s, &n));

@@ -94,11 +94,60 @@ combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const in
     }
 }
 
+// A few tokens: one thread per 8 output columns, so every load of the step is
+// in flight at once instead of one warp walking a row (same arithmetic order).
+template <typename YT, typename OT>
+__global__ void __launch_bounds__(256)
+combine_small_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const int32_t *__restrict__ pos,
+                     const int32_t *__restrict__ topk_idx, const float *__restrict__ topk_w, int T, int d, int k,
+                     int e_local) {
+    const int vec = d / 8;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= T * vec) return;
+    const int t = idx / vec, c = (idx % vec) * 8;
+    float acc[8];
+    for (int j = 0; j < k; j++) {
+        const int r = __ldg(pos + (size_t)t * k + j);
+        const int q = __ldg(topk_idx + (size_t)t * k + j) / e_local;
+        const float w = __ldg(topk_w + (size_t)t * k + j);
+        const YT *src = static_cast<const YT *>(out_table[q]) + (size_t)r * d + c;
+        float v[8];
+        if constexpr (sizeof(YT) == 2) {
+            unpack8(__ldcs(reinterpret_cast<const uint4 *>(src)), v);
+        } else {
+            float4 a = __ldcs(reinterpret_cast<const float4 *>(src));
+            float4 b = __ldcs(reinterpret_cast<const float4 *>(src) + 1);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+            v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[i] = (j == 0) ? w * v[i] : fmaf(w, v[i], acc[i]);
+    }
+    if constexpr (sizeof(OT) == 2) {
+        uint4 o;
+        o.x = pack2(acc[0], acc[1]);
+        o.y = pack2(acc[2], acc[3]);
+        o.z = pack2(acc[4], acc[5]);
+        o.w = pack2(acc[6], acc[7]);
+        *reinterpret_cast<uint4 *>(y + (size_t)t * d + c) = o;
+    } else {
+        float4 *o = reinterpret_cast<float4 *>(y + (size_t)t * d + c);
+        o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+}
+
 template <typename YT, typename OT>
 cudaError_t launch_k(omoe_handle *h, void *y, int T, cudaStream_t s, const EpWait *wait) {
     const int d = h->cfg.d_model, k = h->cfg.top_k, El = h->e_local;
     dim3 grid(ceil_div(T, 8)), block(256);
     OT *out = static_cast<OT *>(y);
+    if (wait == nullptr && (long long)T * (d / 8) <= 65536) {
+        const int threads = T * (d / 8);
+        combine_small_kernel<YT, OT><<<ceil_div(threads, 256), 256, 0, s>>>(h->d_out_table, out, h->pos, h->topk_idx,
+                                                                           h->topk_w, T, d, k, El);
+        return cudaGetLastError();
+    }
     EpWait wt = wait ? *wait : EpWait{nullptr, 1, 0, 0};
 #define OMOE_COMBINE(KK)                                                                                         \
     combine_kernel<YT, OT, KK><<<grid, block, 0, s>>>(h->d_out_table, out, h->pos, h->topk_idx, h->topk_w, T, d, k, \

@@ -109,6 +109,9 @@ namespace omoe {
 
 cudaError_t launch_router(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n);
 cudaError_t launch_scan(omoe_handle *h, int T, cudaStream_t s, int *n);
+// Router + scan + dispatch in one launch for T <= route_small_max_tokens() (single GPU, bf16 layer).
+cudaError_t launch_route_small(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n);
+int route_small_max_tokens();
 // sig != nullptr: after the last block has written its rows, raise the
 // "rows have landed" flag on every rank (expert-parallel dispatch).
 struct EpSignal;
@@ -121,6 +124,9 @@ struct EpWait;
 cudaError_t launch_combine(omoe_handle *h, void *y, int io_dtype, int T, cudaStream_t s, int *n, const EpWait *wait);
 cudaError_t launch_experts_f32(omoe_handle *h, cudaStream_t s, int *n);
 cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid);
+// Weight-streaming expert products for decode steps (T <= decode_tokens_threshold(), bf16).
+cudaError_t launch_experts_decode(omoe_handle *h, int T, cudaStream_t s, int *n, cudaEvent_t mid);
+int decode_tokens_threshold();
 cudaError_t launch_convert_f32_to_bf16(const float *src, __nv_bfloat16 *dst, int64_t n, cudaStream_t s);
 cudaError_t launch_convert_bf16_to_f32(const __nv_bfloat16 *src, float *dst, int64_t n, cudaStream_t s);
 

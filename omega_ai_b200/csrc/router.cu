@@ -22,6 +22,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "router_common.cuh"
 
 namespace omoe {
 
@@ -188,58 +189,17 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
     constexpr int PL = (EMAX + 31) / 32;  // logits per lane
     for (int tt = warp; tt < TB; tt += kRouterWarps) {
         const int t = t0 + tt;
-        float *lv = sl + tt * EMAX;
         if (t >= T) {
             if (lane < k) sidx[tt * k + lane] = -1;
             continue;
         }
-        float v[PL];
-        float mx = -3.402823466e+38F;
-#pragma unroll
-        for (int m = 0; m < PL; m++) {
-            const int e = lane + 32 * m;
-            v[m] = (e < E) ? lv[e] : -INFINITY;
-            mx = fmaxf(mx, v[m]);
-        }
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        __syncwarp();
-#pragma unroll
-        for (int m = 0; m < PL; m++) {
-            const int e = lane + 32 * m;
-            if (e < E) lv[e] = expf(v[m] - mx);  // the row now holds the exponentials
-        }
-        __syncwarp();
-        float sum = 0.f;
-        for (int e = 0; e < E; e++) sum += lv[e];  // index order, every lane redundantly (broadcast reads)
-        float my_w = 0.f, wsum = 0.f;
-        int my_e = 0;
-#pragma unroll 1
-        for (int j = 0; j < k; j++) {
-            float bv = -INFINITY;
-            int be = 0x7fffffff;
-#pragma unroll
-            for (int m = 0; m < PL; m++) {
-                const int e = lane + 32 * m;
-                if (v[m] > bv || (v[m] == bv && e < be)) { bv = v[m]; be = e; }  // NaN never wins
-            }
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) {
-                float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                int oe = __shfl_xor_sync(0xffffffffu, be, o);
-                if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
-            }
-#pragma unroll
-            for (int m = 0; m < PL; m++)
-                if (lane + 32 * m == be) v[m] = -INFINITY;  // taken
-            const float p = lv[be] / sum;
-            wsum += p;
-            if (lane == j) { my_w = p; my_e = be; }
-        }
+        int my_e;
+        float my_w;
+        warp_softmax_topk<PL>(sl + tt * EMAX, E, k, renorm, lane, my_e, my_w);
         if (lane < k) {
             sidx[tt * k + lane] = my_e;
             topk_idx[(size_t)t * k + lane] = my_e;
-            topk_w[(size_t)t * k + lane] = renorm ? my_w / wsum : my_w;
+            topk_w[(size_t)t * k + lane] = my_w;
         }
     }
     __syncthreads();

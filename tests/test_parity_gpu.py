@@ -143,3 +143,16 @@ def test_errors_are_reported_not_fatal():
         MoELayer(130, 256, 8, 2)  # d_model not a multiple of 8
     with pytest.raises(OmoeError):
         MoELayer(128, 256, 8, 9)  # top_k > experts
+
+
+@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (2, 8, 2), (5, 8, 2), (8, 8, 2), (7, 64, 6)])
+def test_decode_streaming_path_bf16(oracle, T, E, k):
+    """T <= 8 takes the weight-streaming expert kernels; odd sizes exercise the K split and row passes."""
+    x, w_r, w_g, w_u, w_d, _ = make_layer(T, 520, 1096, E, k, seed=13)
+    rb = oracle.bf16_round
+    xb, w_rb = rb(x), rb(w_r)
+    r = oracle.moe_forward(xb, w_rb, w_g, w_u, w_d, k, bf16=True)
+    y, routing, logits, n = run_gpu(xb, w_rb, rb(w_g), rb(w_u), rb(w_d), None, k, torch.bfloat16, torch.bfloat16,
+                                    t_max=64)
+    check_routing(routing, logits, r)
+    assert_close_bf16(y, r.y)
