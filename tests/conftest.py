@@ -10,6 +10,7 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 GPU (run with -m gpu)")
+    config.addinivalue_line("markers", "slow: full-size case (about a minute of CPU oracle time)")
 
 
 @pytest.fixture(scope="session")

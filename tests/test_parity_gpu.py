@@ -156,3 +156,163 @@ def test_decode_streaming_path_bf16(oracle, T, E, k):
                                     t_max=64)
     check_routing(routing, logits, r)
     assert_close_bf16(y, r.y)
+
+
+@pytest.mark.parametrize("T,d,dff,E,k", [
+    (200, 328, 200, 8, 2),     # K and N not multiples of the 64/128/256 tile sizes (tails come from TMA bounds)
+    (77, 64, 64, 4, 1),        # smallest bf16 shapes, top-1
+    (300, 256, 128, 128, 8),   # 128 experts, top-8
+    (150, 192, 256, 24, 3),    # expert count that is not a power of two
+    (513, 128, 384, 12, 12),   # every expert picked (k = E)
+])
+def test_odd_shapes_bf16(oracle, T, d, dff, E, k):
+    x, w_r, w_g, w_u, w_d, _ = make_layer(T, d, dff, E, k, seed=31)
+    rb = oracle.bf16_round
+    xb, w_rb = rb(x), rb(w_r)
+    r = oracle.moe_forward(xb, w_rb, w_g, w_u, w_d, k, bf16=True)
+    y, routing, logits, n = run_gpu(xb, w_rb, rb(w_g), rb(w_u), rb(w_d), None, k, torch.bfloat16, torch.bfloat16)
+    check_routing(routing, logits, r)
+    assert_close_bf16(y, r.y)
+
+
+def test_router_bias_and_raw_gate_weights(oracle):
+    """A router bias and renormalize=0 (gate weights are the softmax values themselves)."""
+    x, w_r, w_g, w_u, w_d, bias = make_layer(260, 256, 256, 16, 4, seed=32, bias_scale=0.5)
+    rb = oracle.bf16_round
+    xb, w_rb, bb = rb(x), rb(w_r), rb(bias)
+    r = oracle.moe_forward(xb, w_rb, w_g, w_u, w_d, 4, bias=bb, bf16=True, renorm=False)
+    y, routing, logits, n = run_gpu(xb, w_rb, rb(w_g), rb(w_u), rb(w_d), bb, 4, torch.bfloat16, torch.bfloat16,
+                                    renorm=False)
+    check_routing(routing, logits, r)
+    assert_close_bf16(y, r.y)
+    assert (routing[1].sum(1) < 1.0).all()
+
+
+@pytest.mark.parametrize("T,d,dff,E,k", [(257, 72, 40, 16, 4), (33, 128, 256, 8, 2), (1, 64, 64, 8, 2)])
+def test_fp32_layer_shapes(oracle, T, d, dff, E, k):
+    x, w_r, w_g, w_u, w_d, _ = make_layer(T, d, dff, E, k, seed=33)
+    r = oracle.moe_forward(x, w_r, w_g, w_u, w_d, k)
+    y, routing, logits, n = run_gpu(x, w_r, w_g, w_u, w_d, None, k, torch.float32, torch.float32)
+    check_routing(routing, logits, r)
+    assert_close_f32(y, r.y)
+
+
+def test_ties_go_to_the_lower_expert():
+    """Identical router rows give identical logits: the picks must be experts 0..k-1, bit for bit."""
+    from omega_ai_b200 import MoELayer
+    T, d, dff, E, k = 40, 128, 128, 8, 3
+    g = torch.Generator(device="cuda").manual_seed(1)
+    w_r = torch.randn(1, d, generator=g, device="cuda").repeat(E, 1).to(torch.bfloat16).contiguous()
+    w = lambda *s: (0.02 * torch.randn(*s, generator=g, device="cuda")).to(torch.bfloat16)
+    layer = MoELayer(d, dff, E, k, t_max=T, compute_dtype=torch.bfloat16)
+    layer.setWeights(w_r, w(E, dff, d), w(E, dff, d), w(E, d, dff))
+    layer.forward_device(torch.randn(T, d, generator=g, device="cuda").to(torch.bfloat16))
+    idx, wts, counts, _, _ = layer.routing(T)
+    assert (idx == np.arange(k)[None, :]).all()
+    np.testing.assert_allclose(wts, 1.0 / k, rtol=1e-6)
+    assert counts[:k].tolist() == [T] * k and counts[k:].sum() == 0
+    layer.close()
+
+
+def test_repeated_forwards_are_deterministic():
+    from omega_ai_b200 import MoELayer
+    layer = MoELayer(512, 768, 8, 2, t_max=1000, compute_dtype=torch.bfloat16)
+    layer.initParam(seed=3)
+    x = torch.randn(1000, 512, device="cuda").to(torch.bfloat16)
+    y0 = layer.forward_device(x).clone()
+    for T in (1000, 7, 1000, 300):
+        y = layer.forward_device(x[:T].contiguous())
+        assert torch.equal(y, y0[:T])  # same bits whatever ran before, and rows do not depend on the batch
+    layer.close()
+
+
+@pytest.mark.slow
+def test_config3_full_size_properties(oracle):
+    """Mixtral-shaped layer at full size (T=16384): routing bit-exact on all tokens, outputs on a token sample."""
+    from omega_ai_b200 import MoELayer
+    T, d, dff, E, k = 16384, 4096, 14336, 8, 2
+    g = torch.Generator(device="cuda").manual_seed(20240611)
+    rn = lambda *s: (0.02 * torch.randn(*s, generator=g, device="cuda", dtype=torch.float32)).to(torch.bfloat16)
+    w_r, w_g, w_u, w_d = rn(E, d), rn(E, dff, d), rn(E, dff, d), rn(E, d, dff)
+    x = torch.randn(T, d, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    layer = MoELayer(d, dff, E, k, t_max=T, compute_dtype=torch.bfloat16)
+    layer.setWeights(w_r, w_g, w_u, w_d)
+    y = layer.forward_device(x).float().cpu().numpy()
+    idx, w, counts, offsets, perm = layer.routing(T)
+    logits = layer.logits(T)
+    layer.close()
+    # size-independent properties
+    assert counts.sum() == T * k and offsets[-1] == T * k
+    assert np.array_equal(np.sort(perm), np.arange(T * k))
+    flat = idx.reshape(-1)
+    assert (np.diff(flat[perm]) >= 0).all()                       # grouped by expert
+    same = flat[perm][1:] == flat[perm][:-1]
+    assert (np.diff(perm)[same] > 0).all()                        # stable inside an expert
+    np.testing.assert_allclose(w.sum(1), 1.0, rtol=1e-5)
+    # oracle: routing for every token, outputs for 12 of them
+    sel = np.sort(np.random.default_rng(1).choice(T, 12, replace=False)).astype(np.int32)
+    f = lambda t: t.float().cpu().numpy()
+    r = oracle.moe_forward(f(x), f(w_r), f(w_g), f(w_u), f(w_d), k, bf16=True, sel=sel)
+    np.testing.assert_array_equal(logits.view(np.uint32), r.logits.view(np.uint32))
+    np.testing.assert_array_equal(idx, r.topk_idx)
+    np.testing.assert_array_equal(counts, r.counts)
+    np.testing.assert_array_equal(perm, r.perm)
+    assert_close_bf16(y[sel], r.y)
+
+
+@pytest.mark.slow
+def test_config4_full_size_skewed(oracle):
+    """Fine-grained layer at full size: T=8192, d=2048, E=64, top-6, d_ff=1408, Zipf(1.1) router bias scaled to 2."""
+    from omega_ai_b200 import MoELayer
+    T, d, dff, E, k = 8192, 2048, 1408, 64, 6
+    g = torch.Generator(device="cuda").manual_seed(20240611)
+    rn = lambda *s: (0.02 * torch.randn(*s, generator=g, device="cuda", dtype=torch.float32)).to(torch.bfloat16)
+    w_r, w_g, w_u, w_d = rn(E, d), rn(E, dff, d), rn(E, dff, d), rn(E, d, dff)
+    z = (torch.randperm(E, generator=g, device="cuda").float() + 1) ** -1.1
+    bias = (2.0 * z / z.max()).to(torch.bfloat16)
+    x = torch.randn(T, d, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    layer = MoELayer(d, dff, E, k, bias=True, t_max=T, compute_dtype=torch.bfloat16)
+    layer.setWeights(w_r, w_g, w_u, w_d, bias)
+    y = layer.forward_device(x).float().cpu().numpy()
+    idx, w, counts, offsets, perm = layer.routing(T)
+    logits = layer.logits(T)
+    layer.close()
+    assert counts.sum() == T * k and np.array_equal(np.sort(perm), np.arange(T * k))
+    assert counts.max() > 4 * counts.mean() and counts.min() < 0.25 * counts.mean()  # the load really is skewed
+    sel = np.sort(np.random.default_rng(2).choice(T, 48, replace=False)).astype(np.int32)
+    f = lambda t: t.float().cpu().numpy()
+    r = oracle.moe_forward(f(x), f(w_r), f(w_g), f(w_u), f(w_d), k, bias=f(bias), bf16=True, sel=sel)
+    np.testing.assert_array_equal(logits.view(np.uint32), r.logits.view(np.uint32))
+    np.testing.assert_array_equal(idx, r.topk_idx)
+    np.testing.assert_array_equal(counts, r.counts)
+    np.testing.assert_array_equal(perm, r.perm)
+    assert_close_bf16(y[sel], r.y)
+
+
+@pytest.fixture(scope="module")
+def decode_layer():
+    """Decode-shaped layer at full size (d=4096, E=8, top-2, d_ff=14336), shared by the token-count sweep."""
+    from omega_ai_b200 import MoELayer
+    d, dff, E, k = 4096, 14336, 8, 2
+    g = torch.Generator(device="cuda").manual_seed(20240611)
+    rn = lambda *s: (0.02 * torch.randn(*s, generator=g, device="cuda", dtype=torch.float32)).to(torch.bfloat16)
+    w = (rn(E, d), rn(E, dff, d), rn(E, dff, d), rn(E, d, dff))
+    layer = MoELayer(d, dff, E, k, t_max=256, compute_dtype=torch.bfloat16)
+    layer.setWeights(*w)
+    host = tuple(t.float().cpu().numpy() for t in w)
+    yield layer, host
+    layer.close()
+
+
+@pytest.mark.slow
+@pytest.mark.parametrize("T", [1, 8, 64, 256])
+def test_config5_full_size_decode(oracle, decode_layer, T):
+    layer, (w_r, w_g, w_u, w_d) = decode_layer
+    g = torch.Generator(device="cuda").manual_seed(100 + T)
+    x = torch.randn(T, 4096, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    y = layer.forward_device(x).float().cpu().numpy()
+    routing, logits = layer.routing(T), layer.logits(T)
+    sel = np.arange(min(T, 8), dtype=np.int32)
+    r = oracle.moe_forward(x.float().cpu().numpy(), w_r, w_g, w_u, w_d, 2, bf16=True, sel=sel)
+    check_routing(routing, logits, r)
+    assert_close_bf16(y[sel], r.y)
