@@ -37,6 +37,9 @@ CONFIGS = {
                name="decode-shaped d=4096 E=8 top2 dff=14336"),
 }
 SEED = 20240611
+# dram__bytes_read.sum + dram__bytes_write.sum of one up/gate launch, from the ncu capture summarised in
+# profiles/grouped_gemm_ncu_full.md (full config-3 workload on one GPU); null for every other workload.
+NCU_TRAFFIC_BYTES = {("c3", 16384, 1): 5917402368 + 950249216}
 
 
 def load_peaks():
@@ -306,7 +309,9 @@ def run_ours(args, cfg):
         timed_s = ms * 1e-3
         peak = peaks["tf_sust"] if timed_s >= 1.0 else peaks["tf_burst"]
         roof = {"bound": "tensor", "kernel": "grouped_gemm_kernel<SWIGLU> (up/gate)", "achieved": ach,
-                "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+                "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                "traffic": NCU_TRAFFIC_BYTES.get((args.config, T, world)),
+                "algorithmic_dram_bytes": 2.0 * (2 * El * d * dff + T_local * k * (d + dff)),
                 "peak_source": peaks["src"] + (" sustained" if timed_s >= 1.0 else " burst"),
                 "frac_of_burst": ach / peaks["tf_burst"], "frac_of_sustained": ach / peaks["tf_sust"],
                 "down_tflops": alg["down_flops"] / (stage_ms["down"] * 1e-3) / 1e12}

@@ -118,6 +118,9 @@ OMOE_API int omoe_forward(omoe_handle *h, const void *x_dev, void *y_dev, int32_
  * whose data lives in its float[] (Tensor.hostToDevice / syncHost,
  * src/main/java/com/omega/engine/tensor/Tensor.java:559-579): H2D copy of x,
  * forward, D2H copy of y, then a stream synchronise so y is readable on return.
+ * On one GPU a batch of 8192 tokens or more is cut into chunks of at least 4096 whose
+ * copies overlap the kernels of their neighbours (tokens are independent, so
+ * y is bit-identical); the routing read-outs then describe the last chunk.
  */
 OMOE_API int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host, int32_t T,
                       int32_t io_dtype, void *cuda_stream);

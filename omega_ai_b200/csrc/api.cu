@@ -103,13 +103,19 @@ int omoe_destroy(omoe_handle *h) {
     if (!h) return OMOE_OK;
     ep_destroy(h);
     void *ptrs[] = {h->w_router, h->router_bias, h->w_gate, h->w_up, h->w_down, h->logits, h->topk_idx,
-                    h->topk_w, h->block_counts, h->block_base, h->counts, h->offsets, h->poffsets, h->tile_expert, h->pos,
+                    h->topk_w, h->block_counts, h->block_base, h->counts, h->offsets, h->poffsets, h->tile_expert, h->pos, h->lrank,
                     h->perm_out, h->dev_err, h->xp, h->hbuf, h->yp, h->x_stage, h->y_stage, h->d_row_table,
                     h->d_out_table, h->ticket, h->dst_base != h->poffsets ? h->dst_base : nullptr};
     for (void *p : ptrs)
         if (p) cudaFree(p);
     for (int i = 0; i <= OMOE_N_STAGES; i++)
         if (h->ev[i]) cudaEventDestroy(h->ev[i]);
+    for (int i = 0; i < kHostChunksMax; i++) {
+        if (h->ev_in[i]) cudaEventDestroy(h->ev_in[i]);
+        if (h->ev_out[i]) cudaEventDestroy(h->ev_out[i]);
+    }
+    if (h->copy_in) cudaStreamDestroy(h->copy_in);
+    if (h->copy_out) cudaStreamDestroy(h->copy_out);
     delete h;
     return OMOE_OK;
 }
@@ -204,6 +210,7 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
     ALLOC(poffsets, E + 1);
     ALLOC(tile_expert, h->rows_cap / kRowAlign);
     ALLOC(pos, tm * k);
+    ALLOC(lrank, tm * k);
     ALLOC(perm_out, tm * k);
     ALLOC(dev_err, 1);
     ALLOC(ticket, 1);
@@ -237,6 +244,19 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
             omoe_destroy(h);
             return rc;
         }
+    // copy streams of omoe_forward_host: non-blocking, so they can overlap kernels on the legacy default stream
+    h->host_chunk_min = 4096;
+    if (const char *v = getenv("OMOE_HOST_CHUNK_MIN")) h->host_chunk_min = atoi(v) > 0 ? atoi(v) : 1 << 30;
+    bool ok_streams = cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking) == cudaSuccess &&
+                      cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking) == cudaSuccess;
+    for (int i = 0; ok_streams && i < kHostChunksMax; i++)
+        ok_streams = cudaEventCreateWithFlags(&h->ev_in[i], cudaEventDisableTiming) == cudaSuccess &&
+                     cudaEventCreateWithFlags(&h->ev_out[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok_streams) {
+        int rc = fail(nullptr, OMOE_ERR_CUDA, "omoe_create: could not create the copy streams");
+        omoe_destroy(h);
+        return rc;
+    }
     if (c.compute_dtype == OMOE_BF16 && !build_tensor_maps(h)) {
         int rc = fail(nullptr, OMOE_ERR_CUDA, "omoe_create: %s", h->err);
         omoe_destroy(h);
@@ -355,11 +375,52 @@ int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host, int32_t 
     if (io_dtype != OMOE_F32 && io_dtype != OMOE_BF16) return fail(h, OMOE_ERR_INVALID, "omoe_forward_host: bad io_dtype");
     if (T > 0 && (!x_host || !y_host)) return fail(h, OMOE_ERR_INVALID, "omoe_forward_host: null buffer");
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
-    const size_t bytes = (size_t)T * h->cfg.d_model * elt_size(io_dtype);
-    if (bytes) CU_TRY(h, cudaMemcpyAsync(h->x_stage, x_host, bytes, cudaMemcpyHostToDevice, s));
-    int rc = omoe_forward(h, h->x_stage, h->y_stage, T, io_dtype, s);
-    if (rc != OMOE_OK) return rc;
-    if (bytes) CU_TRY(h, cudaMemcpyAsync(y_host, h->y_stage, bytes, cudaMemcpyDeviceToHost, s));
+    const size_t row_bytes = (size_t)h->cfg.d_model * elt_size(io_dtype);
+    // Tokens are independent, so a large batch is cut into chunks that run as
+    // separate forwards: the host-to-device copy of chunk i+1 and the
+    // device-to-host copy of chunk i-1 overlap the kernels of chunk i (two
+    // copy streams, ordered against the compute stream with events).  Every
+    // output row has the same bits as in one big forward.
+    int chunks = 1;
+    if (h->cfg.world == 1 && h->copy_in != nullptr) {
+        while (chunks < kHostChunksMax && T / (chunks * 2) >= h->host_chunk_min) chunks *= 2;
+    }
+    if (chunks == 1) {
+        const size_t bytes = (size_t)T * row_bytes;
+        if (bytes) CU_TRY(h, cudaMemcpyAsync(h->x_stage, x_host, bytes, cudaMemcpyHostToDevice, s));
+        int rc = omoe_forward(h, h->x_stage, h->y_stage, T, io_dtype, s);
+        if (rc != OMOE_OK) return rc;
+        if (bytes) CU_TRY(h, cudaMemcpyAsync(y_host, h->y_stage, bytes, cudaMemcpyDeviceToHost, s));
+        CU_TRY(h, cudaStreamSynchronize(s));
+        return check_dev_err(h);
+    }
+    const int per = (T + chunks - 1) / chunks;
+    // the copy streams must not run ahead of work already queued on the caller's stream
+    CU_TRY(h, cudaEventRecord(h->ev_in[0], s));
+    CU_TRY(h, cudaStreamWaitEvent(h->copy_in, h->ev_in[0], 0));
+    CU_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev_in[0], 0));
+    for (int i = 0; i < chunks; i++) {
+        const int t0 = i * per, n = (t0 + per <= T) ? per : T - t0;
+        if (n <= 0) break;
+        const size_t off = (size_t)t0 * row_bytes;
+        CU_TRY(h, cudaMemcpyAsync(static_cast<char *>(h->x_stage) + off, static_cast<const char *>(x_host) + off,
+                                  (size_t)n * row_bytes, cudaMemcpyHostToDevice, h->copy_in));
+        CU_TRY(h, cudaEventRecord(h->ev_in[i], h->copy_in));
+    }
+    for (int i = 0; i < chunks; i++) {
+        const int t0 = i * per, n = (t0 + per <= T) ? per : T - t0;
+        if (n <= 0) break;
+        const size_t off = (size_t)t0 * row_bytes;
+        CU_TRY(h, cudaStreamWaitEvent(s, h->ev_in[i], 0));
+        int rc = omoe_forward(h, static_cast<char *>(h->x_stage) + off, static_cast<char *>(h->y_stage) + off, n,
+                              io_dtype, s);
+        if (rc != OMOE_OK) return rc;
+        CU_TRY(h, cudaEventRecord(h->ev_out[i], s));
+        CU_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev_out[i], 0));
+        CU_TRY(h, cudaMemcpyAsync(static_cast<char *>(y_host) + off, static_cast<char *>(h->y_stage) + off,
+                                  (size_t)n * row_bytes, cudaMemcpyDeviceToHost, h->copy_out));
+    }
+    CU_TRY(h, cudaStreamSynchronize(h->copy_out));
     CU_TRY(h, cudaStreamSynchronize(s));
     return check_dev_err(h);
 }

@@ -60,7 +60,9 @@ combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const in
             src[j] = (j < k) ? static_cast<const YT *>(out_table[qj]) + (size_t)rj * d : nullptr;
         }
     }
-    for (int c = lane * 8; c < d; c += 256) {
+    const int cw = ((d / (int)gridDim.y + 7) / 8) * 8;  // blockIdx.y walks one slice of the row
+    const int c_lo = blockIdx.y * cw, c_hi = min(d, c_lo + cw);
+    for (int c = c_lo + lane * 8; c < c_hi; c += 256) {
         float acc[8];
 #pragma unroll
         for (int j = 0; j < KR; j++) {
@@ -140,7 +142,9 @@ combine_small_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, co
 template <typename YT, typename OT>
 cudaError_t launch_k(omoe_handle *h, void *y, int T, cudaStream_t s, const EpWait *wait) {
     const int d = h->cfg.d_model, k = h->cfg.top_k, El = h->e_local;
-    dim3 grid(ceil_div(T, 8)), block(256);
+    int split = 1;
+    while (split < 8 && (long long)T * split < 32LL * h->sm_count && d / (split * 2) >= 512) split *= 2;
+    dim3 grid(ceil_div(T, 8), split), block(256);
     OT *out = static_cast<OT *>(y);
     if (wait == nullptr && (long long)T * (d / 8) <= 65536) {
         const int threads = T * (d / 8);

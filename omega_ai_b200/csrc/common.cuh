@@ -18,6 +18,7 @@ constexpr int kRowAlign = 128;
 constexpr int kMaxTopK = 16;
 constexpr int kMaxExperts = 128;
 constexpr int kRouterWarps = 8;  // warps per router block
+constexpr int kHostChunksMax = 8;  // pieces a host-buffer forward is cut into to overlap copies and kernels
 constexpr int kMaxWorld = 8;     // expert-parallel ranks (GPUs of one NVSwitch node)
 
 // Device-side error word bits (set by kernels instead of trapping).
@@ -67,6 +68,7 @@ struct omoe_handle {
     // Views the expert kernels read.  On one GPU they alias the arrays above;
     // with expert parallelism they describe the rows received from all ranks.
     int32_t *ex_counts, *ex_poffsets, *ex_tile_expert;
+    int32_t *lrank;       // [t_max*k] rank of each pick among its router block's picks of the same expert
     int32_t *pos;         // [t_max*k] row of each pick in its owner's padded dispatch buffer
     // Where this rank's picks of expert e start in the dispatch buffer of the
     // rank that owns e.  On one GPU this is poffsets; with expert parallelism
@@ -84,6 +86,9 @@ struct omoe_handle {
     // staging for omoe_forward_host
     void *x_stage, *y_stage;
     size_t stage_bytes;
+    cudaStream_t copy_in, copy_out;
+    cudaEvent_t ev_in[omoe::kHostChunksMax], ev_out[omoe::kHostChunksMax];
+    int host_chunk_min;  // smallest chunk (tokens) worth its own forward
 
     omoe::TensorMaps maps;
     bool maps_ready;

@@ -17,6 +17,8 @@
 // Every wait on an mbarrier is bounded: when it runs out the kernel raises a
 // flag in the device error word, lets outstanding copies land, frees its tensor
 // memory and returns, so the context stays usable.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace omoe {
@@ -37,7 +39,6 @@ constexpr int kOutSubBytes = 128 * 64 * 2;          // one [128 x 64] bf16 sub-t
 constexpr int kOutBytes = 2 * kOutSubBytes;         // 32 KB: 128 output columns per pass
 constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 constexpr int kThreads = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 epilogue
-constexpr int kBand = 16;      // m-tiles per band of the tile order (L2 reuse of A rows)
 constexpr unsigned long long kWaitNs = 2000000000ull;  // 2 s bound on any single wait
 
 // ---- PTX wrappers ---------------------------------------------------------
@@ -187,11 +188,13 @@ struct TileCoord {
     int mt, nt;
 };
 
-__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m_tiles, int n_tiles) {
-    int per_band = kBand * n_tiles;
+// Tiles are walked in bands of `band` m-tiles x all n-tiles, m fastest, so the
+// rows of a band stay in L2 while the weight tiles stream past them.
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m_tiles, int n_tiles, int kband) {
+    int per_band = kband * n_tiles;
     int band = tile / per_band, r = tile % per_band;
-    int m0 = band * kBand;
-    int bm = min(kBand, num_m_tiles - m0);
+    int m0 = band * kband;
+    int bm = min(kband, num_m_tiles - m0);
     TileCoord c;
     c.mt = m0 + r % bm;
     c.nt = r / bm;
@@ -206,7 +209,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                     const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_out, int n_out,
                     int K, const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ poffsets,
-                    int E, int32_t *dev_err) {
+                    int E, int kband, int32_t *dev_err) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;  // stages need 1024-byte alignment for the swizzle
@@ -258,12 +261,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t phase = 0;
             bool ok = true;
             // the expert of the next tile is fetched while the current tile streams
-            int e_next = (int)blockIdx.x < total ? tile_expert[tile_coord(blockIdx.x, num_m_tiles, n_tiles).mt] : 0;
+            int e_next = (int)blockIdx.x < total ? tile_expert[tile_coord(blockIdx.x, num_m_tiles, n_tiles, kband).mt] : 0;
             for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
-                TileCoord tc = tile_coord(tile, num_m_tiles, n_tiles);
+                TileCoord tc = tile_coord(tile, num_m_tiles, n_tiles, kband);
                 const int e = e_next;
                 if (tile + (int)gridDim.x < total)
-                    e_next = tile_expert[tile_coord(tile + gridDim.x, num_m_tiles, n_tiles).mt];
+                    e_next = tile_expert[tile_coord(tile + gridDim.x, num_m_tiles, n_tiles, kband).mt];
                 const int row_a = tc.mt * BLOCK_M;
                 const int row_b0 = e * n_out + tc.nt * n_tile_w;
                 const int row_b1 = SWIGLU ? row_b0 : row_b0 + 128;
@@ -332,7 +335,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint32_t aphase = 0;
         int ti = 0;
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ti++) {
-            TileCoord tc = tile_coord(tile, num_m_tiles, n_tiles);
+            TileCoord tc = tile_coord(tile, num_m_tiles, n_tiles, kband);
             bool ok = mbar_wait(tfull_bar(as), aphase, abort_flag, dev_err);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -476,17 +479,19 @@ cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEven
         attr_done = true;
     }
     const int d = h->cfg.d_model, dff = h->cfg.d_ff;
+    static int band_up = getenv("OMOE_BAND_UP") ? atoi(getenv("OMOE_BAND_UP")) : 16;
+    static int band_dn = getenv("OMOE_BAND_DOWN") ? atoi(getenv("OMOE_BAND_DOWN")) : 16;
     dim3 grid(h->sm_count), block(kThreads);
     grouped_gemm_kernel<true><<<grid, block, kSmemBytes, s>>>(
         h->maps.a_x, h->maps.b_gate, h->maps.b_up, h->maps.a_h, dff, d,
-        h->ex_tile_expert, h->ex_poffsets, h->e_local, h->dev_err);
+        h->ex_tile_expert, h->ex_poffsets, h->e_local, band_up, h->dev_err);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     (*n)++;
     if (mid) cudaEventRecord(mid, s);
     grouped_gemm_kernel<false><<<grid, block, kSmemBytes, s>>>(
         h->maps.a_h, h->maps.b_down, h->maps.b_down, h->maps.c_y, d, dff,
-        h->ex_tile_expert, h->ex_poffsets, h->e_local, h->dev_err);
+        h->ex_tile_expert, h->ex_poffsets, h->e_local, band_dn, h->dev_err);
     e = cudaGetLastError();
     if (e == cudaSuccess) (*n)++;
     return e;

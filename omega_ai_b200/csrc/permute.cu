@@ -96,7 +96,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 template <typename XT, typename OT>
 __global__ void __launch_bounds__(256)
 permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, const int32_t *__restrict__ topk_idx,
-               int32_t *__restrict__ pos, const int32_t *__restrict__ block_base,
+               const int32_t *__restrict__ lrank, int32_t *__restrict__ pos, const int32_t *__restrict__ block_base,
                const int32_t *__restrict__ dst_base, int T, int d, int n_blocks, int e_local, int k, int tokens_per_block,
                EpSignal sig, int32_t *ticket) {
     const int lane = threadIdx.x & 31;
@@ -106,9 +106,9 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
         int f = t * k + lane;
         int e = topk_idx[f];
         int b = t / tokens_per_block;
-        my = dst_base[e] + block_base[(size_t)e * n_blocks + b] + pos[f];
+        my = dst_base[e] + block_base[(size_t)e * n_blocks + b] + lrank[f];
         owner = e / e_local;
-        pos[f] = my;
+        if (blockIdx.y == 0) pos[f] = my;
     }
     if (t < T) {
     OT *dst[kMaxTopK];
@@ -119,10 +119,13 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
         dst[j] = (j < k) ? static_cast<OT *>(row_table[q]) + (size_t)row * d : nullptr;
     }
 
+    // blockIdx.y walks one slice of the row (more warps in flight when there are few tokens)
+    const int cw = ((d / (int)gridDim.y + 7) / 8) * 8;
+    const int c_lo = blockIdx.y * cw, c_hi = min(d, c_lo + cw);
     const XT *src = x + (size_t)t * d;
     if constexpr (sizeof(XT) == sizeof(OT)) {
         constexpr int V = 16 / sizeof(XT);
-        for (int c = lane * V; c < d; c += 32 * V) {
+        for (int c = c_lo + lane * V; c < c_hi; c += 32 * V) {
             uint4 v = __ldg(reinterpret_cast<const uint4 *>(src + c));
 #pragma unroll
             for (int j = 0; j < kMaxTopK; j++)
@@ -130,7 +133,7 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
         }
     } else {
         // fp32 rows in, bf16 rows out: 8 elements per lane per step
-        for (int c = lane * 8; c < d; c += 32 * 8) {
+        for (int c = c_lo + lane * 8; c < c_hi; c += 32 * 8) {
             float4 a = __ldg(reinterpret_cast<const float4 *>(src + c));
             float4 b = __ldg(reinterpret_cast<const float4 *>(src + c) + 1);
             uint4 v;
@@ -150,7 +153,7 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
         __threadfence_system();
         __syncthreads();
         __shared__ int s_last;
-        if (threadIdx.x == 0) s_last = (atomicAdd(ticket, 1) == (int)gridDim.x - 1);
+        if (threadIdx.x == 0) s_last = (atomicAdd(ticket, 1) == (int)(gridDim.x * gridDim.y) - 1);
         __syncthreads();
         if (s_last && (int)threadIdx.x < sig.world) {
             __threadfence_system();
@@ -186,21 +189,24 @@ cudaError_t launch_permute(omoe_handle *h, const void *x, int io_dtype, int T, c
     const int d = h->cfg.d_model, k = h->cfg.top_k, El = h->e_local;
     const int nb = ceil_div(T, h->tokens_per_block);
     const int wpb = 8;
-    dim3 grid(ceil_div(T, wpb)), block(wpb * 32);
+    // enough warps to keep every SM's memory pipes busy: split rows when there are few tokens
+    int split = 1;
+    while (split < 8 && (long long)T * split < 32LL * h->sm_count && d / (split * 2) >= 512) split *= 2;
+    dim3 grid(ceil_div(T, wpb), split), block(wpb * 32);
     const bool cbf = h->cfg.compute_dtype == OMOE_BF16;
     EpSignal sg = sig ? *sig : EpSignal{nullptr, 1, 0, 0};
     if (io_dtype == OMOE_F32 && !cbf)
         permute_kernel<float, float><<<grid, block, 0, s>>>(
-            static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->pos, h->block_base, h->dst_base, T, d,
+            static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->lrank, h->pos, h->block_base, h->dst_base, T, d,
             nb, El, k, h->tokens_per_block, sg, h->ticket);
     else if (io_dtype == OMOE_F32 && cbf)
         permute_kernel<float, __nv_bfloat16><<<grid, block, 0, s>>>(
-            static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->pos, h->block_base, h->dst_base, T, d,
+            static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->lrank, h->pos, h->block_base, h->dst_base, T, d,
             nb, El, k, h->tokens_per_block, sg, h->ticket);
     else if (io_dtype == OMOE_BF16 && cbf)
         permute_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, block, 0, s>>>(
-            static_cast<const __nv_bfloat16 *>(x), h->d_row_table, h->topk_idx, h->pos, h->block_base,
-            h->dst_base, T, d, nb, El, k, h->tokens_per_block, sg, h->ticket);
+            static_cast<const __nv_bfloat16 *>(x), h->d_row_table, h->topk_idx, h->lrank, h->pos,
+            h->block_base, h->dst_base, T, d, nb, El, k, h->tokens_per_block, sg, h->ticket);
     else
         return cudaErrorInvalidValue;  // bf16 rows into an fp32 layer are rejected by the API
     (*n)++;

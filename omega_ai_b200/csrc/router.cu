@@ -232,7 +232,7 @@ cudaError_t launch_one(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
     int blocks = ceil_div(T, C::TB);
     kern<<<blocks, kRouterWarps * 32, smem, s>>>(x, h->w_router, h->router_bias, T, h->cfg.d_model,
                                                   h->cfg.n_experts, k, h->cfg.renormalize, h->logits,
-                                                  h->topk_idx, h->topk_w, h->block_counts, h->pos);
+                                                  h->topk_idx, h->topk_w, h->block_counts, h->lrank);
     return cudaGetLastError();
 }
 
@@ -378,7 +378,7 @@ int omoe_route_noalloc(const void *x_dev, const float *w_router_dev, const float
     hd.router_bias = const_cast<float *>(router_bias_dev);
     hd.logits = reinterpret_cast<float *>(scratch);
     hd.block_counts = reinterpret_cast<int32_t *>(scratch + kNaLogitsBytes);
-    hd.pos = reinterpret_cast<int32_t *>(scratch + kNaLogitsBytes + kNaBlocksBytes);
+    hd.lrank = reinterpret_cast<int32_t *>(scratch + kNaLogitsBytes + kNaBlocksBytes);
     hd.topk_idx = topk_idx_dev;
     hd.topk_w = topk_w_dev;
     if (T > 0) {
