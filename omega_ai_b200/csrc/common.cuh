@@ -129,6 +129,8 @@ struct EpWait;
 cudaError_t launch_combine(omoe_handle *h, void *y, int io_dtype, int T, cudaStream_t s, int *n, const EpWait *wait);
 cudaError_t launch_experts_f32(omoe_handle *h, cudaStream_t s, int *n);
 cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid);
+// The same two products on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles per pair).
+cudaError_t launch_experts_bf16_pair(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid);
 // Weight-streaming expert products for decode steps (T <= decode_tokens_threshold(), bf16).
 cudaError_t launch_experts_decode(omoe_handle *h, int T, cudaStream_t s, int *n, cudaEvent_t mid);
 int decode_tokens_threshold();

@@ -20,15 +20,13 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace omoe {
 
 namespace {
 
-constexpr int BLOCK_M = 128;
-constexpr int BLOCK_N = 256;   // accumulator columns per tile (gate 128 + up 128, or 256 of down)
-constexpr int BLOCK_K = 64;    // 64 bf16 = 128 bytes = one swizzle row
-constexpr int UMMA_K = 16;
+using namespace sm100;
 constexpr int kStages = 4;
 constexpr int kAccStages = 2;
 constexpr int kTmemCols = 512;
@@ -39,135 +37,6 @@ constexpr int kOutSubBytes = 128 * 64 * 2;          // one [128 x 64] bf16 sub-t
 constexpr int kOutBytes = 2 * kOutSubBytes;         // 32 KB: 128 output columns per pass
 constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 constexpr int kThreads = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 epilogue
-constexpr unsigned long long kWaitNs = 2000000000ull;  // 2 s bound on any single wait
-
-// ---- PTX wrappers ---------------------------------------------------------
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Bounded wait.  Returns false when the wait ran out or another role already
-// gave up (abort flag in shared memory); the caller then leaves its loop.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          int32_t *dev_err) {
-    if (mbar_try_wait(bar, parity)) return true;
-    unsigned long long t0 = 0;
-    for (uint32_t spin = 1;; spin++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 0xffu) == 0) {
-            if (*abort_flag) return false;
-            unsigned long long now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitNs) {
-                *abort_flag = 1;
-                atomicOr(dev_err, kDevErrTimeout);
-                return false;
-            }
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-        : "memory");
-}
-
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src),
-                 "r"(x), "r"(y)
-                 : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-// D[tmem] (+)= A[smem desc] * B[smem desc]^T
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                            uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// 32 lanes x 32 columns of fp32: thread i of the warp gets row (lane base + i).
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128
-// bytes apart, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
-    uint64_t desc = 0;
-    desc |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);  // start address, 16-byte units
-    desc |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle)
-    desc |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row groups
-    desc |= (uint64_t)1 << 46;                        // descriptor version of this architecture
-    desc |= (uint64_t)2 << 61;                        // 128-byte swizzle
-    return desc;
-}
-
-// Instruction descriptor: fp32 accumulator, bf16 A and B, both K-major, N=256, M=128.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_N >> 3) << 17) |
-                            ((uint32_t)(BLOCK_M >> 4) << 24);
-
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t *>(&v);
-}
-
-// x / (1 + exp(-x)) with the fast exponential and reciprocal (the result is rounded to bf16 next)
-__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 #ifdef OMOE_TRACE
 // Debug build only: per-CTA, per-tile timestamps (ns) of the MMA and epilogue
@@ -469,6 +338,8 @@ bool build_tensor_maps(omoe_handle *h) {
 }
 
 cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid) {
+    static int use_pair = getenv("OMOE_PAIR") ? atoi(getenv("OMOE_PAIR")) : 0;
+    if (use_pair) return launch_experts_bf16_pair(h, s, n, mid);
     static bool attr_done = false;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
