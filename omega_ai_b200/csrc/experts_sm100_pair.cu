@@ -10,7 +10,7 @@
 // operand is halved.  For the up/gate product the two halves are natural: the
 // leader loads the gate rows, its peer the up rows.
 //
-// All loads are plain 2-D TMA tile loads (no multicast); completion of both
+// Every load is a plain 2-D TMA tile load into the issuing CTA only; completion of both
 // CTAs' loads is counted on the leader's barrier; the leader signals "stage
 // free" and "accumulator ready" to both CTAs with one tcgen05.commit per
 // barrier.  Every wait is bounded as in the single-CTA kernel.
