@@ -229,6 +229,11 @@ def run_ours(args, cfg):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.block:
+        gamma = torch.ones(d, device=dev, dtype=torch.float32)
+        plain_forward = layer.forward_device
+        layer.forward_device = lambda xx, yy=None: layer.forward_block(xx, gamma, yy)
+
     # ---- device-resident timing -------------------------------------------
     for _ in range(args.warmup):
         layer.forward_device(x, y)
@@ -337,7 +342,7 @@ def run_ours(args, cfg):
         "metric": "MoE-layer forward tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
-        "config": {"workload": cfg["name"], "tokens_global": T, "tokens_per_gpu": T_local, "experts_per_gpu": El,
+        "config": {"workload": cfg["name"] + (" + RMSNorm + residual" if args.block else ""), "tokens_global": T, "tokens_per_gpu": T_local, "experts_per_gpu": El,
                    "parallelism": f"ep{world}", "l2": l2_note},
         "stage_ms": stage_ms,
         "layer_tflops": alg["total_flops"] / (ms_per_step * 1e-3) / 1e12,
@@ -361,6 +366,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override the token count (decode sweep)")
     ap.add_argument("--cpu-tokens", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--block", action="store_true",
+                    help="time y = x + MoE(rmsnorm(x)*gamma) (omoe_forward_block) instead of the bare layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     cfg = dict(CONFIGS[args.config])

@@ -113,6 +113,22 @@ OMOE_API int omoe_forward(omoe_handle *h, const void *x_dev, void *y_dev, int32_
                  int32_t io_dtype, void *cuda_stream);
 
 /*
+ * The feed-forward half of a transformer block in one call:
+ *   y = x + MoE( rmsnorm(x) * gamma )
+ * i.e. norm2 -> mlp -> residual add of LlamaTransformerBlock.output()
+ * (src/main/java/com/omega/engine/nn/layer/llama/LlamaTransformerBlock.java:134-136),
+ * with the RMSNorm arithmetic of rmsnorm_forward_kernel2
+ * (src/main/resources/cu/RMSKernel.cu:185-224: rms = sqrtf(sum(x^2)/d + eps),
+ * (x / rms) * gamma; the reference fixes eps = 1e-5).  The normalised rows are
+ * written once in the layer's compute dtype and the residual add happens inside
+ * the combine kernel, so the two extra passes over [T, d] that the reference's
+ * RMS and add kernels make disappear.  gamma_dev [d_model] fp32 on the device;
+ * x_dev must not alias y_dev.
+ */
+OMOE_API int omoe_forward_block(omoe_handle *h, const void *x_dev, const float *gamma_dev, float eps,
+                                void *y_dev, int32_t T, int32_t io_dtype, void *cuda_stream);
+
+/*
  * Same layer with x and y in HOST memory (pinned memory makes the copies
  * asynchronous).  This is the call behind Layer.forward(Tensor) for a Tensor
  * whose data lives in its float[] (Tensor.hostToDevice / syncHost,

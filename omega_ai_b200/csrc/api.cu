@@ -104,7 +104,7 @@ int omoe_destroy(omoe_handle *h) {
     ep_destroy(h);
     void *ptrs[] = {h->w_router, h->router_bias, h->w_gate, h->w_up, h->w_down, h->logits, h->topk_idx,
                     h->topk_w, h->block_counts, h->block_base, h->counts, h->offsets, h->poffsets, h->tile_expert, h->pos, h->lrank,
-                    h->perm_out, h->dev_err, h->xp, h->hbuf, h->yp, h->x_stage, h->y_stage, h->d_row_table,
+                    h->perm_out, h->dev_err, h->xp, h->hbuf, h->yp, h->xn, h->x_stage, h->y_stage, h->d_row_table,
                     h->d_out_table, h->ticket, h->dst_base != h->poffsets ? h->dst_base : nullptr};
     for (void *p : ptrs)
         if (p) cudaFree(p);
@@ -187,7 +187,8 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
             {&h->w_gate, (size_t)h->e_local * dff * d * cs}, {&h->w_up, (size_t)h->e_local * dff * d * cs},
             {&h->w_down, (size_t)h->e_local * dff * d * cs}, {&h->xp, (size_t)h->rows_cap * d * cs},
             {&h->hbuf, (size_t)h->rows_cap * dff * cs},      {&h->yp, (size_t)h->rows_cap * d * cs},
-            {&h->x_stage, (size_t)tm * d * 4},               {&h->y_stage, (size_t)tm * d * 4}};
+            {&h->x_stage, (size_t)tm * d * 4},               {&h->y_stage, (size_t)tm * d * 4},
+            {&h->xn, (size_t)tm * d * cs}};
         h->stage_bytes = (size_t)tm * d * 4;
         for (auto &b : bufs) {
             cudaError_t e = cudaMalloc(b.p, b.bytes ? b.bytes : 1);
@@ -313,38 +314,37 @@ int omoe_set_weights(omoe_handle *h, const void *w_router, const void *router_bi
     return OMOE_OK;
 }
 
-int omoe_forward(omoe_handle *h, const void *x_dev, void *y_dev, int32_t T, int32_t io_dtype, void *cuda_stream) {
-    if (!h) return OMOE_ERR_INVALID;
-    if (!h->weights_set) return fail(h, OMOE_ERR_STATE, "omoe_forward: call omoe_set_weights first");
-    if (T < 0) return fail(h, OMOE_ERR_INVALID, "omoe_forward: negative token count");
-    if (T > h->cfg.t_max) return fail(h, OMOE_ERR_TOO_LARGE, "omoe_forward: T=%d exceeds t_max=%d", T, h->cfg.t_max);
-    if (io_dtype != OMOE_F32 && io_dtype != OMOE_BF16) return fail(h, OMOE_ERR_INVALID, "omoe_forward: bad io_dtype");
-    if (h->cfg.compute_dtype == OMOE_F32 && io_dtype != OMOE_F32)
-        return fail(h, OMOE_ERR_UNSUPPORTED, "omoe_forward: an fp32 layer takes fp32 rows");
-    if (T > 0 && (!x_dev || !y_dev)) return fail(h, OMOE_ERR_INVALID, "omoe_forward: null buffer");
-    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+// The layer proper.  x (x_dtype) feeds router and dispatch; y and the optional
+// residual rows have y_dtype.  pre != 0: kernels already launched for this
+// forward (the block entry point's RMSNorm).
+static int forward_impl(omoe_handle *h, const void *x_dev, int x_dtype, void *y_dev, int y_dtype, const void *resid,
+                        int32_t T, cudaStream_t s, int pre) {
     h->last_T = T;
-    h->last_io_dtype = io_dtype;
+    h->last_io_dtype = y_dtype;
     h->last_stream = s;
     h->last_launches = 0;
     h->ev_valid = false;
-    if (h->cfg.world > 1) return ep_forward(h, x_dev, y_dev, T, io_dtype, s);
+    if (h->cfg.world > 1) {
+        int rc = ep_forward(h, x_dev, x_dtype, y_dev, y_dtype, resid, T, s);
+        h->last_launches += pre;
+        return rc;
+    }
     if (T == 0) return OMOE_OK;
 
-    int n = 0;
+    int n = pre;
     const bool prof = h->profiling;
 #define MARK(i) do { if (prof) cudaEventRecord(h->ev[i], s); } while (0)
     MARK(0);
     if (h->cfg.compute_dtype == OMOE_BF16 && T <= route_small_max_tokens()) {
-        CU_TRY(h, launch_route_small(h, x_dev, io_dtype, T, s, &n));
+        CU_TRY(h, launch_route_small(h, x_dev, x_dtype, T, s, &n));
         MARK(1);
         MARK(2);
     } else {
-        CU_TRY(h, launch_router(h, x_dev, io_dtype, T, s, &n));
+        CU_TRY(h, launch_router(h, x_dev, x_dtype, T, s, &n));
         MARK(1);
         CU_TRY(h, launch_scan(h, T, s, &n));
         MARK(2);
-        CU_TRY(h, launch_permute(h, x_dev, io_dtype, T, s, &n, nullptr));
+        CU_TRY(h, launch_permute(h, x_dev, x_dtype, T, s, &n, nullptr));
     }
     MARK(3);
     MARK(4);
@@ -358,12 +358,43 @@ int omoe_forward(omoe_handle *h, const void *x_dev, void *y_dev, int32_t T, int3
     }
     MARK(6);
     MARK(7);
-    CU_TRY(h, launch_combine(h, y_dev, io_dtype, T, s, &n, nullptr));
+    CU_TRY(h, launch_combine(h, y_dev, y_dtype, T, s, &n, nullptr, resid));
     MARK(8);
 #undef MARK
     h->ev_valid = prof;
     h->last_launches = n;
     return OMOE_OK;
+}
+
+static int check_forward_args(omoe_handle *h, const void *x_dev, void *y_dev, int32_t T, int32_t io_dtype,
+                              const char *who) {
+    if (!h->weights_set) return fail(h, OMOE_ERR_STATE, "%s: call omoe_set_weights first", who);
+    if (T < 0) return fail(h, OMOE_ERR_INVALID, "%s: negative token count", who);
+    if (T > h->cfg.t_max) return fail(h, OMOE_ERR_TOO_LARGE, "%s: T=%d exceeds t_max=%d", who, T, h->cfg.t_max);
+    if (io_dtype != OMOE_F32 && io_dtype != OMOE_BF16) return fail(h, OMOE_ERR_INVALID, "%s: bad io_dtype", who);
+    if (h->cfg.compute_dtype == OMOE_F32 && io_dtype != OMOE_F32)
+        return fail(h, OMOE_ERR_UNSUPPORTED, "%s: an fp32 layer takes fp32 rows", who);
+    if (T > 0 && (!x_dev || !y_dev)) return fail(h, OMOE_ERR_INVALID, "%s: null buffer", who);
+    return OMOE_OK;
+}
+
+int omoe_forward(omoe_handle *h, const void *x_dev, void *y_dev, int32_t T, int32_t io_dtype, void *cuda_stream) {
+    if (!h) return OMOE_ERR_INVALID;
+    int rc = check_forward_args(h, x_dev, y_dev, T, io_dtype, "omoe_forward");
+    if (rc != OMOE_OK) return rc;
+    return forward_impl(h, x_dev, io_dtype, y_dev, io_dtype, nullptr, T, static_cast<cudaStream_t>(cuda_stream), 0);
+}
+
+int omoe_forward_block(omoe_handle *h, const void *x_dev, const float *gamma_dev, float eps, void *y_dev, int32_t T,
+                       int32_t io_dtype, void *cuda_stream) {
+    if (!h) return OMOE_ERR_INVALID;
+    int rc = check_forward_args(h, x_dev, y_dev, T, io_dtype, "omoe_forward_block");
+    if (rc != OMOE_OK) return rc;
+    if (!gamma_dev) return fail(h, OMOE_ERR_INVALID, "omoe_forward_block: null gamma");
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    int pre = 0;
+    if (T > 0) CU_TRY(h, launch_rmsnorm(h, x_dev, io_dtype, gamma_dev, eps, T, s, &pre));
+    return forward_impl(h, h->xn, h->cfg.compute_dtype, y_dev, io_dtype, x_dev, T, s, pre);
 }
 
 int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host, int32_t T, int32_t io_dtype,

@@ -25,12 +25,26 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
+// y = residual + combined rows: the residual add of the transformer block
+// (LlamaTransformerBlock.java:136) folded into this pass; fp32 add, one rounding.
+__device__ __forceinline__ void add_residual(const float *r, float (&acc)[8]) {
+    float4 a = __ldg(reinterpret_cast<const float4 *>(r)), b = __ldg(reinterpret_cast<const float4 *>(r) + 1);
+    acc[0] = a.x + acc[0]; acc[1] = a.y + acc[1]; acc[2] = a.z + acc[2]; acc[3] = a.w + acc[3];
+    acc[4] = b.x + acc[4]; acc[5] = b.y + acc[5]; acc[6] = b.z + acc[6]; acc[7] = b.w + acc[7];
+}
+__device__ __forceinline__ void add_residual(const __nv_bfloat16 *r, float (&acc)[8]) {
+    float v[8];
+    unpack8(__ldg(reinterpret_cast<const uint4 *>(r)), v);
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] = v[i] + acc[i];
+}
+
 // One warp per token, 8 columns per lane per step (16 bytes of bf16 / 32 bytes of fp32).
 template <typename YT, typename OT, int K>
 __global__ void __launch_bounds__(256)
-combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const int32_t *__restrict__ pos,
-               const int32_t *__restrict__ topk_idx, const float *__restrict__ topk_w, int T, int d, int k_rt,
-               int e_local, EpWait wait, int32_t *dev_err) {
+combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const OT *__restrict__ resid,
+               const int32_t *__restrict__ pos, const int32_t *__restrict__ topk_idx,
+               const float *__restrict__ topk_w, int T, int d, int k_rt, int e_local, EpWait wait, int32_t *dev_err) {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (wait.flags != nullptr) {
@@ -81,6 +95,7 @@ combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const in
                 for (int i = 0; i < 8; i++) acc[i] = (j == 0) ? w[0] * v[i] : fmaf(w[j], v[i], acc[i]);
             }
         }
+        if (resid != nullptr) add_residual(resid + (size_t)t * d + c, acc);
         if constexpr (sizeof(OT) == 2) {
             uint4 o;
             o.x = pack2(acc[0], acc[1]);
@@ -100,9 +115,9 @@ combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const in
 // in flight at once instead of one warp walking a row (same arithmetic order).
 template <typename YT, typename OT>
 __global__ void __launch_bounds__(256)
-combine_small_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const int32_t *__restrict__ pos,
-                     const int32_t *__restrict__ topk_idx, const float *__restrict__ topk_w, int T, int d, int k,
-                     int e_local) {
+combine_small_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const OT *__restrict__ resid,
+                     const int32_t *__restrict__ pos, const int32_t *__restrict__ topk_idx,
+                     const float *__restrict__ topk_w, int T, int d, int k, int e_local) {
     const int vec = d / 8;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= T * vec) return;
@@ -125,6 +140,7 @@ combine_small_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, co
 #pragma unroll
         for (int i = 0; i < 8; i++) acc[i] = (j == 0) ? w * v[i] : fmaf(w, v[i], acc[i]);
     }
+    if (resid != nullptr) add_residual(resid + (size_t)t * d + c, acc);
     if constexpr (sizeof(OT) == 2) {
         uint4 o;
         o.x = pack2(acc[0], acc[1]);
@@ -140,21 +156,22 @@ combine_small_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, co
 }
 
 template <typename YT, typename OT>
-cudaError_t launch_k(omoe_handle *h, void *y, int T, cudaStream_t s, const EpWait *wait) {
+cudaError_t launch_k(omoe_handle *h, void *y, const void *resid_v, int T, cudaStream_t s, const EpWait *wait) {
     const int d = h->cfg.d_model, k = h->cfg.top_k, El = h->e_local;
     int split = 1;
     while (split < 8 && (long long)T * split < 32LL * h->sm_count && d / (split * 2) >= 512) split *= 2;
     dim3 grid(ceil_div(T, 8), split), block(256);
     OT *out = static_cast<OT *>(y);
+    const OT *resid = static_cast<const OT *>(resid_v);
     if (wait == nullptr && (long long)T * (d / 8) <= 65536) {
         const int threads = T * (d / 8);
-        combine_small_kernel<YT, OT><<<ceil_div(threads, 256), 256, 0, s>>>(h->d_out_table, out, h->pos, h->topk_idx,
+        combine_small_kernel<YT, OT><<<ceil_div(threads, 256), 256, 0, s>>>(h->d_out_table, out, resid, h->pos, h->topk_idx,
                                                                            h->topk_w, T, d, k, El);
         return cudaGetLastError();
     }
     EpWait wt = wait ? *wait : EpWait{nullptr, 1, 0, 0};
 #define OMOE_COMBINE(KK)                                                                                         \
-    combine_kernel<YT, OT, KK><<<grid, block, 0, s>>>(h->d_out_table, out, h->pos, h->topk_idx, h->topk_w, T, d, k, \
+    combine_kernel<YT, OT, KK><<<grid, block, 0, s>>>(h->d_out_table, out, resid, h->pos, h->topk_idx, h->topk_w, T, d, k, \
                                                       El, wt, h->dev_err)
     switch (k) {
         case 1: OMOE_COMBINE(1); break;
@@ -170,15 +187,16 @@ cudaError_t launch_k(omoe_handle *h, void *y, int T, cudaStream_t s, const EpWai
 
 }  // namespace
 
-cudaError_t launch_combine(omoe_handle *h, void *y, int io_dtype, int T, cudaStream_t s, int *n, const EpWait *wait) {
+cudaError_t launch_combine(omoe_handle *h, void *y, int io_dtype, int T, cudaStream_t s, int *n, const EpWait *wait,
+                           const void *resid) {
     const bool cbf = h->cfg.compute_dtype == OMOE_BF16;
     cudaError_t e;
     if (cbf && io_dtype == OMOE_BF16)
-        e = launch_k<__nv_bfloat16, __nv_bfloat16>(h, y, T, s, wait);
+        e = launch_k<__nv_bfloat16, __nv_bfloat16>(h, y, resid, T, s, wait);
     else if (cbf && io_dtype == OMOE_F32)
-        e = launch_k<__nv_bfloat16, float>(h, y, T, s, wait);
+        e = launch_k<__nv_bfloat16, float>(h, y, resid, T, s, wait);
     else if (!cbf && io_dtype == OMOE_F32)
-        e = launch_k<float, float>(h, y, T, s, wait);
+        e = launch_k<float, float>(h, y, resid, T, s, wait);
     else
         return cudaErrorInvalidValue;
     if (e == cudaSuccess) (*n)++;

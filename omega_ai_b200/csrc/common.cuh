@@ -83,6 +83,7 @@ struct omoe_handle {
 
     // activations (device, compute dtype)
     void *xp, *hbuf, *yp;
+    void *xn;  // [t_max, d] normalised rows of omoe_forward_block (compute dtype)
     // staging for omoe_forward_host
     void *x_stage, *y_stage;
     size_t stage_bytes;
@@ -126,7 +127,12 @@ cudaError_t launch_perm_readout(omoe_handle *h, int T, cudaStream_t s);
 // wait != nullptr: every block first waits (bounded) until all ranks have
 // published their expert outputs (expert-parallel return).
 struct EpWait;
-cudaError_t launch_combine(omoe_handle *h, void *y, int io_dtype, int T, cudaStream_t s, int *n, const EpWait *wait);
+// resid != nullptr: rows of y's element type added to the combined output (the block's residual).
+cudaError_t launch_combine(omoe_handle *h, void *y, int io_dtype, int T, cudaStream_t s, int *n, const EpWait *wait,
+                           const void *resid);
+// xn = (x / rms(x)) * gamma per row, in the layer's compute dtype (the block's pre-FFN RMSNorm).
+cudaError_t launch_rmsnorm(omoe_handle *h, const void *x, int x_dtype, const float *gamma, float eps, int T,
+                           cudaStream_t s, int *n);
 cudaError_t launch_experts_f32(omoe_handle *h, cudaStream_t s, int *n);
 cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid);
 // The same two products on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles per pair).

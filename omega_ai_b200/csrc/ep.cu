@@ -255,7 +255,8 @@ int ep_import(omoe_handle *h, const void *all_blobs) {
     return OMOE_OK;
 }
 
-int ep_forward(omoe_handle *h, const void *x, void *y, int T, int io_dtype, cudaStream_t s) {
+int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype, const void *resid, int T,
+               cudaStream_t s) {
     EpState *st = static_cast<EpState *>(h->ep);
     if (!st || !st->imported) {
         snprintf(h->err, sizeof(h->err), "omoe_forward: call omoe_ep_export / omoe_ep_import on every rank first");
@@ -274,7 +275,7 @@ int ep_forward(omoe_handle *h, const void *x, void *y, int T, int io_dtype, cuda
     } while (0)
     MARK(0);
     if (T > 0) {
-        TRY(launch_router(h, x, io_dtype, T, s, &n));
+        TRY(launch_router(h, x, x_dtype, T, s, &n));
     }
     MARK(1);
     TRY(launch_scan(h, T, s, &n));  // T == 0: zero blocks, all counts zero
@@ -286,7 +287,7 @@ int ep_forward(omoe_handle *h, const void *x, void *y, int T, int io_dtype, cuda
     n++;
     EpSignal sig{st->d_rows_flags, W, r, seq};
     if (T > 0) {
-        TRY(launch_permute(h, x, io_dtype, T, s, &n, &sig));
+        TRY(launch_permute(h, x, x_dtype, T, s, &n, &sig));
     } else {
         ep_signal_kernel<<<1, 32, 0, s>>>(st->d_rows_flags, W, r, seq);
         TRY(cudaGetLastError());
@@ -310,7 +311,7 @@ int ep_forward(omoe_handle *h, const void *x, void *y, int T, int io_dtype, cuda
     MARK(7);
     EpWait wt{st->ctl->flag_out, W, seq, st->timeout_ns};
     if (T > 0) {
-        TRY(launch_combine(h, y, io_dtype, T, s, &n, &wt));
+        TRY(launch_combine(h, y, y_dtype, T, s, &n, &wt, resid));
     } else {
         // still wait: the owners' outputs of this step must not be overwritten
         // by a later step before every rank has passed this point

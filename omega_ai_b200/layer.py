@@ -118,13 +118,15 @@ class MoELayer(Layer):
     """
 
     def __init__(self, embedDim, dff, numExperts, topK, bias=False, network=None, *, t_max=4096,
-                 compute_dtype=torch.bfloat16, renormalize=True, world=1, rank=0, recv_rows_max=0):
+                 compute_dtype=torch.bfloat16, renormalize=True, world=1, rank=0, recv_rows_max=0,
+                 keep_weights=False):
         super().__init__(network)
         self.embedDim, self.dff, self.numExperts, self.topK = embedDim, dff, numExperts, topK
         self.hasBias = bool(bias)
         self.compute_dtype = compute_dtype
         self.t_max = t_max
         self.world, self.rank = world, rank
+        self.keep_weights = keep_weights  # keep the source tensors so saveModel can write them
         self._h = C.c_void_p()
         cfg = Config(t_max=t_max, d_model=embedDim, d_ff=dff, n_experts=numExperts, top_k=topK,
                      compute_dtype=_dt(compute_dtype), renormalize=int(renormalize),
@@ -167,7 +169,27 @@ class MoELayer(Layer):
             self._h, w_router.data_ptr(), router_bias.data_ptr() if router_bias is not None else None,
             w_gate.data_ptr(), w_up.data_ptr(), w_down.data_ptr(), _dt(dt), s))
         torch.cuda.current_stream().synchronize()
-        self._weights = True
+        self._weights = (w_router, w_gate, w_up, w_down, router_bias) if self.keep_weights else True
+
+    # ---- checkpoint (the engine's headerless little-endian float32 stream) ----
+    def saveModel(self, f):
+        """Writes router (weight, bias), then per expert gate, up, down — the order
+        LlamaMLPLayer.saveModel uses for linear1, linear3, linear2 (LlamaMLPLayer.java:273-277)."""
+        from . import checkpoint
+
+        if not isinstance(self._weights, tuple):
+            raise OmoeError(-4, "saveModel needs the layer to be built with keep_weights=True")
+        w_router, w_gate, w_up, w_down, bias = (None if t is None else t.float().cpu().numpy() for t in self._weights)
+        checkpoint.write_moe(f, w_router, bias, w_gate, w_up, w_down)
+
+    def loadModel(self, f, device="cuda"):
+        from . import checkpoint
+
+        El = self.numExperts // self.world
+        assert self.world == 1, "load per rank: read the file and pass this rank's experts to setWeights"
+        w_router, bias, w_gate, w_up, w_down = checkpoint.read_moe(f, self.numExperts, self.embedDim, self.dff, self.hasBias)
+        dev = lambda a: None if a is None else torch.from_numpy(a).to(device).to(self.compute_dtype).contiguous()
+        self.setWeights(dev(w_router), dev(w_gate[:El]), dev(w_up[:El]), dev(w_down[:El]), dev(bias))
 
     # ---- forward ---------------------------------------------------------
     def init(self):
@@ -188,6 +210,18 @@ class MoELayer(Layer):
             y = torch.empty_like(x)
         s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
         check(self._h, self._lib.omoe_forward(self._h, x.data_ptr(), y.data_ptr(), x.shape[0], _dt(x.dtype), s))
+        return y
+
+    def forward_block(self, x: torch.Tensor, gamma: torch.Tensor, y: torch.Tensor | None = None, eps: float = 1e-5,
+                      stream=None) -> torch.Tensor:
+        """y = x + MoE(rmsnorm(x) * gamma): norm2 -> mlp -> residual add of the transformer block
+        (LlamaTransformerBlock.java:134-136) in one call. ``gamma`` [d] fp32 on the device."""
+        assert x.is_cuda and x.is_contiguous() and gamma.is_cuda and gamma.dtype == torch.float32
+        if y is None:
+            y = torch.empty_like(x)
+        s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        check(self._h, self._lib.omoe_forward_block(self._h, x.data_ptr(), gamma.data_ptr(), eps, y.data_ptr(),
+                                                    x.shape[0], _dt(x.dtype), s))
         return y
 
     def forward_host(self, x: torch.Tensor, y: torch.Tensor, stream=None) -> torch.Tensor:

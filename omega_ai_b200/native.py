@@ -29,7 +29,7 @@ ERRORS = {
 # every symbol include/omoe.h declares
 SYMBOLS = (
     "omoe_create", "omoe_destroy", "omoe_last_error", "omoe_set_weights", "omoe_forward",
-    "omoe_forward_host", "omoe_get_routing", "omoe_get_logits", "omoe_last_launch_count",
+    "omoe_forward_host", "omoe_forward_block", "omoe_get_routing", "omoe_get_logits", "omoe_last_launch_count",
     "omoe_set_profiling", "omoe_get_stage_ms", "omoe_ep_export", "omoe_ep_import",
     "omoe_route_noalloc", "omoe_route_noalloc_error",
 )
@@ -91,6 +91,7 @@ def lib():
     L.omoe_set_weights.argtypes = [vp, vp, vp, vp, vp, vp, i32, vp]
     L.omoe_forward.argtypes = [vp, vp, vp, i32, i32, vp]
     L.omoe_forward_host.argtypes = [vp, vp, vp, i32, i32, vp]
+    L.omoe_forward_block.argtypes = [vp, vp, vp, C.c_float, vp, i32, i32, vp]
     L.omoe_get_routing.argtypes = [vp, vp, vp, vp, vp, vp]
     L.omoe_get_logits.argtypes = [vp, vp]
     L.omoe_last_launch_count.argtypes = [vp]

@@ -99,6 +99,38 @@ void ref_softmax_rows(const float *in, float *out, int64_t rows, int64_t n) {
     }
 }
 
+/* RMSNorm in front of the layer: src/main/resources/cu/RMSKernel.cu:185-224
+ * (rmsnorm_forward_kernel2, the kernel RMSLayer.output() launches):
+ * rms = sqrtf(sum(x*x) / C + eps), out = (x / rms) * weight.  The reference
+ * leaves the order of its warp reduction open; it is fixed here like the router
+ * tree (lane (i/8)%32 owns element i, one fmaf chain per lane in ascending i,
+ * xor butterfly 16..1) so that the rows entering the router are reproducible
+ * bit for bit. */
+void ref_rmsnorm_rows(const float *x, const float *gamma, float eps, int64_t T, int64_t d, int bf16_out, float *out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t t = 0; t < T; t++) {
+        const float *xr = x + t * d;
+        float lane[32];
+        for (int l = 0; l < 32; l++) lane[l] = 0.0f;
+        for (int64_t i = 0; i < d; i++) {
+            int l = (int)((i >> 3) & 31);
+            lane[l] = fmaf(xr[i], xr[i], lane[l]);
+        }
+        for (int m = 16; m >= 1; m >>= 1) {
+            float nxt[32];
+            for (int l = 0; l < 32; l++) nxt[l] = lane[l] + lane[l ^ m];
+            for (int l = 0; l < 32; l++) lane[l] = nxt[l];
+        }
+        float mean = lane[0] / (float)d;
+        float rms = sqrtf(mean + eps);
+        for (int64_t i = 0; i < d; i++) {
+            float n = xr[i] / rms;
+            float v = n * gamma[i];
+            out[t * d + i] = bf16_out ? ref_bf16_round(v) : v;
+        }
+    }
+}
+
 /* ---- routing (no reference counterpart; rules fixed here) ---------------- */
 
 /* Router logits = x * W_r^T (+ bias), FullyLayer semantics as above, but with a

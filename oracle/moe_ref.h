@@ -51,6 +51,9 @@ void ref_silu(const float *x, float *out, int64_t n);
  * sequential in k with separate multiply and add. */
 void ref_linear_nt(const float *X, const float *W, float *Y, int64_t m, int64_t n, int64_t k);
 
+/* rows normalised as the block's RMSNorm does: (x / sqrtf(mean(x^2) + eps)) * gamma, fixed reduction tree */
+void ref_rmsnorm_rows(const float *x, const float *gamma, float eps, int64_t T, int64_t d, int bf16_out, float *out);
+
 /* row softmax, three passes */
 void ref_softmax_rows(const float *in, float *out, int64_t rows, int64_t n);
 

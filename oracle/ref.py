@@ -47,6 +47,7 @@ def lib():
         _lib.ref_silu.argtypes = [fp, fp, i64]
         _lib.ref_linear_nt.argtypes = [fp, fp, fp, i64, i64, i64]
         _lib.ref_softmax_rows.argtypes = [fp, fp, i64, i64]
+        _lib.ref_rmsnorm_rows.argtypes = [fp, fp, C.c_float, i64, i64, C.c_int, fp]
         _lib.ref_router_logits.argtypes = [fp, fp, fp, i64, i64, i64, fp]
         _lib.ref_topk_gate.argtypes = [fp, i64, i64, i64, C.c_int, ip, fp]
         _lib.ref_histogram_permute.argtypes = [ip, i64, i64, i64, ip, ip, ip, ip]
@@ -100,6 +101,28 @@ def softmax_rows(x: np.ndarray) -> np.ndarray:
     out = np.empty_like(x)
     lib().ref_softmax_rows(_f(x), _f(out), x.shape[0], x.shape[1])
     return out
+
+
+def rmsnorm(x, gamma, eps: float = 1e-5, bf16: bool = False) -> np.ndarray:
+    x, gamma = _cf(x), _cf(gamma)
+    out = np.empty_like(x)
+    lib().ref_rmsnorm_rows(_f(x), _f(gamma), eps, x.shape[0], x.shape[1], int(bf16), _f(out))
+    return out
+
+
+def moe_block(x, gamma, w_r, w_gate, w_up, w_down, k: int, *, eps=1e-5, bias=None, renorm=True, bf16=False,
+              out_bf16=None, sel=None) -> "MoEResult":
+    """y = x + MoE(rmsnorm(x) * gamma): norm2 -> mlp -> residual add of the transformer block
+    (LlamaTransformerBlock.java:134-136).  The sum x + (combined rows) is formed in fp32 and rounded once."""
+    x = _cf(x)
+    if out_bf16 is None:
+        out_bf16 = bf16
+    xn = rmsnorm(x, gamma, eps, bf16)
+    r = moe_forward(xn, w_r, w_gate, w_up, w_down, k, bias=bias, renorm=renorm, bf16=bf16, out_bf16=False, sel=sel)
+    rows = x if sel is None else x[np.asarray(sel)]
+    y = rows + r.y
+    r.y = bf16_round(y) if out_bf16 else y
+    return r
 
 
 def router_logits(x, w_r, bias=None) -> np.ndarray:

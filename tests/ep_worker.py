@@ -44,6 +44,7 @@ def run_case(rank, world, tokens, d, dff, E, k, compute, zipf, steps=2):
         idx, w, counts, offsets, perm = layer.routing(T)
         if T == 0:
             assert counts.sum() == 0
+            layer.forward_block(xd, torch.ones(d, device="cuda"))  # every rank makes the same number of calls
             continue
         r = ref.moe_forward(x, w_r, w_g, w_u, w_d, k, bias=bias, bf16=bf)
         np.testing.assert_array_equal(idx, r.topk_idx)
@@ -52,6 +53,12 @@ def run_case(rank, world, tokens, d, dff, E, k, compute, zipf, steps=2):
         np.testing.assert_array_equal(perm, r.perm)
         np.testing.assert_allclose(w, r.topk_w, rtol=1e-5, atol=1e-7)
         (assert_close_bf16 if bf else assert_close_f32)(y, r.y)
+        # the block form (RMSNorm in front, residual add in the combine) through the same transport
+        gamma = (1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+        yb = layer.forward_block(xd, torch.from_numpy(gamma).cuda()).float().cpu().numpy()
+        rb_ = ref.moe_block(x, gamma, w_r, w_g, w_u, w_d, k, bias=bias, bf16=bf)
+        np.testing.assert_array_equal(layer.routing(T)[0], rb_.topk_idx)
+        (assert_close_bf16 if bf else assert_close_f32)(yb, rb_.y)
     torch.cuda.synchronize()
     dist.barrier()
     layer.close()

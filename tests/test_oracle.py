@@ -147,3 +147,15 @@ def test_golden_vectors(oracle):
     np.testing.assert_array_equal(r.counts, g["bf16_counts"])
     np.testing.assert_array_equal(r.perm, g["bf16_perm"])
     np.testing.assert_allclose(r.y, g["bf16_y"], rtol=1e-2, atol=1e-6)  # one bf16 ulp of slack for libm's expf
+
+
+def test_rmsnorm_matches_the_reference_formula(oracle):
+    rng = np.random.default_rng(9)
+    x = (3 * rng.standard_normal((7, 200))).astype(np.float32)
+    g = (1 + 0.1 * rng.standard_normal(200)).astype(np.float32)
+    got = oracle.rmsnorm(x, g, 1e-5)
+    X = x.astype(np.float64)
+    want = X / np.sqrt((X * X).mean(1, keepdims=True) + 1e-5) * g
+    np.testing.assert_allclose(got, want, rtol=3e-6)
+    gb = oracle.rmsnorm(x, g, 1e-5, bf16=True)
+    np.testing.assert_array_equal(gb.view(np.uint32), oracle.bf16_round(got).view(np.uint32))

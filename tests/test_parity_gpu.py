@@ -330,3 +330,29 @@ def test_cta_pair_kernels_in_a_subprocess():
            "-k", "small_bf16 or config4_skewed or odd_shapes"]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=root)
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+
+
+@pytest.mark.parametrize("compute,io", [(torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32),
+                                        (torch.float32, torch.float32)])
+@pytest.mark.parametrize("T", [3, 300])
+def test_block_forward_rmsnorm_and_residual(oracle, compute, io, T):
+    """y = x + MoE(rmsnorm(x) * gamma) in one call; logits stay bit-exact because the norm's reduction is fixed."""
+    from omega_ai_b200 import MoELayer
+    d, dff, E, k = 256, 384, 8, 2
+    x, w_r, w_g, w_u, w_d, _ = make_layer(T, d, dff, E, k, seed=41)
+    x = (2.0 * x).astype(np.float32)
+    gamma = (1.0 + 0.2 * np.random.default_rng(3).standard_normal(d)).astype(np.float32)
+    bf = compute == torch.bfloat16
+    rb = oracle.bf16_round
+    if io == torch.bfloat16:
+        x = rb(x)
+    if bf:
+        w_r = rb(w_r)
+    r = oracle.moe_block(x, gamma, w_r, w_g, w_u, w_d, k, bf16=bf, out_bf16=(io == torch.bfloat16))
+    layer = MoELayer(d, dff, E, k, t_max=T, compute_dtype=compute)
+    dev = lambda a, dt: torch.from_numpy(a).cuda().to(dt).contiguous()
+    layer.setWeights(dev(w_r, compute), dev(w_g, compute), dev(w_u, compute), dev(w_d, compute))
+    y = layer.forward_block(dev(x, io), dev(gamma, torch.float32)).float().cpu().numpy()
+    check_routing(layer.routing(T), layer.logits(T), r)
+    (assert_close_bf16 if bf else assert_close_f32)(y, r.y)
+    layer.close()
