@@ -196,7 +196,7 @@ OMOE_API int omoe_ep_import(omoe_handle *h, const void *all_blobs /* [world][OMO
  * device memory and bans allocation on the request path, or any caller that
  * must avoid the device-wide synchronisation an allocation implies).  It runs
  * the same fused router kernel as omoe_forward; the kernel's scratch lives in
- * a fixed array inside the library image (about 3.3 MiB per GPU that loads
+ * a fixed array inside the library image (about 4.3 MiB per GPU that loads
  * the library, held until the process exits) and nothing is allocated or
  * freed, by this call or by anything it calls.
  *

@@ -59,7 +59,7 @@ route_small_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, cons
     const XT *xr = x + (size_t)t * d;
     for (int e = warp; e < E; e += 8) {
         const float *wr = w_r + (size_t)e * d;
-        float acc = 0.f;
+        float acc_even = 0.f, acc_odd = 0.f;  // the two chains of the reduction rule
         for (int i0 = lane * 8; i0 < d; i0 += 4 * 256) {
             float xv[4][8], wv[4][8];
 #pragma unroll
@@ -74,10 +74,14 @@ route_small_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, cons
             for (int u = 0; u < 4; u++) {
                 if (i0 + u * 256 < d) {
 #pragma unroll
-                    for (int j = 0; j < 8; j++) acc = fmaf(xv[u][j], wv[u][j], acc);
+                    for (int j = 0; j < 8; j += 2) {
+                        acc_even = fmaf(xv[u][j], wv[u][j], acc_even);
+                        acc_odd = fmaf(xv[u][j + 1], wv[u][j + 1], acc_odd);
+                    }
                 }
             }
         }
+        float acc = acc_even + acc_odd;
 #pragma unroll
         for (int m = 16; m >= 1; m >>= 1) acc = acc + __shfl_xor_sync(0xffffffffu, acc, m);
         if (lane == 0) {

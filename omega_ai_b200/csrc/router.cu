@@ -8,9 +8,13 @@
 // (max, expf(x-max) summed in index order, divide).
 //
 // Bit-exact routing needs a fixed summation order for the logits.  The order
-// is: lane l of a warp owns the elements i with (i/8)%32 == l and folds them in
-// ascending i with one fmaf chain; the 32 partial sums are then combined by an
-// xor butterfly over distances 16,8,4,2,1; the bias is added last.
+// is: lane l of a warp owns the elements i with (i/8)%32 == l and folds them
+// with two fmaf chains, one over its even-numbered and one over its
+// odd-numbered elements, each in ascending i; the lane's partial is even + odd;
+// the 32 partials are then combined by an xor butterfly over distances
+// 16,8,4,2,1; the bias is added last.  The two chains are the two halves of
+// one packed fma.rn.f32x2, which halves the multiply-add instruction count of
+// this issue-bound kernel.
 //
 // Data movement: a block covers TB tokens and walks d_model in steps of 256
 // columns.  Each step's token rows [TB x 256] and router weights [E x 256] are
@@ -39,21 +43,26 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-__device__ __forceinline__ void lds8(const float *p, float (&v)[8]) {
-    float4 a = *reinterpret_cast<const float4 *>(p);
-    float4 b = *reinterpret_cast<const float4 *>(p + 4);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+// Eight consecutive row elements as four (even, odd) fp32 pairs, each pair packed in 64 bits.
+__device__ __forceinline__ void lds_pairs(const float *p, unsigned long long (&v)[4]) {
+    const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(v[0]), "=l"(v[1]) : "r"(a));
+    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(v[2]), "=l"(v[3]) : "r"(a + 16));
 }
 
-__device__ __forceinline__ void lds8(const __nv_bfloat16 *p, float (&v)[8]) {
+__device__ __forceinline__ void lds_pairs(const __nv_bfloat16 *p, unsigned long long (&v)[4]) {
     uint4 r = *reinterpret_cast<const uint4 *>(p);
     uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        // a 32-bit word holds elements 2i (low half) and 2i+1 (high half); bf16 -> fp32 is a 16-bit shift
+        asm("mov.b64 %0, {%1, %2};" : "=l"(v[i]) : "r"(w[i] << 16), "r"(w[i] & 0xffff0000u));
     }
+}
+
+// (acc.lo, acc.hi) = (x.lo * w.lo + acc.lo, x.hi * w.hi + acc.hi), each half an IEEE fused multiply-add
+__device__ __forceinline__ void fma2(unsigned long long &acc, unsigned long long x, unsigned long long w) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(x), "l"(w));
 }
 
 template <int EMAX, int ES, int TPW, typename XT>
@@ -67,10 +76,10 @@ struct RouterCfg {
     static constexpr int XBYTES = TB * CS * (int)sizeof(XT);
     static constexpr int WBYTES = EMAX * CS * 4;
     static constexpr int STAGE = XBYTES + WBYTES;
-    static constexpr int BUDGET = (EMAX <= 16) ? 100 * 1024 : 200 * 1024;  // two blocks per SM for few experts
+    static constexpr int BUDGET = (EMAX <= 16) ? 100 * 1024 : 212 * 1024;  // two blocks per SM for few experts
     static constexpr int S0 = BUDGET / STAGE;
     static constexpr int S = S0 >= 4 ? 4 : (S0 < 1 ? 1 : S0);             // ring depth
-    static constexpr int MINB = (S * STAGE <= 100 * 1024 && EPW * TPW <= 64) ? 2 : 1;
+    static constexpr int MINB = (S * STAGE <= 100 * 1024 && EPW * TPW <= 32) ? 2 : 1;
 };
 
 // EMAX: experts padded to a power of two (>= E); ES: warps sharing a token
@@ -94,34 +103,48 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
     const int t0 = blockIdx.x * TB;
     const int nsub = (d + CS - 1) / CS;  // stages to walk
 
+    // Copy pattern of a stage.  Thread tid copies 16-byte piece (tid % PPR) of token rows tid/PPR,
+    // tid/PPR + 256/PPR, ... and float4 (tid % 64) of router rows tid/64, tid/64 + 4, ...: everything
+    // but the stage's column offset is fixed per thread, so the addresses are set up once.
+    static_assert(NSUB == 1, "the per-thread copy pattern below assumes one 256-column step per stage");
+    constexpr int PPR = kSub * (int)sizeof(XT) / 16;      // 16-byte pieces per token row (32 bf16 / 64 fp32)
+    constexpr int XROWS_PER_IT = kRouterWarps * 32 / PPR;  // token rows covered per pass of the block
+    constexpr int XIT = (TB + XROWS_PER_IT - 1) / XROWS_PER_IT;
+    constexpr int WIT = EMAX / 4;
+    const int x_row0 = tid / PPR, x_piece = tid % PPR;
+    const int x_col = x_piece * (16 / (int)sizeof(XT));    // column inside the step
+    const XT *x_src0 = x + (size_t)(t0 + x_row0) * d + x_col;
+    const int w_e0 = tid >> 6, w_q = tid & 63;
+    const int w_col = 4 * w_q;
+    const float *w_src0 = w_r + (size_t)w_e0 * d + w_col;
+    const uint32_t w_dst0 = C::XBYTES + (((w_q & 1) * EMAX + w_e0) * 32 + (w_q >> 1)) * 16;  // lane-split layout
     auto issue_stage = [&](int su) {
         const uint32_t st = smem_base + (su % S) * C::STAGE;
         const int c0 = su * CS;
-        constexpr int PPR = CS * (int)sizeof(XT) / 16;  // 16-byte pieces per token row
-        for (int p = tid; p < TB * PPR; p += kRouterWarps * 32) {
-            const int row = p / PPR, piece = p % PPR;
-            const int col = c0 + piece * (16 / (int)sizeof(XT));
-            const bool ok = (t0 + row < T) && (col < d);  // d is a multiple of 8: a piece is whole or absent
-            const XT *src = ok ? x + (size_t)(t0 + row) * d + col : x;
-            cp_async16(st + p * 16, src, ok ? 16 : 0);
+        const bool xcol_ok = c0 + x_col < d;  // d is a multiple of 8: a piece is whole or absent
+#pragma unroll
+        for (int it = 0; it < XIT; it++) {
+            const int row = x_row0 + it * XROWS_PER_IT;
+            if (XIT * XROWS_PER_IT == TB || row < TB) {
+                const bool ok = xcol_ok && (t0 + row < T);
+                const XT *src = ok ? x_src0 + (size_t)it * XROWS_PER_IT * d + c0 : x;
+                cp_async16(st + (uint32_t)(tid + it * kRouterWarps * 32) * 16, src, ok ? 16 : 0);
+            }
         }
-        const uint32_t sw = st + C::XBYTES;
-        for (int p = tid; p < EMAX * 64 * NSUB; p += kRouterWarps * 32) {
-            const int e = p / (64 * NSUB), r = p % (64 * NSUB);
-            const int sub = r >> 6, q = r & 63;  // q: float4 index inside the 256-column step
-            const int col = c0 + sub * kSub + 4 * q;
-            const bool ok = (e < E) && (col < d);
-            const float *src = ok ? w_r + (size_t)e * d + col : w_r;
-            const int ln = q >> 1, half = q & 1;  // lane owns floats 8*ln .. 8*ln+7: two float4 halves
-            cp_async16(sw + (((sub * 2 + half) * EMAX + e) * 32 + ln) * 16, src, ok ? 16 : 0);
+        const bool wcol_ok = c0 + w_col < d;
+#pragma unroll
+        for (int it = 0; it < WIT; it++) {
+            const bool ok = wcol_ok && (w_e0 + 4 * it < E);
+            const float *src = ok ? w_src0 + (size_t)it * 4 * d + c0 : w_r;
+            cp_async16(st + w_dst0 + (uint32_t)it * (4 * 32 * 16), src, ok ? 16 : 0);
         }
     };
 
-    float acc[TPW][EPW];
+    unsigned long long acc[TPW][EPW];  // (even chain, odd chain) of every token x expert
 #pragma unroll
     for (int i = 0; i < TPW; i++)
 #pragma unroll
-        for (int e = 0; e < EPW; e++) acc[i][e] = 0.0f;
+        for (int e = 0; e < EPW; e++) acc[i][e] = 0ull;
 
 #pragma unroll
     for (int su = 0; su < S - 1; su++) {
@@ -149,19 +172,21 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
         for (int sub = 0; sub < NSUB; sub++) {
             if (su * CS + sub * kSub + lane * 8 >= d) break;  // ascending: later steps are absent too
             const float *ws = wst + sub * 2 * EMAX * 128;
-            float xv[TPW][8];
+            unsigned long long xv[TPW][4];
 #pragma unroll
-            for (int i = 0; i < TPW; i++) lds8(xs + (grp * TPW + i) * CS + sub * kSub + lane * 8, xv[i]);
+            for (int i = 0; i < TPW; i++) lds_pairs(xs + (grp * TPW + i) * CS + sub * kSub + lane * 8, xv[i]);
 #pragma unroll
             for (int e = 0; e < EPW; e++) {
                 const int eg = es * EPW + e;
-                float4 wa = *reinterpret_cast<const float4 *>(ws + (eg * 32 + lane) * 4);
-                float4 wb = *reinterpret_cast<const float4 *>(ws + ((EMAX + eg) * 32 + lane) * 4);
-                float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+                unsigned long long wv[4];
+                const uint32_t wa = static_cast<uint32_t>(__cvta_generic_to_shared(ws + (eg * 32 + lane) * 4));
+                const uint32_t wb = static_cast<uint32_t>(__cvta_generic_to_shared(ws + ((EMAX + eg) * 32 + lane) * 4));
+                asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(wv[0]), "=l"(wv[1]) : "r"(wa));
+                asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(wv[2]), "=l"(wv[3]) : "r"(wb));
 #pragma unroll
                 for (int i = 0; i < TPW; i++)
 #pragma unroll
-                    for (int j = 0; j < 8; j++) acc[i][e] = fmaf(xv[i][j], wv[j], acc[i][e]);
+                    for (int j = 0; j < 4; j++) fma2(acc[i][e], xv[i][j], wv[j]);
             }
         }
         if constexpr (S == 1) __syncthreads();
@@ -172,7 +197,7 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
     for (int i = 0; i < TPW; i++)
 #pragma unroll
         for (int e = 0; e < EPW; e++) {
-            float a = acc[i][e];
+            float a = __uint_as_float((uint32_t)acc[i][e]) + __uint_as_float((uint32_t)(acc[i][e] >> 32));  // even + odd
 #pragma unroll
             for (int m = 16; m >= 1; m >>= 1) a = a + __shfl_xor_sync(0xffffffffu, a, m);
             const int eg = es * EPW + e, tt = grp * TPW + i;
@@ -242,7 +267,9 @@ template <int EMAX, int ES, typename XT>
 cudaError_t launch_tpw(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
     const int want_blocks = 2 * (h->sm_count > 0 ? h->sm_count : 148);
     constexpr int NG = kRouterWarps / ES;
-    if (ceil_div(T, NG * 4) >= want_blocks) return launch_one<EMAX, ES, 4, XT>(h, x, T, s);
+    // accumulators take 2 registers per (token, expert): 4 tokens x 16 experts per warp is the most that fits
+    if constexpr (EMAX / ES <= 16)
+        if (ceil_div(T, NG * 4) >= want_blocks) return launch_one<EMAX, ES, 4, XT>(h, x, T, s);
     if (ceil_div(T, NG * 2) >= want_blocks) return launch_one<EMAX, ES, 2, XT>(h, x, T, s);
     return launch_one<EMAX, ES, 1, XT>(h, x, T, s);
 }
@@ -251,16 +278,17 @@ template <typename XT>
 cudaError_t launch_typed(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
     const int E = h->cfg.n_experts;
     if (E <= 8) return launch_tpw<8, 1, XT>(h, x, T, s);
+    // beyond 16 experts several warps share a token group, 16 experts each
     if (E <= 16) return launch_tpw<16, 1, XT>(h, x, T, s);
     if (E <= 32) return launch_tpw<32, 2, XT>(h, x, T, s);
-    if (E <= 64) return launch_tpw<64, 2, XT>(h, x, T, s);
-    return launch_tpw<128, 4, XT>(h, x, T, s);
+    if (E <= 64) return launch_tpw<64, 4, XT>(h, x, T, s);
+    return launch_tpw<128, 8, XT>(h, x, T, s);
 }
 
 }  // namespace
 
 // Smallest number of tokens one router block may cover (sizes the per-block histogram arrays).
-int router_tokens_per_block(int E) { return E <= 16 ? kRouterWarps : (E <= 64 ? kRouterWarps / 2 : kRouterWarps / 4); }
+int router_tokens_per_block(int E) { return E <= 16 ? kRouterWarps : (E <= 32 ? 4 : (E <= 64 ? 2 : 1)); }
 
 cudaError_t launch_router(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n) {
     if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0) return cudaErrorMisalignedAddress;  // 16-byte copies
@@ -298,12 +326,12 @@ namespace {
 
 constexpr int kNaMaxTokens = OMOE_NOALLOC_MAX_TOKENS;
 constexpr size_t kNaLogitsBytes = sizeof(float) * (size_t)kNaMaxTokens * kMaxExperts;      // 2 MiB
-// a router block covers at least 2 tokens (128 experts), 4 (64) or 8 (16 and fewer)
-constexpr size_t kNaBlocksBytes = sizeof(int32_t) * (size_t)(kNaMaxTokens / 2) * kMaxExperts;  // 1 MiB
+// a router block covers at least 1 token (128 experts), 2 (64), 4 (32) or 8 (16 and fewer)
+constexpr size_t kNaBlocksBytes = sizeof(int32_t) * (size_t)kNaMaxTokens * kMaxExperts;  // 2 MiB
 constexpr size_t kNaRankBytes = sizeof(int32_t) * (size_t)kNaMaxTokens * kMaxTopK;         // 256 KiB
 constexpr size_t kNaScratchBytes = kNaLogitsBytes + kNaBlocksBytes + kNaRankBytes;
 
-// Scratch shared by every omoe_route_noalloc call on a device (about 3.3 MiB,
+// Scratch shared by every omoe_route_noalloc call on a device (about 4.3 MiB,
 // held by each GPU that loads the library until the process exits).
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNaScratchBytes];
 

@@ -136,7 +136,10 @@ void ref_rmsnorm_rows(const float *x, const float *gamma, float eps, int64_t T, 
 /* Router logits = x * W_r^T (+ bias), FullyLayer semantics as above, but with a
  * FIXED reduction tree so that a 32-lane GPU warp can reproduce every bit:
  *   lane l in [0,32) owns the elements i with (i / 8) % 32 == l and folds them
- *   in ascending i with acc = fmaf(x[i], w[i], acc), acc starting at +0;
+ *   with TWO fmaf chains, one over its even-numbered elements and one over its
+ *   odd-numbered ones, each in ascending i starting at +0 (the pair maps onto
+ *   one packed two-wide fp32 multiply-add on the GPU); the lane's partial is
+ *   even + odd;
  *   the 32 partials are then combined by an xor butterfly over lane distances
  *   16, 8, 4, 2, 1, every lane computing a[l] = a[l] + a[l ^ m] at once (IEEE
  *   addition commutes, so all lanes agree); lane 0 is the result.
@@ -148,12 +151,14 @@ void ref_router_logits(const float *x, const float *w_r, const float *bias,
         const float *xr = x + t * d;
         for (int64_t e = 0; e < E; e++) {
             const float *w = w_r + e * d;
-            float lane[32];
-            for (int l = 0; l < 32; l++) lane[l] = 0.0f;
+            float even[32], odd[32], lane[32];
+            for (int l = 0; l < 32; l++) { even[l] = 0.0f; odd[l] = 0.0f; }
             for (int64_t i = 0; i < d; i++) {
                 int l = (int)((i >> 3) & 31);
-                lane[l] = fmaf(xr[i], w[i], lane[l]);
+                if (i & 1) odd[l] = fmaf(xr[i], w[i], odd[l]);
+                else even[l] = fmaf(xr[i], w[i], even[l]);
             }
+            for (int l = 0; l < 32; l++) lane[l] = even[l] + odd[l];
             for (int m = 16; m >= 1; m >>= 1) {
                 float nxt[32];
                 for (int l = 0; l < 32; l++) nxt[l] = lane[l] + lane[l ^ m];

@@ -51,11 +51,16 @@ def test_bf16_rounding_matches_torch(oracle):
 
 def _lane_tree_logit(x, w):
     """Independent restatement of the router's reduction order, float32 step by step."""
-    lanes = [np.float32(0.0)] * 32
+    even = [np.float32(0.0)] * 32
+    odd = [np.float32(0.0)] * 32
     for i in range(x.size):
         l = (i // 8) % 32
         # fused multiply-add: exact product and sum in float64, one rounding to float32
-        lanes[l] = np.float32(np.float64(x[i]) * np.float64(w[i]) + np.float64(lanes[l]))
+        if i % 2:
+            odd[l] = np.float32(np.float64(x[i]) * np.float64(w[i]) + np.float64(odd[l]))
+        else:
+            even[l] = np.float32(np.float64(x[i]) * np.float64(w[i]) + np.float64(even[l]))
+    lanes = [np.float32(a + b) for a, b in zip(even, odd)]
     for m in (16, 8, 4, 2, 1):
         lanes = [np.float32(lanes[l] + lanes[l ^ m]) for l in range(32)]
     return lanes[0]
