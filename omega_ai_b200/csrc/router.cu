@@ -101,6 +101,9 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int grp = warp / ES, es = warp % ES;
     const int t0 = blockIdx.x * TB;
+    // the bias is read once per block here, not once per accumulator behind a dependent global load
+    float *sbias = reinterpret_cast<float *>(sidx + TB * kMaxTopK);
+    for (int e = tid; e < EMAX; e += kRouterWarps * 32) sbias[e] = (bias != nullptr && e < E) ? __ldg(bias + e) : 0.f;
     const int nsub = (d + CS - 1) / CS;  // stages to walk
 
     // Copy pattern of a stage.  Thread tid copies 16-byte piece (tid % PPR) of token rows tid/PPR,
@@ -192,39 +195,52 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
         if constexpr (S == 1) __syncthreads();
     }
 
-    // xor butterfly, then lane (e % 32) publishes logit e
+    // xor butterfly over all accumulators first (independent chains overlap), then lane (e % 32) publishes logit e
+    float red[TPW][EPW];
+#pragma unroll
+    for (int i = 0; i < TPW; i++)
+#pragma unroll
+        for (int e = 0; e < EPW; e++)
+            red[i][e] = __uint_as_float((uint32_t)acc[i][e]) + __uint_as_float((uint32_t)(acc[i][e] >> 32));  // even + odd
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1)
+#pragma unroll
+        for (int i = 0; i < TPW; i++)
+#pragma unroll
+            for (int e = 0; e < EPW; e++) red[i][e] = red[i][e] + __shfl_xor_sync(0xffffffffu, red[i][e], m);
 #pragma unroll
     for (int i = 0; i < TPW; i++)
 #pragma unroll
         for (int e = 0; e < EPW; e++) {
-            float a = __uint_as_float((uint32_t)acc[i][e]) + __uint_as_float((uint32_t)(acc[i][e] >> 32));  // even + odd
-#pragma unroll
-            for (int m = 16; m >= 1; m >>= 1) a = a + __shfl_xor_sync(0xffffffffu, a, m);
             const int eg = es * EPW + e, tt = grp * TPW + i;
             if (lane == (e & 31) && eg < E) {
-                float v = a;
-                if (bias != nullptr) v = v + __ldg(bias + eg);
+                float v = red[i][e];
+                if (bias != nullptr) v = v + sbias[eg];
                 sl[tt * EMAX + eg] = v;
                 if (t0 + tt < T) logits[(size_t)(t0 + tt) * E + eg] = v;
             }
         }
     __syncthreads();
 
-    // One warp per token: softmax statistics, top-k on the logits, gate weights.
-    constexpr int PL = (EMAX + 31) / 32;  // logits per lane
-    for (int tt = warp; tt < TB; tt += kRouterWarps) {
+    // Softmax statistics, top-k on the logits, gate weights: a group of GW lanes per token
+    // (8 lanes for up to 8 experts, so a warp works on 4 tokens at once).
+    constexpr int GW = EMAX <= 8 ? 8 : (EMAX <= 16 ? 16 : 32);
+    constexpr int PL = (EMAX + GW - 1) / GW;  // logits per lane
+    constexpr int TPP = 32 / GW;              // tokens per warp pass
+    static_assert(TB % TPP == 0, "a warp pass never straddles the end of the block's tokens");
+    for (int tb = warp * TPP; tb < TB; tb += kRouterWarps * TPP) {
+        const int tt = tb + lane / GW, gl = lane % GW;
         const int t = t0 + tt;
-        if (t >= T) {
-            if (lane < k) sidx[tt * k + lane] = -1;
-            continue;
-        }
+        const bool live = t < T;
         int my_e;
         float my_w;
-        warp_softmax_topk<PL>(sl + tt * EMAX, E, k, renorm, lane, my_e, my_w);
-        if (lane < k) {
-            sidx[tt * k + lane] = my_e;
-            topk_idx[(size_t)t * k + lane] = my_e;
-            topk_w[(size_t)t * k + lane] = my_w;
+        group_softmax_topk<PL, GW>(sl + tt * EMAX, E, k, renorm, gl, my_e, my_w);
+        if (gl < k) {
+            sidx[tt * k + gl] = live ? my_e : -1;
+            if (live) {
+                topk_idx[(size_t)t * k + gl] = my_e;
+                topk_w[(size_t)t * k + gl] = my_w;
+            }
         }
     }
     __syncthreads();
@@ -249,7 +265,8 @@ template <int EMAX, int ES, int TPW, typename XT>
 cudaError_t launch_one(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
     using C = RouterCfg<EMAX, ES, TPW, XT>;
     const int k = h->cfg.top_k;
-    size_t smem = (size_t)C::S * C::STAGE + sizeof(float) * C::TB * EMAX + sizeof(int32_t) * C::TB * k;
+    size_t smem = (size_t)C::S * C::STAGE + sizeof(float) * C::TB * EMAX + sizeof(int32_t) * C::TB * kMaxTopK +
+                  sizeof(float) * EMAX;
     auto kern = router_kernel<EMAX, ES, TPW, XT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
