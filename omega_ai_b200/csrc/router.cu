@@ -34,6 +34,15 @@ namespace {
 
 constexpr int kSub = 256;  // columns per step (32 lanes x 8)
 
+#ifdef OMOE_RTRACE
+// Debug build only (-DOMOE_RTRACE): per-block phase timestamps (SM clock) of the router kernel,
+// read back with omoe_debug_router_trace(long long out[2048][8]).
+__device__ long long g_rtrace[2048][8];
+#define RTRACE(slot) do { if (threadIdx.x == 0 && blockIdx.x < 2048) g_rtrace[blockIdx.x][slot] = clock64(); } while (0)
+#else
+#define RTRACE(slot) ((void)0)
+#endif
+
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
@@ -143,6 +152,7 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
         }
     };
 
+    RTRACE(0);
     unsigned long long acc[TPW][EPW];  // (even chain, odd chain) of every token x expert
 #pragma unroll
     for (int i = 0; i < TPW; i++)
@@ -195,6 +205,7 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
         if constexpr (S == 1) __syncthreads();
     }
 
+    RTRACE(1);
     // xor butterfly over all accumulators first (independent chains overlap), then lane (e % 32) publishes logit e
     float red[TPW][EPW];
 #pragma unroll
@@ -222,6 +233,7 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
         }
     __syncthreads();
 
+    RTRACE(2);
     // Softmax statistics, top-k on the logits, gate weights: a group of GW lanes per token
     // (8 lanes for up to 8 experts, so a warp works on 4 tokens at once).
     constexpr int GW = EMAX <= 8 ? 8 : (EMAX <= 16 ? 16 : 32);
@@ -245,6 +257,7 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
     }
     __syncthreads();
 
+    RTRACE(3);
     // Stable rank of every pick among the block's picks of the same expert, in
     // order of the flat index t*k+j; the last running count is the histogram.
     const int n_entries = TB * k;
@@ -259,6 +272,7 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
         }
         if (lane == 0) block_counts[(size_t)e * gridDim.x + blockIdx.x] = base;  // expert-major
     }
+    RTRACE(4);
 }
 
 template <int EMAX, int ES, int TPW, typename XT>
@@ -303,6 +317,12 @@ cudaError_t launch_typed(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
 }
 
 }  // namespace
+
+#ifdef OMOE_RTRACE
+extern "C" __attribute__((visibility("default"))) int omoe_debug_router_trace(long long *host_out) {
+    return cudaMemcpyFromSymbol(host_out, g_rtrace, sizeof(long long) * 2048 * 8) == cudaSuccess ? 0 : -2;
+}
+#endif
 
 // Smallest number of tokens one router block may cover (sizes the per-block histogram arrays).
 int router_tokens_per_block(int E) { return E <= 16 ? kRouterWarps : (E <= 32 ? 4 : (E <= 64 ? 2 : 1)); }
