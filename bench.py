@@ -194,7 +194,9 @@ def run_ours(args, cfg):
     peaks = load_peaks()
 
     # strong scaling: T is the global batch, sharded T/world per rank; experts E/world per rank
-    T_local = T // world
+    from omega_ai_b200.ep_layout import shard_tokens
+    lo, hi = shard_tokens(T, world, rank)
+    T_local = hi - lo   # ranks may hold different shares when T is not a multiple of world (0 is allowed)
     El = E // world
     g = torch.Generator(device=dev).manual_seed(SEED)
     rn = lambda *s: torch.randn(*s, generator=g, device=dev, dtype=torch.float32)
@@ -217,7 +219,8 @@ def run_ours(args, cfg):
     x = torch.randn(T_local, d, generator=gx, device=dev, dtype=torch.float32).to(cdt)
     y = torch.empty_like(x)
 
-    layer = MoELayer(d, dff, E, k, bias=bias is not None, t_max=T_local, compute_dtype=cdt, world=world, rank=rank)
+    t_max = max(1, -(-T // world))
+    layer = MoELayer(d, dff, E, k, bias=bias is not None, t_max=t_max, compute_dtype=cdt, world=world, rank=rank)
     layer.setWeights(w_r, w_g, w_u, w_d, bias)
     if world > 1:
         layer.ep_connect()
@@ -290,6 +293,13 @@ def run_ours(args, cfg):
     e2e_value = T / (e2e_ms / e2e_steps * 1e-3)
     bpe = 2 if cdt == torch.bfloat16 else 4
 
+    # experts that received at least one token, over all ranks (every rank takes part in the reduction)
+    _, _, counts_local, _, _ = layer.routing(T_local)
+    counts_all = torch.from_numpy(counts_local.astype("int64")).to(dev)
+    if world > 1:
+        dist.all_reduce(counts_all)
+    counts_all = counts_all.cpu().numpy()
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -298,8 +308,8 @@ def run_ours(args, cfg):
     alg = algorithmic(cfg, T_local)
     decode = T <= 256 and cfg["dtype"] == "bf16"
     if decode:
-        idx, _, counts, _, _ = layer.routing(T_local)
-        n_active = int((counts > 0).sum())
+        # the bound is the rank that has the most active experts (one GPU: all active experts)
+        n_active = max(int((counts_all[r * El:(r + 1) * El] > 0).sum()) for r in range(world))
         wbytes = n_active * 3.0 * d * dff * 2
         dur = (stage_ms["up_gate"] + stage_ms["down"]) * 1e-3
         roof = {"bound": "hbm", "kernel": "grouped_gemm_kernel (up/gate + down)",
