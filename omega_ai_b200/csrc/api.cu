@@ -351,7 +351,7 @@ static int forward_impl(omoe_handle *h, const void *x_dev, int x_dtype, void *y_
     if (h->cfg.compute_dtype == OMOE_BF16 && T <= decode_tokens_threshold()) {
         CU_TRY(h, launch_experts_decode(h, T, s, &n, prof ? h->ev[5] : nullptr));
     } else if (h->cfg.compute_dtype == OMOE_BF16) {
-        CU_TRY(h, launch_experts_bf16(h, s, &n, prof ? h->ev[5] : nullptr));
+        CU_TRY(h, launch_experts_bf16(h, s, &n, prof ? h->ev[5] : nullptr, (long)T * h->cfg.top_k));
     } else {
         CU_TRY(h, launch_experts_f32(h, s, &n));
         MARK(5);

@@ -35,6 +35,7 @@ struct TensorMaps {
     CUtensorMap b_up;    // [E_local*dff, d]
     CUtensorMap b_down;  // [E_local*d, dff]
     CUtensorMap c_y;     // expert outputs yp [rows_cap, d] (store target)
+    CUtensorMap b_down64;  // [E_local*d, dff] with a 64-row box (narrow down tiles)
 };
 
 }  // namespace omoe
@@ -134,7 +135,9 @@ cudaError_t launch_combine(omoe_handle *h, void *y, int io_dtype, int T, cudaStr
 cudaError_t launch_rmsnorm(omoe_handle *h, const void *x, int x_dtype, const float *gamma, float eps, int T,
                            cudaStream_t s, int *n);
 cudaError_t launch_experts_f32(omoe_handle *h, cudaStream_t s, int *n);
-cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid);
+// rows_ub: upper bound on the rows (token, expert picks) this GPU's experts hold in the step, -1 if unknown; a small
+// bound makes the down product pick between 256- and 64-column tiles from the row count on the device
+cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid, long rows_ub = -1);
 // The same two products on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles per pair).
 cudaError_t launch_experts_bf16_pair(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid);
 // Weight-streaming expert products for decode steps (T <= decode_tokens_threshold(), bf16).

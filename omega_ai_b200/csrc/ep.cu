@@ -299,7 +299,8 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
     n++;
     MARK(4);
     if (h->cfg.compute_dtype == OMOE_BF16) {
-        TRY(launch_experts_bf16(h, s, &n, prof ? h->ev[5] : nullptr));
+        // rows can come from every rank's tokens; a rank's step holds at most t_max of them
+        TRY(launch_experts_bf16(h, s, &n, prof ? h->ev[5] : nullptr, (long)h->cfg.t_max * W * h->cfg.top_k));
     } else {
         TRY(launch_experts_f32(h, s, &n));
         MARK(5);

@@ -73,12 +73,24 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m_tiles, int n
 // SWIGLU = true : B0 = W_gate, B1 = W_up, tile nt covers output columns [128 nt, 128 nt + 128)
 // SWIGLU = false: B0 = B1 = W_down,     tile nt covers output columns [256 nt, 256 nt + 256)
 // n_out: output features per expert (d_ff or d_model); K: reduction length.
-template <bool SWIGLU>
+constexpr int kPickFew = 1, kPickMany = 2;
+
+// NARROW (down product only): 64-column tiles instead of 256, for steps with so few rows that 256-wide
+// tiles would leave most SMs without work (decode with one or two experts per GPU).
+template <bool SWIGLU, bool NARROW = false>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                     const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_out, int n_out,
                     int K, const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ poffsets,
-                    int E, int kband, int32_t *dev_err) {
+                    int E, int kband, int32_t *dev_err, int pick) {
+    // pick: the down product is launched in both tile widths when the host cannot tell how many rows the step
+    // brought (they arrive from other GPUs); the row count on the device decides which of the two does the work.
+    // 0: always run; kPickFew: run only if 256-wide tiles would fill at most a quarter of the grid; kPickMany:
+    // the complement.  The test is uniform over the grid and comes before any barrier or TMEM allocation.
+    if (pick != 0) {
+        const bool few = (poffsets[E] / kRowAlign) * ((n_out + 255) / 256) * 4 <= (int)gridDim.x;
+        if (few != (pick == kPickFew)) return;
+    }
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;  // stages need 1024-byte alignment for the swizzle
@@ -118,7 +130,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
 
     const int num_m_tiles = poffsets[E] / kRowAlign;
-    const int n_tile_w = SWIGLU ? 128 : 256;
+    static_assert(!(SWIGLU && NARROW), "the narrow tile exists for the down product only");
+    constexpr int n_tile_w = SWIGLU ? 128 : (NARROW ? 64 : 256);
+    constexpr uint32_t stage_tx = NARROW ? kABytes + 64 * BLOCK_K * 2 : kStageBytes;
+    constexpr uint32_t idesc = NARROW ? ((1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24)) : kIdesc;
     const int n_tiles = (n_out + n_tile_w - 1) / n_tile_w;
     const int total = num_m_tiles * n_tiles;
     const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
@@ -142,10 +157,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, dev_err)) { ok = false; break; }
                     const uint32_t sa = base + stage * kStageBytes;
-                    mbar_expect_tx(full_bar(stage), kStageBytes);
+                    mbar_expect_tx(full_bar(stage), stage_tx);
                     tma_load_2d(sa, &map_a, full_bar(stage), kb * BLOCK_K, row_a);
-                    tma_load_2d(sa + kABytes, &map_b0, full_bar(stage), kb * BLOCK_K, row_b0);
-                    tma_load_2d(sa + kABytes + kBHalfBytes, &map_b1, full_bar(stage), kb * BLOCK_K, row_b1);
+                    tma_load_2d(sa + kABytes, &map_b0, full_bar(stage), kb * BLOCK_K, row_b0);  // NARROW: a 64-row box
+                    if constexpr (!NARROW)
+                        tma_load_2d(sa + kABytes + kBHalfBytes, &map_b1, full_bar(stage), kb * BLOCK_K, row_b1);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -176,7 +192,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
                         // advance 32 bytes (16 bf16) inside the swizzled row: +2 in 16-byte units
-                        tc_mma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                        tc_mma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -199,7 +215,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int r = quarter * 32 + lane;
         const uint32_t out_stage = base + kStages * kStageBytes;
         const uint32_t my_row = out_stage + half * kOutSubBytes + r * 128;
-        constexpr int kPasses = SWIGLU ? 1 : 2;
+        constexpr int kPasses = (SWIGLU || NARROW) ? 1 : 2;
         int as = 0;
         uint32_t aphase = 0;
         int ti = 0;
@@ -235,8 +251,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     } else {
                         uint32_t a[32];
-                        tc_ld32(t_acc + col, a);
-                        tc_wait_ld();
+                        if (!NARROW || half == 0) {  // a narrow tile has 64 accumulator columns: half 1 has none
+                            tc_ld32(t_acc + col, a);
+                            tc_wait_ld();
+                        }
                         if (p == kPasses - 1 && c == 1) {
                             tc_fence_before();
                             __syncwarp();
@@ -262,10 +280,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("bar.sync 1, 256;" ::: "memory");
                 if (warp == 2 && lane == 0) {
-                    const int x0 = tc.nt * (SWIGLU ? 128 : 256) + p * 128;
+                    const int x0 = tc.nt * n_tile_w + p * 128;
                     const int y0 = tc.mt * BLOCK_M;
                     if (x0 < n_out) tma_store_2d(&map_out, out_stage, x0, y0);
-                    if (x0 + 64 < n_out) tma_store_2d(&map_out, out_stage + kOutSubBytes, x0 + 64, y0);
+                    if (!NARROW && x0 + 64 < n_out) tma_store_2d(&map_out, out_stage + kOutSubBytes, x0 + 64, y0);
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
@@ -300,10 +318,10 @@ EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D bf16 tensor [rows, cols] row-major, box 128 rows x 64 columns, 128-byte swizzle.
-bool encode_map(EncodeTiledFn fn, CUtensorMap *m, void *ptr, uint64_t rows, uint64_t cols) {
+bool encode_map(EncodeTiledFn fn, CUtensorMap *m, void *ptr, uint64_t rows, uint64_t cols, uint32_t box_rows = 128) {
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {cols * 2};
-    cuuint32_t box[2] = {BLOCK_K, 128};
+    cuuint32_t box[2] = {BLOCK_K, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -331,21 +349,26 @@ bool build_tensor_maps(omoe_handle *h) {
     bool ok = encode_map(fn, &h->maps.a_x, h->xp, rows, d) && encode_map(fn, &h->maps.a_h, h->hbuf, rows, dff) &&
               encode_map(fn, &h->maps.b_gate, h->w_gate, El * dff, d) &&
               encode_map(fn, &h->maps.b_up, h->w_up, El * dff, d) &&
-              encode_map(fn, &h->maps.b_down, h->w_down, El * d, dff) && encode_map(fn, &h->maps.c_y, h->yp, rows, d);
+              encode_map(fn, &h->maps.b_down, h->w_down, El * d, dff) && encode_map(fn, &h->maps.c_y, h->yp, rows, d) &&
+              encode_map(fn, &h->maps.b_down64, h->w_down, El * d, dff, 64);
     if (!ok) snprintf(h->err, sizeof(h->err), "cuTensorMapEncodeTiled failed (d=%d, d_ff=%d)", (int)d, (int)dff);
     h->maps_ready = ok;
     return ok;
 }
 
-cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid) {
+cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid, long rows_ub) {
     static int use_pair = getenv("OMOE_PAIR") ? atoi(getenv("OMOE_PAIR")) : 0;
     if (use_pair) return launch_experts_bf16_pair(h, s, n, mid);
+    // OMOE_NARROW: 1 forces the narrow down tiles, 0 forbids them (tests and tuning); unset: decided per step
+    static int narrow_mode = getenv("OMOE_NARROW") ? atoi(getenv("OMOE_NARROW")) : -1;
     static bool attr_done = false;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kSmemBytes);
         if (e != cudaSuccess) return e;
         e = cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(grouped_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
         attr_done = true;
     }
@@ -355,14 +378,27 @@ cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEven
     dim3 grid(h->sm_count), block(kThreads);
     grouped_gemm_kernel<true><<<grid, block, kSmemBytes, s>>>(
         h->maps.a_x, h->maps.b_gate, h->maps.b_up, h->maps.a_h, dff, d,
-        h->ex_tile_expert, h->ex_poffsets, h->e_local, band_up, h->dev_err);
+        h->ex_tile_expert, h->ex_poffsets, h->e_local, band_up, h->dev_err, 0);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     (*n)++;
     if (mid) cudaEventRecord(mid, s);
-    grouped_gemm_kernel<false><<<grid, block, kSmemBytes, s>>>(
-        h->maps.a_h, h->maps.b_down, h->maps.b_down, h->maps.c_y, d, dff,
-        h->ex_tile_expert, h->ex_poffsets, h->e_local, band_dn, h->dev_err);
+    // Can the step be small enough for narrow tiles?  An expert with rows holds at least one tile.
+    const long tiles_ub = (rows_ub < h->e_local ? rows_ub : h->e_local) + rows_ub / kRowAlign;
+    const bool maybe_few = narrow_mode == 1 || (narrow_mode < 0 && rows_ub >= 0 && tiles_ub * ((d + 255) / 256) <= 4L * h->sm_count);
+    if (maybe_few) {
+        grouped_gemm_kernel<false, true><<<grid, block, kSmemBytes, s>>>(
+            h->maps.a_h, h->maps.b_down64, h->maps.b_down64, h->maps.c_y, d, dff,
+            h->ex_tile_expert, h->ex_poffsets, h->e_local, band_dn, h->dev_err, narrow_mode == 1 ? 0 : kPickFew);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        (*n)++;
+    }
+    if (narrow_mode != 1) {
+        grouped_gemm_kernel<false><<<grid, block, kSmemBytes, s>>>(
+            h->maps.a_h, h->maps.b_down, h->maps.b_down, h->maps.c_y, d, dff,
+            h->ex_tile_expert, h->ex_poffsets, h->e_local, band_dn, h->dev_err, maybe_few ? kPickMany : 0);
+    }
     e = cudaGetLastError();
     if (e == cudaSuccess) (*n)++;
     return e;

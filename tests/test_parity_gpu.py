@@ -332,6 +332,21 @@ def test_cta_pair_kernels_in_a_subprocess():
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
 
 
+@pytest.mark.parametrize("narrow", ["0", "1"])
+def test_down_tile_width_forced_in_a_subprocess(narrow):
+    """The down product runs with 256- or 64-column tiles; a step picks by its row count on the device.
+    OMOE_NARROW (read once per process) forces one width: small and odd-shaped cases must pass with either."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, OMOE_NARROW=narrow)
+    cmd = [sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_parity_gpu.py"), "-x", "-q", "-m", "gpu",
+           "-k", "small_bf16 or config4_skewed or odd_shapes or block_forward"]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=root)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+
+
 @pytest.mark.parametrize("compute,io", [(torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32),
                                         (torch.float32, torch.float32)])
 @pytest.mark.parametrize("T", [3, 300])
