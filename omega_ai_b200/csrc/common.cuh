@@ -139,6 +139,10 @@ cudaError_t launch_experts_f32(omoe_handle *h, cudaStream_t s, int *n);
 // bound makes the down product pick between 256- and 64-column tiles from the row count on the device
 cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid, long rows_ub = -1);
 // The same two products on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles per pair).
+// split-K over a thread-block cluster of S CTAs (experts_sm100_splitk.cu); splitk_ways() picks S, 1 = do not split
+int splitk_ways(long tiles_ub, int num_kb, int sm_count);
+cudaError_t launch_up_gate_splitk(omoe_handle *h, cudaStream_t s, int S);
+cudaError_t launch_down_splitk(omoe_handle *h, cudaStream_t s, int S);
 cudaError_t launch_experts_bf16_pair(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid);
 // Weight-streaming expert products for decode steps (T <= decode_tokens_threshold(), bf16).
 cudaError_t launch_experts_decode(omoe_handle *h, int T, cudaStream_t s, int *n, cudaEvent_t mid);

@@ -376,16 +376,36 @@ cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEven
     static int band_up = getenv("OMOE_BAND_UP") ? atoi(getenv("OMOE_BAND_UP")) : 16;
     static int band_dn = getenv("OMOE_BAND_DOWN") ? atoi(getenv("OMOE_BAND_DOWN")) : 16;
     dim3 grid(h->sm_count), block(kThreads);
-    grouped_gemm_kernel<true><<<grid, block, kSmemBytes, s>>>(
-        h->maps.a_x, h->maps.b_gate, h->maps.b_up, h->maps.a_h, dff, d,
-        h->ex_tile_expert, h->ex_poffsets, h->e_local, band_up, h->dev_err, 0);
-    cudaError_t e = cudaGetLastError();
+    // With very few row tiles, whole tiles per CTA would leave most SMs (and their share of the memory
+    // system) idle: split K over a cluster instead (experts_sm100_splitk.cu).
+    long m_tiles_ub = -1;
+    int s_up = 1, s_dn = 1;
+    if (rows_ub >= 0) {
+        // most tiles any placement of rows_ub rows on e_local experts can give
+        const long act = rows_ub < h->e_local ? rows_ub : h->e_local;
+        m_tiles_ub = act + (rows_ub - act) / kRowAlign;
+        s_up = splitk_ways(m_tiles_ub * ((dff + 127) / 128), (d + BLOCK_K - 1) / BLOCK_K, h->sm_count);
+        s_dn = splitk_ways(m_tiles_ub * ((d + 255) / 256), (dff + BLOCK_K - 1) / BLOCK_K, h->sm_count);
+    }
+    cudaError_t e;
+    if (s_up > 1) {
+        e = launch_up_gate_splitk(h, s, s_up);
+    } else {
+        grouped_gemm_kernel<true><<<grid, block, kSmemBytes, s>>>(
+            h->maps.a_x, h->maps.b_gate, h->maps.b_up, h->maps.a_h, dff, d,
+            h->ex_tile_expert, h->ex_poffsets, h->e_local, band_up, h->dev_err, 0);
+        e = cudaGetLastError();
+    }
     if (e != cudaSuccess) return e;
     (*n)++;
     if (mid) cudaEventRecord(mid, s);
-    // Can the step be small enough for narrow tiles?  An expert with rows holds at least one tile.
-    const long tiles_ub = (rows_ub < h->e_local ? rows_ub : h->e_local) + rows_ub / kRowAlign;
-    const bool maybe_few = narrow_mode == 1 || (narrow_mode < 0 && rows_ub >= 0 && tiles_ub * ((d + 255) / 256) <= 4L * h->sm_count);
+    if (s_dn > 1) {
+        e = launch_down_splitk(h, s, s_dn);
+        if (e == cudaSuccess) (*n)++;
+        return e;
+    }
+    // Can the step be small enough for narrow tiles?
+    const bool maybe_few = narrow_mode == 1 || (narrow_mode < 0 && rows_ub >= 0 && m_tiles_ub * ((d + 255) / 256) <= 4L * h->sm_count);
     if (maybe_few) {
         grouped_gemm_kernel<false, true><<<grid, block, kSmemBytes, s>>>(
             h->maps.a_h, h->maps.b_down64, h->maps.b_down64, h->maps.c_y, d, dff,

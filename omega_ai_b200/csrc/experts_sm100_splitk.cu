@@ -1,0 +1,300 @@
+// Grouped expert products for steps with very few row tiles (compute_dtype = OMOE_BF16): the reduction
+// length is split over the CTAs of a thread-block cluster.
+//
+// Same products as experts_sm100.cu (LlamaMLPLayer.java:117-123: linear1/linear3, SiLU, product, linear2)
+// and the same tile (128 rows x 256 accumulator columns, tcgen05.mma, fp32 accumulators in tensor memory).
+// When a step leaves a GPU one or two row tiles (decode with the experts spread over many GPUs), whole
+// tiles per CTA would put 16 or so CTAs to work and the weights, which are all of the traffic, would be
+// fetched by a tenth of the machine.  Here a cluster of S CTAs shares one tile: CTA c multiplies the
+// c-th slice of K, leaves its fp32 partial tile in its own shared memory (the TMA ring, idle by then),
+// and after a cluster barrier reduces the c-th slice of the tile's columns over all S partials, read
+// through distributed shared memory in rank order, so the sum has one fixed order.  Only rows that hold
+// a token are reduced and written.
+//
+// Every mbarrier wait is bounded (sm100_ptx.cuh).  The cluster barriers are hardware barriers without a
+// bound, so a CTA that gave up keeps walking its tiles, doing nothing, and still arrives at each of them.
+#include <stdlib.h>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace omoe {
+
+namespace {
+
+using namespace sm100;
+constexpr int kStagesK = 4;
+constexpr int kABytesK = BLOCK_M * BLOCK_K * 2;            // 16 KB
+constexpr int kBHalfBytesK = 128 * BLOCK_K * 2;            // 16 KB (one 128-row TMA box)
+constexpr int kStageBytesK = kABytesK + 2 * kBHalfBytesK;  // 48 KB
+constexpr int kPartialBytes = BLOCK_N * BLOCK_M * 4;       // 128 KB, laid over the ring
+static_assert(kPartialBytes <= kStagesK * kStageBytesK, "the partial tile reuses the ring");
+constexpr int kSmemBytesK = kStagesK * kStageBytesK + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int kThreadsK = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 epilogue and reduction
+constexpr int kTmemColsK = 256;
+
+__device__ __forceinline__ uint32_t sreg_cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t sreg_cluster_nctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t sreg_clusterid() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t sreg_nclusterid() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+    return r;
+}
+// every thread of every CTA of the cluster, with all lanes of its warp converged
+__device__ __forceinline__ void cluster_barrier() {
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t a;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
+    return v;
+}
+
+// SWIGLU = true : B0 = W_gate, B1 = W_up; tile nt gives output columns [128 nt, 128 nt + 128) of h
+// SWIGLU = false: B0 = B1 = W_down;      tile nt gives output columns [256 nt, 256 nt + 256) of yp
+// out: [rows, n_out] bf16; counts/poffsets: rows and first (128-aligned) row of each local expert.
+template <bool SWIGLU>
+__global__ void __launch_bounds__(kThreadsK, 1)
+grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
+                           const __grid_constant__ CUtensorMap map_b1, __nv_bfloat16 *__restrict__ out, int n_out,
+                           int K, const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ poffsets,
+                           const int32_t *__restrict__ counts, int E, int32_t *dev_err) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;  // stages need 1024-byte alignment for the swizzle
+    unsigned char *base_ptr = smem_raw + (base - raw);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(base_ptr + kStagesK * kStageBytesK);
+    const uint32_t bar0 = base + kStagesK * kStageBytesK;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kStagesK + s); };
+    const uint32_t tfull_bar = bar0 + 8u * (2 * kStagesK);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStagesK + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *partial = reinterpret_cast<float *>(base_ptr);  // [256 accumulator columns][128 rows]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = sreg_cluster_ctarank(), S = sreg_cluster_nctarank();
+    const int cid = (int)sreg_clusterid(), ncl = (int)sreg_nclusterid();
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStagesK; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(tfull_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemColsK)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_m_tiles = poffsets[E] / kRowAlign;
+    constexpr int n_tile_w = SWIGLU ? 128 : 256;
+    const int n_tiles = (n_out + n_tile_w - 1) / n_tile_w;
+    const int total = num_m_tiles * n_tiles;
+    const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    const int kb0 = (int)(((long long)num_kb * rank) / S), kb1 = (int)(((long long)num_kb * (rank + 1)) / S);
+
+    // ring position and accumulator phase live across tiles (each role keeps its own copy)
+    int stage = 0;
+    uint32_t phase = 0, tphase = 0;
+    bool ok = true;
+
+    for (int tile = cid; tile < total; tile += ncl) {
+        const int mt = tile % num_m_tiles, nt = tile / num_m_tiles;  // row tiles fastest: a weight tile is fetched once
+        const int e = tile_expert[mt];
+        const int m_valid = min(BLOCK_M, counts[e] - (mt * BLOCK_M - poffsets[e]));
+        // all lanes are converged here; a role that gave up (or whose CTA did) sits out the remaining tiles
+        ok = __all_sync(0xffffffffu, ok && !*abort_flag);
+
+        if (warp == 0) {
+            // ---------------- producer: this CTA's slice of K into the ring ----------------
+            if (lane == 0 && ok) {
+                // the ring held the previous tile's partial sums, written and read with ordinary accesses
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                const int row_a = mt * BLOCK_M;
+                const int row_b0 = e * n_out + nt * n_tile_w;
+                const int row_b1 = SWIGLU ? row_b0 : row_b0 + 128;
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, dev_err)) { ok = false; break; }
+                    const uint32_t sa = base + stage * kStageBytesK;
+                    mbar_expect_tx(full_bar(stage), kStageBytesK);
+                    tma_load_2d(sa, &map_a, full_bar(stage), kb * BLOCK_K, row_a);
+                    tma_load_2d(sa + kABytesK, &map_b0, full_bar(stage), kb * BLOCK_K, row_b0);
+                    tma_load_2d(sa + kABytesK + kBHalfBytesK, &map_b1, full_bar(stage), kb * BLOCK_K, row_b1);
+                    if (++stage == kStagesK) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) {
+                    // let copies that were already issued land before anything else happens to the ring
+                    unsigned long long t0 = globaltimer_ns();
+                    while (globaltimer_ns() - t0 < 2000000ull) { }
+                }
+            }
+        } else if (warp == 1) {
+            // ---------------- MMA issuer ----------------
+            if (lane == 0 && ok) {
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, dev_err)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = base + stage * kStageBytesK;
+                    const uint64_t adesc = make_sw128_desc(sa);
+                    const uint64_t bdesc = make_sw128_desc(sa + kABytesK);
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; k++)
+                        tc_mma_bf16(tmem_base, adesc + 2u * k, bdesc + 2u * k, kIdesc, (kb > kb0 || k != 0) ? 1u : 0u);
+                    tc_commit(empty_bar(stage));
+                    if (++stage == kStagesK) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) tc_commit(tfull_bar);  // accumulator complete, and every stage of the ring has been read
+            }
+        } else {
+            // ---------------- partial tile: TMEM -> registers -> own shared memory ----------------
+            // warp%4 selects the 32 TMEM lanes (rows) the hardware lets a warp read, (warp-2)/4 a 128-column half
+            const int quarter = warp & 3, half = (warp - 2) >> 2;
+            if (ok) {  // uniform over the warp
+                const bool got = mbar_wait(tfull_bar, tphase, abort_flag, dev_err);
+                ok = __all_sync(0xffffffffu, got);
+            }
+            tphase ^= 1u;
+            if (ok && quarter * 32 < m_valid) {
+                tc_fence_after();
+                const int row = quarter * 32 + lane;
+                const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int col = half * 128 + c * 32;
+                    uint32_t a[32];
+                    if (kb1 > kb0) {
+                        tc_ld32(t_acc + col, a);
+                        tc_wait_ld();
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) a[j] = 0u;  // an empty slice of K adds nothing
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; j++) partial[(col + j) * BLOCK_M + row] = __uint_as_float(a[j]);
+                }
+            }
+            tc_fence_before();
+        }
+
+        cluster_barrier();  // all S partial tiles are in place
+
+        if (warp >= 2 && !*abort_flag) {
+            // ---------------- reduction of this CTA's slice of the columns, in rank order ----------------
+            constexpr int kOutCols = SWIGLU ? 128 : 256;
+            const int w = kOutCols / (int)S;  // output columns per CTA
+            const int mv = (m_valid + 31) & ~31;
+            const uint32_t p0 = smem_u32(partial);
+            for (int i = threadIdx.x - 64; i < w * mv; i += kThreadsK - 64) {
+                const int row = i % mv, j = (int)rank * w + i / mv;  // j: output column inside the tile
+                const int oc = nt * kOutCols + j;
+                if (row >= m_valid || oc >= n_out) continue;
+                float g = 0.f, u = 0.f;
+                for (uint32_t s = 0; s < S; s++) {
+                    g += ld_peer_f32(p0 + 4u * (uint32_t)(j * BLOCK_M + row), s);
+                    if (SWIGLU) u += ld_peer_f32(p0 + 4u * (uint32_t)((128 + j) * BLOCK_M + row), s);
+                }
+                const float v = SWIGLU ? silu_f(g) * u : g;
+                out[(size_t)(mt * BLOCK_M + row) * n_out + oc] = __float2bfloat16_rn(v);
+            }
+        }
+
+        cluster_barrier();  // nobody reads this CTA's partial tile or accumulator any more
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColsK)
+                     : "memory");
+    }
+}
+
+template <bool SWIGLU>
+cudaError_t launch_splitk(omoe_handle *h, cudaStream_t s, int S, const CUtensorMap &a, const CUtensorMap &b0,
+                          const CUtensorMap &b1, void *out, int n_out, int K) {
+    auto kern = grouped_gemm_splitk_kernel<SWIGLU>;
+    static bool attr_done = false;  // one flag per instantiation
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesK);
+        if (e != cudaSuccess) return e;
+        attr_done = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = S;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(kThreadsK);
+    cfg.dynamicSmemBytes = kSmemBytesK;
+    cfg.stream = s;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    // as many clusters as can be resident at once (a cluster lives inside one GPC)
+    static int max_clusters[9] = {0};
+    if (max_clusters[S] == 0) {
+        cfg.gridDim = dim3(h->sm_count / S * S);
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+        if (e != cudaSuccess) return e;
+        if (n < 1) return cudaErrorInvalidConfiguration;
+        max_clusters[S] = n < h->sm_count / S ? n : h->sm_count / S;
+    }
+    cfg.gridDim = dim3(max_clusters[S] * S);
+    return cudaLaunchKernelEx(&cfg, kern, a, b0, b1, static_cast<__nv_bfloat16 *>(out), n_out, K,
+                              (const int32_t *)h->ex_tile_expert, (const int32_t *)h->ex_poffsets,
+                              (const int32_t *)h->ex_counts, h->e_local, h->dev_err);
+}
+
+}  // namespace
+
+// Number of CTAs to share one tile of a product with `tiles_ub` tiles at most and `num_kb` blocks of K:
+// the largest power of two (at most 8, the portable cluster size) that still leaves every CTA a few blocks
+// and does not ask for more CTAs than the GPU has SMs.  1: do not split.
+int splitk_ways(long tiles_ub, int num_kb, int sm_count) {
+    static int forced = getenv("OMOE_SPLITK") ? atoi(getenv("OMOE_SPLITK")) : -1;  // tests and tuning: 0/1 off, 2, 4, 8
+    if (forced >= 0) return forced == 2 || forced == 4 || forced == 8 ? forced : 1;
+    int s = 1;
+    while (s < 8 && tiles_ub * (s * 2) <= sm_count && num_kb >= 8 * (s * 2)) s *= 2;
+    return s;
+}
+
+cudaError_t launch_up_gate_splitk(omoe_handle *h, cudaStream_t s, int S) {
+    return launch_splitk<true>(h, s, S, h->maps.a_x, h->maps.b_gate, h->maps.b_up, h->hbuf, h->cfg.d_ff,
+                               h->cfg.d_model);
+}
+
+cudaError_t launch_down_splitk(omoe_handle *h, cudaStream_t s, int S) {
+    return launch_splitk<false>(h, s, S, h->maps.a_h, h->maps.b_down, h->maps.b_down, h->yp, h->cfg.d_model,
+                                h->cfg.d_ff);
+}
+
+}  // namespace omoe

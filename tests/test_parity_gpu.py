@@ -332,15 +332,18 @@ def test_cta_pair_kernels_in_a_subprocess():
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
 
 
-@pytest.mark.parametrize("narrow", ["0", "1"])
-def test_down_tile_width_forced_in_a_subprocess(narrow):
-    """The down product runs with 256- or 64-column tiles; a step picks by its row count on the device.
-    OMOE_NARROW (read once per process) forces one width: small and odd-shaped cases must pass with either."""
+@pytest.mark.parametrize("knob", ["OMOE_NARROW=0", "OMOE_NARROW=1", "OMOE_SPLITK=2", "OMOE_SPLITK=8"])
+def test_few_row_variants_forced_in_a_subprocess(knob):
+    """Steps with few row tiles switch the expert products to other kernels: 64-column tiles for the down
+    product (picked by the row count on the device) or K split over a cluster of 2/4/8 CTAs (picked from the
+    host's bound on the rows).  The knobs, read once per process, force one choice for every step: small,
+    skewed and odd-shaped cases must pass with each."""
     import os
     import subprocess
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, OMOE_NARROW=narrow)
+    name, value = knob.split("=")
+    env = dict(os.environ, **{name: value})
     cmd = [sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_parity_gpu.py"), "-x", "-q", "-m", "gpu",
            "-k", "small_bf16 or config4_skewed or odd_shapes or block_forward"]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=root)
