@@ -35,7 +35,7 @@ struct TensorMaps {
     CUtensorMap b_up;    // [E_local*dff, d]
     CUtensorMap b_down;  // [E_local*d, dff]
     CUtensorMap c_y;     // expert outputs yp [rows_cap, d] (store target)
-    CUtensorMap b_down64;  // [E_local*d, dff] with a 64-row box (narrow down tiles)
+    CUtensorMap a_x32, a_h32;  // xp and h with a 32-row box (tiles with few tokens, split-K kernels)
 };
 
 }  // namespace omoe
@@ -136,11 +136,13 @@ cudaError_t launch_rmsnorm(omoe_handle *h, const void *x, int x_dtype, const flo
                            cudaStream_t s, int *n);
 cudaError_t launch_experts_f32(omoe_handle *h, cudaStream_t s, int *n);
 // rows_ub: upper bound on the rows (token, expert picks) this GPU's experts hold in the step, -1 if unknown; a small
-// bound makes the down product pick between 256- and 64-column tiles from the row count on the device
+// bound sends a product with few tiles to the split-K kernels
 cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid, long rows_ub = -1);
 // The same two products on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles per pair).
 // split-K over a thread-block cluster of S CTAs (experts_sm100_splitk.cu); splitk_ways() picks S, 1 = do not split
-int splitk_ways(long tiles_ub, int num_kb, int sm_count);
+// m_tiles_ub: bound on the step's 128-row tiles, -1 if unknown
+int splitk_ways_up_gate(omoe_handle *h, long m_tiles_ub);
+int splitk_ways_down(omoe_handle *h, long m_tiles_ub);
 cudaError_t launch_up_gate_splitk(omoe_handle *h, cudaStream_t s, int S);
 cudaError_t launch_down_splitk(omoe_handle *h, cudaStream_t s, int S);
 cudaError_t launch_experts_bf16_pair(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid);

@@ -73,24 +73,12 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m_tiles, int n
 // SWIGLU = true : B0 = W_gate, B1 = W_up, tile nt covers output columns [128 nt, 128 nt + 128)
 // SWIGLU = false: B0 = B1 = W_down,     tile nt covers output columns [256 nt, 256 nt + 256)
 // n_out: output features per expert (d_ff or d_model); K: reduction length.
-constexpr int kPickFew = 1, kPickMany = 2;
-
-// NARROW (down product only): 64-column tiles instead of 256, for steps with so few rows that 256-wide
-// tiles would leave most SMs without work (decode with one or two experts per GPU).
-template <bool SWIGLU, bool NARROW = false>
+template <bool SWIGLU>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                     const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_out, int n_out,
                     int K, const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ poffsets,
-                    int E, int kband, int32_t *dev_err, int pick) {
-    // pick: the down product is launched in both tile widths when the host cannot tell how many rows the step
-    // brought (they arrive from other GPUs); the row count on the device decides which of the two does the work.
-    // 0: always run; kPickFew: run only if 256-wide tiles would fill at most a quarter of the grid; kPickMany:
-    // the complement.  The test is uniform over the grid and comes before any barrier or TMEM allocation.
-    if (pick != 0) {
-        const bool few = (poffsets[E] / kRowAlign) * ((n_out + 255) / 256) * 4 <= (int)gridDim.x;
-        if (few != (pick == kPickFew)) return;
-    }
+                    int E, int kband, int32_t *dev_err) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;  // stages need 1024-byte alignment for the swizzle
@@ -130,10 +118,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
 
     const int num_m_tiles = poffsets[E] / kRowAlign;
-    static_assert(!(SWIGLU && NARROW), "the narrow tile exists for the down product only");
-    constexpr int n_tile_w = SWIGLU ? 128 : (NARROW ? 64 : 256);
-    constexpr uint32_t stage_tx = NARROW ? kABytes + 64 * BLOCK_K * 2 : kStageBytes;
-    constexpr uint32_t idesc = NARROW ? ((1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24)) : kIdesc;
+    const int n_tile_w = SWIGLU ? 128 : 256;
     const int n_tiles = (n_out + n_tile_w - 1) / n_tile_w;
     const int total = num_m_tiles * n_tiles;
     const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
@@ -157,11 +142,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, dev_err)) { ok = false; break; }
                     const uint32_t sa = base + stage * kStageBytes;
-                    mbar_expect_tx(full_bar(stage), stage_tx);
+                    mbar_expect_tx(full_bar(stage), kStageBytes);
                     tma_load_2d(sa, &map_a, full_bar(stage), kb * BLOCK_K, row_a);
-                    tma_load_2d(sa + kABytes, &map_b0, full_bar(stage), kb * BLOCK_K, row_b0);  // NARROW: a 64-row box
-                    if constexpr (!NARROW)
-                        tma_load_2d(sa + kABytes + kBHalfBytes, &map_b1, full_bar(stage), kb * BLOCK_K, row_b1);
+                    tma_load_2d(sa + kABytes, &map_b0, full_bar(stage), kb * BLOCK_K, row_b0);
+                    tma_load_2d(sa + kABytes + kBHalfBytes, &map_b1, full_bar(stage), kb * BLOCK_K, row_b1);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -192,7 +176,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
                         // advance 32 bytes (16 bf16) inside the swizzled row: +2 in 16-byte units
-                        tc_mma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        tc_mma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -215,7 +199,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int r = quarter * 32 + lane;
         const uint32_t out_stage = base + kStages * kStageBytes;
         const uint32_t my_row = out_stage + half * kOutSubBytes + r * 128;
-        constexpr int kPasses = (SWIGLU || NARROW) ? 1 : 2;
+        constexpr int kPasses = SWIGLU ? 1 : 2;
         int as = 0;
         uint32_t aphase = 0;
         int ti = 0;
@@ -251,10 +235,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     } else {
                         uint32_t a[32];
-                        if (!NARROW || half == 0) {  // a narrow tile has 64 accumulator columns: half 1 has none
-                            tc_ld32(t_acc + col, a);
-                            tc_wait_ld();
-                        }
+                        tc_ld32(t_acc + col, a);
+                        tc_wait_ld();
                         if (p == kPasses - 1 && c == 1) {
                             tc_fence_before();
                             __syncwarp();
@@ -280,10 +262,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("bar.sync 1, 256;" ::: "memory");
                 if (warp == 2 && lane == 0) {
-                    const int x0 = tc.nt * n_tile_w + p * 128;
+                    const int x0 = tc.nt * (SWIGLU ? 128 : 256) + p * 128;
                     const int y0 = tc.mt * BLOCK_M;
                     if (x0 < n_out) tma_store_2d(&map_out, out_stage, x0, y0);
-                    if (!NARROW && x0 + 64 < n_out) tma_store_2d(&map_out, out_stage + kOutSubBytes, x0 + 64, y0);
+                    if (x0 + 64 < n_out) tma_store_2d(&map_out, out_stage + kOutSubBytes, x0 + 64, y0);
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
@@ -350,7 +332,7 @@ bool build_tensor_maps(omoe_handle *h) {
               encode_map(fn, &h->maps.b_gate, h->w_gate, El * dff, d) &&
               encode_map(fn, &h->maps.b_up, h->w_up, El * dff, d) &&
               encode_map(fn, &h->maps.b_down, h->w_down, El * d, dff) && encode_map(fn, &h->maps.c_y, h->yp, rows, d) &&
-              encode_map(fn, &h->maps.b_down64, h->w_down, El * d, dff, 64);
+              encode_map(fn, &h->maps.a_x32, h->xp, rows, d, 32) && encode_map(fn, &h->maps.a_h32, h->hbuf, rows, dff, 32);
     if (!ok) snprintf(h->err, sizeof(h->err), "cuTensorMapEncodeTiled failed (d=%d, d_ff=%d)", (int)d, (int)dff);
     h->maps_ready = ok;
     return ok;
@@ -359,16 +341,12 @@ bool build_tensor_maps(omoe_handle *h) {
 cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid, long rows_ub) {
     static int use_pair = getenv("OMOE_PAIR") ? atoi(getenv("OMOE_PAIR")) : 0;
     if (use_pair) return launch_experts_bf16_pair(h, s, n, mid);
-    // OMOE_NARROW: 1 forces the narrow down tiles, 0 forbids them (tests and tuning); unset: decided per step
-    static int narrow_mode = getenv("OMOE_NARROW") ? atoi(getenv("OMOE_NARROW")) : -1;
     static bool attr_done = false;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kSmemBytes);
         if (e != cudaSuccess) return e;
         e = cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(grouped_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
         attr_done = true;
     }
@@ -379,21 +357,19 @@ cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEven
     // With very few row tiles, whole tiles per CTA would leave most SMs (and their share of the memory
     // system) idle: split K over a cluster instead (experts_sm100_splitk.cu).
     long m_tiles_ub = -1;
-    int s_up = 1, s_dn = 1;
     if (rows_ub >= 0) {
         // most tiles any placement of rows_ub rows on e_local experts can give
         const long act = rows_ub < h->e_local ? rows_ub : h->e_local;
         m_tiles_ub = act + (rows_ub - act) / kRowAlign;
-        s_up = splitk_ways(m_tiles_ub * ((dff + 127) / 128), (d + BLOCK_K - 1) / BLOCK_K, h->sm_count);
-        s_dn = splitk_ways(m_tiles_ub * ((d + 255) / 256), (dff + BLOCK_K - 1) / BLOCK_K, h->sm_count);
     }
+    const int s_up = splitk_ways_up_gate(h, m_tiles_ub), s_dn = splitk_ways_down(h, m_tiles_ub);
     cudaError_t e;
     if (s_up > 1) {
         e = launch_up_gate_splitk(h, s, s_up);
     } else {
         grouped_gemm_kernel<true><<<grid, block, kSmemBytes, s>>>(
             h->maps.a_x, h->maps.b_gate, h->maps.b_up, h->maps.a_h, dff, d,
-            h->ex_tile_expert, h->ex_poffsets, h->e_local, band_up, h->dev_err, 0);
+            h->ex_tile_expert, h->ex_poffsets, h->e_local, band_up, h->dev_err);
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) return e;
@@ -404,21 +380,9 @@ cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEven
         if (e == cudaSuccess) (*n)++;
         return e;
     }
-    // Can the step be small enough for narrow tiles?
-    const bool maybe_few = narrow_mode == 1 || (narrow_mode < 0 && rows_ub >= 0 && m_tiles_ub * ((d + 255) / 256) <= 4L * h->sm_count);
-    if (maybe_few) {
-        grouped_gemm_kernel<false, true><<<grid, block, kSmemBytes, s>>>(
-            h->maps.a_h, h->maps.b_down64, h->maps.b_down64, h->maps.c_y, d, dff,
-            h->ex_tile_expert, h->ex_poffsets, h->e_local, band_dn, h->dev_err, narrow_mode == 1 ? 0 : kPickFew);
-        e = cudaGetLastError();
-        if (e != cudaSuccess) return e;
-        (*n)++;
-    }
-    if (narrow_mode != 1) {
-        grouped_gemm_kernel<false><<<grid, block, kSmemBytes, s>>>(
-            h->maps.a_h, h->maps.b_down, h->maps.b_down, h->maps.c_y, d, dff,
-            h->ex_tile_expert, h->ex_poffsets, h->e_local, band_dn, h->dev_err, maybe_few ? kPickMany : 0);
-    }
+    grouped_gemm_kernel<false><<<grid, block, kSmemBytes, s>>>(
+        h->maps.a_h, h->maps.b_down, h->maps.b_down, h->maps.c_y, d, dff,
+        h->ex_tile_expert, h->ex_poffsets, h->e_local, band_dn, h->dev_err);
     e = cudaGetLastError();
     if (e == cudaSuccess) (*n)++;
     return e;

@@ -70,9 +70,13 @@ __device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank)
 // SWIGLU = true : B0 = W_gate, B1 = W_up; tile nt gives output columns [128 nt, 128 nt + 128) of h
 // SWIGLU = false: B0 = B1 = W_down;      tile nt gives output columns [256 nt, 256 nt + 256) of yp
 // out: [rows, n_out] bf16; counts/poffsets: rows and first (128-aligned) row of each local expert.
+// map_a32: the same rows as map_a with a 32-row box.  A tile with at most 32 tokens fetches only those rows
+// (an SM takes in about 64 bytes a clock, and 96 padding rows would be a quarter of the stage); the other
+// rows of the shared-memory tile keep stale bytes, whose accumulator rows nobody reads.
 template <bool SWIGLU>
 __global__ void __launch_bounds__(kThreadsK, 1)
-grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
+grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a32,
+                           const __grid_constant__ CUtensorMap map_b0,
                            const __grid_constant__ CUtensorMap map_b1, __nv_bfloat16 *__restrict__ out, int n_out,
                            int K, const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ poffsets,
                            const int32_t *__restrict__ counts, int E, int32_t *dev_err) {
@@ -143,8 +147,13 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
                 for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, dev_err)) { ok = false; break; }
                     const uint32_t sa = base + stage * kStageBytesK;
-                    mbar_expect_tx(full_bar(stage), kStageBytesK);
-                    tma_load_2d(sa, &map_a, full_bar(stage), kb * BLOCK_K, row_a);
+                    if (m_valid <= 32) {
+                        mbar_expect_tx(full_bar(stage), kStageBytesK - kABytesK + 32 * BLOCK_K * 2);
+                        tma_load_2d(sa, &map_a32, full_bar(stage), kb * BLOCK_K, row_a);
+                    } else {
+                        mbar_expect_tx(full_bar(stage), kStageBytesK);
+                        tma_load_2d(sa, &map_a, full_bar(stage), kb * BLOCK_K, row_a);
+                    }
                     tma_load_2d(sa + kABytesK, &map_b0, full_bar(stage), kb * BLOCK_K, row_b0);
                     tma_load_2d(sa + kABytesK + kBHalfBytesK, &map_b1, full_bar(stage), kb * BLOCK_K, row_b1);
                     if (++stage == kStagesK) { stage = 0; phase ^= 1u; }
@@ -238,8 +247,7 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
 }
 
 template <bool SWIGLU>
-cudaError_t launch_splitk(omoe_handle *h, cudaStream_t s, int S, const CUtensorMap &a, const CUtensorMap &b0,
-                          const CUtensorMap &b1, void *out, int n_out, int K) {
+cudaError_t prepare_splitk(omoe_handle *h, int S, cudaLaunchConfig_t *cfg, cudaLaunchAttribute *at, int *clusters) {
     auto kern = grouped_gemm_splitk_kernel<SWIGLU>;
     static bool attr_done = false;  // one flag per instantiation
     if (!attr_done) {
@@ -247,54 +255,86 @@ cudaError_t launch_splitk(omoe_handle *h, cudaStream_t s, int S, const CUtensorM
         if (e != cudaSuccess) return e;
         attr_done = true;
     }
-    cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = S;
-    at[0].val.clusterDim.y = 1;
-    at[0].val.clusterDim.z = 1;
-    cfg.blockDim = dim3(kThreadsK);
-    cfg.dynamicSmemBytes = kSmemBytesK;
-    cfg.stream = s;
-    cfg.attrs = at;
-    cfg.numAttrs = 1;
+    *cfg = cudaLaunchConfig_t{};
+    at->id = cudaLaunchAttributeClusterDimension;
+    at->val.clusterDim.x = S;
+    at->val.clusterDim.y = 1;
+    at->val.clusterDim.z = 1;
+    cfg->blockDim = dim3(kThreadsK);
+    cfg->dynamicSmemBytes = kSmemBytesK;
+    cfg->attrs = at;
+    cfg->numAttrs = 1;
     // as many clusters as can be resident at once (a cluster lives inside one GPC)
     static int max_clusters[9] = {0};
     if (max_clusters[S] == 0) {
-        cfg.gridDim = dim3(h->sm_count / S * S);
+        cfg->gridDim = dim3(h->sm_count / S * S);
         int n = 0;
-        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, cfg);
         if (e != cudaSuccess) return e;
         if (n < 1) return cudaErrorInvalidConfiguration;
         max_clusters[S] = n < h->sm_count / S ? n : h->sm_count / S;
     }
-    cfg.gridDim = dim3(max_clusters[S] * S);
-    return cudaLaunchKernelEx(&cfg, kern, a, b0, b1, static_cast<__nv_bfloat16 *>(out), n_out, K,
-                              (const int32_t *)h->ex_tile_expert, (const int32_t *)h->ex_poffsets,
-                              (const int32_t *)h->ex_counts, h->e_local, h->dev_err);
+    *clusters = max_clusters[S];
+    cfg->gridDim = dim3(max_clusters[S] * S);
+    return cudaSuccess;
+}
+
+template <bool SWIGLU>
+cudaError_t launch_splitk(omoe_handle *h, cudaStream_t s, int S, const CUtensorMap &a, const CUtensorMap &a32,
+                          const CUtensorMap &b0, const CUtensorMap &b1, void *out, int n_out, int K) {
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute at;
+    int clusters = 0;
+    cudaError_t e = prepare_splitk<SWIGLU>(h, S, &cfg, &at, &clusters);
+    if (e != cudaSuccess) return e;
+    cfg.stream = s;
+    return cudaLaunchKernelEx(&cfg, grouped_gemm_splitk_kernel<SWIGLU>, a, a32, b0, b1,
+                              static_cast<__nv_bfloat16 *>(out), n_out, K, (const int32_t *)h->ex_tile_expert,
+                              (const int32_t *)h->ex_poffsets, (const int32_t *)h->ex_counts, h->e_local, h->dev_err);
+}
+
+// Number of CTAs to share one tile of a product with `tiles_ub` tiles at most and `num_kb` blocks of K:
+// the largest power of two (at most 8, the portable cluster size) for which all tiles are in flight at once
+// (one tile per resident cluster) and every CTA still gets a few blocks.  1: do not split.
+template <bool SWIGLU>
+int splitk_ways(omoe_handle *h, long tiles_ub, int num_kb) {
+    static int forced = getenv("OMOE_SPLITK") ? atoi(getenv("OMOE_SPLITK")) : -1;  // tests and tuning: 0/1 off, 2, 4, 8
+    if (forced >= 0) return forced == 2 || forced == 4 || forced == 8 ? forced : 1;
+    if (tiles_ub < 0 || tiles_ub * 2 > h->sm_count) return 1;
+    for (int S = 8; S >= 2; S /= 2) {
+        if (num_kb < 8 * S) continue;
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute at;
+        int clusters = 0;
+        if (prepare_splitk<SWIGLU>(h, S, &cfg, &at, &clusters) != cudaSuccess) {
+            cudaGetLastError();
+            continue;
+        }
+        if (tiles_ub <= clusters) return S;
+    }
+    return 1;
 }
 
 }  // namespace
 
-// Number of CTAs to share one tile of a product with `tiles_ub` tiles at most and `num_kb` blocks of K:
-// the largest power of two (at most 8, the portable cluster size) that still leaves every CTA a few blocks
-// and does not ask for more CTAs than the GPU has SMs.  1: do not split.
-int splitk_ways(long tiles_ub, int num_kb, int sm_count) {
-    static int forced = getenv("OMOE_SPLITK") ? atoi(getenv("OMOE_SPLITK")) : -1;  // tests and tuning: 0/1 off, 2, 4, 8
-    if (forced >= 0) return forced == 2 || forced == 4 || forced == 8 ? forced : 1;
-    int s = 1;
-    while (s < 8 && tiles_ub * (s * 2) <= sm_count && num_kb >= 8 * (s * 2)) s *= 2;
-    return s;
+int splitk_ways_up_gate(omoe_handle *h, long m_tiles_ub) {
+    return splitk_ways<true>(h, m_tiles_ub < 0 ? -1 : m_tiles_ub * ((h->cfg.d_ff + 127) / 128),
+                             (h->cfg.d_model + BLOCK_K - 1) / BLOCK_K);
+}
+
+int splitk_ways_down(omoe_handle *h, long m_tiles_ub) {
+    return splitk_ways<false>(h, m_tiles_ub < 0 ? -1 : m_tiles_ub * ((h->cfg.d_model + 255) / 256),
+                              (h->cfg.d_ff + BLOCK_K - 1) / BLOCK_K);
 }
 
 cudaError_t launch_up_gate_splitk(omoe_handle *h, cudaStream_t s, int S) {
-    return launch_splitk<true>(h, s, S, h->maps.a_x, h->maps.b_gate, h->maps.b_up, h->hbuf, h->cfg.d_ff,
-                               h->cfg.d_model);
+    return launch_splitk<true>(h, s, S, h->maps.a_x, h->maps.a_x32, h->maps.b_gate, h->maps.b_up, h->hbuf,
+                               h->cfg.d_ff, h->cfg.d_model);
 }
 
 cudaError_t launch_down_splitk(omoe_handle *h, cudaStream_t s, int S) {
-    return launch_splitk<false>(h, s, S, h->maps.a_h, h->maps.b_down, h->maps.b_down, h->yp, h->cfg.d_model,
-                                h->cfg.d_ff);
+    return launch_splitk<false>(h, s, S, h->maps.a_h, h->maps.a_h32, h->maps.b_down, h->maps.b_down, h->yp,
+                                h->cfg.d_model, h->cfg.d_ff);
 }
 
 }  // namespace omoe

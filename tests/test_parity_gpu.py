@@ -332,12 +332,11 @@ def test_cta_pair_kernels_in_a_subprocess():
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
 
 
-@pytest.mark.parametrize("knob", ["OMOE_NARROW=0", "OMOE_NARROW=1", "OMOE_SPLITK=2", "OMOE_SPLITK=8"])
+@pytest.mark.parametrize("knob", ["OMOE_SPLITK=0", "OMOE_SPLITK=2", "OMOE_SPLITK=4", "OMOE_SPLITK=8"])
 def test_few_row_variants_forced_in_a_subprocess(knob):
-    """Steps with few row tiles switch the expert products to other kernels: 64-column tiles for the down
-    product (picked by the row count on the device) or K split over a cluster of 2/4/8 CTAs (picked from the
-    host's bound on the rows).  The knobs, read once per process, force one choice for every step: small,
-    skewed and odd-shaped cases must pass with each."""
+    """Steps with few row tiles run the expert products with K split over a cluster of 2, 4 or 8 CTAs (picked
+    from the host's bound on the step's rows).  The knob, read once per process, forces one choice for every
+    step: small, skewed and odd-shaped cases must pass with each, and with the split switched off."""
     import os
     import subprocess
     import sys
