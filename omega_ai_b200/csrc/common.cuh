@@ -139,7 +139,8 @@ cudaError_t launch_experts_f32(omoe_handle *h, cudaStream_t s, int *n);
 // bound sends a product with few tiles to the split-K kernels
 cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid, long rows_ub = -1);
 // The same two products on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles per pair).
-// split-K over a thread-block cluster of S CTAs (experts_sm100_splitk.cu); splitk_ways() picks S, 1 = do not split
+// split-K over a thread-block cluster of S CTAs (experts_sm100_splitk.cu); splitk_ways_*() pick S, 0 = use the
+// persistent kernels of experts_sm100.cu
 // m_tiles_ub: bound on the step's 128-row tiles, -1 if unknown
 int splitk_ways_up_gate(omoe_handle *h, long m_tiles_ub);
 int splitk_ways_down(omoe_handle *h, long m_tiles_ub);

@@ -364,7 +364,7 @@ cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEven
     }
     const int s_up = splitk_ways_up_gate(h, m_tiles_ub), s_dn = splitk_ways_down(h, m_tiles_ub);
     cudaError_t e;
-    if (s_up > 1) {
+    if (s_up > 0) {
         e = launch_up_gate_splitk(h, s, s_up);
     } else {
         grouped_gemm_kernel<true><<<grid, block, kSmemBytes, s>>>(
@@ -375,7 +375,7 @@ cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEven
     if (e != cudaSuccess) return e;
     (*n)++;
     if (mid) cudaEventRecord(mid, s);
-    if (s_dn > 1) {
+    if (s_dn > 0) {
         e = launch_down_splitk(h, s, s_dn);
         if (e == cudaSuccess) (*n)++;
         return e;

@@ -23,13 +23,21 @@ namespace omoe {
 namespace {
 
 using namespace sm100;
-constexpr int kStagesK = 4;
-constexpr int kABytesK = BLOCK_M * BLOCK_K * 2;            // 16 KB
+// Two shapes of the ring.  A step in which no expert holds more than 32 tokens (the case this kernel is for)
+// fetches 32 rows of A per stage and fits six stages; the copies in flight are what hides the memory latency
+// when only a fraction of the SMs pulls on HBM.  Otherwise four stages with all 128 rows, as in experts_sm100.cu.
 constexpr int kBHalfBytesK = 128 * BLOCK_K * 2;            // 16 KB (one 128-row TMA box)
-constexpr int kStageBytesK = kABytesK + 2 * kBHalfBytesK;  // 48 KB
+constexpr int kABytesBig = BLOCK_M * BLOCK_K * 2;          // 16 KB
+constexpr int kABytesSmall = 32 * BLOCK_K * 2;             // 4 KB
+constexpr int kStagesBig = 4, kStagesSmall = 6, kStagesMax = 6;
+constexpr int kStageBytesBig = kABytesBig + 2 * kBHalfBytesK;      // 48 KB
+constexpr int kStageBytesSmall = kABytesSmall + 2 * kBHalfBytesK;  // 36 KB
+constexpr int kRingBytes = kStagesSmall * kStageBytesSmall;        // 216 KB
+static_assert(kRingBytes >= kStagesBig * kStageBytesBig, "both shapes fit the ring");
 constexpr int kPartialBytes = BLOCK_N * BLOCK_M * 4;       // 128 KB, laid over the ring
-static_assert(kPartialBytes <= kStagesK * kStageBytesK, "the partial tile reuses the ring");
-constexpr int kSmemBytesK = kStagesK * kStageBytesK + 1024 /*align slack*/ + 256 /*barriers*/;
+static_assert(kPartialBytes <= kRingBytes, "the partial tile reuses the ring");
+constexpr int kSmemBytesK = kRingBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+static_assert(kSmemBytesK <= 227 * 1024, "shared memory of one CTA");
 constexpr int kThreadsK = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 epilogue and reduction
 constexpr int kTmemColsK = 256;
 
@@ -70,9 +78,9 @@ __device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank)
 // SWIGLU = true : B0 = W_gate, B1 = W_up; tile nt gives output columns [128 nt, 128 nt + 128) of h
 // SWIGLU = false: B0 = B1 = W_down;      tile nt gives output columns [256 nt, 256 nt + 256) of yp
 // out: [rows, n_out] bf16; counts/poffsets: rows and first (128-aligned) row of each local expert.
-// map_a32: the same rows as map_a with a 32-row box.  A tile with at most 32 tokens fetches only those rows
-// (an SM takes in about 64 bytes a clock, and 96 padding rows would be a quarter of the stage); the other
-// rows of the shared-memory tile keep stale bytes, whose accumulator rows nobody reads.
+// map_a32: the same rows as map_a with a 32-row box, for steps in which no expert holds more than 32 tokens:
+// the MMA still multiplies 128 rows, but rows 32.. are whatever follows in shared memory (the weight tile),
+// and nobody reads their accumulator rows.
 template <bool SWIGLU>
 __global__ void __launch_bounds__(kThreadsK, 1)
 grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a32,
@@ -84,13 +92,14 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;  // stages need 1024-byte alignment for the swizzle
     unsigned char *base_ptr = smem_raw + (base - raw);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(base_ptr + kStagesK * kStageBytesK);
-    const uint32_t bar0 = base + kStagesK * kStageBytesK;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(base_ptr + kRingBytes);
+    const uint32_t bar0 = base + kRingBytes;
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
-    auto empty_bar = [&](int s) { return bar0 + 8u * (kStagesK + s); };
-    const uint32_t tfull_bar = bar0 + 8u * (2 * kStagesK);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStagesK + 1);
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kStagesMax + s); };
+    const uint32_t tfull_bar = bar0 + 8u * (2 * kStagesMax);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStagesMax + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    volatile int *small_flag = abort_flag + 1;
     float *partial = reinterpret_cast<float *>(base_ptr);  // [256 accumulator columns][128 rows]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -98,13 +107,19 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     const int cid = (int)sreg_clusterid(), ncl = (int)sreg_nclusterid();
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStagesK; s++) {
+        for (int s = 0; s < kStagesMax; s++) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
         mbar_init(tfull_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {  // does any expert hold more than 32 tokens?
+        int mx = 0;
+        for (int e = lane; e < E; e += 32) mx = max(mx, counts[e]);
+        mx = __reduce_max_sync(0xffffffffu, mx);
+        if (lane == 0) *small_flag = mx <= 32;
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
@@ -116,6 +131,10 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const bool small = *small_flag != 0;
+    const int n_stages = small ? kStagesSmall : kStagesBig;
+    const uint32_t stage_bytes = small ? kStageBytesSmall : kStageBytesBig;
+    const uint32_t a_bytes = small ? kABytesSmall : kABytesBig;
 
     const int num_m_tiles = poffsets[E] / kRowAlign;
     constexpr int n_tile_w = SWIGLU ? 128 : 256;
@@ -146,17 +165,13 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
                 const int row_b1 = SWIGLU ? row_b0 : row_b0 + 128;
                 for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, dev_err)) { ok = false; break; }
-                    const uint32_t sa = base + stage * kStageBytesK;
-                    if (m_valid <= 32) {
-                        mbar_expect_tx(full_bar(stage), kStageBytesK - kABytesK + 32 * BLOCK_K * 2);
-                        tma_load_2d(sa, &map_a32, full_bar(stage), kb * BLOCK_K, row_a);
-                    } else {
-                        mbar_expect_tx(full_bar(stage), kStageBytesK);
-                        tma_load_2d(sa, &map_a, full_bar(stage), kb * BLOCK_K, row_a);
-                    }
-                    tma_load_2d(sa + kABytesK, &map_b0, full_bar(stage), kb * BLOCK_K, row_b0);
-                    tma_load_2d(sa + kABytesK + kBHalfBytesK, &map_b1, full_bar(stage), kb * BLOCK_K, row_b1);
-                    if (++stage == kStagesK) { stage = 0; phase ^= 1u; }
+                    const uint32_t sa = base + stage * stage_bytes;
+                    mbar_expect_tx(full_bar(stage), stage_bytes);
+                    if (small) tma_load_2d(sa, &map_a32, full_bar(stage), kb * BLOCK_K, row_a);
+                    else tma_load_2d(sa, &map_a, full_bar(stage), kb * BLOCK_K, row_a);
+                    tma_load_2d(sa + a_bytes, &map_b0, full_bar(stage), kb * BLOCK_K, row_b0);
+                    tma_load_2d(sa + a_bytes + kBHalfBytesK, &map_b1, full_bar(stage), kb * BLOCK_K, row_b1);
+                    if (++stage == n_stages) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) {
                     // let copies that were already issued land before anything else happens to the ring
@@ -170,14 +185,14 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
                 for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag, dev_err)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t sa = base + stage * kStageBytesK;
-                    const uint64_t adesc = make_sw128_desc(sa);
-                    const uint64_t bdesc = make_sw128_desc(sa + kABytesK);
+                    const uint32_t sa = base + stage * stage_bytes;
+                    const uint64_t adesc = make_sw128_desc(sa);  // small: rows 32.. of the tile alias the B rows
+                    const uint64_t bdesc = make_sw128_desc(sa + a_bytes);
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; k++)
                         tc_mma_bf16(tmem_base, adesc + 2u * k, bdesc + 2u * k, kIdesc, (kb > kb0 || k != 0) ? 1u : 0u);
                     tc_commit(empty_bar(stage));
-                    if (++stage == kStagesK) { stage = 0; phase ^= 1u; }
+                    if (++stage == n_stages) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) tc_commit(tfull_bar);  // accumulator complete, and every stage of the ring has been read
             }
@@ -294,15 +309,16 @@ cudaError_t launch_splitk(omoe_handle *h, cudaStream_t s, int S, const CUtensorM
 }
 
 // Number of CTAs to share one tile of a product with `tiles_ub` tiles at most and `num_kb` blocks of K:
-// the largest power of two (at most 8, the portable cluster size) for which all tiles are in flight at once
-// (one tile per resident cluster) and every CTA still gets a few blocks.  1: do not split.
+// the largest of 8 (the portable cluster size), 4, 2, 1 for which all tiles are in flight at once (one tile
+// per resident cluster) and every CTA still gets a few blocks.  With 1 the tile is not split, but the step
+// still gains the deeper ring.  0: too many tiles for this kernel, use the persistent one.
 template <bool SWIGLU>
 int splitk_ways(omoe_handle *h, long tiles_ub, int num_kb) {
-    static int forced = getenv("OMOE_SPLITK") ? atoi(getenv("OMOE_SPLITK")) : -1;  // tests and tuning: 0/1 off, 2, 4, 8
-    if (forced >= 0) return forced == 2 || forced == 4 || forced == 8 ? forced : 1;
-    if (tiles_ub < 0 || tiles_ub * 2 > h->sm_count) return 1;
-    for (int S = 8; S >= 2; S /= 2) {
-        if (num_kb < 8 * S) continue;
+    static int forced = getenv("OMOE_SPLITK") ? atoi(getenv("OMOE_SPLITK")) : -1;  // tests and tuning: 0, 1, 2, 4, 8
+    if (forced >= 0) return forced == 1 || forced == 2 || forced == 4 || forced == 8 ? forced : 0;
+    if (tiles_ub < 0 || tiles_ub > h->sm_count) return 0;
+    for (int S = 8; S >= 1; S /= 2) {
+        if (S > 1 && num_kb < 8 * S) continue;
         cudaLaunchConfig_t cfg;
         cudaLaunchAttribute at;
         int clusters = 0;
@@ -312,7 +328,7 @@ int splitk_ways(omoe_handle *h, long tiles_ub, int num_kb) {
         }
         if (tiles_ub <= clusters) return S;
     }
-    return 1;
+    return 0;
 }
 
 }  // namespace

@@ -332,9 +332,9 @@ def test_cta_pair_kernels_in_a_subprocess():
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
 
 
-@pytest.mark.parametrize("knob", ["OMOE_SPLITK=0", "OMOE_SPLITK=2", "OMOE_SPLITK=4", "OMOE_SPLITK=8"])
+@pytest.mark.parametrize("knob", ["OMOE_SPLITK=0", "OMOE_SPLITK=1", "OMOE_SPLITK=2", "OMOE_SPLITK=4", "OMOE_SPLITK=8"])
 def test_few_row_variants_forced_in_a_subprocess(knob):
-    """Steps with few row tiles run the expert products with K split over a cluster of 2, 4 or 8 CTAs (picked
+    """Steps with few row tiles run the expert products with K split over a cluster of 1, 2, 4 or 8 CTAs (picked
     from the host's bound on the step's rows).  The knob, read once per process, forces one choice for every
     step: small, skewed and odd-shaped cases must pass with each, and with the split switched off."""
     import os
