@@ -312,7 +312,10 @@ def run_ours(args, cfg):
         n_active = max(int((counts_all[r * El:(r + 1) * El] > 0).sum()) for r in range(world))
         wbytes = n_active * 3.0 * d * dff * 2
         dur = (stage_ms["up_gate"] + stage_ms["down"]) * 1e-3
-        roof = {"bound": "hbm", "kernel": "grouped_gemm_kernel (up/gate + down)",
+        # which kernels ran depends on the step: the streaming kernels for one or two tokens, the split-K cluster
+        # kernels while a product's tiles fit one round of resident clusters, else the persistent kernels
+        roof = {"bound": "hbm", "kernel": "expert products (up/gate + down): decode_gemv / grouped_gemm_splitk / "
+                                          "grouped_gemm kernels, picked per step",
                 "achieved": wbytes / dur / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
                 "frac": wbytes / dur / 1e9 / peaks["hbm"], "traffic": None, "peak_source": peaks["src"],
                 "active_experts": n_active, "weight_bytes": wbytes,
