@@ -1,10 +1,12 @@
 /*
  * moe_ref.c — CPU oracle for the mixture-of-experts FFN forward path.
  *
- * TEST INFRASTRUCTURE ONLY (see moe_ref.h).  PARITY UNPINNED: the reference has
- * no MoE layer and no golden vectors for this path; each function below cites
- * the reference primitive whose arithmetic it restates, and the routing rules
- * that have no reference counterpart are stated where they are implemented.
+ * TEST INFRASTRUCTURE ONLY (see moe_ref.h).  The reference has no MoE layer and
+ * no golden vectors for this path; each function below cites the reference
+ * primitive whose arithmetic it restates.  Those restatements are pinned to the
+ * reference's own kernels, compiled into oracle/_ref and run on a GPU by
+ * tests/test_reference_kernels_gpu.py.  The routing rules that have no reference
+ * counterpart are stated where they are implemented: PARITY UNPINNED for them.
  *
  * Build with -ffp-contract=off: the reference's host code is Java, which never
  * fuses a multiply and an add, so every `a*b + c` here must stay two roundings.

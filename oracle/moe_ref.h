@@ -5,13 +5,21 @@
  * calls this code; it exists so tests and the benchmark's CPU-baseline leg can
  * check the CUDA path against a plain-C restatement of the arithmetic.
  *
- * PARITY UNPINNED: the reference engine (dromara/Omega-AI) has no
- * mixture-of-experts layer, router, top-k or permutation code and ships no
- * golden vectors for the dense pieces either, so this oracle is assembled from
- * the reference's dense primitives (cited per function in moe_ref.c) plus
- * routing/permutation/combine rules fixed by this project.  The only reference
- * values it can be pinned to are the SiLU demo inputs and the all-ones GEMM
- * check (see ref_silu / ref_linear_nt).
+ * PARITY: the reference engine (dromara/Omega-AI) has no mixture-of-experts
+ * layer, router, top-k or permutation code and ships no golden vectors, so
+ * this oracle is assembled from the reference's dense primitives (cited per
+ * function in moe_ref.c) plus routing/permutation/combine rules fixed by this
+ * project.
+ *   - Pinned to the reference itself: softmax, SiLU, the element-wise product,
+ *     RMSNorm, the X*W^T product and the dense SwiGLU sequence.  The reference's
+ *     own CUDA kernels for these are compiled from its source files into
+ *     oracle/_ref (Makefile target ref_kernels) and run beside cuBLAS SGEMM by
+ *     refk_driver.cu; tests/test_reference_kernels_gpu.py holds this oracle
+ *     (and the product) against their outputs.  Also pinned: the SiLU demo
+ *     inputs and the all-ones GEMM check found in the reference's sources.
+ *   - PARITY UNPINNED for what the reference does not have: the router's
+ *     reduction order, top-k and tie rule, gate renormalisation, permutation
+ *     and combine are defined here and have nothing to be pinned to.
  */
 #ifndef OMOE_ORACLE_MOE_REF_H
 #define OMOE_ORACLE_MOE_REF_H

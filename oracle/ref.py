@@ -1,9 +1,10 @@
 """ctypes front end of the CPU oracle (``oracle/moe_ref.c``).
 
 TEST INFRASTRUCTURE ONLY: imported by the tests, by the smoke check and by the
-benchmark's CPU-baseline leg, never by the product package.  PARITY UNPINNED —
-see the header of ``moe_ref.h`` for why (the reference has no MoE layer and no
-golden vectors for this path).
+benchmark's CPU-baseline leg, never by the product package.  Parity: the stages
+the reference has (softmax, SiLU, product, RMSNorm, X*W^T, the dense SwiGLU
+sequence) are pinned to the reference's own kernels (``oracle/refk.py``); PARITY
+UNPINNED for the routing rules the reference lacks — see the header of ``moe_ref.h``.
 """
 from __future__ import annotations
 
