@@ -424,3 +424,191 @@ void ref_moe_forward(const ref_moe_shape *s,
     omp_set_num_threads(saved);
 #endif
 }
+
+/* ---- backward of the whole layer ---------------------------------------- */
+
+/* C[M,N] = sum_p A(m,p) * B(p,n); element (i,j) of A is A[i*sa0 + j*sa1], of B
+ * B[i*sb0 + j*sb1].  One chain per output, p ascending, every product rounded
+ * on its own: the order of the engine's host SGEMM
+ * (src/main/java/com/omega/engine/cpu/SimplePerfCpuBlasBatchSgemmJdk8.java:106-131). */
+static void gemm_strided(const float *A, int64_t sa0, int64_t sa1, const float *B, int64_t sb0, int64_t sb1,
+                         float *C, int64_t M, int64_t N, int64_t K) {
+#pragma omp parallel for schedule(static)
+    for (int64_t m = 0; m < M; m++)
+        for (int64_t n = 0; n < N; n++) {
+            float acc = 0.0f;
+            for (int64_t p = 0; p < K; p++) acc += A[m * sa0 + p * sa1] * B[p * sb0 + n * sb1];
+            C[m * N + n] = acc;
+        }
+}
+
+static void round_if(float *v, int64_t n, int bf16) {
+    if (bf16) ref_bf16_round_array(v, n);
+}
+
+/* d SiLU / dx as the reference's silu_backward computes it
+ * (src/main/resources/cu/activeFunction.cu:182-190): s = 1/(1+exp(-x)), s*(1 + x*(1-s)). */
+static inline float silu_grad1(float x) {
+    float sg = 1.0f / (1.0f + expf(-x));
+    return sg * (1.0f + x * (1.0f - sg));
+}
+
+void ref_silu_backward(const float *x, const float *delta, float *diff, int64_t n) {
+    for (int64_t i = 0; i < n; i++) diff[i] = delta[i] * silu_grad1(x[i]);
+}
+
+/* Softmax backward, row by row, as the reference's softmax_back
+ * (src/main/resources/cu/SoftmaxKernel.cu:100-112): sum = sum_i out_i*delta_i in
+ * index order, diff_i = (delta_i - sum) * out_i. */
+void ref_softmax_back_rows(const float *out, const float *delta, float *diff, int64_t rows, int64_t n) {
+    for (int64_t r = 0; r < rows; r++) {
+        float sum = 0.0f;
+        for (int64_t i = 0; i < n; i++) sum += out[r * n + i] * delta[r * n + i];
+        for (int64_t i = 0; i < n; i++) diff[r * n + i] = (delta[r * n + i] - sum) * out[r * n + i];
+    }
+}
+
+/* Gradients of y = MoE(x) for a given dy.  The chain follows the reference's dense layers:
+ *   LlamaMLPLayer.diff() (src/main/java/com/omega/engine/nn/layer/llama/LlamaMLPLayer.java:139-158):
+ *     linear2.back(delta); d_up = d_h * silu(g); d_gate = silu_backward(g, d_h * u);
+ *     diff = linear1.diff + linear3.diff
+ *   FullyLayer.diff() (src/main/java/com/omega/engine/nn/layer/FullyLayer.java:292-334):
+ *     diffW = delta^T * input (overwritten, not accumulated), diff = delta * W, diffB = column sums of delta
+ *   softmax_back (SoftmaxKernel.cu:100-112) for the router probabilities.
+ * Rules with no reference counterpart: the picks are constants (no gradient through the selection);
+ * with renormalised gates w_j = p_j / s, s = sum of the picked p, d p_j = (d w_j - sum_i d w_i w_i) / s;
+ * d w_j = <dy[t], yp_j>; dx[t] = ((dxp_0 + dxp_1) + ...) in pick order, then the router's term
+ * (sum over experts in index order, one chain) added last.  No auxiliary load-balancing loss.
+ * bf16 mode rounds where the tensor-core path stores bf16: xp, g, u, h, yp, dyp, dh, dg, du, dxp
+ * (weight gradients and everything on the router's side stay fp32); dx is rounded when out_bf16. */
+void ref_moe_backward(const ref_moe_shape *s, const float *x, const float *w_r, const float *bias,
+                      const float *w_gate, const float *w_up, const float *w_down, const float *dy,
+                      float *dx, float *d_w_r, float *d_bias, float *d_w_gate, float *d_w_up, float *d_w_down,
+                      int nthreads) {
+    const int64_t T = s->T, d = s->d, dff = s->dff, E = s->E, k = s->k;
+    const int bf = s->bf16;
+#ifdef _OPENMP
+    int saved = omp_get_max_threads();
+    if (nthreads > 0) omp_set_num_threads(nthreads);
+#else
+    (void)nthreads;
+#endif
+    float *logits = (float *)malloc(sizeof(float) * (size_t)(T * E));
+    float *probs = (float *)malloc(sizeof(float) * (size_t)(T * E));
+    int32_t *idx = (int32_t *)malloc(sizeof(int32_t) * (size_t)(T * k));
+    float *gw = (float *)malloc(sizeof(float) * (size_t)(T * k));
+    int32_t *counts = (int32_t *)malloc(sizeof(int32_t) * (size_t)E);
+    int32_t *offsets = (int32_t *)malloc(sizeof(int32_t) * (size_t)(E + 1));
+    int32_t *perm = (int32_t *)malloc(sizeof(int32_t) * (size_t)(T * k));
+    int32_t *pos = (int32_t *)malloc(sizeof(int32_t) * (size_t)(T * k));
+    ref_router_logits(x, w_r, bias, T, d, E, logits);
+    ref_topk_gate(logits, T, E, k, s->renorm, idx, gw);
+    ref_histogram_permute(idx, T, E, k, counts, offsets, perm, pos);
+    ref_softmax_rows(logits, probs, T, E);
+
+    float *dgw = (float *)malloc(sizeof(float) * (size_t)(T * k));       /* d w[t,j] */
+    float *dxp = (float *)malloc(sizeof(float) * (size_t)(T * k * d + 1));
+    for (int64_t e = 0; e < E; e++) {
+        const int64_t m = counts[e], r0 = offsets[e];
+        float *dWg = d_w_gate + e * dff * d, *dWu = d_w_up + e * dff * d, *dWd = d_w_down + e * d * dff;
+        if (m == 0) { /* diffW = delta^T * input over no rows */
+            memset(dWg, 0, sizeof(float) * (size_t)(dff * d));
+            memset(dWu, 0, sizeof(float) * (size_t)(dff * d));
+            memset(dWd, 0, sizeof(float) * (size_t)(dff * d));
+            continue;
+        }
+        const float *Wg = w_gate + e * dff * d, *Wu = w_up + e * dff * d, *Wd = w_down + e * d * dff;
+        float *Xe = (float *)malloc(sizeof(float) * (size_t)(m * d));
+        float *dYp = (float *)malloc(sizeof(float) * (size_t)(m * d));
+        float *Yp = (float *)malloc(sizeof(float) * (size_t)(m * d));
+        float *G = (float *)malloc(sizeof(float) * (size_t)(m * dff));
+        float *U = (float *)malloc(sizeof(float) * (size_t)(m * dff));
+        float *H = (float *)malloc(sizeof(float) * (size_t)(m * dff));
+        float *dH = (float *)malloc(sizeof(float) * (size_t)(m * dff));
+        float *dG = (float *)malloc(sizeof(float) * (size_t)(m * dff));
+        float *dU = (float *)malloc(sizeof(float) * (size_t)(m * dff));
+        float *t1 = (float *)malloc(sizeof(float) * (size_t)(m * d));
+        for (int64_t r = 0; r < m; r++) {
+            const int64_t f = perm[r0 + r], t = f / k;
+            for (int64_t c = 0; c < d; c++) {
+                Xe[r * d + c] = bf ? ref_bf16_round(x[t * d + c]) : x[t * d + c];
+                dYp[r * d + c] = gw[f] * dy[t * d + c];
+            }
+        }
+        round_if(dYp, m * d, bf);
+        /* forward again, keeping what the backward needs */
+        gemm_strided(Xe, d, 1, Wg, 1, d, G, m, dff, d);
+        gemm_strided(Xe, d, 1, Wu, 1, d, U, m, dff, d);
+        round_if(G, m * dff, bf);
+        round_if(U, m * dff, bf);
+        for (int64_t i = 0; i < m * dff; i++) H[i] = silu1(G[i]) * U[i];
+        round_if(H, m * dff, bf);
+        gemm_strided(H, dff, 1, Wd, 1, dff, Yp, m, d, dff);
+        round_if(Yp, m * d, bf);
+        for (int64_t r = 0; r < m; r++) { /* d w = <dy[t], yp> */
+            const int64_t f = perm[r0 + r], t = f / k;
+            float acc = 0.0f;
+            for (int64_t c = 0; c < d; c++) acc += dy[t * d + c] * Yp[r * d + c];
+            dgw[f] = acc;
+        }
+        /* linear2.back: diffW = delta^T * input, diff = delta * W */
+        gemm_strided(dYp, 1, d, H, dff, 1, dWd, d, dff, m);
+        gemm_strided(dYp, d, 1, Wd, dff, 1, dH, m, dff, d);
+        round_if(dH, m * dff, bf);
+        for (int64_t i = 0; i < m * dff; i++) {
+            dU[i] = dH[i] * silu1(G[i]);
+            dG[i] = (dH[i] * U[i]) * silu_grad1(G[i]);
+        }
+        round_if(dU, m * dff, bf);
+        round_if(dG, m * dff, bf);
+        gemm_strided(dG, 1, dff, Xe, d, 1, dWg, dff, d, m);
+        gemm_strided(dU, 1, dff, Xe, d, 1, dWu, dff, d, m);
+        /* diff = linear1.diff + linear3.diff */
+        gemm_strided(dG, dff, 1, Wg, d, 1, t1, m, d, dff);
+        gemm_strided(dU, dff, 1, Wu, d, 1, dxp + r0 * d, m, d, dff);
+        for (int64_t i = 0; i < m * d; i++) dxp[r0 * d + i] = t1[i] + dxp[r0 * d + i];
+        round_if(dxp + r0 * d, m * d, bf);
+        free(Xe); free(dYp); free(Yp); free(G); free(U); free(H); free(dH); free(dG); free(dU); free(t1);
+    }
+
+    /* router: d w -> d p (picks only) -> d logits (softmax_back) */
+    float *dp = (float *)calloc((size_t)(T * E), sizeof(float));
+    float *dl = (float *)malloc(sizeof(float) * (size_t)(T * E));
+    for (int64_t t = 0; t < T; t++) {
+        if (s->renorm) {
+            float ssum = 0.0f, dot = 0.0f;
+            for (int64_t j = 0; j < k; j++) ssum += probs[t * E + idx[t * k + j]];
+            for (int64_t j = 0; j < k; j++) dot += dgw[t * k + j] * gw[t * k + j];
+            for (int64_t j = 0; j < k; j++) dp[t * E + idx[t * k + j]] = (dgw[t * k + j] - dot) / ssum;
+        } else {
+            for (int64_t j = 0; j < k; j++) dp[t * E + idx[t * k + j]] = dgw[t * k + j];
+        }
+    }
+    ref_softmax_back_rows(probs, dp, dl, T, E);
+    /* router's FullyLayer.diff(): diffW = dl^T * x, diffB = column sums, diff = dl * W_r */
+    gemm_strided(dl, 1, E, x, d, 1, d_w_r, E, d, T);
+    if (d_bias)
+        for (int64_t e = 0; e < E; e++) {
+            float acc = 0.0f;
+            for (int64_t t = 0; t < T; t++) acc += dl[t * E + e];
+            d_bias[e] = acc;
+        }
+#pragma omp parallel for schedule(static)
+    for (int64_t t = 0; t < T; t++)
+        for (int64_t c = 0; c < d; c++) {
+            float acc = 0.0f;
+            for (int64_t j = 0; j < k; j++) {
+                float v = dxp[(int64_t)pos[t * k + j] * d + c];
+                acc = (j == 0) ? v : acc + v;
+            }
+            float r = 0.0f;
+            for (int64_t e = 0; e < E; e++) r += dl[t * E + e] * w_r[e * d + c];
+            acc += r;
+            dx[t * d + c] = s->out_bf16 ? ref_bf16_round(acc) : acc;
+        }
+    free(dp); free(dl); free(dxp); free(dgw);
+    free(logits); free(probs); free(idx); free(gw); free(counts); free(offsets); free(perm); free(pos);
+#ifdef _OPENMP
+    omp_set_num_threads(saved);
+#endif
+}

@@ -94,6 +94,20 @@ void ref_moe_forward(const ref_moe_shape *shape,
                      int32_t *counts, int32_t *offsets, int32_t *perm,
                      const int32_t *sel, int64_t n_sel, float *y, int nthreads);
 
+/* SiLU and softmax backward, element by element / row by row as the reference's kernels
+ * silu_backward (activeFunction.cu:182-190) and softmax_back (SoftmaxKernel.cu:100-112) compute them. */
+void ref_silu_backward(const float *x, const float *delta, float *diff, int64_t n);
+void ref_softmax_back_rows(const float *out, const float *delta, float *diff, int64_t rows, int64_t n);
+
+/* Backward of the whole layer for a given dy [T,d]: dx [T,d], d_w_r [E,d], d_bias [E] (nullable),
+ * d_w_gate/d_w_up [E,dff,d], d_w_down [E,d,dff], all overwritten (the reference's FullyLayer.diff()
+ * overwrites diffW).  Routing is recomputed from x; shape.pretransposed must be 0.  The rules and the
+ * bf16 rounding points are stated at the definition. */
+void ref_moe_backward(const ref_moe_shape *shape, const float *x, const float *w_r, const float *bias,
+                      const float *w_gate, const float *w_up, const float *w_down, const float *dy,
+                      float *dx, float *d_w_r, float *d_bias, float *d_w_gate, float *d_w_up, float *d_w_down,
+                      int nthreads);
+
 int ref_num_threads(void);
 
 #ifdef __cplusplus

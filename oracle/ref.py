@@ -55,6 +55,9 @@ def lib():
         _lib.ref_moe_forward.argtypes = [
             C.POINTER(_Shape), fp, fp, fp, fp, fp, fp, fp, ip, fp, ip, ip, ip, ip, i64, fp, C.c_int,
         ]
+        _lib.ref_silu_backward.argtypes = [fp, fp, fp, i64]
+        _lib.ref_softmax_back_rows.argtypes = [fp, fp, fp, i64, i64]
+        _lib.ref_moe_backward.argtypes = [C.POINTER(_Shape)] + [fp] * 13 + [C.c_int]
         _lib.ref_num_threads.restype = C.c_int
     return _lib
 
@@ -207,3 +210,50 @@ def moe_forward(x, w_r, w_gate, w_up, w_down, k: int, *, bias=None, renorm=True,
                           _f(logits), _i(idx), _f(w), _i(counts), _i(offsets), _i(perm),
                           _i(sel_a), n_sel, _f(y), nthreads)
     return MoEResult(logits, idx, w, counts, offsets, perm, y, sel_a)
+
+
+def silu_backward(x: np.ndarray, delta: np.ndarray) -> np.ndarray:
+    x, delta = _cf(x), _cf(delta)
+    out = np.empty_like(x)
+    lib().ref_silu_backward(_f(x), _f(delta), _f(out), x.size)
+    return out
+
+
+def softmax_back_rows(out: np.ndarray, delta: np.ndarray) -> np.ndarray:
+    out, delta = _cf(out), _cf(delta)
+    diff = np.empty_like(out)
+    lib().ref_softmax_back_rows(_f(out), _f(delta), _f(diff), out.shape[0], out.shape[1])
+    return diff
+
+
+@dataclass
+class MoEGrads:
+    dx: np.ndarray
+    d_w_r: np.ndarray
+    d_bias: np.ndarray
+    d_w_gate: np.ndarray
+    d_w_up: np.ndarray
+    d_w_down: np.ndarray
+
+
+def moe_backward(x, w_r, w_gate, w_up, w_down, k: int, dy, *, bias=None, renorm=True, bf16=False,
+                 out_bf16=None, nthreads: int = 0) -> MoEGrads:
+    """Gradients of the whole layer for ``dy`` [T,d]; same conventions as :func:`moe_forward`."""
+    x, w_r, dy = _cf(x), _cf(w_r), _cf(dy)
+    w_gate, w_up, w_down = _cf(w_gate), _cf(w_up), _cf(w_down)
+    if bf16:
+        w_gate, w_up, w_down = bf16_round(w_gate), bf16_round(w_up), bf16_round(w_down)
+    bias = None if bias is None else _cf(bias)
+    T, d = x.shape
+    E, dff, _ = w_gate.shape
+    assert dy.shape == (T, d) and w_r.shape == (E, d) and w_up.shape == (E, dff, d) and w_down.shape == (E, d, dff)
+    if out_bf16 is None:
+        out_bf16 = bf16
+    shp = _Shape(T, d, dff, E, k, int(renorm), int(bf16), int(out_bf16), 0)
+    g = MoEGrads(np.empty((T, d), np.float32), np.empty((E, d), np.float32), np.empty(E, np.float32),
+                 np.empty((E, dff, d), np.float32), np.empty((E, dff, d), np.float32),
+                 np.empty((E, d, dff), np.float32))
+    lib().ref_moe_backward(C.byref(shp), _f(x), _f(w_r), _f(bias), _f(w_gate), _f(w_up), _f(w_down), _f(dy),
+                           _f(g.dx), _f(g.d_w_r), _f(g.d_bias), _f(g.d_w_gate), _f(g.d_w_up), _f(g.d_w_down),
+                           nthreads)
+    return g
