@@ -142,6 +142,39 @@ OMOE_API int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host,
                       int32_t io_dtype, void *cuda_stream);
 
 /*
+ * Training mode and the backward pass (one GPU, world == 1).
+ *
+ * omoe_set_training(h, 1) allocates the buffers of the backward pass (first call only) and makes every
+ * following omoe_forward / omoe_forward_block keep what the backward needs: the pre-activation rows of
+ * the gate and up products, h, the expert outputs and the routing.  The reference's layers keep the same
+ * things as the output tensors of linear1, the SiLU layer and linear3
+ * (src/main/java/com/omega/engine/nn/layer/llama/LlamaMLPLayer.java:117-123).  A training-mode forward runs
+ * the gate and up products unfused (their outputs must be stored) and rounds g and u to the compute dtype
+ * before SiLU; on a bf16 layer its output can differ from the inference forward's in the last bf16 place.
+ * omoe_set_training(h, 0) goes back to the inference kernels and keeps the buffers.
+ *
+ * omoe_backward replaces LlamaMLPLayer.diff() (LlamaMLPLayer.java:139-158) and the FullyLayer.diff() calls
+ * under it (src/main/java/com/omega/engine/nn/layer/FullyLayer.java:292-334): given dy_dev [T, d_model]
+ * (gradient of the output of the LAST forward, which must have run in training mode with the same T,
+ * io_dtype and x_dev contents), it writes dx_dev [T, d_model] of io_dtype and the weight gradients
+ * (library-owned, fp32, OVERWRITTEN by every call as FullyLayer.diff() overwrites diffW):
+ * d W_gate, d W_up [E, d_ff, d_model], d W_down [E, d_model, d_ff], d W_router [E, d_model],
+ * d router_bias [E].  The expert picks are constants (no gradient flows through the selection); the gate
+ * weights' gradient reaches the router through the renormalisation and the reference's softmax_back rule
+ * (src/main/resources/cu/SoftmaxKernel.cu:100-112).  No auxiliary load-balancing loss is added.
+ * omoe_forward_block's RMSNorm and residual are not differentiated here: call omoe_backward with the
+ * normalised rows' gradient handling left to the caller, or use omoe_forward.  Does not synchronise the host.
+ *
+ * omoe_get_weight_grads copies the gradients of the last omoe_backward into the caller's DEVICE (or host)
+ * fp32 buffers (any may be NULL) and synchronises the stream.
+ */
+OMOE_API int omoe_set_training(omoe_handle *h, int32_t on);
+OMOE_API int omoe_backward(omoe_handle *h, const void *x_dev, const void *dy_dev, void *dx_dev, int32_t T,
+                           int32_t io_dtype, void *cuda_stream);
+OMOE_API int omoe_get_weight_grads(omoe_handle *h, float *d_router, float *d_router_bias, float *d_gate,
+                                   float *d_up, float *d_down, void *cuda_stream);
+
+/*
  * Routing results of the last forward on this rank, copied to HOST buffers
  * (any may be NULL).  Synchronises the stream of that forward.
  *   topk_idx [T, k] int32, topk_w [T, k] fp32, counts [E] int32,

@@ -6,6 +6,7 @@
 
 #include <new>
 
+#include "backward.cuh"
 #include "common.cuh"
 #include "ep.cuh"
 
@@ -102,6 +103,7 @@ const char *omoe_last_error(const omoe_handle *h) { return h ? h->err : g_create
 int omoe_destroy(omoe_handle *h) {
     if (!h) return OMOE_OK;
     ep_destroy(h);
+    bw_destroy(h);
     void *ptrs[] = {h->w_router, h->router_bias, h->w_gate, h->w_up, h->w_down, h->logits, h->topk_idx,
                     h->topk_w, h->block_counts, h->block_base, h->counts, h->offsets, h->poffsets, h->tile_expert, h->pos, h->lrank,
                     h->perm_out, h->dev_err, h->xp, h->hbuf, h->yp, h->xn, h->x_stage, h->y_stage, h->d_row_table,
@@ -311,6 +313,7 @@ int omoe_set_weights(omoe_handle *h, const void *w_router, const void *router_bi
         }
     }
     h->weights_set = true;
+    bw_weights_changed(h);
     return OMOE_OK;
 }
 
@@ -324,6 +327,7 @@ static int forward_impl(omoe_handle *h, const void *x_dev, int x_dtype, void *y_
     h->last_stream = s;
     h->last_launches = 0;
     h->ev_valid = false;
+    bw_forward_invalidate(h);  // the rows a backward pass would read are about to be overwritten
     if (h->cfg.world > 1) {
         int rc = ep_forward(h, x_dev, x_dtype, y_dev, y_dtype, resid, T, s);
         h->last_launches += pre;
@@ -348,7 +352,11 @@ static int forward_impl(omoe_handle *h, const void *x_dev, int x_dtype, void *y_
     }
     MARK(3);
     MARK(4);
-    if (h->cfg.compute_dtype == OMOE_BF16 && T <= decode_tokens_threshold()) {
+    if (bw_training(h)) {
+        // training mode: the pre-activation rows are kept for the backward pass
+        CU_TRY(h, bw_forward_experts(h, T, s, &n));
+        MARK(5);
+    } else if (h->cfg.compute_dtype == OMOE_BF16 && T <= decode_tokens_threshold()) {
         CU_TRY(h, launch_experts_decode(h, T, s, &n, prof ? h->ev[5] : nullptr));
     } else if (h->cfg.compute_dtype == OMOE_BF16) {
         CU_TRY(h, launch_experts_bf16(h, s, &n, prof ? h->ev[5] : nullptr, (long)T * h->cfg.top_k));
@@ -395,6 +403,33 @@ int omoe_forward_block(omoe_handle *h, const void *x_dev, const float *gamma_dev
     int pre = 0;
     if (T > 0) CU_TRY(h, launch_rmsnorm(h, x_dev, io_dtype, gamma_dev, eps, T, s, &pre));
     return forward_impl(h, h->xn, h->cfg.compute_dtype, y_dev, io_dtype, x_dev, T, s, pre);
+}
+
+int omoe_set_training(omoe_handle *h, int32_t on) {
+    if (!h) return OMOE_ERR_INVALID;
+    return bw_set_training(h, on);
+}
+
+int omoe_backward(omoe_handle *h, const void *x_dev, const void *dy_dev, void *dx_dev, int32_t T, int32_t io_dtype,
+                  void *cuda_stream) {
+    if (!h) return OMOE_ERR_INVALID;
+    int rc = check_forward_args(h, x_dev, dx_dev, T, io_dtype, "omoe_backward");
+    if (rc != OMOE_OK) return rc;
+    if (T > 0 && !dy_dev) return fail(h, OMOE_ERR_INVALID, "omoe_backward: null buffer");
+    if (io_dtype != h->last_io_dtype && T > 0)
+        return fail(h, OMOE_ERR_INVALID, "omoe_backward: io_dtype differs from the forward's");
+    int n = 0;
+    rc = bw_backward(h, x_dev, dy_dev, dx_dev, T, io_dtype, static_cast<cudaStream_t>(cuda_stream), &n);
+    h->last_launches = n;
+    return rc;
+}
+
+int omoe_get_weight_grads(omoe_handle *h, float *d_router, float *d_router_bias, float *d_gate, float *d_up,
+                          float *d_down, void *cuda_stream) {
+    if (!h) return OMOE_ERR_INVALID;
+    int rc = bw_get_grads(h, d_router, d_router_bias, d_gate, d_up, d_down, static_cast<cudaStream_t>(cuda_stream));
+    if (rc != OMOE_OK) return rc;
+    return check_dev_err(h);
 }
 
 int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host, int32_t T, int32_t io_dtype,

@@ -105,6 +105,7 @@ struct omoe_handle {
     bool ev_valid;
 
     void *ep;  // expert-parallel state (ep.cu)
+    void *bw;  // backward-pass state (backward.cu), null until training mode is first switched on
 
     char err[512];
 };

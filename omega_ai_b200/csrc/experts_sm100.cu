@@ -19,6 +19,7 @@
 // memory and returns, so the context stays usable.
 #include <stdlib.h>
 
+#include "backward.cuh"
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -338,17 +339,48 @@ bool build_tensor_maps(omoe_handle *h) {
     return ok;
 }
 
+namespace {
+cudaError_t set_smem_attrs() {
+    static bool attr_done = false;
+    if (attr_done) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_done = true;
+    return cudaSuccess;
+}
+}  // namespace
+
+bool encode_map_bf16(CUtensorMap *m, void *ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {BLOCK_K, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+cudaError_t launch_grouped_plain(omoe_handle *h, cudaStream_t s, const CUtensorMap &a, const CUtensorMap &b,
+                                 const CUtensorMap &c, int n_out, int K) {
+    cudaError_t e = set_smem_attrs();
+    if (e != cudaSuccess) return e;
+    static int band = getenv("OMOE_BAND_DOWN") ? atoi(getenv("OMOE_BAND_DOWN")) : 16;
+    grouped_gemm_kernel<false><<<dim3(h->sm_count), dim3(kThreads), kSmemBytes, s>>>(
+        a, b, b, c, n_out, K, h->ex_tile_expert, h->ex_poffsets, h->e_local, band, h->dev_err);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid, long rows_ub) {
     static int use_pair = getenv("OMOE_PAIR") ? atoi(getenv("OMOE_PAIR")) : 0;
     if (use_pair) return launch_experts_bf16_pair(h, s, n, mid);
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kSmemBytes);
-        if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
+    {
+        cudaError_t e0 = set_smem_attrs();
+        if (e0 != cudaSuccess) return e0;
     }
     const int d = h->cfg.d_model, dff = h->cfg.d_ff;
     static int band_up = getenv("OMOE_BAND_UP") ? atoi(getenv("OMOE_BAND_UP")) : 16;

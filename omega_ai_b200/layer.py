@@ -224,6 +224,36 @@ class MoELayer(Layer):
                                                     x.shape[0], _dt(x.dtype), s))
         return y
 
+    # ---- training --------------------------------------------------------
+    def set_training(self, on: bool = True):
+        """Training mode: forwards keep what :meth:`backward` needs (the outputs of linear1, SiLU and
+        linear3 that the reference's LlamaMLPLayer keeps, LlamaMLPLayer.java:117-123)."""
+        check(self._h, self._lib.omoe_set_training(self._h, int(on)))
+
+    def backward(self, x: torch.Tensor, dy: torch.Tensor, dx: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+        """LlamaMLPLayer.diff() for the MoE layer (LlamaMLPLayer.java:139-158): ``dy`` is the gradient of the
+        last training-mode forward's output, ``x`` that forward's input; returns dx and leaves the weight
+        gradients in the library (:meth:`weight_grads`)."""
+        assert x.is_cuda and dy.is_cuda and x.is_contiguous() and dy.is_contiguous() and x.dtype == dy.dtype
+        if dx is None:
+            dx = torch.empty_like(x)
+        s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        check(self._h, self._lib.omoe_backward(self._h, x.data_ptr(), dy.data_ptr(), dx.data_ptr(), x.shape[0],
+                                               _dt(x.dtype), s))
+        return dx
+
+    def weight_grads(self, stream=None) -> dict:
+        """fp32 device tensors d_router [E,d], d_bias [E], d_gate/d_up [E,dff,d], d_down [E,d,dff] of the last
+        backward (diffW of the reference's FullyLayer, FullyLayer.java:292-301)."""
+        E, d, dff = self.numExperts, self.embedDim, self.dff
+        mk = lambda *shape: torch.empty(*shape, dtype=torch.float32, device="cuda")
+        g = dict(d_router=mk(E, d), d_bias=mk(E), d_gate=mk(E, dff, d), d_up=mk(E, dff, d), d_down=mk(E, d, dff))
+        s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        check(self._h, self._lib.omoe_get_weight_grads(self._h, g["d_router"].data_ptr(), g["d_bias"].data_ptr(),
+                                                       g["d_gate"].data_ptr(), g["d_up"].data_ptr(),
+                                                       g["d_down"].data_ptr(), s))
+        return g
+
     def forward_host(self, x: torch.Tensor, y: torch.Tensor, stream=None) -> torch.Tensor:
         """Host buffers in and out (pinned for asynchronous copies): H2D, forward, D2H, sync."""
         assert not x.is_cuda and not y.is_cuda and x.is_contiguous() and y.is_contiguous()

@@ -32,6 +32,7 @@ SYMBOLS = (
     "omoe_forward_host", "omoe_forward_block", "omoe_get_routing", "omoe_get_logits", "omoe_last_launch_count",
     "omoe_set_profiling", "omoe_get_stage_ms", "omoe_ep_export", "omoe_ep_import",
     "omoe_route_noalloc", "omoe_route_noalloc_error",
+    "omoe_set_training", "omoe_backward", "omoe_get_weight_grads",
 )
 NOALLOC_MAX_TOKENS = 4096
 
@@ -100,6 +101,9 @@ def lib():
     L.omoe_ep_export.argtypes = [vp, vp]
     L.omoe_ep_import.argtypes = [vp, vp]
     L.omoe_route_noalloc.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]
+    L.omoe_set_training.argtypes = [vp, i32]
+    L.omoe_backward.argtypes = [vp, vp, vp, vp, i32, i32, vp]
+    L.omoe_get_weight_grads.argtypes = [vp, vp, vp, vp, vp, vp, vp]
     L.omoe_route_noalloc_error.argtypes = []
     L.omoe_route_noalloc_error.restype = C.c_char_p
     for name in SYMBOLS:

@@ -1,0 +1,117 @@
+"""Backward pass through the C ABI against the oracle's backward (same rules, CPU)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_close_bf16, assert_close_f32, make_layer
+
+pytestmark = pytest.mark.gpu
+
+NAMES = ("dx", "d_w_r", "d_w_gate", "d_w_up", "d_w_down")
+
+
+def dev(a, dt=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda().to(dt).contiguous()
+
+
+def run_layer(T, d, dff, E, k, compute, io, x, w_r, w_g, w_u, w_d, dy, bias=None, renorm=True):
+    from omega_ai_b200 import MoELayer
+    layer = MoELayer(d, dff, E, k, t_max=max(T, 1), compute_dtype=compute, bias=bias is not None, renormalize=renorm)
+    layer.setWeights(dev(w_r, compute), dev(w_g, compute), dev(w_u, compute), dev(w_d, compute),
+                     router_bias=None if bias is None else dev(bias, compute))
+    layer.set_training(True)
+    xd = dev(x, io)
+    y = layer.forward_device(xd)
+    dx = layer.backward(xd, dev(dy, io))
+    g = layer.weight_grads()
+    out = dict(y=y.float().cpu().numpy(), dx=dx.float().cpu().numpy(), d_w_r=g["d_router"].cpu().numpy(),
+               d_bias=g["d_bias"].cpu().numpy(), d_w_gate=g["d_gate"].cpu().numpy(), d_w_up=g["d_up"].cpu().numpy(),
+               d_w_down=g["d_down"].cpu().numpy())
+    routing = layer.routing(T)
+    layer.close()
+    return out, routing
+
+
+def close_scaled(got, ref, name, rtol):
+    scale = np.abs(ref).max() + 1e-30
+    err = np.abs(got - ref).max()
+    assert err <= rtol * scale, f"{name}: max err {err:.3e} against scale {scale:.3e}"
+
+
+@pytest.mark.parametrize("T,d,dff,E,k,renorm,with_bias", [
+    (64, 128, 256, 8, 2, True, False),      # the reference-sized configuration
+    (300, 256, 384, 8, 2, True, True),
+    (130, 64, 136, 16, 4, False, True),     # d_ff not a multiple of 64, no renormalisation
+    (5, 128, 128, 8, 2, True, False),       # experts without rows: zero weight gradients
+])
+def test_fp32_backward_matches_oracle(oracle, T, d, dff, E, k, renorm, with_bias):
+    x, w_r, w_g, w_u, w_d, _ = make_layer(T, d, dff, E, k, seed=21)
+    w_r = (w_r * 10).astype(np.float32)
+    w_g, w_u, w_d = (w_g * 3).astype(np.float32), (w_u * 3).astype(np.float32), (w_d * 3).astype(np.float32)
+    bias = (0.3 * np.random.default_rng(2).standard_normal(E)).astype(np.float32) if with_bias else None
+    dy = np.random.default_rng(3).standard_normal((T, d)).astype(np.float32)
+    got, routing = run_layer(T, d, dff, E, k, torch.float32, torch.float32, x, w_r, w_g, w_u, w_d, dy, bias, renorm)
+    r = oracle.moe_forward(x, w_r, w_g, w_u, w_d, k, bias=bias, renorm=renorm)
+    assert np.array_equal(routing[0], r.topk_idx)
+    assert_close_f32(got["y"], r.y)  # the training-mode forward is still the layer
+    ref = oracle.moe_backward(x, w_r, w_g, w_u, w_d, k, dy, bias=bias, renorm=renorm)
+    for name in NAMES:
+        close_scaled(got[name], getattr(ref, name), name, 2e-4)
+    if with_bias:
+        close_scaled(got["d_bias"], ref.d_bias, "d_bias", 2e-4)
+    for e in np.nonzero(r.counts == 0)[0]:
+        assert not got["d_w_gate"][e].any() and not got["d_w_up"][e].any() and not got["d_w_down"][e].any()
+
+
+@pytest.mark.parametrize("T,d,dff,E,k,io", [
+    (512, 256, 512, 8, 2, torch.bfloat16),
+    (300, 320, 448, 8, 2, torch.float32),    # odd tile counts, fp32 rows in and out
+    (700, 128, 256, 16, 4, torch.bfloat16),
+    (9, 256, 256, 8, 2, torch.bfloat16),     # experts without rows
+])
+def test_bf16_backward_matches_oracle(oracle, T, d, dff, E, k, io):
+    x, w_r, w_g, w_u, w_d, _ = make_layer(T, d, dff, E, k, seed=22)
+    rb = oracle.bf16_round
+    x, w_r = rb(x), rb(w_r * 10)
+    w_g, w_u, w_d = rb(w_g * 3), rb(w_u * 3), rb(w_d * 3)
+    dy = rb(np.random.default_rng(4).standard_normal((T, d)).astype(np.float32))
+    got, routing = run_layer(T, d, dff, E, k, torch.bfloat16, io, x, w_r, w_g, w_u, w_d, dy)
+    out_bf16 = io == torch.bfloat16
+    r = oracle.moe_forward(x, w_r, w_g, w_u, w_d, k, bf16=True, out_bf16=out_bf16)
+    assert np.array_equal(routing[0], r.topk_idx)
+    assert_close_bf16(got["y"], r.y)
+    ref = oracle.moe_backward(x, w_r, w_g, w_u, w_d, k, dy, bf16=True, out_bf16=out_bf16)
+    for name in NAMES:
+        assert_close_bf16(got[name], getattr(ref, name))
+    for e in np.nonzero(r.counts == 0)[0]:
+        assert not got["d_w_gate"][e].any() and not got["d_w_up"][e].any() and not got["d_w_down"][e].any()
+
+
+def test_backward_call_order_and_modes(oracle):
+    from omega_ai_b200 import MoELayer
+    from omega_ai_b200.native import OmoeError
+    T, d, dff, E, k = 64, 128, 256, 8, 2
+    x, w_r, w_g, w_u, w_d, _ = make_layer(T, d, dff, E, k, seed=23)
+    layer = MoELayer(d, dff, E, k, t_max=T, compute_dtype=torch.bfloat16)
+    b = lambda a: dev(a, torch.bfloat16)
+    layer.setWeights(b(w_r), b(w_g), b(w_u), b(w_d))
+    xd, dy = b(x), b(np.ones((T, d), np.float32))
+    y_inf = layer.forward_device(xd).float().cpu().numpy()
+    with pytest.raises(OmoeError):   # not in training mode
+        layer.backward(xd, dy)
+    layer.set_training(True)
+    with pytest.raises(OmoeError):   # no training-mode forward yet
+        layer.backward(xd, dy)
+    y_tr = layer.forward_device(xd).float().cpu().numpy()
+    assert_close_bf16(y_tr, y_inf)
+    dx1 = layer.backward(xd, dy).float().cpu().numpy()
+    g1 = {n: v.cpu().numpy() for n, v in layer.weight_grads().items()}
+    layer.forward_device(xd)
+    dx2 = layer.backward(xd, dy).float().cpu().numpy()
+    g2 = {n: v.cpu().numpy() for n, v in layer.weight_grads().items()}
+    assert np.array_equal(dx1, dx2) and all(np.array_equal(g1[n], g2[n]) for n in g1)   # reproducible, overwritten
+    layer.set_training(False)
+    layer.forward_device(xd)
+    with pytest.raises(OmoeError):   # the inference forward overwrote what the backward reads
+        layer.backward(xd, dy)
+    layer.close()
