@@ -144,7 +144,7 @@ swiglu_bwd_kernel(const T *__restrict__ dh, const T *__restrict__ gu, T *__restr
 
 // ---- combine backward + router backward: one warp per token ---------------------------------------
 // dyp[pos_j] = w_j * dy[t];  d w_j = <dy[t], yp[pos_j]>;  then lane 0 turns the k values d w into the
-// E values d logits (gate renormalisation, softmax_back), serially and in index order as the oracle does.
+// E values d logits (gate renormalisation, softmax_back), serially and in index order like softmax_back itself.
 template <typename YT, typename OT>
 __global__ void __launch_bounds__(256)
 combine_bwd_kernel(const OT *__restrict__ dy, const YT *__restrict__ yp, YT *__restrict__ dyp,
