@@ -272,6 +272,35 @@ def run_ours(args, cfg):
     layer.set_profiling(False)
     stage_ms = {a: v / n_prof for a, v in stage_sum.items()}
 
+    # ---- optional: a training step (training-mode forward + backward), one GPU ----
+    train = None
+    if args.train and world == 1 and not args.block:
+        layer.set_training(True)
+        dy = torch.randn((T_local, d), device=dev, dtype=torch.float32).to(cdt)
+        dx = torch.empty_like(x)
+        t_steps = max(3, min(args.steps, 10))
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        for _ in range(2):
+            layer.forward_device(x, y)
+            layer.backward(x, dy, dx)
+        torch.cuda.synchronize()
+        f_ms = b_ms = 0.0
+        for _ in range(t_steps):
+            evs[0].record()
+            layer.forward_device(x, y)
+            evs[1].record()
+            layer.backward(x, dy, dx)
+            evs[2].record()
+            torch.cuda.synchronize()
+            f_ms += evs[0].elapsed_time(evs[1])
+            b_ms += evs[1].elapsed_time(evs[2])
+        f_ms, b_ms = f_ms / t_steps, b_ms / t_steps
+        flops = 3 * 6.0 * T_local * k * d * dff  # forward + input gradients + weight gradients of the expert products
+        train = {"forward_ms": f_ms, "backward_ms": b_ms, "tokens_per_s": T / ((f_ms + b_ms) * 1e-3),
+                 "expert_tflops": flops / ((f_ms + b_ms) * 1e-3) / 1e12, "backward_launches": layer.launch_count(),
+                 "steps": t_steps}
+        layer.set_training(False)
+
     # ---- end to end through the host-buffer entry point --------------------
     xh = torch.empty((T_local, d), dtype=cdt).pin_memory()
     xh.copy_(x.cpu())
@@ -364,6 +393,8 @@ def run_ours(args, cfg):
                 "d2h_bytes_per_step": T_local * d * bpe},
         "gpu_launches": launches,
     }
+    if train is not None:
+        line["train"] = train
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -379,6 +410,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override the token count (decode sweep)")
     ap.add_argument("--cpu-tokens", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--train", action="store_true",
+                    help="also time a training step (training-mode forward + backward) on one GPU; adds a 'train' object")
     ap.add_argument("--block", action="store_true",
                     help="time y = x + MoE(rmsnorm(x)*gamma) (omoe_forward_block) instead of the bare layer")
     args = ap.parse_args()
