@@ -57,7 +57,9 @@ struct BwState {
     CUtensorMap m_g_out, m_u_out;          // halves of gu as store targets
     CUtensorMap m_dyp_a, m_wdT_b, m_dh_c;  // dh = dyp * W_down
     CUtensorMap m_dgu_a, m_wguT_b, m_dxp_c;  // dxp = [dg|du] * [Wg;Wu]
-    CUtensorMap m_dypT, m_hT, m_dguT, m_xpT;  // weight-gradient operands
+    CUtensorMap m_dypT, m_hT, m_dguT, m_xpT;  // weight-gradient operands, transposed copies (older path)
+    CUtensorMap m_dyp_r, m_h_r, m_dgu_r, m_xp_r;  // weight-gradient operands read in place (64-row boxes)
+    bool wgrad_transposed;  // OMOE_WGRAD_TRANSPOSED=1: use the transposed copies
 };
 
 namespace {
@@ -294,6 +296,21 @@ __global__ void __launch_bounds__(256) dbias_kernel(const float *__restrict__ dl
     if (threadIdx.x == 0) out[e] = s[0];
 }
 
+// Zero the padding rows of every expert's segment (rows [poffsets[e] + counts[e], poffsets[e+1])) of buf
+// [rows, ld] (16-byte vectors; ld*sizeof(T) is a multiple of 16).  blockIdx.x = expert.
+template <typename T>
+__global__ void __launch_bounds__(256)
+zero_pad_rows_kernel(T *__restrict__ buf, int ld, const int32_t *__restrict__ poffsets,
+                     const int32_t *__restrict__ counts) {
+    const int e = blockIdx.x;
+    const int r0 = poffsets[e] + counts[e], r1 = poffsets[e + 1];
+    const int vec_per_row = ld * (int)sizeof(T) / 16;
+    const int64_t total = (int64_t)(r1 - r0) * vec_per_row;
+    uint4 *base = reinterpret_cast<uint4 *>(buf + (size_t)r0 * ld);
+    for (int64_t i = (int64_t)blockIdx.y * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.y * blockDim.x)
+        base[i] = make_uint4(0u, 0u, 0u, 0u);
+}
+
 // ---- transposes (bf16 layers) ---------------------------------------------------------------------
 // dst[c, r] = src[r, c] for the rows in use, r < *rows_in_use (a multiple of 128); rows of an expert's
 // segment beyond its count are written as zeros, so a reduction over the padded segment adds nothing.
@@ -437,6 +454,11 @@ cudaError_t forward_experts_t(omoe_handle *h, BwState *b, cudaStream_t s, int *n
     const int d = h->cfg.d_model, dff = h->cfg.d_ff, El = h->e_local;
     const int32_t *rows_in_use = h->ex_poffsets + El;
     CT *gu = static_cast<CT *>(b->gu);
+    // padding rows hold rows of earlier steps: zero them, so that g, u and h are zero there too and a
+    // reduction over a padded segment (the weight gradients) adds nothing
+    zero_pad_rows_kernel<CT><<<dim3(El, 8), 256, 0, s>>>(static_cast<CT *>(h->xp), d, h->ex_poffsets, h->ex_counts);
+    BW_TRY(cudaGetLastError());
+    (*n)++;
     if constexpr (sizeof(CT) == 2) {
         BW_TRY(launch_grouped_plain(h, s, h->maps.a_x, h->maps.b_gate, b->m_g_out, dff, d));
         BW_TRY(launch_grouped_plain(h, s, h->maps.a_x, h->maps.b_up, b->m_u_out, dff, d));
@@ -499,8 +521,9 @@ cudaError_t backward_t(omoe_handle *h, BwState *b, const void *x, const void *dy
     combine_bwd_kernel<CT, OT><<<tblocks, 256, 0, s>>>(
         static_cast<const OT *>(dy), static_cast<const CT *>(h->yp), static_cast<CT *>(b->dyp), h->pos, h->topk_idx,
         h->topk_w, h->logits, b->dgw, b->dl, T, d, k, E, h->cfg.renormalize);
+    zero_pad_rows_kernel<CT><<<dim3(El, 8), 256, 0, s>>>(static_cast<CT *>(b->dyp), d, h->ex_poffsets, h->ex_counts);
     BW_TRY(cudaGetLastError());
-    (*n)++;
+    *n += 2;
     const int ew_grid = grid_for(h->rows_cap * (int64_t)dff / 8, h->sm_count);
     if constexpr (sizeof(CT) == 2) {
         if (!b->wt_valid) BW_TRY(transpose_weights(h, b, s, n));
@@ -514,21 +537,27 @@ cudaError_t backward_t(omoe_handle *h, BwState *b, const void *x, const void *dy
         // dxp = [dg | du] * [W_gate ; W_up]: one product over K = 2*dff
         BW_TRY(launch_grouped_plain(h, s, b->m_dgu_a, b->m_wguT_b, b->m_dxp_c, d, 2 * dff));
         (*n)++;
-        // weight gradients reduce over an expert's rows: transposed activations, padding rows zeroed
-        auto tr = [&](const void *src, int ld, void *dst, int C) {
-            transpose_rows_kernel<<<dim3((unsigned)(h->rows_cap / 64), (unsigned)ceil_div(C, 64)), 256, 0, s>>>(
-                static_cast<const __nv_bfloat16 *>(src), ld, static_cast<__nv_bfloat16 *>(dst), (int)h->rows_cap, C,
-                rows_in_use, h->ex_tile_expert, h->ex_poffsets, h->ex_counts);
-            (*n)++;
-        };
-        tr(b->dyp, d, b->dypT, d);
-        tr(h->hbuf, dff, b->hT, dff);
-        tr(b->dgu, 2 * dff, b->dguT, 2 * dff);
-        tr(h->xp, d, b->xpT, d);
-        BW_TRY(cudaGetLastError());
         // d W_down[e] [d, dff] = dyp_e^T * h_e;  [d W_gate ; d W_up][e] [2*dff, d] = [dg | du]_e^T * xp_e
-        BW_TRY(launch_wgrad_bf16(h, s, b->m_dypT, b->m_hT, d, dff, d, b->d_down, b->d_down));
-        BW_TRY(launch_wgrad_bf16(h, s, b->m_dguT, b->m_xpT, 2 * dff, d, dff, b->d_gate, b->d_up));
+        if (!b->wgrad_transposed) {
+            // operands read in place as MN-major tiles; dyp's padding rows are zero, hence dh's and [dg|du]'s
+            BW_TRY(launch_wgrad_bf16_rows(h, s, b->m_dyp_r, b->m_h_r, d, dff, d, b->d_down, b->d_down));
+            BW_TRY(launch_wgrad_bf16_rows(h, s, b->m_dgu_r, b->m_xp_r, 2 * dff, d, dff, b->d_gate, b->d_up));
+        } else {
+            // transposed copies with each expert's padding rows zero-filled, then K-major operands
+            auto tr = [&](const void *src, int ld, void *dst, int C) {
+                transpose_rows_kernel<<<dim3((unsigned)(h->rows_cap / 64), (unsigned)ceil_div(C, 64)), 256, 0, s>>>(
+                    static_cast<const __nv_bfloat16 *>(src), ld, static_cast<__nv_bfloat16 *>(dst), (int)h->rows_cap, C,
+                    rows_in_use, h->ex_tile_expert, h->ex_poffsets, h->ex_counts);
+                (*n)++;
+            };
+            tr(b->dyp, d, b->dypT, d);
+            tr(h->hbuf, dff, b->hT, dff);
+            tr(b->dgu, 2 * dff, b->dguT, 2 * dff);
+            tr(h->xp, d, b->xpT, d);
+            BW_TRY(cudaGetLastError());
+            BW_TRY(launch_wgrad_bf16(h, s, b->m_dypT, b->m_hT, d, dff, d, b->d_down, b->d_down));
+            BW_TRY(launch_wgrad_bf16(h, s, b->m_dguT, b->m_xpT, 2 * dff, d, dff, b->d_gate, b->d_up));
+        }
         *n += 2;
     } else {
         const float *dyp = static_cast<const float *>(b->dyp);
@@ -615,10 +644,15 @@ int bw_set_training(omoe_handle *h, int on) {
         {(void **)&b->d_up, El * dff * d * 4}, {(void **)&b->d_down, El * dff * d * 4}};
     bool ok = true;
     for (auto &x : bufs) ok = ok && cudaMalloc(x.p, x.bytes ? x.bytes : 1) == cudaSuccess;
+    const char *wt = getenv("OMOE_WGRAD_TRANSPOSED");
+    b->wgrad_transposed = wt && atoi(wt) != 0;
     if (ok && cs == 2) {
-        struct { void **p; size_t bytes; } tb[] = {
-            {&b->wdT, El * dff * d * 2}, {&b->wguT, El * d * 2 * dff * 2}, {&b->xpT, d * rows * 2},
-            {&b->hT, dff * rows * 2}, {&b->dypT, d * rows * 2}, {&b->dguT, 2 * dff * rows * 2}};
+        struct { void **p; size_t bytes; } tb[] = {{&b->wdT, El * dff * d * 2}, {&b->wguT, El * d * 2 * dff * 2}};
+        for (auto &x : tb) ok = ok && cudaMalloc(x.p, x.bytes) == cudaSuccess;
+    }
+    if (ok && cs == 2 && b->wgrad_transposed) {
+        struct { void **p; size_t bytes; } tb[] = {{&b->xpT, d * rows * 2}, {&b->hT, dff * rows * 2},
+                                                   {&b->dypT, d * rows * 2}, {&b->dguT, 2 * dff * rows * 2}};
         for (auto &x : tb) ok = ok && cudaMalloc(x.p, x.bytes) == cudaSuccess;
     }
     if (!ok) {
@@ -641,10 +675,15 @@ int bw_set_training(omoe_handle *h, int on) {
                  encode_map_bf16(&b->m_dgu_a, b->dgu, rows, 2 * dff, 2 * dff, 128) &&
                  encode_map_bf16(&b->m_wguT_b, b->wguT, El * d, 2 * dff, 2 * dff, 128) &&
                  encode_map_bf16(&b->m_dxp_c, b->dxp, rows, d, d, 128) &&
-                 encode_map_bf16(&b->m_dypT, b->dypT, d, rows, rows, 128) &&
-                 encode_map_bf16(&b->m_hT, b->hT, dff, rows, rows, 128) &&
-                 encode_map_bf16(&b->m_dguT, b->dguT, 2 * dff, rows, rows, 128) &&
-                 encode_map_bf16(&b->m_xpT, b->xpT, d, rows, rows, 128);
+                 encode_map_bf16(&b->m_dyp_r, b->dyp, rows, d, d, 64) &&
+                 encode_map_bf16(&b->m_h_r, h->hbuf, rows, dff, dff, 64) &&
+                 encode_map_bf16(&b->m_dgu_r, b->dgu, rows, 2 * dff, 2 * dff, 64) &&
+                 encode_map_bf16(&b->m_xp_r, h->xp, rows, d, d, 64);
+        if (m && b->wgrad_transposed)
+            m = encode_map_bf16(&b->m_dypT, b->dypT, d, rows, rows, 128) &&
+                encode_map_bf16(&b->m_hT, b->hT, dff, rows, rows, 128) &&
+                encode_map_bf16(&b->m_dguT, b->dguT, 2 * dff, rows, rows, 128) &&
+                encode_map_bf16(&b->m_xpT, b->xpT, d, rows, rows, 128);
         if (!m) {
             free_state(b);
             snprintf(h->err, sizeof(h->err), "omoe_set_training: cuTensorMapEncodeTiled failed");

@@ -29,4 +29,9 @@ cudaError_t launch_grouped_plain(omoe_handle *h, cudaStream_t s, const CUtensorM
 cudaError_t launch_wgrad_bf16(omoe_handle *h, cudaStream_t s, const CUtensorMap &at, const CUtensorMap &bt, int M,
                               int N, int split, float *out0, float *out1);
 
+// The same product straight from the row-major activations a [rows_cap, M], b [rows_cap, N] (tensor maps with a
+// 64-row box): MN-major tensor-core operands, no transposed copies.  Padding rows of a must be zero, of b finite.
+cudaError_t launch_wgrad_bf16_rows(omoe_handle *h, cudaStream_t s, const CUtensorMap &a, const CUtensorMap &b, int M,
+                                   int N, int split, float *out0, float *out1);
+
 }  // namespace omoe

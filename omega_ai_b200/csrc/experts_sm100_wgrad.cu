@@ -4,9 +4,15 @@
 // (src/main/java/com/omega/engine/nn/layer/FullyLayer.java:292-301).  Here every expert has its own rows,
 // so the product is grouped the other way round from the forward: per expert e
 //     C_e [M, N] = sum over the expert's rows r of  A[r, m] * B[r, n]
-// with the row index as the reduction.  The operands arrive transposed (AT [M, rows], BT [N, rows], bf16,
-// written by backward.cu with each expert's padding rows zero-filled), which makes both of them K-major
-// and lets the mainloop be the forward's: one CTA per SM walks (expert, n-tile, m-tile) triples; a producer
+// with the row index as the reduction.  The activations are stored [rows, features], so in this product the
+// reduction index is the SLOW one of both operands: they are "MN-major" tiles for the tensor core.  TMA
+// brings 64-feature x 64-row boxes (128-byte swizzle; a 128 x 64 A tile is two boxes, a 256 x 64 B tile
+// four), the shared-memory descriptors say: 64 features contiguous, next row of the reduction 128 bytes on,
+// next group of 8 rows 1024 bytes on, next 64 features one box (8 KB) on, and the instruction descriptor
+// marks both operands MN-major.  Padding rows of an expert's segment must be zero in the A operand and
+// finite in the B operand (backward.cu zeroes them).  MN_MAJOR = false is the older form of the same
+// kernel on explicitly transposed copies (AT [M, rows], BT [N, rows], K-major as in the forward).
+// The mainloop is otherwise the forward's: one CTA per SM walks (expert, n-tile, m-tile) triples; a producer
 // thread feeds a 4-stage TMA ring (128-byte swizzle), one thread issues tcgen05.mma (M=128, N=256, K=16)
 // into a double-buffered accumulator in tensor memory, eight epilogue warps read it with tcgen05.ld and
 // store fp32 rows straight to the gradient (each thread owns one row and writes 128 contiguous bytes at a
@@ -46,6 +52,23 @@ __device__ __forceinline__ WTile wtile(int tile, int m_tiles, int n_tiles) {
     return t;
 }
 
+// 64 (MN) x 64 (K) bf16 box: 8 KB
+constexpr int kBoxBytesW = 64 * BLOCK_K * 2;
+
+// MN-major operand, 128-byte swizzle: blocks of 64 MN-elements kBoxBytesW apart (leading byte offset),
+// groups of 8 reduction rows 1024 bytes apart (stride byte offset).
+__device__ __forceinline__ uint64_t make_mn_sw128_desc(uint32_t smem_addr) {
+    uint64_t desc = 0;
+    desc |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+    desc |= (uint64_t)(kBoxBytesW >> 4) << 16;
+    desc |= (uint64_t)(1024 >> 4) << 32;
+    desc |= (uint64_t)1 << 46;
+    desc |= (uint64_t)2 << 61;
+    return desc;
+}
+constexpr uint32_t kIdescMN = kIdesc | (1u << 15) | (1u << 16);  // A and B MN-major
+
+template <bool MN_MAJOR>
 __global__ void __launch_bounds__(kThreadsW, 1)
 wgrad_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
              float *__restrict__ out0, float *__restrict__ out1, int M, int N, int split,
@@ -106,9 +129,20 @@ wgrad_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                     const uint32_t sa = base + stage * kStageBytesW;
                     const int x = seg0 + kb * BLOCK_K;  // a multiple of 64 elements: 128-byte aligned
                     mbar_expect_tx(full_bar(stage), kStageBytesW);
-                    tma_load_2d(sa, &map_a, full_bar(stage), x, t.mt * BLOCK_M);
-                    tma_load_2d(sa + kABytesW, &map_b, full_bar(stage), x, t.nt * BLOCK_N);
-                    tma_load_2d(sa + kABytesW + kBHalfBytesW, &map_b, full_bar(stage), x, t.nt * BLOCK_N + 128);
+                    if constexpr (MN_MAJOR) {
+                        // maps are [rows, features]: the feature index is the inner coordinate
+#pragma unroll
+                        for (int i = 0; i < 2; i++)
+                            tma_load_2d(sa + i * kBoxBytesW, &map_a, full_bar(stage), t.mt * BLOCK_M + 64 * i, x);
+#pragma unroll
+                        for (int i = 0; i < 4; i++)
+                            tma_load_2d(sa + kABytesW + i * kBoxBytesW, &map_b, full_bar(stage),
+                                        t.nt * BLOCK_N + 64 * i, x);
+                    } else {
+                        tma_load_2d(sa, &map_a, full_bar(stage), x, t.mt * BLOCK_M);
+                        tma_load_2d(sa + kABytesW, &map_b, full_bar(stage), x, t.nt * BLOCK_N);
+                        tma_load_2d(sa + kABytesW + kBHalfBytesW, &map_b, full_bar(stage), x, t.nt * BLOCK_N + 128);
+                    }
                     if (++stage == kStagesW) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -134,11 +168,20 @@ wgrad_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                     if (!mbar_wait(full_bar(stage), phase, abort_flag, dev_err)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = base + stage * kStageBytesW;
-                    const uint64_t adesc = make_sw128_desc(sa);
-                    const uint64_t bdesc = make_sw128_desc(sa + kABytesW);
+                    if constexpr (MN_MAJOR) {
+                        const uint64_t adesc = make_mn_sw128_desc(sa);
+                        const uint64_t bdesc = make_mn_sw128_desc(sa + kABytesW);
+                        // 16 rows of the reduction are 16 x 128 bytes further on: +128 in 16-byte units
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; k++)
-                        tc_mma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                        for (int k = 0; k < BLOCK_K / UMMA_K; k++)
+                            tc_mma_bf16(d_tmem, adesc + 128u * k, bdesc + 128u * k, kIdescMN, (kb | k) != 0 ? 1u : 0u);
+                    } else {
+                        const uint64_t adesc = make_sw128_desc(sa);
+                        const uint64_t bdesc = make_sw128_desc(sa + kABytesW);
+#pragma unroll
+                        for (int k = 0; k < BLOCK_K / UMMA_K; k++)
+                            tc_mma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                    }
                     tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
                     if (++stage == kStagesW) { stage = 0; phase ^= 1u; }
                 }
@@ -212,18 +255,29 @@ wgrad_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
 
 }  // namespace
 
-cudaError_t launch_wgrad_bf16(omoe_handle *h, cudaStream_t s, const CUtensorMap &at, const CUtensorMap &bt, int M,
-                              int N, int split, float *out0, float *out1) {
-    static bool attr_done = false;
+template <bool MN_MAJOR>
+static cudaError_t launch_wgrad_t(omoe_handle *h, cudaStream_t s, const CUtensorMap &a, const CUtensorMap &b, int M,
+                                  int N, int split, float *out0, float *out1) {
+    static bool attr_done = false;  // one per instantiation
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesW);
+        cudaError_t e = cudaFuncSetAttribute(wgrad_kernel<MN_MAJOR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kSmemBytesW);
         if (e != cudaSuccess) return e;
         attr_done = true;
     }
-    wgrad_kernel<<<dim3(h->sm_count), dim3(kThreadsW), kSmemBytesW, s>>>(at, bt, out0, out1, M, N, split,
-                                                                        h->ex_poffsets, h->ex_counts, h->e_local,
-                                                                        h->dev_err);
+    wgrad_kernel<MN_MAJOR><<<dim3(h->sm_count), dim3(kThreadsW), kSmemBytesW, s>>>(
+        a, b, out0, out1, M, N, split, h->ex_poffsets, h->ex_counts, h->e_local, h->dev_err);
     return cudaGetLastError();
+}
+
+cudaError_t launch_wgrad_bf16(omoe_handle *h, cudaStream_t s, const CUtensorMap &at, const CUtensorMap &bt, int M,
+                              int N, int split, float *out0, float *out1) {
+    return launch_wgrad_t<false>(h, s, at, bt, M, N, split, out0, out1);
+}
+
+cudaError_t launch_wgrad_bf16_rows(omoe_handle *h, cudaStream_t s, const CUtensorMap &a, const CUtensorMap &b, int M,
+                                   int N, int split, float *out0, float *out1) {
+    return launch_wgrad_t<true>(h, s, a, b, M, N, split, out0, out1);
 }
 
 }  // namespace omoe

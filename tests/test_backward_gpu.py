@@ -115,3 +115,18 @@ def test_backward_call_order_and_modes(oracle):
     with pytest.raises(OmoeError):   # the inference forward overwrote what the backward reads
         layer.backward(xd, dy)
     layer.close()
+
+
+def test_weight_gradients_on_transposed_copies_in_a_subprocess():
+    """The weight-gradient products read the activations in place (MN-major tensor-core operands) by default;
+    OMOE_WGRAD_TRANSPOSED=1, read when training mode is switched on, selects the older path through explicit
+    transposed copies.  Both must give the oracle's gradients."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, OMOE_WGRAD_TRANSPOSED="1")
+    cmd = [sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_backward_gpu.py"), "-x", "-q", "-m", "gpu",
+           "-k", "bf16_backward"]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=root)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
