@@ -60,7 +60,6 @@ struct BwState {
     CUtensorMap m_dypT, m_hT, m_dguT, m_xpT;  // weight-gradient operands, transposed copies (older path)
     CUtensorMap m_dyp_r, m_h_r, m_dgu_r, m_xp_r;  // weight-gradient operands read in place (64-row boxes)
     bool wgrad_transposed;  // OMOE_WGRAD_TRANSPOSED=1: use the transposed copies
-    bool unfused;           // OMOE_TRAIN_UNFUSED=1: separate SwiGLU passes instead of the fused epilogues
 };
 
 namespace {
@@ -461,18 +460,8 @@ cudaError_t forward_experts_t(omoe_handle *h, BwState *b, cudaStream_t s, int *n
     BW_TRY(cudaGetLastError());
     (*n)++;
     if constexpr (sizeof(CT) == 2) {
-        if (!b->unfused) {
-            // the inference kernel with one more duty: its epilogue also stores g and u
-            BW_TRY(launch_up_gate_keep(h, s, gu));
-            (*n)++;
-        } else {
-            BW_TRY(launch_grouped_plain(h, s, h->maps.a_x, h->maps.b_gate, b->m_g_out, dff, d));
-            BW_TRY(launch_grouped_plain(h, s, h->maps.a_x, h->maps.b_up, b->m_u_out, dff, d));
-            swiglu_fwd_kernel<CT><<<grid_for(h->rows_cap * (int64_t)dff / 8, h->sm_count), 256, 0, s>>>(
-                gu, static_cast<CT *>(h->hbuf), rows_in_use, dff);
-            BW_TRY(cudaGetLastError());
-            *n += 3;
-        }
+        BW_TRY(launch_grouped_plain(h, s, h->maps.a_x, h->maps.b_gate, b->m_g_out, dff, d));
+        BW_TRY(launch_grouped_plain(h, s, h->maps.a_x, h->maps.b_up, b->m_u_out, dff, d));
     } else {
         dim3 grid((unsigned)(h->rows_cap / 64), (unsigned)ceil_div(dff, 64));
         const float *xp = static_cast<const float *>(h->xp);
@@ -483,11 +472,13 @@ cudaError_t forward_experts_t(omoe_handle *h, BwState *b, cudaStream_t s, int *n
         sgemm_rows_kernel<<<grid, 256, 0, s>>>(xp, d, static_cast<const float *>(h->w_up), (size_t)dff * d, 1, d,
                                                reinterpret_cast<float *>(gu) + dff, 2 * dff, dff, d, rows_in_use,
                                                h->ex_tile_expert, 0);
-        swiglu_fwd_kernel<CT><<<grid_for(h->rows_cap * (int64_t)dff / 8, h->sm_count), 256, 0, s>>>(
-            gu, static_cast<CT *>(h->hbuf), rows_in_use, dff);
         BW_TRY(cudaGetLastError());
-        *n += 3;
     }
+    *n += 2;
+    swiglu_fwd_kernel<CT><<<grid_for(h->rows_cap * (int64_t)dff / 8, h->sm_count), 256, 0, s>>>(
+        gu, static_cast<CT *>(h->hbuf), rows_in_use, dff);
+    BW_TRY(cudaGetLastError());
+    (*n)++;
     if constexpr (sizeof(CT) == 2) {
         BW_TRY(launch_grouped_plain(h, s, h->maps.a_h, h->maps.b_down, h->maps.c_y, d, dff));
     } else {
@@ -537,18 +528,12 @@ cudaError_t backward_t(omoe_handle *h, BwState *b, const void *x, const void *dy
     if constexpr (sizeof(CT) == 2) {
         if (!b->wt_valid) BW_TRY(transpose_weights(h, b, s, n));
         // dh = dyp * W_down      (rows x d) * (d x dff): the forward's kernel on W_down^T
-        if (!b->unfused) {
-            // ... whose epilogue turns dh into [dg | du] at once
-            BW_TRY(launch_dh_swiglu_bwd(h, s, b->m_dyp_a, b->m_wdT_b, b->gu, b->dgu));
-            (*n)++;
-        } else {
-            BW_TRY(launch_grouped_plain(h, s, b->m_dyp_a, b->m_wdT_b, b->m_dh_c, dff, d));
-            swiglu_bwd_kernel<CT><<<ew_grid, 256, 0, s>>>(static_cast<const CT *>(b->dh),
-                                                          static_cast<const CT *>(b->gu), static_cast<CT *>(b->dgu),
-                                                          rows_in_use, dff);
-            BW_TRY(cudaGetLastError());
-            *n += 2;
-        }
+        BW_TRY(launch_grouped_plain(h, s, b->m_dyp_a, b->m_wdT_b, b->m_dh_c, dff, d));
+        (*n)++;
+        swiglu_bwd_kernel<CT><<<ew_grid, 256, 0, s>>>(static_cast<const CT *>(b->dh), static_cast<const CT *>(b->gu),
+                                                      static_cast<CT *>(b->dgu), rows_in_use, dff);
+        BW_TRY(cudaGetLastError());
+        (*n)++;
         // dxp = [dg | du] * [W_gate ; W_up]: one product over K = 2*dff
         BW_TRY(launch_grouped_plain(h, s, b->m_dgu_a, b->m_wguT_b, b->m_dxp_c, d, 2 * dff));
         (*n)++;
@@ -661,8 +646,6 @@ int bw_set_training(omoe_handle *h, int on) {
     for (auto &x : bufs) ok = ok && cudaMalloc(x.p, x.bytes ? x.bytes : 1) == cudaSuccess;
     const char *wt = getenv("OMOE_WGRAD_TRANSPOSED");
     b->wgrad_transposed = wt && atoi(wt) != 0;
-    const char *uf = getenv("OMOE_TRAIN_UNFUSED");
-    b->unfused = uf && atoi(uf) != 0;
     if (ok && cs == 2) {
         struct { void **p; size_t bytes; } tb[] = {{&b->wdT, El * dff * d * 2}, {&b->wguT, El * d * 2 * dff * 2}};
         for (auto &x : tb) ok = ok && cudaMalloc(x.p, x.bytes) == cudaSuccess;

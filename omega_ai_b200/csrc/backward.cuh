@@ -23,11 +23,6 @@ bool encode_map_bf16(CUtensorMap *m, void *ptr, uint64_t rows, uint64_t cols, ui
 // the persistent tcgen05 kernel of the forward's down product with other operands (experts_sm100.cu).
 cudaError_t launch_grouped_plain(omoe_handle *h, cudaStream_t s, const CUtensorMap &a, const CUtensorMap &b,
                                  const CUtensorMap &c, int n_out, int K);
-// Fused training epilogues of the same kernel: the up/gate product that also keeps g and u in gu [rows_cap, 2*dff],
-// and dh = a * b^T turned into [dg | du] in the epilogue (dh is never stored).
-cudaError_t launch_up_gate_keep(omoe_handle *h, cudaStream_t s, void *gu);
-cudaError_t launch_dh_swiglu_bwd(omoe_handle *h, cudaStream_t s, const CUtensorMap &a, const CUtensorMap &b,
-                                 const void *gu, void *dgu);
 // Per local expert e: C_e [M, N] (fp32) = AT[:, seg_e] * BT[:, seg_e]^T, seg_e = the expert's (padded, zero-filled)
 // rows; at [M, rows_cap], bt [N, rows_cap] bf16.  Row m of C_e goes to out0[e][m][:] when m < split, else to
 // out1[e][m - split][:].  (experts_sm100_wgrad.cu)

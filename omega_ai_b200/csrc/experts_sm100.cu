@@ -74,31 +74,12 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m_tiles, int n
 // SWIGLU = true : B0 = W_gate, B1 = W_up, tile nt covers output columns [128 nt, 128 nt + 128)
 // SWIGLU = false: B0 = B1 = W_down,     tile nt covers output columns [256 nt, 256 nt + 256)
 // n_out: output features per expert (d_ff or d_model); K: reduction length.
-// Epilogue variants of the training path (EXTRA), both on a buffer aux [rows, 2*n_out] whose left half holds the
-// gate-side and whose right half the up-side values of a row:
-//   kKeepGU (with SWIGLU):   besides h, the pre-activation values g and u are stored to aux0 (bf16), which is what
-//                            the backward pass needs; h itself is computed from the fp32 accumulators as always.
-//   kSwigluBwd (no SWIGLU):  the product is dh; the epilogue reads g and u from aux0 and writes
-//                            dg = (dh*u)*silu'(g), du = dh*silu(g) to aux1 (silu_backward, activeFunction.cu:182-190);
-//                            dh itself is never stored and map_out is unused.
-constexpr int kKeepGU = 1, kSwigluBwd = 2;
-
-__device__ __forceinline__ void unpack8_bf16(const uint4 &r, float (&v)[8]) {
-    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-}
-
-template <bool SWIGLU, int EXTRA = 0>
+template <bool SWIGLU>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                     const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_out, int n_out,
                     int K, const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ poffsets,
-                    int E, int kband, int32_t *dev_err, __nv_bfloat16 *aux0 = nullptr, __nv_bfloat16 *aux1 = nullptr) {
-    static_assert(EXTRA == 0 || (EXTRA == kKeepGU && SWIGLU) || (EXTRA == kSwigluBwd && !SWIGLU), "epilogue variant");
+                    int E, int kband, int32_t *dev_err) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;  // stages need 1024-byte alignment for the swizzle
@@ -247,76 +228,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             __syncwarp();
                             if (lane == 0) mbar_arrive(tempty_bar(as));
                         }
-                        if constexpr (EXTRA == kKeepGU) {
-                            // this thread's 32 gate and 32 up values of one row: 64 contiguous bytes each
-                            const int gcol = tc.nt * 128 + half * 64 + c * 32;
-                            __nv_bfloat16 *pg = aux0 + (size_t)(tc.mt * BLOCK_M + r) * (2 * n_out) + gcol;
-#pragma unroll
-                            for (int v = 0; v < 4; v++)
-                                if (gcol + 8 * v < n_out) {  // n_out is a multiple of 8
-                                    uint4 qg, qu;
-                                    qg.x = pack_bf16(__uint_as_float(g[8 * v]), __uint_as_float(g[8 * v + 1]));
-                                    qg.y = pack_bf16(__uint_as_float(g[8 * v + 2]), __uint_as_float(g[8 * v + 3]));
-                                    qg.z = pack_bf16(__uint_as_float(g[8 * v + 4]), __uint_as_float(g[8 * v + 5]));
-                                    qg.w = pack_bf16(__uint_as_float(g[8 * v + 6]), __uint_as_float(g[8 * v + 7]));
-                                    qu.x = pack_bf16(__uint_as_float(u[8 * v]), __uint_as_float(u[8 * v + 1]));
-                                    qu.y = pack_bf16(__uint_as_float(u[8 * v + 2]), __uint_as_float(u[8 * v + 3]));
-                                    qu.z = pack_bf16(__uint_as_float(u[8 * v + 4]), __uint_as_float(u[8 * v + 5]));
-                                    qu.w = pack_bf16(__uint_as_float(u[8 * v + 6]), __uint_as_float(u[8 * v + 7]));
-                                    *reinterpret_cast<uint4 *>(pg + 8 * v) = qg;
-                                    *reinterpret_cast<uint4 *>(pg + n_out + 8 * v) = qu;
-                                }
-                        }
 #pragma unroll
                         for (int i = 0; i < 16; i++) {
                             float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
                             float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
                             o[i] = pack_bf16(silu_f(g0) * u0, silu_f(g1) * u1);
                         }
-                    } else if constexpr (EXTRA == kSwigluBwd) {
-                        // dh chunk -> dg, du for the same 32 columns of this thread's row; nothing is staged
-                        const int dcol = tc.nt * 256 + col;
-                        const size_t off = (size_t)(tc.mt * BLOCK_M + r) * (2 * n_out) + dcol;
-                        uint4 qg[4], qu[4];
-#pragma unroll
-                        for (int v = 0; v < 4; v++)
-                            if (dcol + 8 * v < n_out) {
-                                qg[v] = *reinterpret_cast<const uint4 *>(aux0 + off + 8 * v);
-                                qu[v] = *reinterpret_cast<const uint4 *>(aux0 + off + n_out + 8 * v);
-                            }
-                        uint32_t a[32];
-                        tc_ld32(t_acc + col, a);
-                        tc_wait_ld();
-                        if (p == kPasses - 1 && c == 1) {
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(tempty_bar(as));
-                        }
-#pragma unroll
-                        for (int v = 0; v < 4; v++)
-                            if (dcol + 8 * v < n_out) {
-                                float gv[8], uv[8];
-                                unpack8_bf16(qg[v], gv);
-                                unpack8_bf16(qu[v], uv);
-                                uint32_t og[4], ou[4];
-#pragma unroll
-                                for (int i = 0; i < 4; i++) {
-                                    float dgv[2], duv[2];
-#pragma unroll
-                                    for (int q = 0; q < 2; q++) {
-                                        const float x = gv[2 * i + q], dv = __uint_as_float(a[8 * v + 2 * i + q]);
-                                        const float sg = __fdividef(1.0f, 1.0f + __expf(-x));
-                                        duv[q] = dv * (x * sg);
-                                        dgv[q] = (dv * uv[2 * i + q]) * (sg * (1.0f + x * (1.0f - sg)));
-                                    }
-                                    og[i] = pack_bf16(dgv[0], dgv[1]);
-                                    ou[i] = pack_bf16(duv[0], duv[1]);
-                                }
-                                *reinterpret_cast<uint4 *>(aux1 + off + 8 * v) = make_uint4(og[0], og[1], og[2], og[3]);
-                                *reinterpret_cast<uint4 *>(aux1 + off + n_out + 8 * v) =
-                                    make_uint4(ou[0], ou[1], ou[2], ou[3]);
-                            }
-                        continue;  // next chunk: no staging, no store through map_out
                     } else {
                         uint32_t a[32];
                         tc_ld32(t_acc + col, a);
@@ -343,16 +260,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                      : "memory");
                     }
                 }
-                if constexpr (EXTRA != kSwigluBwd) {
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    asm volatile("bar.sync 1, 256;" ::: "memory");
-                    if (warp == 2 && lane == 0) {
-                        const int x0 = tc.nt * (SWIGLU ? 128 : 256) + p * 128;
-                        const int y0 = tc.mt * BLOCK_M;
-                        if (x0 < n_out) tma_store_2d(&map_out, out_stage, x0, y0);
-                        if (x0 + 64 < n_out) tma_store_2d(&map_out, out_stage + kOutSubBytes, x0 + 64, y0);
-                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    const int x0 = tc.nt * (SWIGLU ? 128 : 256) + p * 128;
+                    const int y0 = tc.mt * BLOCK_M;
+                    if (x0 < n_out) tma_store_2d(&map_out, out_stage, x0, y0);
+                    if (x0 + 64 < n_out) tma_store_2d(&map_out, out_stage + kOutSubBytes, x0 + 64, y0);
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
             if (warp == 2 && lane == 0) TRACE(ti, 3);
@@ -457,40 +372,6 @@ cudaError_t launch_grouped_plain(omoe_handle *h, cudaStream_t s, const CUtensorM
     static int band = getenv("OMOE_BAND_DOWN") ? atoi(getenv("OMOE_BAND_DOWN")) : 16;
     grouped_gemm_kernel<false><<<dim3(h->sm_count), dim3(kThreads), kSmemBytes, s>>>(
         a, b, b, c, n_out, K, h->ex_tile_expert, h->ex_poffsets, h->e_local, band, h->dev_err);
-    return cudaGetLastError();
-}
-
-// Training forward: h = silu(g) * u as in the inference kernel, and g, u kept in gu [rows_cap, 2*dff].
-cudaError_t launch_up_gate_keep(omoe_handle *h, cudaStream_t s, void *gu) {
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<true, kKeepGU>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
-    }
-    static int band = getenv("OMOE_BAND_UP") ? atoi(getenv("OMOE_BAND_UP")) : 16;
-    grouped_gemm_kernel<true, kKeepGU><<<dim3(h->sm_count), dim3(kThreads), kSmemBytes, s>>>(
-        h->maps.a_x, h->maps.b_gate, h->maps.b_up, h->maps.a_h, h->cfg.d_ff, h->cfg.d_model, h->ex_tile_expert,
-        h->ex_poffsets, h->e_local, band, h->dev_err, static_cast<__nv_bfloat16 *>(gu), nullptr);
-    return cudaGetLastError();
-}
-
-// Backward: [dg | du] = SwiGLU-backward(dyp * W_down, g, u) in one kernel; a = dyp, b = W_down^T [El*dff, d].
-cudaError_t launch_dh_swiglu_bwd(omoe_handle *h, cudaStream_t s, const CUtensorMap &a, const CUtensorMap &b,
-                                 const void *gu, void *dgu) {
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<false, kSwigluBwd>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
-    }
-    static int band = getenv("OMOE_BAND_DOWN") ? atoi(getenv("OMOE_BAND_DOWN")) : 16;
-    grouped_gemm_kernel<false, kSwigluBwd><<<dim3(h->sm_count), dim3(kThreads), kSmemBytes, s>>>(
-        a, b, b, a /*unused*/, h->cfg.d_ff, h->cfg.d_model, h->ex_tile_expert, h->ex_poffsets, h->e_local, band,
-        h->dev_err, const_cast<__nv_bfloat16 *>(static_cast<const __nv_bfloat16 *>(gu)),
-        static_cast<__nv_bfloat16 *>(dgu));
     return cudaGetLastError();
 }
 
