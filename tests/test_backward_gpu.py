@@ -82,7 +82,10 @@ def test_bf16_backward_matches_oracle(oracle, T, d, dff, E, k, io):
     assert_close_bf16(got["y"], r.y)
     ref = oracle.moe_backward(x, w_r, w_g, w_u, w_d, k, dy, bf16=True, out_bf16=out_bf16)
     for name in NAMES:
-        assert_close_bf16(got[name], getattr(ref, name))
+        try:
+            assert_close_bf16(got[name], getattr(ref, name))
+        except AssertionError as e:
+            raise AssertionError(f"{name}: {e}") from None
     for e in np.nonzero(r.counts == 0)[0]:
         assert not got["d_w_gate"][e].any() and not got["d_w_up"][e].any() and not got["d_w_down"][e].any()
 
