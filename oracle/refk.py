@@ -63,6 +63,18 @@ def silu(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def silu_backward(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    diff = torch.empty_like(x)
+    _check(lib().refk_silu_backward(_p(x), _p(x), _p(delta), _p(diff), x.numel()))
+    return diff
+
+
+def softmax_back(out: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    diff = torch.empty_like(out)
+    _check(lib().refk_softmax_back(_p(out), _p(delta), _p(diff), out.shape[0], out.shape[1]))
+    return diff
+
+
 def mul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     out = torch.empty_like(a)
     _check(lib().refk_mul(_p(a), _p(b), _p(out), a.numel()))

@@ -10,6 +10,7 @@
 //                 (grid ceil(rows/1024), block 1024: one thread per row)
 //   SiLU          activeFunction.cu:173 `silu_forward`, launched as
 //                 nn/layer/active/gpu/SiLUKernel.java:125-146 (grid ceil(n/1024), block 1024)
+//   backward      activeFunction.cu:182 `silu_backward`, SoftmaxKernel.cu:101 `softmax_back` (same launch shapes)
 //   product       OPKernel.cu:1040 `mul_kernel`, launched as ad/op/gpu/OPKernel.java:742-758
 //   RMSNorm       RMSKernel.cu:185 `rmsnorm_forward_kernel2`, launched as
 //                 nn/layer/normalization/gpu/RMSKernel.java:232-249 (grid ceil((B*32+1023)/1024), block 1024)
@@ -26,9 +27,9 @@
 
 namespace {
 
-char g_err[512] = "";
+char g_err[1280] = "";
 CUmodule g_mod[4];
-CUfunction g_softmax, g_silu, g_mul, g_rms;
+CUfunction g_softmax, g_silu, g_mul, g_rms, g_silu_back, g_softmax_back;
 cublasHandle_t g_blas = nullptr;
 bool g_ready = false;
 constexpr int kThreads = 1024;  // CAFFE_CUDA_NUM_THREADS in every wrapper class
@@ -72,6 +73,10 @@ int refk_init(const char *dir) {
     if ((r = cuModuleGetFunction(&g_mul, g_mod[2], "mul_kernel")) != CUDA_SUCCESS) return fail("mul_kernel", (int)r);
     if ((r = cuModuleGetFunction(&g_rms, g_mod[3], "rmsnorm_forward_kernel2")) != CUDA_SUCCESS)
         return fail("rmsnorm_forward_kernel2", (int)r);
+    if ((r = cuModuleGetFunction(&g_silu_back, g_mod[1], "silu_backward")) != CUDA_SUCCESS)
+        return fail("silu_backward", (int)r);
+    if ((r = cuModuleGetFunction(&g_softmax_back, g_mod[0], "softmax_back")) != CUDA_SUCCESS)
+        return fail("softmax_back", (int)r);
     cublasStatus_t bs = cublasCreate(&g_blas);
     if (bs != CUBLAS_STATUS_SUCCESS) return fail("cublasCreate", (int)bs);
     g_ready = true;
@@ -86,6 +91,19 @@ int refk_softmax(float *in, float *out, int rows, int n) {
 int refk_silu(float *x, float *out, int n) {
     void *p[] = {&x, &out, &n};
     return launch(g_silu, blocks(n), p);
+}
+
+// silu_backward(x, output, delta, diff, n): activeFunction.cu:182, launched as SiLUKernel.backward does
+// (grid ceil(n/1024), block 1024); `output` is not read by the kernel.
+int refk_silu_backward(float *x, float *out, float *delta, float *diff, int n) {
+    void *p[] = {&x, &out, &delta, &diff, &n};
+    return launch(g_silu_back, blocks(n), p);
+}
+
+// softmax_back(output, delta, diff, batch, n): SoftmaxKernel.cu:101, one thread per row.
+int refk_softmax_back(float *out, float *delta, float *diff, int rows, int n) {
+    void *p[] = {&out, &delta, &diff, &rows, &n};
+    return launch(g_softmax_back, blocks(rows), p);
 }
 
 int refk_mul(float *a, float *b, float *r, int n) {

@@ -49,6 +49,18 @@ def test_silu_kernel_pins_the_oracle(oracle, refk):
     np.testing.assert_allclose(oracle.silu(x), got, rtol=2e-6, atol=1e-9)
 
 
+def test_backward_kernels_pin_the_oracle(oracle, refk):
+    rng = np.random.default_rng(10)
+    x = (3 * rng.standard_normal(5000)).astype(np.float32)
+    dl = rng.standard_normal(5000).astype(np.float32)
+    got = refk.silu_backward(dev(x), dev(dl)).cpu().numpy()
+    np.testing.assert_allclose(oracle.silu_backward(x, dl), got, rtol=3e-6, atol=1e-7)
+    p = oracle.softmax_rows((2 * rng.standard_normal((300, 64))).astype(np.float32))
+    dp = rng.standard_normal((300, 64)).astype(np.float32)
+    got = refk.softmax_back(dev(p), dev(dp)).cpu().numpy()
+    np.testing.assert_allclose(oracle.softmax_back_rows(p, dp), got, rtol=1e-5, atol=1e-7)
+
+
 def test_mul_kernel_is_a_plain_product(refk):
     rng = np.random.default_rng(7)
     a, b = rng.standard_normal(4097).astype(np.float32), rng.standard_normal(4097).astype(np.float32)
