@@ -189,40 +189,100 @@ public class MoELayer extends Layer {
         }
     }
 
-    // ---- training surface: this layer is forward-only ----
+    // ---- training surface (LlamaMLPLayer.java:139-158, 182-237 is the pattern) ----
+    private Tensor packedDGate, packedDUp, packedDDown;
+    private boolean training;
+
+    /** Switches the native layer to training mode (forwards keep g, u, h and the routing). */
+    public void setTraining(boolean on) {
+        check(OmoeNative.setTraining(handle, on ? 1 : 0));
+        training = on;
+    }
+
     @Override
     public void initBack() {
+        if (this.diff == null || this.number != this.diff.number) {
+            this.diff = new Tensor(number, 1, 1, embedDim, true, true);
+        }
+        if (packedDGate == null) {
+            packedDGate = new Tensor(numExperts, 1, dff, embedDim, true, true);
+            packedDUp = new Tensor(numExperts, 1, dff, embedDim, true, true);
+            packedDDown = new Tensor(numExperts, 1, embedDim, dff, true, true);
+            router.initBack();
+            for (int e = 0; e < numExperts; e++) {
+                gate[e].initBack();
+                up[e].initBack();
+                down[e].initBack();
+            }
+        }
     }
 
     @Override
     public void initParam() {
     }
 
+    private static void copyFrom(Tensor dst, Tensor src, long floatOffset) {
+        JCuda.cudaMemcpy(dst.getGpuData(), src.getGpuData().withByteOffset(floatOffset * Sizeof.FLOAT),
+                (long) dst.dataLength * Sizeof.FLOAT, cudaMemcpyKind.cudaMemcpyDeviceToDevice);
+    }
+
+    /** One native call computes diff and every diffW; the packed gradients are then handed to the FullyLayers
+     *  whose updaters the network already walks (FullyLayer.java:57-70, 292-301). */
     @Override
     public void diff() {
-        throw new UnsupportedOperationException("MoELayer: backward is not implemented");
+        if (!training) {
+            throw new IllegalStateException("MoELayer: call setTraining(true) before the forward of a training step");
+        }
+        check(OmoeNative.backward(handle, addr(input.getGpuData()), addr(delta.getGpuData()), addr(diff.getGpuData()),
+                number, OmoeNative.F32));
+        check(OmoeNative.getWeightGrads(handle, addr(router.diffW.getGpuData()),
+                bias ? addr(router.diffB.getGpuData()) : 0L, addr(packedDGate.getGpuData()),
+                addr(packedDUp.getGpuData()), addr(packedDDown.getGpuData())));
+        for (int e = 0; e < numExperts; e++) {
+            copyFrom(gate[e].diffW, packedDGate, (long) e * dff * embedDim);
+            copyFrom(up[e].diffW, packedDUp, (long) e * dff * embedDim);
+            copyFrom(down[e].diffW, packedDDown, (long) e * embedDim * dff);
+        }
     }
 
     @Override
     public void back() {
-        diff();
+        this.initBack();
+        this.setDelta();
+        this.diff();
     }
 
     @Override
     public void back(Tensor delta) {
-        diff();
+        this.initBack();
+        this.setDelta(delta);
+        this.diff();
     }
 
     @Override
     public void backTemp() {
     }
 
+    /** The FullyLayers' own updaters change the weights; the native copies follow. */
     @Override
     public void update() {
+        router.update();
+        for (int e = 0; e < numExperts; e++) {
+            gate[e].update();
+            up[e].update();
+            down[e].update();
+        }
+        syncWeights();
     }
 
     @Override
     public void accGrad(float scale) {
+        router.accGrad(scale);
+        for (int e = 0; e < numExperts; e++) {
+            gate[e].accGrad(scale);
+            up[e].accGrad(scale);
+            down[e].accGrad(scale);
+        }
     }
 
     @Override

@@ -43,6 +43,15 @@ public final class OmoeNative {
     public static native int getRouting(long handle, int[] topkIdx, float[] topkW, int[] counts, int[] offsets,
                                         int[] perm);
 
+    /** omoe_set_training: forwards keep what the backward pass needs. */
+    public static native int setTraining(long handle, int on);
+
+    /** omoe_backward: device addresses of the forward's input, of delta and of diff (all [tokens, d_model]). */
+    public static native int backward(long handle, long xDev, long dyDev, long dxDev, int tokens, int ioDtype);
+
+    /** omoe_get_weight_grads: fp32 device addresses (0 = skip): router [E,d], bias [E], gate/up [E,dff,d], down [E,d,dff]. */
+    public static native int getWeightGrads(long handle, long dRouter, long dBias, long dGate, long dUp, long dDown);
+
     public static native int epExport(long handle, byte[] blob192);
 
     public static native int epImport(long handle, byte[] allBlobs);

@@ -73,6 +73,20 @@ JFN(jint, getRouting)(JNIEnv *env, jclass c, jlong h, jintArray idx, jfloatArray
     return rc;
 }
 
+JFN(jint, setTraining)(JNIEnv *env, jclass c, jlong h, jint on) {
+    return omoe_set_training((omoe_handle *)(intptr_t)h, on);
+}
+
+JFN(jint, backward)(JNIEnv *env, jclass c, jlong h, jlong x, jlong dy, jlong dx, jint T, jint io) {
+    return omoe_backward((omoe_handle *)(intptr_t)h, (const void *)(intptr_t)x, (const void *)(intptr_t)dy,
+                         (void *)(intptr_t)dx, T, io, NULL);
+}
+
+JFN(jint, getWeightGrads)(JNIEnv *env, jclass c, jlong h, jlong dr, jlong db, jlong dg, jlong du, jlong dd) {
+    return omoe_get_weight_grads((omoe_handle *)(intptr_t)h, (float *)(intptr_t)dr, (float *)(intptr_t)db,
+                                 (float *)(intptr_t)dg, (float *)(intptr_t)du, (float *)(intptr_t)dd, NULL);
+}
+
 JFN(jint, epExport)(JNIEnv *env, jclass c, jlong h, jbyteArray blob) {
     jbyte *p = (*env)->GetByteArrayElements(env, blob, NULL);
     int rc = omoe_ep_export((omoe_handle *)(intptr_t)h, p);
