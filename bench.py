@@ -241,6 +241,18 @@ def run_ours(args, cfg):
     for _ in range(args.warmup):
         layer.forward_device(x, y)
     barrier()
+    step = lambda: layer.forward_device(x, y)
+    if args.graph:
+        # the forward only enqueues kernels (the expert-parallel flags and sequence number live on the device),
+        # so one capture replays as many steps as wanted: what a serving loop does for launch-bound decode steps
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            layer.forward_device(x, y)
+        launches_per_step = layer.launch_count()
+        step = graph.replay
+        for _ in range(3):
+            step()
+        barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -248,12 +260,12 @@ def run_ours(args, cfg):
     barrier()
     ev0.record()
     for _ in range(args.steps):
-        layer.forward_device(x, y)
+        step()
     ev1.record()
     barrier()
     ms = ev0.elapsed_time(ev1)
     clocks = sampler.stop() if rank == 0 else None
-    launches = layer.launch_count() * args.steps
+    launches = (launches_per_step if args.graph else layer.launch_count()) * args.steps
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -385,7 +397,8 @@ def run_ours(args, cfg):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
         "config": {"workload": cfg["name"] + (" + RMSNorm + residual" if args.block else ""), "tokens_global": T, "tokens_per_gpu": T_local, "experts_per_gpu": El,
-                   "parallelism": f"ep{world}", "l2": l2_note},
+                   "parallelism": f"ep{world}", "l2": l2_note,
+                   "launch": "cuda graph replay" if args.graph else "direct calls"},
         "stage_ms": stage_ms,
         "layer_tflops": alg["total_flops"] / (ms_per_step * 1e-3) / 1e12,
         "roofline": roof, "cpu_baseline": cpu, "clocks": clocks,
@@ -410,6 +423,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override the token count (decode sweep)")
     ap.add_argument("--cpu-tokens", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="time replays of one captured forward (CUDA graph) instead of direct calls")
     ap.add_argument("--train", action="store_true",
                     help="also time a training step (training-mode forward + backward) on one GPU; adds a 'train' object")
     ap.add_argument("--block", action="store_true",

@@ -50,7 +50,7 @@ combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const OT
     if (wait.flags != nullptr) {
         // expert-parallel return: rows are read from the owners' output buffers
         // over NVLink once every rank has published them
-        if ((int)threadIdx.x < wait.world) ep_wait_flag(wait.flags + threadIdx.x, wait.seq, wait.timeout_ns, dev_err);
+        if ((int)threadIdx.x < wait.world) ep_wait_flag(wait.flags + threadIdx.x, *wait.seq, wait.timeout_ns, dev_err);
         __syncthreads();
     }
     if (t >= T) return;

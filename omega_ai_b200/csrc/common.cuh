@@ -161,15 +161,17 @@ bool build_tensor_maps(omoe_handle *h);
 int router_tokens_per_block(int E);
 
 // Flag words the expert-parallel kernels exchange through peer-mapped memory.
+// The step's sequence number lives in device memory (the count-exchange kernel, first of a step, advances
+// it): no kernel argument changes from step to step, so a captured forward replays correctly.
 struct EpSignal {
     uint32_t *const *flags;  // device table [world]: address of flag_rows[0] on every rank
     int world, rank;
-    uint32_t seq;
+    const uint32_t *seq;     // device: sequence number of the running step
 };
 struct EpWait {
     const uint32_t *flags;   // this rank's flag_yp[world]
     int world;
-    uint32_t seq;
+    const uint32_t *seq;     // device: sequence number of the running step
     unsigned long long timeout_ns;
 };
 

@@ -47,7 +47,7 @@ struct EpState {
     int32_t *ex_counts, *ex_poffsets, *ex_tile_expert;  // layout of the rows this rank receives
     void *peer_ptrs[kMaxWorld][3];  // opened IPC mappings (ctl, xp, yp), null for self
     bool imported;
-    uint32_t seq;
+    uint32_t *d_seq;  // device: sequence number of the last step started on this rank
     unsigned long long timeout_ns;
 };
 
@@ -63,7 +63,7 @@ __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
 // One block of 256 threads.
 __global__ void __launch_bounds__(256)
 ep_exchange_kernel(EpCtl *self, EpCtl *const *__restrict__ peers, const int32_t *__restrict__ counts, int W, int r,
-                   int E, int El, uint32_t seq, int rows_cap, int32_t *__restrict__ dst_base,
+                   int E, int El, uint32_t *seq_ptr, int rows_cap, int32_t *__restrict__ dst_base,
                    int32_t *__restrict__ ex_counts, int32_t *__restrict__ ex_poffsets,
                    int32_t *__restrict__ ex_tile_expert, int max_tiles, int32_t *ticket, int32_t *dev_err,
                    unsigned long long timeout_ns) {
@@ -72,8 +72,13 @@ ep_exchange_kernel(EpCtl *self, EpCtl *const *__restrict__ peers, const int32_t 
     __shared__ int32_t s_rpoff[kMaxExperts + kMaxWorld];  // padded start of expert e in its owner's buffer
     __shared__ int32_t s_mypoff[kMaxExperts + 1];
     __shared__ int s_bad;
-    const int tid = threadIdx.x, par = seq & 1u;
-    if (tid == 0) { *ticket = 0; s_bad = 0; }
+    __shared__ uint32_t s_seq;
+    const int tid = threadIdx.x;
+    // a new step begins: this kernel is the first of the step to need the number, the later ones read it
+    if (tid == 0) { s_seq = *seq_ptr + 1u; *seq_ptr = s_seq; *ticket = 0; s_bad = 0; }
+    __syncthreads();
+    const uint32_t seq = s_seq;
+    const int par = seq & 1u;
     // publish my counts to every rank (my own included)
     for (int i = tid; i < W * E; i += blockDim.x) {
         int q = i / E, e = i % E;
@@ -138,15 +143,15 @@ ep_exchange_kernel(EpCtl *self, EpCtl *const *__restrict__ peers, const int32_t 
     }
 }
 
-__global__ void ep_wait_kernel(const uint32_t *flags, int W, uint32_t seq, int32_t *dev_err,
+__global__ void ep_wait_kernel(const uint32_t *flags, int W, const uint32_t *seq, int32_t *dev_err,
                                unsigned long long timeout_ns) {
-    if ((int)threadIdx.x < W) ep_wait_flag(flags + threadIdx.x, seq, timeout_ns, dev_err);
+    if ((int)threadIdx.x < W) ep_wait_flag(flags + threadIdx.x, *seq, timeout_ns, dev_err);
 }
 
 // flags[q] points at the flag array on rank q; slot `r` there belongs to this rank.
-__global__ void ep_signal_kernel(uint32_t *const *flags, int W, int r, uint32_t seq) {
+__global__ void ep_signal_kernel(uint32_t *const *flags, int W, int r, const uint32_t *seq) {
     __threadfence_system();
-    if ((int)threadIdx.x < W) st_release_sys(flags[threadIdx.x] + r, seq);
+    if ((int)threadIdx.x < W) st_release_sys(flags[threadIdx.x] + r, *seq);
 }
 
 int ep_fail(omoe_handle *h, int code, const char *what, cudaError_t e) {
@@ -167,14 +172,15 @@ int ep_create(omoe_handle *h) {
     if ((e = cudaMalloc(&st->d_ctl_table, sizeof(void *) * W)) != cudaSuccess ||
         (e = cudaMalloc(&st->d_rows_flags, sizeof(void *) * W)) != cudaSuccess ||
         (e = cudaMalloc(&st->d_out_flags, sizeof(void *) * W)) != cudaSuccess ||
+        (e = cudaMalloc(&st->d_seq, sizeof(uint32_t))) != cudaSuccess ||
         (e = cudaMalloc(&st->ex_counts, sizeof(int32_t) * El)) != cudaSuccess ||
         (e = cudaMalloc(&st->ex_poffsets, sizeof(int32_t) * (El + 1))) != cudaSuccess ||
         (e = cudaMalloc(&st->ex_tile_expert, sizeof(int32_t) * (h->rows_cap / kRowAlign))) != cudaSuccess)
         return ep_fail(h, OMOE_ERR_NOMEM, "cudaMalloc(expert-parallel state)", e);
+    cudaMemset(st->d_seq, 0, sizeof(uint32_t));
     h->ex_counts = st->ex_counts;
     h->ex_poffsets = st->ex_poffsets;
     h->ex_tile_expert = st->ex_tile_expert;
-    st->seq = 0;
     st->timeout_ns = 10ull * 1000 * 1000 * 1000;
     if (const char *v = getenv("OMOE_EP_WAIT_MS")) {
         long ms = atol(v);
@@ -189,7 +195,7 @@ void ep_destroy(omoe_handle *h) {
     for (int q = 0; q < kMaxWorld; q++)
         for (int i = 0; i < 3; i++)
             if (st->peer_ptrs[q][i]) cudaIpcCloseMemHandle(st->peer_ptrs[q][i]);
-    void *ptrs[] = {st->ctl, st->d_ctl_table, st->d_rows_flags, st->d_out_flags, st->ex_counts, st->ex_poffsets,
+    void *ptrs[] = {st->ctl, st->d_ctl_table, st->d_rows_flags, st->d_out_flags, st->d_seq, st->ex_counts, st->ex_poffsets,
                     st->ex_tile_expert};
     for (void *p : ptrs)
         if (p) cudaFree(p);
@@ -263,7 +269,7 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
         return OMOE_ERR_STATE;
     }
     const int W = h->cfg.world, r = h->cfg.rank, E = h->cfg.n_experts, El = h->e_local;
-    const uint32_t seq = ++st->seq;
+    uint32_t *const seq = st->d_seq;  // advanced on the device by the count exchange
     int n = 0;
     cudaError_t e = cudaSuccess;
     const bool prof = h->profiling;

@@ -158,7 +158,7 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
         if (s_last && (int)threadIdx.x < sig.world) {
             __threadfence_system();
             uint32_t *f = sig.flags[threadIdx.x] + sig.rank;
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(sig.seq) : "memory");
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(*sig.seq) : "memory");
         }
     }
 }
