@@ -161,7 +161,7 @@ OMOE_API int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host,
  * d W_gate, d W_up [E, d_ff, d_model], d W_down [E, d_model, d_ff], d W_router [E, d_model],
  * d router_bias [E].  The expert picks are constants (no gradient flows through the selection); the gate
  * weights' gradient reaches the router through the renormalisation and the reference's softmax_back rule
- * (src/main/resources/cu/SoftmaxKernel.cu:100-112).  No auxiliary load-balancing loss is added.
+ * (src/main/resources/cu/SoftmaxKernel.cu:100-112).
  * omoe_forward_block's RMSNorm and residual are not differentiated here: call omoe_backward with the
  * normalised rows' gradient handling left to the caller, or use omoe_forward.  Does not synchronise the host.
  *
@@ -173,6 +173,19 @@ OMOE_API int omoe_backward(omoe_handle *h, const void *x_dev, const void *dy_dev
                            int32_t io_dtype, void *cuda_stream);
 OMOE_API int omoe_get_weight_grads(omoe_handle *h, float *d_router, float *d_router_bias, float *d_gate,
                                    float *d_up, float *d_down, void *cuda_stream);
+
+/*
+ * Auxiliary load-balancing loss (no reference counterpart; the usual switch-routing form):
+ *   L = E * sum_e f_e * P_e,  f_e = counts[e] / (T * top_k),  P_e = mean over the step's tokens of the
+ *   router probability of expert e.
+ * omoe_set_aux_loss(h, coef) (training mode on) makes every following omoe_backward return the gradients of
+ * <dy, y> + coef * L: the extra term coef * E * f_e / T enters at the router's probabilities (f_e is a
+ * constant) and reaches d W_router, d router_bias and dx.  coef = 0 (the default) switches it off.
+ * omoe_get_aux_loss writes L of the last forward to *loss_host; it launches one small kernel on that
+ * forward's stream and synchronises it.
+ */
+OMOE_API int omoe_set_aux_loss(omoe_handle *h, float coef);
+OMOE_API int omoe_get_aux_loss(omoe_handle *h, float *loss_host);
 
 /*
  * Routing results of the last forward on this rank, copied to HOST buffers

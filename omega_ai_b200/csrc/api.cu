@@ -432,6 +432,16 @@ int omoe_get_weight_grads(omoe_handle *h, float *d_router, float *d_router_bias,
     return check_dev_err(h);
 }
 
+int omoe_set_aux_loss(omoe_handle *h, float coef) {
+    if (!h) return OMOE_ERR_INVALID;
+    return bw_set_aux(h, coef);
+}
+
+int omoe_get_aux_loss(omoe_handle *h, float *loss_host) {
+    if (!h || !loss_host) return OMOE_ERR_INVALID;
+    return bw_aux_loss(h, loss_host, h->last_stream);
+}
+
 int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host, int32_t T, int32_t io_dtype,
                       void *cuda_stream) {
     if (!h) return OMOE_ERR_INVALID;

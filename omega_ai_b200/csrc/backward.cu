@@ -38,6 +38,8 @@ struct BwState {
     bool fwd_valid;   // the last forward ran in training mode and its saved rows are intact
     bool wt_valid;    // transposed weight copies match the current weights
     int fwd_T;
+    float aux_coef;   // weight of the auxiliary load-balancing loss in the objective (0: none)
+    float *aux_ps;    // [E] column sums of the router probabilities (omoe_get_aux_loss)
     void *gu;         // [rows_cap, 2*dff] g | u (compute dtype)
     void *dyp;        // [rows_cap, d]
     void *dh;         // [rows_cap, dff]
@@ -152,7 +154,8 @@ __global__ void __launch_bounds__(256)
 combine_bwd_kernel(const OT *__restrict__ dy, const YT *__restrict__ yp, YT *__restrict__ dyp,
                    const int32_t *__restrict__ pos, const int32_t *__restrict__ topk_idx,
                    const float *__restrict__ topk_w, const float *__restrict__ logits, float *__restrict__ dgw,
-                   float *__restrict__ dl, int T, int d, int k, int E, int renorm) {
+                   float *__restrict__ dl, int T, int d, int k, int E, int renorm, float aux_c,
+                   const int32_t *__restrict__ counts) {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= T) return;
@@ -190,21 +193,53 @@ combine_bwd_kernel(const OT *__restrict__ dy, const YT *__restrict__ yp, YT *__r
             ssum += expf(lg[topk_idx[(size_t)t * k + j]] - mx) / sum;
             dot += dw[j] * topk_w[(size_t)t * k + j];
         }
-        // d p is zero off the picks; softmax_back: sum_i p_i dp_i, then (dp_i - sum) * p_i
+        // d p: the picks' terms, plus aux_c * f_e on every expert when the auxiliary loss is on (f_e = share
+        // of the step's picks that went to e; aux_c = coef * E / T).  softmax_back: sum_i p_i dp_i, then
+        // (dp_i - sum) * p_i.
+        const float inv_picks = 1.0f / ((float)T * (float)k);
         float pd = 0.f;
+        if (aux_c != 0.f)
+            for (int e = 0; e < E; e++) pd += (expf(lg[e] - mx) / sum) * (aux_c * ((float)counts[e] * inv_picks));
         for (int j = 0; j < k; j++) {
             const float p = expf(lg[topk_idx[(size_t)t * k + j]] - mx) / sum;
             const float dp = renorm ? (dw[j] - dot) / ssum : dw[j];
             pd += p * dp;
         }
-        for (int e = 0; e < E; e++) out[e] = (0.f - pd) * (expf(lg[e] - mx) / sum);
+        for (int e = 0; e < E; e++) {
+            const float a = aux_c != 0.f ? aux_c * ((float)counts[e] * inv_picks) : 0.f;
+            out[e] = (a - pd) * (expf(lg[e] - mx) / sum);
+        }
         for (int j = 0; j < k; j++) {
             const int e = topk_idx[(size_t)t * k + j];
             const float p = expf(lg[e] - mx) / sum;
-            const float dp = renorm ? (dw[j] - dot) / ssum : dw[j];
+            const float a = aux_c != 0.f ? aux_c * ((float)counts[e] * inv_picks) : 0.f;
+            const float dp = (renorm ? (dw[j] - dot) / ssum : dw[j]) + a;
             out[e] = (dp - pd) * p;
         }
     }
+}
+
+// ps[e] = sum_t softmax(logits[t, :])[e]: one block per expert, threads stride the tokens, fixed tree at the end.
+__global__ void __launch_bounds__(256)
+prob_colsum_kernel(const float *__restrict__ logits, float *__restrict__ ps, int T, int E) {
+    __shared__ float s[256];
+    const int e = blockIdx.x;
+    float acc = 0.f;
+    for (int t = threadIdx.x; t < T; t += 256) {
+        const float *lg = logits + (size_t)t * E;
+        float mx = lg[0];
+        for (int i = 1; i < E; i++) mx = fmaxf(mx, lg[i]);
+        float sum = 0.f;
+        for (int i = 0; i < E; i++) sum += expf(lg[i] - mx);
+        acc += expf(lg[e] - mx) / sum;
+    }
+    s[threadIdx.x] = acc;
+    __syncthreads();
+    for (int o = 128; o >= 1; o >>= 1) {
+        if ((int)threadIdx.x < o) s[threadIdx.x] += s[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) ps[e] = s[0];
 }
 
 // dx[t] = ((dxp[pos_0] + dxp[pos_1]) + ...) + sum_e dl[t,e] * W_r[e,:]   (one warp per token)
@@ -520,7 +555,8 @@ cudaError_t backward_t(omoe_handle *h, BwState *b, const void *x, const void *dy
     const int warps = 8, tblocks = ceil_div(T, warps);
     combine_bwd_kernel<CT, OT><<<tblocks, 256, 0, s>>>(
         static_cast<const OT *>(dy), static_cast<const CT *>(h->yp), static_cast<CT *>(b->dyp), h->pos, h->topk_idx,
-        h->topk_w, h->logits, b->dgw, b->dl, T, d, k, E, h->cfg.renormalize);
+        h->topk_w, h->logits, b->dgw, b->dl, T, d, k, E, h->cfg.renormalize,
+        b->aux_coef != 0.f ? b->aux_coef * (float)E / (float)T : 0.f, h->counts);
     zero_pad_rows_kernel<CT><<<dim3(El, 8), 256, 0, s>>>(static_cast<CT *>(b->dyp), d, h->ex_poffsets, h->ex_counts);
     BW_TRY(cudaGetLastError());
     *n += 2;
@@ -610,7 +646,7 @@ cudaError_t backward_t(omoe_handle *h, BwState *b, const void *x, const void *dy
 
 void free_state(BwState *b) {
     void *ptrs[] = {b->gu, b->dyp, b->dh, b->dgu, b->dxp, b->dgw, b->dl, b->dwr_part, b->wdT, b->wguT, b->xpT, b->hT,
-                    b->dypT, b->dguT, b->d_router, b->d_bias, b->d_gate, b->d_up, b->d_down};
+                    b->dypT, b->dguT, b->d_router, b->d_bias, b->d_gate, b->d_up, b->d_down, b->aux_ps};
     for (void *p : ptrs)
         if (p) cudaFree(p);
     delete b;
@@ -640,7 +676,7 @@ int bw_set_training(omoe_handle *h, int on) {
         {&b->gu, rows * 2 * dff * cs}, {&b->dyp, rows * d * cs}, {&b->dh, rows * dff * cs},
         {&b->dgu, rows * 2 * dff * cs}, {&b->dxp, rows * d * cs}, {(void **)&b->dgw, tm * k * 4},
         {(void **)&b->dl, tm * E * 4}, {(void **)&b->dwr_part, (size_t)b->dwr_slices * E * d * 4},
-        {(void **)&b->d_router, E * d * 4}, {(void **)&b->d_bias, E * 4}, {(void **)&b->d_gate, El * dff * d * 4},
+        {(void **)&b->d_router, E * d * 4}, {(void **)&b->d_bias, E * 4}, {(void **)&b->aux_ps, E * 4}, {(void **)&b->d_gate, El * dff * d * 4},
         {(void **)&b->d_up, El * dff * d * 4}, {(void **)&b->d_down, El * dff * d * 4}};
     bool ok = true;
     for (auto &x : bufs) ok = ok && cudaMalloc(x.p, x.bytes ? x.bytes : 1) == cudaSuccess;
@@ -768,6 +804,41 @@ int bw_get_grads(omoe_handle *h, float *d_router, float *d_bias, float *d_gate, 
             return OMOE_ERR_CUDA;
         }
     if (cudaStreamSynchronize(s) != cudaSuccess) return OMOE_ERR_CUDA;
+    return OMOE_OK;
+}
+
+int bw_set_aux(omoe_handle *h, float coef) {
+    BwState *b = static_cast<BwState *>(h->bw);
+    if (!b) {
+        snprintf(h->err, sizeof(h->err), "omoe_set_aux_loss: switch training mode on first");
+        return OMOE_ERR_STATE;
+    }
+    b->aux_coef = coef;
+    return OMOE_OK;
+}
+
+int bw_aux_loss(omoe_handle *h, float *loss_host, cudaStream_t s) {
+    BwState *b = static_cast<BwState *>(h->bw);
+    if (!b) {
+        snprintf(h->err, sizeof(h->err), "omoe_get_aux_loss: switch training mode on first");
+        return OMOE_ERR_STATE;
+    }
+    const int T = h->last_T, E = h->cfg.n_experts, k = h->cfg.top_k;
+    *loss_host = 0.f;
+    if (T == 0) return OMOE_OK;
+    prob_colsum_kernel<<<E, 256, 0, s>>>(h->logits, b->aux_ps, T, E);
+    float ps[kMaxExperts];
+    int32_t cnt[kMaxExperts];
+    if (cudaGetLastError() != cudaSuccess ||
+        cudaMemcpyAsync(ps, b->aux_ps, sizeof(float) * E, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaMemcpyAsync(cnt, h->counts, sizeof(int32_t) * E, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess) {
+        snprintf(h->err, sizeof(h->err), "omoe_get_aux_loss: CUDA error");
+        return OMOE_ERR_CUDA;
+    }
+    float loss = 0.f;
+    for (int e = 0; e < E; e++) loss += ((float)cnt[e] / ((float)T * (float)k)) * (ps[e] / (float)T);
+    *loss_host = (float)E * loss;
     return OMOE_OK;
 }
 

@@ -15,6 +15,8 @@ int bw_backward(omoe_handle *h, const void *x, const void *dy, void *dx, int T, 
                 int *launches);
 int bw_get_grads(omoe_handle *h, float *d_router, float *d_bias, float *d_gate, float *d_up, float *d_down,
                  cudaStream_t s);
+int bw_set_aux(omoe_handle *h, float coef);
+int bw_aux_loss(omoe_handle *h, float *loss_host, cudaStream_t s);
 void bw_destroy(omoe_handle *h);
 
 // 2-D bf16 tensor map: [rows, cols] with `ld` elements between rows, box box_rows x 64 columns, 128-byte swizzle.

@@ -242,6 +242,16 @@ class MoELayer(Layer):
                                                _dt(x.dtype), s))
         return dx
 
+    def set_aux_loss(self, coef: float):
+        """Weight of the auxiliary load-balancing loss E * sum_e f_e * P_e in the objective :meth:`backward` differentiates."""
+        check(self._h, self._lib.omoe_set_aux_loss(self._h, float(coef)))
+
+    def aux_loss(self) -> float:
+        """The auxiliary load-balancing loss of the last forward."""
+        v = C.c_float(0.0)
+        check(self._h, self._lib.omoe_get_aux_loss(self._h, C.byref(v)))
+        return float(v.value)
+
     def weight_grads(self, stream=None) -> dict:
         """fp32 device tensors d_router [E,d], d_bias [E], d_gate/d_up [E,dff,d], d_down [E,d,dff] of the last
         backward (diffW of the reference's FullyLayer, FullyLayer.java:292-301)."""

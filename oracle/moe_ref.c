@@ -478,11 +478,29 @@ void ref_softmax_back_rows(const float *out, const float *delta, float *diff, in
  * Rules with no reference counterpart: the picks are constants (no gradient through the selection);
  * with renormalised gates w_j = p_j / s, s = sum of the picked p, d p_j = (d w_j - sum_i d w_i w_i) / s;
  * d w_j = <dy[t], yp_j>; dx[t] = ((dxp_0 + dxp_1) + ...) in pick order, then the router's term
- * (sum over experts in index order, one chain) added last.  No auxiliary load-balancing loss.
+ * (sum over experts in index order, one chain) added last.  aux_coef != 0 adds aux_coef * L_aux
+ * (ref_aux_loss) to the objective: its gradient enters at the router's probabilities.
  * bf16 mode rounds where the tensor-core path stores bf16: xp, g, u, h, yp, dyp, dh, dg, du, dxp
  * (weight gradients and everything on the router's side stay fp32); dx is rounded when out_bf16. */
+/* Auxiliary load-balancing loss of a step (no reference counterpart; the usual switch-routing form):
+ *   L = E * sum_e f_e * P_e,  f_e = counts[e] / (T*k) (share of the picks that went to e, a constant),
+ *   P_e = (1/T) * sum_t p[t,e] (mean router probability).  Sums in index order.  T == 0: 0. */
+float ref_aux_loss(const float *logits, const int32_t *counts, int64_t T, int64_t E, int64_t k) {
+    if (T == 0) return 0.0f;
+    float *p = (float *)malloc(sizeof(float) * (size_t)(T * E));
+    ref_softmax_rows(logits, p, T, E);
+    float loss = 0.0f;
+    for (int64_t e = 0; e < E; e++) {
+        float ps = 0.0f;
+        for (int64_t t = 0; t < T; t++) ps += p[t * E + e];
+        loss += ((float)counts[e] / (float)(T * k)) * (ps / (float)T);
+    }
+    free(p);
+    return (float)E * loss;
+}
+
 void ref_moe_backward(const ref_moe_shape *s, const float *x, const float *w_r, const float *bias,
-                      const float *w_gate, const float *w_up, const float *w_down, const float *dy,
+                      const float *w_gate, const float *w_up, const float *w_down, const float *dy, float aux_coef,
                       float *dx, float *d_w_r, float *d_bias, float *d_w_gate, float *d_w_up, float *d_w_down,
                       int nthreads) {
     const int64_t T = s->T, d = s->d, dff = s->dff, E = s->E, k = s->k;
@@ -583,6 +601,10 @@ void ref_moe_backward(const ref_moe_shape *s, const float *x, const float *w_r, 
         } else {
             for (int64_t j = 0; j < k; j++) dp[t * E + idx[t * k + j]] = dgw[t * k + j];
         }
+        /* aux_coef * dL/dp[t,e] = aux_coef * E * f_e / T, added to every expert's entry */
+        if (aux_coef != 0.0f)
+            for (int64_t e = 0; e < E; e++)
+                dp[t * E + e] += (aux_coef * (float)E / (float)T) * ((float)counts[e] / (float)(T * k));
     }
     ref_softmax_back_rows(probs, dp, dl, T, E);
     /* router's FullyLayer.diff(): diffW = dl^T * x, diffB = column sums, diff = dl * W_r */

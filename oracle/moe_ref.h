@@ -104,9 +104,13 @@ void ref_softmax_back_rows(const float *out, const float *delta, float *diff, in
  * overwrites diffW).  Routing is recomputed from x; shape.pretransposed must be 0.  The rules and the
  * bf16 rounding points are stated at the definition. */
 void ref_moe_backward(const ref_moe_shape *shape, const float *x, const float *w_r, const float *bias,
-                      const float *w_gate, const float *w_up, const float *w_down, const float *dy,
+                      const float *w_gate, const float *w_up, const float *w_down, const float *dy, float aux_coef,
                       float *dx, float *d_w_r, float *d_bias, float *d_w_gate, float *d_w_up, float *d_w_down,
                       int nthreads);
+
+/* Auxiliary load-balancing loss L = E * sum_e (counts[e]/(T*k)) * mean_t p[t,e]; ref_moe_backward's aux_coef
+ * adds aux_coef * L to the objective whose gradient it returns. */
+float ref_aux_loss(const float *logits, const int32_t *counts, int64_t T, int64_t E, int64_t k);
 
 int ref_num_threads(void);
 

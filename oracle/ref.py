@@ -57,7 +57,9 @@ def lib():
         ]
         _lib.ref_silu_backward.argtypes = [fp, fp, fp, i64]
         _lib.ref_softmax_back_rows.argtypes = [fp, fp, fp, i64, i64]
-        _lib.ref_moe_backward.argtypes = [C.POINTER(_Shape)] + [fp] * 13 + [C.c_int]
+        _lib.ref_moe_backward.argtypes = [C.POINTER(_Shape)] + [fp] * 7 + [C.c_float] + [fp] * 6 + [C.c_int]
+        _lib.ref_aux_loss.argtypes = [fp, ip, i64, i64, i64]
+        _lib.ref_aux_loss.restype = C.c_float
         _lib.ref_num_threads.restype = C.c_int
     return _lib
 
@@ -236,8 +238,15 @@ class MoEGrads:
     d_w_down: np.ndarray
 
 
+def aux_loss(logits: np.ndarray, counts: np.ndarray, k: int) -> float:
+    """E * sum_e (counts[e]/(T*k)) * mean_t softmax(logits)[t,e]."""
+    logits = _cf(logits)
+    counts = np.ascontiguousarray(counts, dtype=np.int32)
+    return float(lib().ref_aux_loss(_f(logits), _i(counts), logits.shape[0], logits.shape[1], k))
+
+
 def moe_backward(x, w_r, w_gate, w_up, w_down, k: int, dy, *, bias=None, renorm=True, bf16=False,
-                 out_bf16=None, nthreads: int = 0) -> MoEGrads:
+                 out_bf16=None, aux_coef: float = 0.0, nthreads: int = 0) -> MoEGrads:
     """Gradients of the whole layer for ``dy`` [T,d]; same conventions as :func:`moe_forward`."""
     x, w_r, dy = _cf(x), _cf(w_r), _cf(dy)
     w_gate, w_up, w_down = _cf(w_gate), _cf(w_up), _cf(w_down)
@@ -253,7 +262,7 @@ def moe_backward(x, w_r, w_gate, w_up, w_down, k: int, dy, *, bias=None, renorm=
     g = MoEGrads(np.empty((T, d), np.float32), np.empty((E, d), np.float32), np.empty(E, np.float32),
                  np.empty((E, dff, d), np.float32), np.empty((E, dff, d), np.float32),
                  np.empty((E, d, dff), np.float32))
-    lib().ref_moe_backward(C.byref(shp), _f(x), _f(w_r), _f(bias), _f(w_gate), _f(w_up), _f(w_down), _f(dy),
+    lib().ref_moe_backward(C.byref(shp), _f(x), _f(w_r), _f(bias), _f(w_gate), _f(w_up), _f(w_down), _f(dy), float(aux_coef),
                            _f(g.dx), _f(g.d_w_r), _f(g.d_bias), _f(g.d_w_gate), _f(g.d_w_up), _f(g.d_w_down),
                            nthreads)
     return g

@@ -90,6 +90,38 @@ def test_bf16_backward_matches_oracle(oracle, T, d, dff, E, k, io):
         assert not got["d_w_gate"][e].any() and not got["d_w_up"][e].any() and not got["d_w_down"][e].any()
 
 
+@pytest.mark.parametrize("compute", [torch.float32, torch.bfloat16])
+def test_aux_loss_value_and_gradient(oracle, compute):
+    from omega_ai_b200 import MoELayer
+    T, d, dff, E, k = 200, 128, 256, 16, 2
+    x, w_r, w_g, w_u, w_d, _ = make_layer(T, d, dff, E, k, seed=24)
+    rb = oracle.bf16_round
+    x, w_r = rb(x), rb(w_r * 10)
+    dy = rb((0.01 * np.random.default_rng(7).standard_normal((T, d))).astype(np.float32))
+    bf = compute == torch.bfloat16
+    layer = MoELayer(d, dff, E, k, t_max=T, compute_dtype=compute)
+    layer.setWeights(dev(w_r, compute), dev(w_g, compute), dev(w_u, compute), dev(w_d, compute))
+    layer.set_training(True)
+    layer.set_aux_loss(0.5)
+    xd = dev(x, compute)
+    layer.forward_device(xd)
+    _, _, counts, _, _ = layer.routing(T)
+    want = oracle.aux_loss(layer.logits(T), counts, k)
+    assert abs(layer.aux_loss() - want) <= 1e-5 * want
+    dx = layer.backward(xd, dev(dy, compute)).float().cpu().numpy()
+    g = layer.weight_grads()
+    ref = oracle.moe_backward(x, w_r, w_g, w_u, w_d, k, dy, bf16=bf, aux_coef=0.5)
+    ref0 = oracle.moe_backward(x, w_r, w_g, w_u, w_d, k, dy, bf16=bf)
+    assert np.abs(ref.d_w_r - ref0.d_w_r).max() > 10 * np.abs(ref0.d_w_r).max() * 1e-3   # the term matters here
+    if bf:
+        assert_close_bf16(g["d_router"].cpu().numpy(), ref.d_w_r)
+        assert_close_bf16(dx, ref.dx)
+    else:
+        close_scaled(g["d_router"].cpu().numpy(), ref.d_w_r, "d_w_r", 2e-4)
+        close_scaled(dx, ref.dx, "dx", 2e-4)
+    layer.close()
+
+
 def test_backward_call_order_and_modes(oracle):
     from omega_ai_b200 import MoELayer
     from omega_ai_b200.native import OmoeError

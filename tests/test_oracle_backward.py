@@ -16,7 +16,7 @@ def autograd_grads(x, w_r, w_g, w_u, w_d, k, dy, bias=None, renorm=True):
     return (X, Wr, B, Wg, Wu, Wd), logits
 
 
-def run_autograd(oracle, x, w_r, w_g, w_u, w_d, k, dy, bias=None, renorm=True):
+def run_autograd(oracle, x, w_r, w_g, w_u, w_d, k, dy, bias=None, renorm=True, aux_coef=0.0):
     (X, Wr, B, Wg, Wu, Wd), logits = autograd_grads(x, w_r, w_g, w_u, w_d, k, dy, bias, renorm)
     r = oracle.moe_forward(x, w_r, w_g, w_u, w_d, k, bias=bias, renorm=renorm)
     idx = torch.tensor(r.topk_idx.astype(np.int64))
@@ -30,7 +30,12 @@ def run_autograd(oracle, x, w_r, w_g, w_u, w_d, k, dy, bias=None, renorm=True):
         u = torch.einsum("td,tfd->tf", X, Wu[e])
         h = torch.nn.functional.silu(g) * u
         y = y + w[:, j:j + 1] * torch.einsum("tf,tdf->td", h, Wd[e])
-    y.backward(torch.tensor(dy, dtype=torch.float64))
+    objective = (y * torch.tensor(dy, dtype=torch.float64)).sum()
+    if aux_coef:
+        T, E = p.shape
+        f = torch.tensor(r.counts.astype(np.float64)) / (T * k)
+        objective = objective + aux_coef * E * (f * p.mean(dim=0)).sum()
+    objective.backward()
     out = dict(dx=X.grad, d_w_r=Wr.grad, d_w_gate=Wg.grad, d_w_up=Wu.grad, d_w_down=Wd.grad)
     if B is not None:
         out["d_bias"] = B.grad
@@ -92,3 +97,21 @@ def test_elementwise_backward_rules(oracle):
     p.backward(torch.tensor(dp))
     got = oracle.softmax_back_rows(p.detach().numpy().astype(np.float32), dp.astype(np.float32))
     np.testing.assert_allclose(got, lg.grad.numpy(), rtol=1e-4, atol=1e-6)
+
+
+def test_aux_loss_value_and_gradient(oracle):
+    T, d, dff, E, k = 48, 32, 48, 8, 2
+    x, w_r, w_g, w_u, w_d, _ = make_layer(T, d, dff, E, k, seed=13)
+    w_r = (w_r * 20).astype(np.float32)
+    dy = (0.01 * np.random.default_rng(6).standard_normal((T, d))).astype(np.float32)
+    r = oracle.moe_forward(x, w_r, w_g, w_u, w_d, k)
+    p = torch.softmax(torch.tensor(r.logits, dtype=torch.float64), dim=1).numpy()
+    want = E * ((r.counts / (T * k)) * p.mean(axis=0)).sum()
+    assert abs(oracle.aux_loss(r.logits, r.counts, k) - want) < 1e-5
+    ref, _ = run_autograd(oracle, x, w_r, w_g, w_u, w_d, k, dy, aux_coef=0.5)
+    g = oracle.moe_backward(x, w_r, w_g, w_u, w_d, k, dy, aux_coef=0.5)
+    g0 = oracle.moe_backward(x, w_r, w_g, w_u, w_d, k, dy)
+    for name in ("dx", "d_w_r", "d_w_gate", "d_w_up", "d_w_down"):
+        close(getattr(g, name), ref[name], name)
+    assert np.abs(g.d_w_r - g0.d_w_r).max() > 1e-4          # the term is there
+    assert np.array_equal(g.d_w_down, g0.d_w_down)           # and touches the router's side only
