@@ -190,6 +190,8 @@ def run_ours(args, cfg):
     T, d, dff, E, k = cfg["T"], cfg["d"], cfg["dff"], cfg["E"], cfg["k"]
     if args.tokens:
         T = args.tokens
+    if args.weak:
+        T *= world   # weak scaling: the per-GPU share of the tokens stays that of the one-GPU run
     cdt = torch.bfloat16 if cfg["dtype"] == "bf16" else torch.float32
     peaks = load_peaks()
 
@@ -395,7 +397,7 @@ def run_ours(args, cfg):
     line = {
         "metric": "MoE-layer forward tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
+        "scaling": "weak" if args.weak else "strong", "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
         "config": {"workload": cfg["name"] + (" + RMSNorm + residual" if args.block else ""), "tokens_global": T, "tokens_per_gpu": T_local, "experts_per_gpu": El,
                    "parallelism": f"ep{world}", "l2": l2_note,
                    "launch": "cuda graph replay" if args.graph else "direct calls"},
@@ -423,6 +425,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override the token count (decode sweep)")
     ap.add_argument("--cpu-tokens", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--weak", action="store_true",
+                    help="weak scaling: the global token count is the configuration's times the number of GPUs")
     ap.add_argument("--graph", action="store_true",
                     help="time replays of one captured forward (CUDA graph) instead of direct calls")
     ap.add_argument("--train", action="store_true",
