@@ -5,8 +5,6 @@
 // No reference kernel exists for this stage; the nearest idiom is the
 // accumulate kernel axpy_kernel (src/main/java/com/omega/engine/gpu/BaseKernel.java:306-329)
 // and the residual add at LlamaTransformerBlock.java:136.
-#include <stdlib.h>
-
 #include "common.cuh"
 
 namespace omoe {
@@ -42,7 +40,7 @@ __device__ __forceinline__ void add_residual(const __nv_bfloat16 *r, float (&acc
 }
 
 // One warp per token, 8 columns per lane per step (16 bytes of bf16 / 32 bytes of fp32).
-template <typename YT, typename OT, int K, int U>
+template <typename YT, typename OT, int K>
 __global__ void __launch_bounds__(256)
 combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const OT *__restrict__ resid,
                const int32_t *__restrict__ pos, const int32_t *__restrict__ topk_idx,
@@ -78,97 +76,37 @@ combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const OT
     }
     const int cw = ((d / (int)gridDim.y + 7) / 8) * 8;  // blockIdx.y walks one slice of the row
     const int c_lo = blockIdx.y * cw, c_hi = min(d, c_lo + cw);
-    // U column chunks per step, all their loads issued before the first use: rows that come over NVLink
-    // have a few microseconds of latency to cover
-    if constexpr (U == 1) {
-        for (int c = c_lo + lane * 8; c < c_hi; c += 256) {
-            float acc[8];
+    for (int c = c_lo + lane * 8; c < c_hi; c += 256) {
+        float acc[8];
 #pragma unroll
-            for (int j = 0; j < KR; j++) {
-                if (j < k) {
-                    float v[8];
-                    if constexpr (sizeof(YT) == 2) {
-                        uint4 r = __ldcs(reinterpret_cast<const uint4 *>(src[j] + c));
-                        unpack8(r, v);
-                    } else {
-                        float4 a = __ldcs(reinterpret_cast<const float4 *>(src[j] + c));
-                        float4 b = __ldcs(reinterpret_cast<const float4 *>(src[j] + c) + 1);
-                        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-                        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-                    }
-#pragma unroll
-                    for (int i = 0; i < 8; i++) acc[i] = (j == 0) ? w[0] * v[i] : fmaf(w[j], v[i], acc[i]);
+        for (int j = 0; j < KR; j++) {
+            if (j < k) {
+                float v[8];
+                if constexpr (sizeof(YT) == 2) {
+                    uint4 r = __ldcs(reinterpret_cast<const uint4 *>(src[j] + c));
+                    unpack8(r, v);
+                } else {
+                    float4 a = __ldcs(reinterpret_cast<const float4 *>(src[j] + c));
+                    float4 b = __ldcs(reinterpret_cast<const float4 *>(src[j] + c) + 1);
+                    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+                    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
                 }
-            }
-            if (resid != nullptr) add_residual(resid + (size_t)t * d + c, acc);
-            if constexpr (sizeof(OT) == 2) {
-                uint4 o;
-                o.x = pack2(acc[0], acc[1]);
-                o.y = pack2(acc[2], acc[3]);
-                o.z = pack2(acc[4], acc[5]);
-                o.w = pack2(acc[6], acc[7]);
-                *reinterpret_cast<uint4 *>(y + (size_t)t * d + c) = o;
-            } else {
-                float4 *o = reinterpret_cast<float4 *>(y + (size_t)t * d + c);
-                o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc[i] = (j == 0) ? w[0] * v[i] : fmaf(w[j], v[i], acc[i]);
             }
         }
-        return;
-    }
-    for (int c0 = c_lo + lane * 8; c0 < c_hi; c0 += 256 * U) {
-        uint4 raw[U][(sizeof(YT) == 2) ? KR : 1];
-        float4 rawf[U][(sizeof(YT) == 2) ? 1 : 2 * KR];
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int c = c0 + 256 * u;
-            if (c < c_hi) {
-#pragma unroll
-                for (int j = 0; j < KR; j++) {
-                    if (j < k) {
-                        if constexpr (sizeof(YT) == 2) {
-                            raw[u][j] = __ldcs(reinterpret_cast<const uint4 *>(src[j] + c));
-                        } else {
-                            rawf[u][2 * j] = __ldcs(reinterpret_cast<const float4 *>(src[j] + c));
-                            rawf[u][2 * j + 1] = __ldcs(reinterpret_cast<const float4 *>(src[j] + c) + 1);
-                        }
-                    }
-                }
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int c = c0 + 256 * u;
-            if (c >= c_hi) continue;
-            float acc[8];
-#pragma unroll
-            for (int j = 0; j < KR; j++) {
-                if (j < k) {
-                    float v[8];
-                    if constexpr (sizeof(YT) == 2) {
-                        unpack8(raw[u][j], v);
-                    } else {
-                        const float4 a = rawf[u][2 * j], b = rawf[u][2 * j + 1];
-                        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-                        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-                    }
-#pragma unroll
-                    for (int i = 0; i < 8; i++) acc[i] = (j == 0) ? w[0] * v[i] : fmaf(w[j], v[i], acc[i]);
-                }
-            }
-            if (resid != nullptr) add_residual(resid + (size_t)t * d + c, acc);
-            if constexpr (sizeof(OT) == 2) {
-                uint4 o;
-                o.x = pack2(acc[0], acc[1]);
-                o.y = pack2(acc[2], acc[3]);
-                o.z = pack2(acc[4], acc[5]);
-                o.w = pack2(acc[6], acc[7]);
-                *reinterpret_cast<uint4 *>(y + (size_t)t * d + c) = o;
-            } else {
-                float4 *o = reinterpret_cast<float4 *>(y + (size_t)t * d + c);
-                o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-            }
+        if (resid != nullptr) add_residual(resid + (size_t)t * d + c, acc);
+        if constexpr (sizeof(OT) == 2) {
+            uint4 o;
+            o.x = pack2(acc[0], acc[1]);
+            o.y = pack2(acc[2], acc[3]);
+            o.z = pack2(acc[4], acc[5]);
+            o.w = pack2(acc[6], acc[7]);
+            *reinterpret_cast<uint4 *>(y + (size_t)t * d + c) = o;
+        } else {
+            float4 *o = reinterpret_cast<float4 *>(y + (size_t)t * d + c);
+            o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
         }
     }
 }
@@ -232,19 +170,16 @@ cudaError_t launch_k(omoe_handle *h, void *y, const void *resid_v, int T, cudaSt
         return cudaGetLastError();
     }
     EpWait wt = wait ? *wait : EpWait{nullptr, 1, 0, 0};
-    // rows read from other GPUs: several column chunks in flight per lane (as registers allow for this k)
-    static int u_env = getenv("OMOE_COMBINE_U") ? atoi(getenv("OMOE_COMBINE_U")) : 0;
-    const bool deep = u_env ? u_env > 1 : (wait != nullptr && d / split >= 1024);
-#define OMOE_COMBINE(KK, UU)                                                                                     \
-    combine_kernel<YT, OT, KK, UU><<<grid, block, 0, s>>>(h->d_out_table, out, resid, h->pos, h->topk_idx, h->topk_w, T, d, \
-                                                          k, El, wt, h->dev_err)
+#define OMOE_COMBINE(KK)                                                                                         \
+    combine_kernel<YT, OT, KK><<<grid, block, 0, s>>>(h->d_out_table, out, resid, h->pos, h->topk_idx, h->topk_w, T, d, k, \
+                                                      El, wt, h->dev_err)
     switch (k) {
-        case 1: if (deep) OMOE_COMBINE(1, 4); else OMOE_COMBINE(1, 1); break;
-        case 2: if (deep) OMOE_COMBINE(2, 4); else OMOE_COMBINE(2, 1); break;
-        case 4: if (deep) OMOE_COMBINE(4, 2); else OMOE_COMBINE(4, 1); break;
-        case 6: OMOE_COMBINE(6, 1); break;
-        case 8: OMOE_COMBINE(8, 1); break;
-        default: OMOE_COMBINE(0, 1); break;
+        case 1: OMOE_COMBINE(1); break;
+        case 2: OMOE_COMBINE(2); break;
+        case 4: OMOE_COMBINE(4); break;
+        case 6: OMOE_COMBINE(6); break;
+        case 8: OMOE_COMBINE(8); break;
+        default: OMOE_COMBINE(0); break;
     }
 #undef OMOE_COMBINE
     return cudaGetLastError();
