@@ -165,3 +165,38 @@ def test_weight_gradients_on_transposed_copies_in_a_subprocess():
            "-k", "bf16_backward"]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=root)
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+
+
+def test_full_size_backward_properties():
+    """Config 3 at full size (16384 tokens, d=4096, d_ff=14336, 8 experts, top-2), where the CPU oracle would take
+    minutes: properties that need no oracle.  Doubling dy is exact in floating point, so every gradient must double
+    bit for bit; a second run must reproduce the first bit for bit; the rows of d logits sum to zero (softmax_back),
+    so d router_bias sums to (nearly) zero; nothing is NaN or infinite."""
+    from omega_ai_b200 import MoELayer
+    T, d, dff, E, k = 16384, 4096, 14336, 8, 2
+    g = torch.Generator(device="cuda").manual_seed(5)
+    mk = lambda *s, sc=0.02: (torch.randn(*s, device="cuda", generator=g) * sc).to(torch.bfloat16)
+    layer = MoELayer(d, dff, E, k, bias=True, t_max=T, compute_dtype=torch.bfloat16)
+    layer.setWeights(mk(E, d), mk(E, dff, d), mk(E, dff, d), mk(E, d, dff), router_bias=mk(E, sc=0.1))
+    x, dy = mk(T, d, sc=1.0), mk(T, d, sc=1.0)
+    layer.set_training(True)
+
+    def step(grad):
+        layer.forward_device(x)
+        dx = layer.backward(x, grad).clone()
+        return dx, {n: v.clone() for n, v in layer.weight_grads().items()}
+
+    dx1, g1 = step(dy)
+    dx1b, g1b = step(dy)
+    assert torch.equal(dx1, dx1b) and all(torch.equal(g1[n], g1b[n]) for n in g1)
+    del dx1b, g1b
+    dx2, g2 = step(dy * 2)
+    assert torch.equal(dx2.float(), dx1.float() * 2)
+    for n in g1:
+        assert torch.isfinite(g1[n]).all(), n
+        assert torch.equal(g2[n], g1[n] * 2), n
+    assert g1["d_bias"].abs().max() > 0
+    assert abs(float(g1["d_bias"].sum())) <= 1e-3 * float(g1["d_bias"].abs().sum())
+    _, _, counts, _, _ = layer.routing(T)
+    assert counts.sum() == T * k
+    layer.close()
