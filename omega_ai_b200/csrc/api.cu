@@ -327,6 +327,7 @@ static int forward_impl(omoe_handle *h, const void *x_dev, int x_dtype, void *y_
     h->last_stream = s;
     h->last_launches = 0;
     h->ev_valid = false;
+    h->last_resid = resid != nullptr;
     bw_forward_invalidate(h);  // the rows a backward pass would read are about to be overwritten
     if (h->cfg.world > 1) {
         int rc = ep_forward(h, x_dev, x_dtype, y_dev, y_dtype, resid, T, s);
@@ -419,6 +420,10 @@ int omoe_backward(omoe_handle *h, const void *x_dev, const void *dy_dev, void *d
     if (io_dtype != h->last_io_dtype && T > 0)
         return fail(h, OMOE_ERR_INVALID, "omoe_backward: io_dtype differs from the forward's");
     int n = 0;
+    if (h->last_resid)
+        return fail(h, OMOE_ERR_STATE,
+                    "omoe_backward: the last forward was omoe_forward_block; its RMSNorm and residual are not "
+                    "differentiated here - run the training forward with omoe_forward");
     rc = bw_backward(h, x_dev, dy_dev, dx_dev, T, io_dtype, static_cast<cudaStream_t>(cuda_stream), &n);
     h->last_launches = n;
     return rc;

@@ -98,6 +98,7 @@ struct omoe_handle {
     // bookkeeping of the last forward
     int last_T;
     int last_io_dtype;
+    bool last_resid;  // the last forward was the block form (RMSNorm in front, residual added)
     cudaStream_t last_stream;
     int last_launches;
     bool profiling;

@@ -145,6 +145,9 @@ def test_backward_call_order_and_modes(oracle):
     dx2 = layer.backward(xd, dy).float().cpu().numpy()
     g2 = {n: v.cpu().numpy() for n, v in layer.weight_grads().items()}
     assert np.array_equal(dx1, dx2) and all(np.array_equal(g1[n], g2[n]) for n in g1)   # reproducible, overwritten
+    layer.forward_block(xd, torch.ones(d, device="cuda"))
+    with pytest.raises(OmoeError):   # the block form's RMSNorm and residual are not differentiated
+        layer.backward(xd, dy)
     layer.set_training(False)
     layer.forward_device(xd)
     with pytest.raises(OmoeError):   # the inference forward overwrote what the backward reads
