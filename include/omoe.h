@@ -142,7 +142,7 @@ OMOE_API int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host,
                       int32_t io_dtype, void *cuda_stream);
 
 /*
- * Training mode and the backward pass (one GPU, world == 1).
+ * Training mode and the backward pass.
  *
  * omoe_set_training(h, 1) allocates the buffers of the backward pass (first call only) and makes every
  * following omoe_forward / omoe_forward_block keep what the backward needs: the pre-activation rows of
@@ -158,12 +158,18 @@ OMOE_API int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host,
  * (gradient of the output of the LAST forward, which must have run in training mode with the same T,
  * io_dtype and x_dev contents), it writes dx_dev [T, d_model] of io_dtype and the weight gradients
  * (library-owned, fp32, OVERWRITTEN by every call as FullyLayer.diff() overwrites diffW):
- * d W_gate, d W_up [E, d_ff, d_model], d W_down [E, d_model, d_ff], d W_router [E, d_model],
+ * d W_gate, d W_up [E/world, d_ff, d_model], d W_down [E/world, d_model, d_ff], d W_router [E, d_model],
  * d router_bias [E].  The expert picks are constants (no gradient flows through the selection); the gate
  * weights' gradient reaches the router through the renormalisation and the reference's softmax_back rule
  * (src/main/resources/cu/SoftmaxKernel.cu:100-112).
  * omoe_forward_block's RMSNorm and residual are not differentiated here: call omoe_backward with the
  * normalised rows' gradient handling left to the caller, or use omoe_forward.  Does not synchronise the host.
+ *
+ * With world > 1 omoe_backward is a collective call like omoe_forward (every rank calls it, T may differ per
+ * rank): the gradient rows travel to the experts' owners and the input-gradient rows back through peer memory,
+ * ordered by the same device-side flags.  The expert weight gradients of a rank ([n_experts/world, ...]) are
+ * complete; d W_router and d router_bias cover the rank's own tokens and must be summed over the ranks by the
+ * caller (the router is replicated); the auxiliary loss term uses the rank's own tokens and counts.
  *
  * omoe_get_weight_grads copies the gradients of the last omoe_backward into the caller's DEVICE (or host)
  * fp32 buffers (any may be NULL) and synchronises the stream.
@@ -231,7 +237,7 @@ OMOE_API int omoe_get_stage_ms(omoe_handle *h, float *ms /* [OMOE_N_STAGES] */);
  * they return normally and the next synchronising call reports
  * OMOE_ERR_DEVICE.
  */
-#define OMOE_EP_BLOB_BYTES 192
+#define OMOE_EP_BLOB_BYTES 320
 OMOE_API int omoe_ep_export(omoe_handle *h, void *blob /* [OMOE_EP_BLOB_BYTES] */);
 OMOE_API int omoe_ep_import(omoe_handle *h, const void *all_blobs /* [world][OMOE_EP_BLOB_BYTES] */);
 

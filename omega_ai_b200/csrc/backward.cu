@@ -30,6 +30,7 @@
 
 #include "backward.cuh"
 #include "common.cuh"
+#include "ep.cuh"
 
 namespace omoe {
 
@@ -46,6 +47,8 @@ struct BwState {
     void *dgu;        // [rows_cap, 2*dff] dg | du
     void *dxp;        // [rows_cap, d]
     float *dgw;       // [t_max*k] gradient of the gate weights
+    void **dyp_table, **dxp_table;  // device [world]: every rank's dyp / dxp buffer (entry `rank` is this GPU's)
+    bool own_grad_rows;  // dyp, dxp and the tables were allocated here (one GPU); else they belong to the transport
     float *dl;        // [t_max, E] gradient of the logits
     float *dwr_part;  // [slices][E][d] partial sums of d W_router
     int dwr_slices;
@@ -149,19 +152,25 @@ swiglu_bwd_kernel(const T *__restrict__ dh, const T *__restrict__ gu, T *__restr
 // ---- combine backward + router backward: one warp per token ---------------------------------------
 // dyp[pos_j] = w_j * dy[t];  d w_j = <dy[t], yp[pos_j]>;  then lane 0 turns the k values d w into the
 // E values d logits (gate renormalisation, softmax_back), serially and in index order like softmax_back itself.
+// With expert parallelism the yp row is read from, and the dyp row written to, the buffers of the rank that
+// owns the pick's expert (peer loads and stores); the last block to finish raises "rows have landed" on
+// every rank, as the forward's dispatch does.
 template <typename YT, typename OT>
 __global__ void __launch_bounds__(256)
-combine_bwd_kernel(const OT *__restrict__ dy, const YT *__restrict__ yp, YT *__restrict__ dyp,
-                   const int32_t *__restrict__ pos, const int32_t *__restrict__ topk_idx,
+combine_bwd_kernel(const OT *__restrict__ dy, void *const *__restrict__ yp_table, void *const *__restrict__ dyp_table,
+                   int e_local, EpSignal sig, int32_t *ticket, const int32_t *__restrict__ pos, const int32_t *__restrict__ topk_idx,
                    const float *__restrict__ topk_w, const float *__restrict__ logits, float *__restrict__ dgw,
                    float *__restrict__ dl, int T, int d, int k, int E, int renorm, float aux_c,
                    const int32_t *__restrict__ counts) {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (t >= T) return;
+    if (t < T) {
     float dw[kMaxTopK];
     for (int j = 0; j < k; j++) {
         const int r = pos[(size_t)t * k + j];
+        const int q = topk_idx[(size_t)t * k + j] / e_local;  // rank that owns the pick's expert
+        const YT *yp = static_cast<const YT *>(yp_table[q]);
+        YT *dyp = static_cast<YT *>(dyp_table[q]);
         const float w = topk_w[(size_t)t * k + j];
         float acc = 0.f;
         for (int c = lane * 8; c < d; c += 256) {
@@ -217,6 +226,20 @@ combine_bwd_kernel(const OT *__restrict__ dy, const YT *__restrict__ yp, YT *__r
             out[e] = (dp - pd) * p;
         }
     }
+    }  // t < T
+    if (sig.flags != nullptr) {
+        // make this block's rows visible system-wide, take a ticket, and let the last block tell every rank
+        __threadfence_system();
+        __syncthreads();
+        __shared__ int s_last;
+        if (threadIdx.x == 0) s_last = (atomicAdd(ticket, 1) == (int)gridDim.x - 1);
+        __syncthreads();
+        if (s_last && (int)threadIdx.x < sig.world) {
+            __threadfence_system();
+            uint32_t *f = sig.flags[threadIdx.x] + sig.rank;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(*sig.seq) : "memory");
+        }
+    }
 }
 
 // ps[e] = sum_t softmax(logits[t, :])[e]: one block per expert, threads stride the tokens, fixed tree at the end.
@@ -243,13 +266,20 @@ prob_colsum_kernel(const float *__restrict__ logits, float *__restrict__ ps, int
 }
 
 // dx[t] = ((dxp[pos_0] + dxp[pos_1]) + ...) + sum_e dl[t,e] * W_r[e,:]   (one warp per token)
+// With expert parallelism the dxp rows are read from their owners' buffers once every owner has raised
+// "outputs ready" for this step (bounded wait).
 template <typename YT, typename OT>
 __global__ void __launch_bounds__(256)
-dx_kernel(const YT *__restrict__ dxp, const int32_t *__restrict__ pos, const float *__restrict__ dl,
+dx_kernel(void *const *__restrict__ dxp_table, int e_local, const int32_t *__restrict__ topk_idx, EpWait wait,
+          int32_t *dev_err, const int32_t *__restrict__ pos, const float *__restrict__ dl,
           const float *__restrict__ w_r, OT *__restrict__ dx, int T, int d, int k, int E) {
     extern __shared__ float s_dl[];  // [warps][E]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (wait.flags != nullptr) {
+        if ((int)threadIdx.x < wait.world) ep_wait_flag(wait.flags + threadIdx.x, *wait.seq, wait.timeout_ns, dev_err);
+        __syncthreads();
+    }
     if (t >= T) return;
     float *my = s_dl + warp * E;
     for (int e = lane; e < E; e += 32) my[e] = dl[(size_t)t * E + e];
@@ -258,6 +288,7 @@ dx_kernel(const YT *__restrict__ dxp, const int32_t *__restrict__ pos, const flo
         float acc[8];
         for (int j = 0; j < k; j++) {
             float v[8];
+            const YT *dxp = static_cast<const YT *>(dxp_table[topk_idx[(size_t)t * k + j] / e_local]);
             load8(dxp + (size_t)pos[(size_t)t * k + j] * d + c, v);
 #pragma unroll
             for (int i = 0; i < 8; i++) acc[i] = (j == 0) ? v[i] : acc[i] + v[i];
@@ -553,13 +584,30 @@ cudaError_t backward_t(omoe_handle *h, BwState *b, const void *x, const void *dy
     const int d = h->cfg.d_model, dff = h->cfg.d_ff, El = h->e_local, E = h->cfg.n_experts, k = h->cfg.top_k;
     const int32_t *rows_in_use = h->ex_poffsets + El;
     const int warps = 8, tblocks = ceil_div(T, warps);
-    combine_bwd_kernel<CT, OT><<<tblocks, 256, 0, s>>>(
-        static_cast<const OT *>(dy), static_cast<const CT *>(h->yp), static_cast<CT *>(b->dyp), h->pos, h->topk_idx,
-        h->topk_w, h->logits, b->dgw, b->dl, T, d, k, E, h->cfg.renormalize,
-        b->aux_coef != 0.f ? b->aux_coef * (float)E / (float)T : 0.f, h->counts);
+    const bool ep = h->cfg.world > 1;
+    EpSignal sig{nullptr, 1, 0, nullptr};
+    if (ep) {
+        BW_TRY(ep_bw_advance(h, s));  // the backward is a step of its own for the flags
+        (*n)++;
+        sig = ep_rows_signal(h);
+    }
+    if (T > 0) {
+        combine_bwd_kernel<CT, OT><<<tblocks, 256, 0, s>>>(
+            static_cast<const OT *>(dy), h->d_out_table, b->dyp_table, El, sig, h->ticket, h->pos, h->topk_idx,
+            h->topk_w, h->logits, b->dgw, b->dl, T, d, k, E, h->cfg.renormalize,
+            b->aux_coef != 0.f ? b->aux_coef * (float)E / (float)T : 0.f, h->counts);
+        BW_TRY(cudaGetLastError());
+    } else {
+        BW_TRY(ep_signal_rows(h, s));  // no tokens here: nothing to send, but the owners wait for every rank
+    }
+    (*n)++;
+    if (ep) {
+        BW_TRY(ep_wait_rows(h, s));  // every rank's gradient rows for my experts have landed
+        (*n)++;
+    }
     zero_pad_rows_kernel<CT><<<dim3(El, 8), 256, 0, s>>>(static_cast<CT *>(b->dyp), d, h->ex_poffsets, h->ex_counts);
     BW_TRY(cudaGetLastError());
-    *n += 2;
+    (*n)++;
     const int ew_grid = grid_for(h->rows_cap * (int64_t)dff / 8, h->sm_count);
     if constexpr (sizeof(CT) == 2) {
         if (!b->wt_valid) BW_TRY(transpose_weights(h, b, s, n));
@@ -573,6 +621,11 @@ cudaError_t backward_t(omoe_handle *h, BwState *b, const void *x, const void *dy
         // dxp = [dg | du] * [W_gate ; W_up]: one product over K = 2*dff
         BW_TRY(launch_grouped_plain(h, s, b->m_dgu_a, b->m_wguT_b, b->m_dxp_c, d, 2 * dff));
         (*n)++;
+        if (ep) {
+            // the input-gradient rows are complete: the token ranks may fetch them while the weight gradients run
+            BW_TRY(ep_signal_out(h, s));
+            (*n)++;
+        }
         // d W_down[e] [d, dff] = dyp_e^T * h_e;  [d W_gate ; d W_up][e] [2*dff, d] = [dg | du]_e^T * xp_e
         if (!b->wgrad_transposed) {
             // operands read in place as MN-major tiles; dyp's padding rows are zero, hence dh's and [dg|du]'s
@@ -612,6 +665,10 @@ cudaError_t backward_t(omoe_handle *h, BwState *b, const void *x, const void *dy
         sgemm_rows_kernel<<<g2, 256, 0, s>>>(dgu + dff, 2 * dff, static_cast<const float *>(h->w_up), (size_t)dff * d,
                                              d, 1, static_cast<float *>(b->dxp), d, d, dff, rows_in_use,
                                              h->ex_tile_expert, 1);
+        if (ep) {
+            BW_TRY(ep_signal_out(h, s));
+            (*n)++;
+        }
         // d W_down[e][c][f] = sum_r dyp[r, c] * h[r, f];  d W_gate[e][f][c] = sum_r dg[r, f] * xp[r, c]
         sgemm_wgrad_kernel<<<dim3(ceil_div(dff, 64), ceil_div(d, 64), El), 256, 0, s>>>(
             dyp, d, static_cast<const float *>(h->hbuf), dff, b->d_down, d, dff, h->ex_poffsets, h->ex_counts);
@@ -637,15 +694,19 @@ cudaError_t backward_t(omoe_handle *h, BwState *b, const void *x, const void *dy
         BW_TRY(cudaGetLastError());
         *n += 3;
     }
-    dx_kernel<CT, OT><<<tblocks, 256, warps * E * sizeof(float), s>>>(static_cast<const CT *>(b->dxp), h->pos, b->dl,
-                                                                     h->w_router, static_cast<OT *>(dx), T, d, k, E);
-    BW_TRY(cudaGetLastError());
-    (*n)++;
+    if (T > 0) {
+        const EpWait wt = ep ? ep_out_wait(h) : EpWait{nullptr, 1, nullptr, 0};
+        dx_kernel<CT, OT><<<tblocks, 256, warps * E * sizeof(float), s>>>(
+            b->dxp_table, El, h->topk_idx, wt, h->dev_err, h->pos, b->dl, h->w_router, static_cast<OT *>(dx), T, d, k, E);
+        BW_TRY(cudaGetLastError());
+        (*n)++;
+    }
     return cudaSuccess;
 }
 
 void free_state(BwState *b) {
-    void *ptrs[] = {b->gu, b->dyp, b->dh, b->dgu, b->dxp, b->dgw, b->dl, b->dwr_part, b->wdT, b->wguT, b->xpT, b->hT,
+    if (!b->own_grad_rows) b->dyp = b->dxp = nullptr, b->dyp_table = b->dxp_table = nullptr;
+    void *ptrs[] = {b->dyp_table, b->dxp_table, b->gu, b->dyp, b->dh, b->dgu, b->dxp, b->dgw, b->dl, b->dwr_part, b->wdT, b->wguT, b->xpT, b->hT,
                     b->dypT, b->dguT, b->d_router, b->d_bias, b->d_gate, b->d_up, b->d_down, b->aux_ps};
     for (void *p : ptrs)
         if (p) cudaFree(p);
@@ -660,10 +721,6 @@ int bw_set_training(omoe_handle *h, int on) {
         if (b) { b->training = false; b->fwd_valid = false; }
         return OMOE_OK;
     }
-    if (h->cfg.world > 1) {
-        snprintf(h->err, sizeof(h->err), "omoe_set_training: the backward pass is built for one GPU (world == 1)");
-        return OMOE_ERR_UNSUPPORTED;
-    }
     if (b) { b->training = true; return OMOE_OK; }
     b = new (std::nothrow) BwState();
     if (!b) return OMOE_ERR_NOMEM;
@@ -673,13 +730,27 @@ int bw_set_training(omoe_handle *h, int on) {
     const size_t E = h->cfg.n_experts, tm = h->cfg.t_max, k = h->cfg.top_k;
     b->dwr_slices = (int)(tm >= 4096 ? 64 : (tm >= 256 ? 8 : 1));
     struct { void **p; size_t bytes; } bufs[] = {
-        {&b->gu, rows * 2 * dff * cs}, {&b->dyp, rows * d * cs}, {&b->dh, rows * dff * cs},
-        {&b->dgu, rows * 2 * dff * cs}, {&b->dxp, rows * d * cs}, {(void **)&b->dgw, tm * k * 4},
+        {&b->gu, rows * 2 * dff * cs}, {&b->dh, rows * dff * cs},
+        {&b->dgu, rows * 2 * dff * cs}, {(void **)&b->dgw, tm * k * 4},
         {(void **)&b->dl, tm * E * 4}, {(void **)&b->dwr_part, (size_t)b->dwr_slices * E * d * 4},
         {(void **)&b->d_router, E * d * 4}, {(void **)&b->d_bias, E * 4}, {(void **)&b->aux_ps, E * 4}, {(void **)&b->d_gate, El * dff * d * 4},
         {(void **)&b->d_up, El * dff * d * 4}, {(void **)&b->d_down, El * dff * d * 4}};
     bool ok = true;
     for (auto &x : bufs) ok = ok && cudaMalloc(x.p, x.bytes ? x.bytes : 1) == cudaSuccess;
+    if (h->cfg.world > 1) {
+        // gradient rows cross GPUs: the buffers the peers can reach belong to the transport
+        ep_grad_buffers(h, &b->dyp, &b->dxp, &b->dyp_table, &b->dxp_table);
+        b->own_grad_rows = false;
+    } else {
+        b->own_grad_rows = true;
+        ok = ok && cudaMalloc(&b->dyp, rows * d * cs) == cudaSuccess && cudaMalloc(&b->dxp, rows * d * cs) == cudaSuccess &&
+             cudaMalloc(&b->dyp_table, sizeof(void *)) == cudaSuccess &&
+             cudaMalloc(&b->dxp_table, sizeof(void *)) == cudaSuccess;
+        if (ok) {
+            cudaMemcpy(b->dyp_table, &b->dyp, sizeof(void *), cudaMemcpyHostToDevice);
+            cudaMemcpy(b->dxp_table, &b->dxp, sizeof(void *), cudaMemcpyHostToDevice);
+        }
+    }
     const char *wt = getenv("OMOE_WGRAD_TRANSPOSED");
     b->wgrad_transposed = wt && atoi(wt) != 0;
     if (ok && cs == 2) {
@@ -699,7 +770,7 @@ int bw_set_training(omoe_handle *h, int on) {
     }
     // padding rows are read by the row-wise products (their results are never used): keep them finite
     cudaMemset(b->gu, 0, rows * 2 * dff * cs);
-    cudaMemset(b->dyp, 0, rows * d * cs);
+    if (b->own_grad_rows) cudaMemset(b->dyp, 0, rows * d * cs);
     cudaMemset(b->dgu, 0, rows * 2 * dff * cs);
     if (cs == 2) {
         // columns of the transposed buffers beyond the rows in use are never read
@@ -761,11 +832,15 @@ int bw_backward(omoe_handle *h, const void *x, const void *dy, void *dx, int T, 
         snprintf(h->err, sizeof(h->err), "omoe_backward: call omoe_set_training(h, 1) and a forward first");
         return OMOE_ERR_STATE;
     }
+    if (h->cfg.world > 1 && !ep_ready(h)) {
+        snprintf(h->err, sizeof(h->err), "omoe_backward: call omoe_ep_export / omoe_ep_import on every rank first");
+        return OMOE_ERR_STATE;
+    }
     if (!b->fwd_valid || b->fwd_T != T) {
         snprintf(h->err, sizeof(h->err), "omoe_backward: no training-mode forward of T=%d rows precedes this call", T);
         return OMOE_ERR_STATE;
     }
-    if (T == 0) {  // no rows: every gradient is zero
+    if (T == 0 && h->cfg.world == 1) {  // no rows: every gradient is zero
         const size_t E = h->cfg.n_experts, d = h->cfg.d_model, dff = h->cfg.d_ff, El = h->e_local;
         cudaMemsetAsync(b->d_router, 0, E * d * 4, s);
         cudaMemsetAsync(b->d_bias, 0, E * 4, s);

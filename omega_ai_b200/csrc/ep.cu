@@ -26,6 +26,7 @@
 #include <string.h>
 
 #include "ep.cuh"
+#include "backward.cuh"
 
 namespace omoe {
 
@@ -45,14 +46,16 @@ struct EpState {
     uint32_t **d_rows_flags;    // device [world]: &peer_ctl[q]->flag_rows[0]
     uint32_t **d_out_flags;     // device [world]: &peer_ctl[q]->flag_out[0]
     int32_t *ex_counts, *ex_poffsets, *ex_tile_expert;  // layout of the rows this rank receives
-    void *peer_ptrs[kMaxWorld][3];  // opened IPC mappings (ctl, xp, yp), null for self
+    void *peer_ptrs[kMaxWorld][5];  // opened IPC mappings (ctl, xp, yp, dyp, dxp), null for self
+    void *dyp, *dxp;            // [rows_cap, d] gradient rows of the backward pass (peers write dyp, read dxp)
+    void **d_dyp_table, **d_dxp_table;  // device [world]
     bool imported;
     uint32_t *d_seq;  // device: sequence number of the last step started on this rank
     unsigned long long timeout_ns;
 };
 
 struct IpcBlob {
-    cudaIpcMemHandle_t ctl, xp, yp;
+    cudaIpcMemHandle_t ctl, xp, yp, dyp, dxp;
 };
 static_assert(sizeof(IpcBlob) == OMOE_EP_BLOB_BYTES, "blob size is part of the ABI");
 
@@ -166,6 +169,7 @@ int ep_create(omoe_handle *h) {
     if (!st) return OMOE_ERR_NOMEM;
     h->ep = st;
     const int W = h->cfg.world, El = h->e_local;
+    const size_t grad_bytes = (size_t)h->rows_cap * h->cfg.d_model * (h->cfg.compute_dtype == OMOE_BF16 ? 2 : 4);
     cudaError_t e;
     if ((e = cudaMalloc(&st->ctl, sizeof(EpCtl))) != cudaSuccess) return ep_fail(h, OMOE_ERR_NOMEM, "cudaMalloc(ctl)", e);
     cudaMemset(st->ctl, 0, sizeof(EpCtl));
@@ -173,11 +177,16 @@ int ep_create(omoe_handle *h) {
         (e = cudaMalloc(&st->d_rows_flags, sizeof(void *) * W)) != cudaSuccess ||
         (e = cudaMalloc(&st->d_out_flags, sizeof(void *) * W)) != cudaSuccess ||
         (e = cudaMalloc(&st->d_seq, sizeof(uint32_t))) != cudaSuccess ||
+        (e = cudaMalloc(&st->d_dyp_table, sizeof(void *) * W)) != cudaSuccess ||
+        (e = cudaMalloc(&st->d_dxp_table, sizeof(void *) * W)) != cudaSuccess ||
+        (e = cudaMalloc(&st->dyp, grad_bytes)) != cudaSuccess || (e = cudaMalloc(&st->dxp, grad_bytes)) != cudaSuccess ||
         (e = cudaMalloc(&st->ex_counts, sizeof(int32_t) * El)) != cudaSuccess ||
         (e = cudaMalloc(&st->ex_poffsets, sizeof(int32_t) * (El + 1))) != cudaSuccess ||
         (e = cudaMalloc(&st->ex_tile_expert, sizeof(int32_t) * (h->rows_cap / kRowAlign))) != cudaSuccess)
         return ep_fail(h, OMOE_ERR_NOMEM, "cudaMalloc(expert-parallel state)", e);
     cudaMemset(st->d_seq, 0, sizeof(uint32_t));
+    cudaMemset(st->dyp, 0, grad_bytes);
+    cudaMemset(st->dxp, 0, grad_bytes);
     h->ex_counts = st->ex_counts;
     h->ex_poffsets = st->ex_poffsets;
     h->ex_tile_expert = st->ex_tile_expert;
@@ -193,9 +202,10 @@ void ep_destroy(omoe_handle *h) {
     EpState *st = static_cast<EpState *>(h->ep);
     if (!st) return;
     for (int q = 0; q < kMaxWorld; q++)
-        for (int i = 0; i < 3; i++)
+        for (int i = 0; i < 5; i++)
             if (st->peer_ptrs[q][i]) cudaIpcCloseMemHandle(st->peer_ptrs[q][i]);
-    void *ptrs[] = {st->ctl, st->d_ctl_table, st->d_rows_flags, st->d_out_flags, st->d_seq, st->ex_counts, st->ex_poffsets,
+    void *ptrs[] = {st->ctl, st->d_ctl_table, st->d_rows_flags, st->d_out_flags, st->d_seq, st->d_dyp_table,
+                    st->d_dxp_table, st->dyp, st->dxp, st->ex_counts, st->ex_poffsets,
                     st->ex_tile_expert};
     for (void *p : ptrs)
         if (p) cudaFree(p);
@@ -212,7 +222,9 @@ int ep_export(omoe_handle *h, void *blob) {
     IpcBlob b;
     cudaError_t e;
     if ((e = cudaIpcGetMemHandle(&b.ctl, st->ctl)) != cudaSuccess || (e = cudaIpcGetMemHandle(&b.xp, h->xp)) != cudaSuccess ||
-        (e = cudaIpcGetMemHandle(&b.yp, h->yp)) != cudaSuccess)
+        (e = cudaIpcGetMemHandle(&b.yp, h->yp)) != cudaSuccess ||
+        (e = cudaIpcGetMemHandle(&b.dyp, st->dyp)) != cudaSuccess ||
+        (e = cudaIpcGetMemHandle(&b.dxp, st->dxp)) != cudaSuccess)
         return ep_fail(h, OMOE_ERR_COMM, "cudaIpcGetMemHandle", e);
     memcpy(blob, &b, sizeof(b));
     return OMOE_OK;
@@ -230,22 +242,26 @@ int ep_import(omoe_handle *h, const void *all_blobs) {
     }
     const int W = h->cfg.world, r = h->cfg.rank;
     const IpcBlob *blobs = static_cast<const IpcBlob *>(all_blobs);
-    void *ctl[kMaxWorld], *xp[kMaxWorld], *yp[kMaxWorld];
+    void *ctl[kMaxWorld], *xp[kMaxWorld], *yp[kMaxWorld], *dyp[kMaxWorld], *dxp[kMaxWorld];
     uint32_t *rows_flags[kMaxWorld], *out_flags[kMaxWorld];
     for (int q = 0; q < W; q++) {
         if (q == r) {
             ctl[q] = st->ctl;
             xp[q] = h->xp;
             yp[q] = h->yp;
+            dyp[q] = st->dyp;
+            dxp[q] = st->dxp;
         } else {
-            const cudaIpcMemHandle_t *hs[3] = {&blobs[q].ctl, &blobs[q].xp, &blobs[q].yp};
-            for (int i = 0; i < 3; i++) {
+            const cudaIpcMemHandle_t *hs[5] = {&blobs[q].ctl, &blobs[q].xp, &blobs[q].yp, &blobs[q].dyp, &blobs[q].dxp};
+            for (int i = 0; i < 5; i++) {
                 cudaError_t e = cudaIpcOpenMemHandle(&st->peer_ptrs[q][i], *hs[i], cudaIpcMemLazyEnablePeerAccess);
                 if (e != cudaSuccess) return ep_fail(h, OMOE_ERR_COMM, "cudaIpcOpenMemHandle (is peer access available?)", e);
             }
             ctl[q] = st->peer_ptrs[q][0];
             xp[q] = st->peer_ptrs[q][1];
             yp[q] = st->peer_ptrs[q][2];
+            dyp[q] = st->peer_ptrs[q][3];
+            dxp[q] = st->peer_ptrs[q][4];
         }
         rows_flags[q] = static_cast<EpCtl *>(ctl[q])->flag_rows;  // address arithmetic only
         out_flags[q] = static_cast<EpCtl *>(ctl[q])->flag_out;
@@ -255,7 +271,9 @@ int ep_import(omoe_handle *h, const void *all_blobs) {
         (e = cudaMemcpy(st->d_rows_flags, rows_flags, sizeof(void *) * W, cudaMemcpyHostToDevice)) != cudaSuccess ||
         (e = cudaMemcpy(st->d_out_flags, out_flags, sizeof(void *) * W, cudaMemcpyHostToDevice)) != cudaSuccess ||
         (e = cudaMemcpy(h->d_row_table, xp, sizeof(void *) * W, cudaMemcpyHostToDevice)) != cudaSuccess ||
-        (e = cudaMemcpy(h->d_out_table, yp, sizeof(void *) * W, cudaMemcpyHostToDevice)) != cudaSuccess)
+        (e = cudaMemcpy(h->d_out_table, yp, sizeof(void *) * W, cudaMemcpyHostToDevice)) != cudaSuccess ||
+        (e = cudaMemcpy(st->d_dyp_table, dyp, sizeof(void *) * W, cudaMemcpyHostToDevice)) != cudaSuccess ||
+        (e = cudaMemcpy(st->d_dxp_table, dxp, sizeof(void *) * W, cudaMemcpyHostToDevice)) != cudaSuccess)
         return ep_fail(h, OMOE_ERR_CUDA, "cudaMemcpy(peer tables)", e);
     st->imported = true;
     return OMOE_OK;
@@ -304,7 +322,10 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
     TRY(cudaGetLastError());
     n++;
     MARK(4);
-    if (h->cfg.compute_dtype == OMOE_BF16) {
+    if (bw_training(h)) {
+        TRY(bw_forward_experts(h, T, s, &n));  // keeps g and u for the backward pass
+        MARK(5);
+    } else if (h->cfg.compute_dtype == OMOE_BF16) {
         // rows can come from every rank's tokens; a rank's step holds at most t_max of them
         TRY(launch_experts_bf16(h, s, &n, prof ? h->ev[5] : nullptr, (long)h->cfg.t_max * W * h->cfg.top_k));
     } else {
@@ -332,6 +353,58 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
     h->ev_valid = prof;
     h->last_launches = n;
     return OMOE_OK;
+}
+
+// ---- pieces the backward pass (backward.cu) builds its expert-parallel form from -----------------------
+namespace {
+__global__ void ep_advance_kernel(uint32_t *seq, int32_t *ticket) {
+    *seq = *seq + 1u;  // a backward pass is a step of its own: gradient rows out, input gradients back
+    *ticket = 0;
+}
+}  // namespace
+
+bool ep_ready(const omoe_handle *h) { return h->ep && static_cast<EpState *>(h->ep)->imported; }
+
+void ep_grad_buffers(omoe_handle *h, void **dyp, void **dxp, void ***dyp_table, void ***dxp_table) {
+    EpState *st = static_cast<EpState *>(h->ep);
+    *dyp = st->dyp;
+    *dxp = st->dxp;
+    *dyp_table = st->d_dyp_table;
+    *dxp_table = st->d_dxp_table;
+}
+
+cudaError_t ep_bw_advance(omoe_handle *h, cudaStream_t s) {
+    EpState *st = static_cast<EpState *>(h->ep);
+    ep_advance_kernel<<<1, 1, 0, s>>>(st->d_seq, h->ticket);
+    return cudaGetLastError();
+}
+
+EpSignal ep_rows_signal(omoe_handle *h) {
+    EpState *st = static_cast<EpState *>(h->ep);
+    return EpSignal{st->d_rows_flags, h->cfg.world, h->cfg.rank, st->d_seq};
+}
+
+EpWait ep_out_wait(omoe_handle *h) {
+    EpState *st = static_cast<EpState *>(h->ep);
+    return EpWait{st->ctl->flag_out, h->cfg.world, st->d_seq, st->timeout_ns};
+}
+
+cudaError_t ep_signal_rows(omoe_handle *h, cudaStream_t s) {
+    EpState *st = static_cast<EpState *>(h->ep);
+    ep_signal_kernel<<<1, 32, 0, s>>>(st->d_rows_flags, h->cfg.world, h->cfg.rank, st->d_seq);
+    return cudaGetLastError();
+}
+
+cudaError_t ep_wait_rows(omoe_handle *h, cudaStream_t s) {
+    EpState *st = static_cast<EpState *>(h->ep);
+    ep_wait_kernel<<<1, 32, 0, s>>>(st->ctl->flag_rows, h->cfg.world, st->d_seq, h->dev_err, st->timeout_ns);
+    return cudaGetLastError();
+}
+
+cudaError_t ep_signal_out(omoe_handle *h, cudaStream_t s) {
+    EpState *st = static_cast<EpState *>(h->ep);
+    ep_signal_kernel<<<1, 32, 0, s>>>(st->d_out_flags, h->cfg.world, h->cfg.rank, st->d_seq);
+    return cudaGetLastError();
 }
 
 }  // namespace omoe

@@ -13,4 +13,16 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
                cudaStream_t s);
 void ep_destroy(omoe_handle *h);
 
+// Pieces of the expert-parallel backward pass.  A backward is a step of its own (ep_bw_advance): gradient rows
+// travel to the experts' owners like the forward's rows (peer stores, "rows landed" flags), input-gradient
+// rows are read back from the owners like the forward's outputs (peer loads behind "outputs ready" flags).
+bool ep_ready(const omoe_handle *h);
+void ep_grad_buffers(omoe_handle *h, void **dyp, void **dxp, void ***dyp_table, void ***dxp_table);
+cudaError_t ep_bw_advance(omoe_handle *h, cudaStream_t s);
+EpSignal ep_rows_signal(omoe_handle *h);
+EpWait ep_out_wait(omoe_handle *h);
+cudaError_t ep_signal_rows(omoe_handle *h, cudaStream_t s);
+cudaError_t ep_wait_rows(omoe_handle *h, cudaStream_t s);
+cudaError_t ep_signal_out(omoe_handle *h, cudaStream_t s);
+
 }  // namespace omoe

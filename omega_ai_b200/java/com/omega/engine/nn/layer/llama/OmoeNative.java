@@ -52,7 +52,7 @@ public final class OmoeNative {
     /** omoe_get_weight_grads: fp32 device addresses (0 = skip): router [E,d], bias [E], gate/up [E,dff,d], down [E,d,dff]. */
     public static native int getWeightGrads(long handle, long dRouter, long dBias, long dGate, long dUp, long dDown);
 
-    public static native int epExport(long handle, byte[] blob192);
+    public static native int epExport(long handle, byte[] blob320);
 
     public static native int epImport(long handle, byte[] allBlobs);
 }

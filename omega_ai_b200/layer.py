@@ -253,11 +253,14 @@ class MoELayer(Layer):
         return float(v.value)
 
     def weight_grads(self, stream=None) -> dict:
-        """fp32 device tensors d_router [E,d], d_bias [E], d_gate/d_up [E,dff,d], d_down [E,d,dff] of the last
-        backward (diffW of the reference's FullyLayer, FullyLayer.java:292-301)."""
+        """fp32 device tensors d_router [E,d], d_bias [E], d_gate/d_up [El,dff,d], d_down [El,d,dff] of the last
+        backward (diffW of the reference's FullyLayer, FullyLayer.java:292-301).  With expert parallelism El is
+        this rank's share of the experts (their gradients are complete: all ranks' rows are here) and the
+        router's gradients cover this rank's tokens only: sum them over the ranks."""
         E, d, dff = self.numExperts, self.embedDim, self.dff
+        El = E // self.world
         mk = lambda *shape: torch.empty(*shape, dtype=torch.float32, device="cuda")
-        g = dict(d_router=mk(E, d), d_bias=mk(E), d_gate=mk(E, dff, d), d_up=mk(E, dff, d), d_down=mk(E, d, dff))
+        g = dict(d_router=mk(E, d), d_bias=mk(E), d_gate=mk(El, dff, d), d_up=mk(El, dff, d), d_down=mk(El, d, dff))
         s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
         check(self._h, self._lib.omoe_get_weight_grads(self._h, g["d_router"].data_ptr(), g["d_bias"].data_ptr(),
                                                        g["d_gate"].data_ptr(), g["d_up"].data_ptr(),

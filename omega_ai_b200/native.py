@@ -18,7 +18,7 @@ OMOE_F32 = 0
 OMOE_BF16 = 1
 N_STAGES = 8
 STAGE_NAMES = ("router", "scan", "permute", "dispatch", "up_gate", "down", "return", "combine")
-EP_BLOB_BYTES = 192
+EP_BLOB_BYTES = 320
 
 ERRORS = {
     0: "OMOE_OK", -1: "OMOE_ERR_INVALID", -2: "OMOE_ERR_CUDA", -3: "OMOE_ERR_TOO_LARGE",

@@ -64,6 +64,58 @@ def run_case(rank, world, tokens, d, dff, E, k, compute, zipf, steps=2):
     layer.close()
 
 
+def run_backward_case(rank, world, compute):
+    """Expert-parallel training step: each rank's dx against the oracle run on ALL ranks' tokens (rank-major), the
+    local experts' weight gradients against the oracle's for those experts, the router's gradients summed over
+    the ranks.  Two steps with different rows; one rank has fewer tokens, and in the second step none."""
+    d, dff, E, k = 128, 256, 8, 2
+    El = E // world
+    bf = compute == torch.bfloat16
+    _, w_r, w_g, w_u, w_d, _ = make_layer(1, d, dff, E, k, seed=79)
+    w_r, w_g, w_u, w_d = (w_r * 10), (w_g * 3), (w_u * 3), (w_d * 3)
+    if bf:
+        w_r, w_g, w_u, w_d = (ref.bf16_round(a) for a in (w_r, w_g, w_u, w_d))
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda().to(compute).contiguous()
+    t_cap = 96
+    layer = MoELayer(d, dff, E, k, t_max=t_cap, compute_dtype=compute, world=world, rank=rank)
+    sl = slice(rank * El, (rank + 1) * El)
+    layer.setWeights(dev(w_r), dev(w_g[sl]), dev(w_u[sl]), dev(w_d[sl]))
+    layer.ep_connect()
+    layer.set_training(True)
+    for step in range(2):
+        counts_t = [t_cap if q != world - 1 else (40 if step == 0 else 0) for q in range(world)]
+        xs, dys = [], []
+        for q in range(world):  # every rank can regenerate every rank's rows: nothing to exchange in the test
+            rng = np.random.Generator(np.random.Philox(key=2000 + 10 * step + q))
+            xq = rng.standard_normal((counts_t[q], d), dtype=np.float32)
+            dq = rng.standard_normal((counts_t[q], d), dtype=np.float32)
+            if bf:
+                xq, dq = ref.bf16_round(xq), ref.bf16_round(dq)
+            xs.append(xq)
+            dys.append(dq)
+        T = counts_t[rank]
+        xd = dev(xs[rank]) if T else torch.empty(0, d, device="cuda", dtype=compute)
+        dyd = dev(dys[rank]) if T else torch.empty(0, d, device="cuda", dtype=compute)
+        layer.forward_device(xd)
+        dx = layer.backward(xd, dyd).float().cpu().numpy()
+        g = layer.weight_grads()
+        d_router = g["d_router"].clone()
+        dist.all_reduce(d_router)
+        want = ref.moe_backward(np.concatenate(xs), w_r, w_g, w_u, w_d, k, np.concatenate(dys), bf16=bf)
+        lo = sum(counts_t[:rank])
+        close = (lambda a, b_, n: assert_close_bf16(a, b_)) if bf else (
+            lambda a, b_, n: np.testing.assert_allclose(a, b_, rtol=0, atol=2e-4 * (np.abs(b_).max() + 1e-30), err_msg=n))
+        if T:
+            close(dx, want.dx[lo:lo + T], "dx")
+        close(g["d_gate"].cpu().numpy(), want.d_w_gate[sl], "d_w_gate")
+        close(g["d_up"].cpu().numpy(), want.d_w_up[sl], "d_w_up")
+        close(g["d_down"].cpu().numpy(), want.d_w_down[sl], "d_w_down")
+        close(d_router.cpu().numpy(), want.d_w_r, "d_w_r")
+    torch.cuda.synchronize()
+    dist.barrier()
+    layer.close()
+
+
 def run_graph_case(rank, world):
     """A captured expert-parallel forward replays: flags and the step's sequence number live on the device, so
     nothing in the kernels' arguments changes between steps.  Replays with fresh rows in the captured input
@@ -109,6 +161,8 @@ def main():
     run_case(rank, world, [256, 128], 256, 256, 64, 6, torch.bfloat16, True, steps=2)
     run_case(rank, world, [64, 40], 128, 256, 8, 2, torch.float32, False, steps=2)
     run_graph_case(rank, world)
+    run_backward_case(rank, world, torch.float32)
+    run_backward_case(rank, world, torch.bfloat16)
     dist.destroy_process_group()
     if rank == 0:
         print("ep parity ok")

@@ -25,6 +25,7 @@ def _worker(rank, world, port, q):
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
         dist.init_process_group("gloo", rank=rank, world_size=world)
         from omega_ai_b200 import ep_layout as L
+        from omega_ai_b200 import native
         from omega_ai_b200.layer import MoELayer
         from oracle import ref
 
@@ -34,7 +35,7 @@ def _worker(rank, world, port, q):
                 self.world, self.rank, self.got = world, rank, None
 
             def ep_export(self):
-                return bytes([rank]) * 192
+                return bytes([rank]) * native.EP_BLOB_BYTES
 
             def ep_import(self, blobs):
                 self.got = blobs
@@ -45,7 +46,7 @@ def _worker(rank, world, port, q):
         torch.cuda.synchronize = lambda *a, **k: None  # no GPU here
         f = Fake()
         f.ep_connect()
-        assert [b[0] for b in f.got] == list(range(world)) and all(len(b) == 192 for b in f.got)
+        assert [b[0] for b in f.got] == list(range(world)) and all(len(b) == native.EP_BLOB_BYTES for b in f.got)
 
         # (b) layout rules
         E, k, d, T_all = 8, 2, 16, 301
