@@ -162,8 +162,14 @@ OMOE_API int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host,
  * d router_bias [E].  The expert picks are constants (no gradient flows through the selection); the gate
  * weights' gradient reaches the router through the renormalisation and the reference's softmax_back rule
  * (src/main/resources/cu/SoftmaxKernel.cu:100-112).
- * omoe_forward_block's RMSNorm and residual are not differentiated here: call omoe_backward with the
- * normalised rows' gradient handling left to the caller, or use omoe_forward.  Does not synchronise the host.
+ * Does not synchronise the host.
+ *
+ * omoe_backward_block is the backward of omoe_forward_block (y = x + MoE(rmsnorm(x) * gamma)), i.e. of
+ * norm2 -> mlp -> residual add in LlamaTransformerBlock (LlamaTransformerBlock.java:134-136): the layer's
+ * backward on the normalised rows the forward kept, then the RMSNorm backward of rmsnorm_backward_kernel2
+ * (src/main/resources/cu/RMSKernel.cu:225-275) with the residual branch's dy added in the same pass.
+ * x_dev must hold the rows given to that forward; dgamma_dev [d_model] fp32 is overwritten (the reference
+ * accumulates it with atomics; here the sum has a fixed order).
  *
  * With world > 1 omoe_backward is a collective call like omoe_forward (every rank calls it, T may differ per
  * rank): the gradient rows travel to the experts' owners and the input-gradient rows back through peer memory,
@@ -177,6 +183,9 @@ OMOE_API int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host,
 OMOE_API int omoe_set_training(omoe_handle *h, int32_t on);
 OMOE_API int omoe_backward(omoe_handle *h, const void *x_dev, const void *dy_dev, void *dx_dev, int32_t T,
                            int32_t io_dtype, void *cuda_stream);
+OMOE_API int omoe_backward_block(omoe_handle *h, const void *x_dev, const float *gamma_dev, float eps,
+                                 const void *dy_dev, void *dx_dev, float *dgamma_dev, int32_t T, int32_t io_dtype,
+                                 void *cuda_stream);
 OMOE_API int omoe_get_weight_grads(omoe_handle *h, float *d_router, float *d_router_bias, float *d_gate,
                                    float *d_up, float *d_down, void *cuda_stream);
 

@@ -422,9 +422,25 @@ int omoe_backward(omoe_handle *h, const void *x_dev, const void *dy_dev, void *d
     int n = 0;
     if (h->last_resid)
         return fail(h, OMOE_ERR_STATE,
-                    "omoe_backward: the last forward was omoe_forward_block; its RMSNorm and residual are not "
-                    "differentiated here - run the training forward with omoe_forward");
-    rc = bw_backward(h, x_dev, dy_dev, dx_dev, T, io_dtype, static_cast<cudaStream_t>(cuda_stream), &n);
+                    "omoe_backward: the last forward was omoe_forward_block; its backward is omoe_backward_block");
+    rc = bw_backward(h, x_dev, false, dy_dev, dx_dev, T, io_dtype, static_cast<cudaStream_t>(cuda_stream), &n);
+    h->last_launches = n;
+    return rc;
+}
+
+int omoe_backward_block(omoe_handle *h, const void *x_dev, const float *gamma_dev, float eps, const void *dy_dev,
+                        void *dx_dev, float *dgamma_dev, int32_t T, int32_t io_dtype, void *cuda_stream) {
+    if (!h) return OMOE_ERR_INVALID;
+    int rc = check_forward_args(h, x_dev, dx_dev, T, io_dtype, "omoe_backward_block");
+    if (rc != OMOE_OK) return rc;
+    if (!gamma_dev || !dgamma_dev || (T > 0 && !dy_dev)) return fail(h, OMOE_ERR_INVALID, "omoe_backward_block: null buffer");
+    if (!h->last_resid)
+        return fail(h, OMOE_ERR_STATE, "omoe_backward_block: the last forward was not omoe_forward_block");
+    if (io_dtype != h->last_io_dtype && T > 0)
+        return fail(h, OMOE_ERR_INVALID, "omoe_backward_block: io_dtype differs from the forward's");
+    int n = 0;
+    rc = bw_backward_block(h, x_dev, gamma_dev, eps, dy_dev, dx_dev, dgamma_dev, T, io_dtype,
+                           static_cast<cudaStream_t>(cuda_stream), &n);
     h->last_launches = n;
     return rc;
 }

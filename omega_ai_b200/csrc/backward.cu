@@ -27,6 +27,7 @@
 #include <string.h>
 
 #include <new>
+#include <type_traits>
 
 #include "backward.cuh"
 #include "common.cuh"
@@ -41,6 +42,8 @@ struct BwState {
     int fwd_T;
     float aux_coef;   // weight of the auxiliary load-balancing loss in the objective (0: none)
     float *aux_ps;    // [E] column sums of the router probabilities (omoe_get_aux_loss)
+    void *dxn;        // [t_max, d] gradient of the normalised rows (block form), io dtype
+    float *inv_rms;   // [t_max] 1/rms of every row (block form)
     void *gu;         // [rows_cap, 2*dff] g | u (compute dtype)
     void *dyp;        // [rows_cap, d]
     void *dh;         // [rows_cap, dff]
@@ -579,8 +582,8 @@ cudaError_t transpose_weights(omoe_handle *h, BwState *b, cudaStream_t s, int *n
 }
 
 template <typename CT, typename OT>
-cudaError_t backward_t(omoe_handle *h, BwState *b, const void *x, const void *dy, void *dx, int T, cudaStream_t s,
-                       int *n) {
+cudaError_t backward_t(omoe_handle *h, BwState *b, const void *x, bool x_is_compute, const void *dy, void *dx, int T,
+                       cudaStream_t s, int *n) {
     const int d = h->cfg.d_model, dff = h->cfg.d_ff, El = h->e_local, E = h->cfg.n_experts, k = h->cfg.top_k;
     const int32_t *rows_in_use = h->ex_poffsets + El;
     const int warps = 8, tblocks = ceil_div(T, warps);
@@ -683,12 +686,17 @@ cudaError_t backward_t(omoe_handle *h, BwState *b, const void *x, const void *dy
     {
         const int slices = b->dwr_slices;
         dim3 grid((unsigned)ceil_div(d, 32), (unsigned)slices);
-        const OT *xr = static_cast<const OT *>(x);
-        if (E <= 8) dwr_partial_kernel<OT, 1><<<grid, 256, 0, s>>>(xr, b->dl, b->dwr_part, T, d, E, slices);
-        else if (E <= 16) dwr_partial_kernel<OT, 2><<<grid, 256, 0, s>>>(xr, b->dl, b->dwr_part, T, d, E, slices);
-        else if (E <= 32) dwr_partial_kernel<OT, 4><<<grid, 256, 0, s>>>(xr, b->dl, b->dwr_part, T, d, E, slices);
-        else if (E <= 64) dwr_partial_kernel<OT, 8><<<grid, 256, 0, s>>>(xr, b->dl, b->dwr_part, T, d, E, slices);
-        else dwr_partial_kernel<OT, 16><<<grid, 256, 0, s>>>(xr, b->dl, b->dwr_part, T, d, E, slices);
+        auto run = [&](auto *xr) {
+            using XT = typename std::remove_cv<typename std::remove_pointer<decltype(xr)>::type>::type;
+            if (E <= 8) dwr_partial_kernel<XT, 1><<<grid, 256, 0, s>>>(xr, b->dl, b->dwr_part, T, d, E, slices);
+            else if (E <= 16) dwr_partial_kernel<XT, 2><<<grid, 256, 0, s>>>(xr, b->dl, b->dwr_part, T, d, E, slices);
+            else if (E <= 32) dwr_partial_kernel<XT, 4><<<grid, 256, 0, s>>>(xr, b->dl, b->dwr_part, T, d, E, slices);
+            else if (E <= 64) dwr_partial_kernel<XT, 8><<<grid, 256, 0, s>>>(xr, b->dl, b->dwr_part, T, d, E, slices);
+            else dwr_partial_kernel<XT, 16><<<grid, 256, 0, s>>>(xr, b->dl, b->dwr_part, T, d, E, slices);
+        };
+        // x: the rows the router saw (the caller's rows, or the normalised rows of the block form)
+        if (x_is_compute) run(static_cast<const CT *>(x));
+        else run(static_cast<const OT *>(x));
         dwr_reduce_kernel<<<ceil_div(E * d, 256), 256, 0, s>>>(b->dwr_part, b->d_router, E * d, slices);
         dbias_kernel<<<E, 256, 0, s>>>(b->dl, b->d_bias, T, E);
         BW_TRY(cudaGetLastError());
@@ -707,7 +715,7 @@ cudaError_t backward_t(omoe_handle *h, BwState *b, const void *x, const void *dy
 void free_state(BwState *b) {
     if (!b->own_grad_rows) b->dyp = b->dxp = nullptr, b->dyp_table = b->dxp_table = nullptr;
     void *ptrs[] = {b->dyp_table, b->dxp_table, b->gu, b->dyp, b->dh, b->dgu, b->dxp, b->dgw, b->dl, b->dwr_part, b->wdT, b->wguT, b->xpT, b->hT,
-                    b->dypT, b->dguT, b->d_router, b->d_bias, b->d_gate, b->d_up, b->d_down, b->aux_ps};
+                    b->dypT, b->dguT, b->d_router, b->d_bias, b->d_gate, b->d_up, b->d_down, b->aux_ps, b->dxn, b->inv_rms};
     for (void *p : ptrs)
         if (p) cudaFree(p);
     delete b;
@@ -825,8 +833,8 @@ cudaError_t bw_forward_experts(omoe_handle *h, int T, cudaStream_t s, int *n) {
     return e;
 }
 
-int bw_backward(omoe_handle *h, const void *x, const void *dy, void *dx, int T, int io_dtype, cudaStream_t s,
-                int *launches) {
+int bw_backward(omoe_handle *h, const void *x, bool x_is_compute, const void *dy, void *dx, int T, int io_dtype,
+                cudaStream_t s, int *launches) {
     BwState *b = static_cast<BwState *>(h->bw);
     if (!b || !b->training) {
         snprintf(h->err, sizeof(h->err), "omoe_backward: call omoe_set_training(h, 1) and a forward first");
@@ -851,10 +859,10 @@ int bw_backward(omoe_handle *h, const void *x, const void *dy, void *dx, int T, 
     }
     cudaError_t e;
     if (h->cfg.compute_dtype == OMOE_BF16)
-        e = io_dtype == OMOE_BF16 ? backward_t<__nv_bfloat16, __nv_bfloat16>(h, b, x, dy, dx, T, s, launches)
-                                  : backward_t<__nv_bfloat16, float>(h, b, x, dy, dx, T, s, launches);
+        e = io_dtype == OMOE_BF16 ? backward_t<__nv_bfloat16, __nv_bfloat16>(h, b, x, x_is_compute, dy, dx, T, s, launches)
+                                  : backward_t<__nv_bfloat16, float>(h, b, x, x_is_compute, dy, dx, T, s, launches);
     else
-        e = backward_t<float, float>(h, b, x, dy, dx, T, s, launches);
+        e = backward_t<float, float>(h, b, x, x_is_compute, dy, dx, T, s, launches);
     if (e != cudaSuccess) {
         snprintf(h->err, sizeof(h->err), "omoe_backward: %s", cudaGetErrorString(e));
         return OMOE_ERR_CUDA;
@@ -879,6 +887,118 @@ int bw_get_grads(omoe_handle *h, float *d_router, float *d_bias, float *d_gate, 
             return OMOE_ERR_CUDA;
         }
     if (cudaStreamSynchronize(s) != cudaSuccess) return OMOE_ERR_CUDA;
+    return OMOE_OK;
+}
+
+namespace {
+
+// RMSNorm backward of one row per warp, after rmsnorm_backward_kernel2 (src/main/resources/cu/RMSKernel.cu:225-275):
+//   rms = sqrtf(sum(x^2)/C + eps);  drms = sum(x * dout * w) * (-1 / (rms^3 * C));
+//   dinp = dout * w / rms + drms * x.
+// Here dx = dy + dinp (the residual branch of the block adds dy itself) and 1/rms is kept per row for the
+// weight gradient, which the reference accumulates with atomics and this build sums in a fixed order.
+template <typename OT>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_kernel(const OT *__restrict__ x, const float *__restrict__ gamma, const OT *__restrict__ dxn,
+                   const OT *__restrict__ dy, OT *__restrict__ dx, float *__restrict__ inv_rms, float eps, int T,
+                   int d) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T) return;
+    const OT *xr = x + (size_t)t * d, *gr = dxn + (size_t)t * d;
+    float ss = 0.f, dot = 0.f;
+    for (int c = lane * 8; c < d; c += 256) {
+        float xv[8], gv[8], wv[8];
+        load8(xr + c, xv);
+        load8(gr + c, gv);
+        load8(gamma + c, wv);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            ss = fmaf(xv[i], xv[i], ss);
+            dot = fmaf(xv[i] * gv[i], wv[i], dot);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    }
+    const float rms = sqrtf(ss / (float)d + eps);
+    const float drms = dot * (-1.0f / (rms * rms * rms * (float)d));
+    if (lane == 0) inv_rms[t] = 1.0f / rms;
+    for (int c = lane * 8; c < d; c += 256) {
+        float xv[8], gv[8], wv[8], dv[8], o[8];
+        load8(xr + c, xv);
+        load8(gr + c, gv);
+        load8(gamma + c, wv);
+        load8(dy + (size_t)t * d + c, dv);
+#pragma unroll
+        for (int i = 0; i < 8; i++) o[i] = dv[i] + (gv[i] * wv[i] / rms + drms * xv[i]);
+        store8(dx + (size_t)t * d + c, o);
+    }
+}
+
+// d gamma[c] = sum_t (x[t,c] / rms_t) * dxn[t,c]: thread = column, blockIdx.y = slice of the tokens;
+// partials [slices][d] are added in order by dwr_reduce_kernel.
+template <typename OT>
+__global__ void __launch_bounds__(256)
+dgamma_partial_kernel(const OT *__restrict__ x, const OT *__restrict__ dxn, const float *__restrict__ inv_rms,
+                      float *__restrict__ part, int T, int d, int slices) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= d) return;
+    const int per = (T + slices - 1) / slices;
+    const int t0 = blockIdx.y * per, t1 = min(T, t0 + per);
+    float acc = 0.f;
+    for (int t = t0; t < t1; t++) acc = fmaf(ldf(x + (size_t)t * d + c) * inv_rms[t], ldf(dxn + (size_t)t * d + c), acc);
+    part[(size_t)blockIdx.y * d + c] = acc;
+}
+
+template <typename OT>
+cudaError_t block_tail_t(omoe_handle *h, BwState *b, const void *x, const float *gamma, float eps, const void *dy,
+                         void *dx, float *dgamma, int T, cudaStream_t s, int *n) {
+    const int d = h->cfg.d_model, slices = b->dwr_slices;
+    if (T > 0)
+        rmsnorm_bwd_kernel<OT><<<ceil_div(T, 8), 256, 0, s>>>(static_cast<const OT *>(x), gamma,
+                                                             static_cast<const OT *>(b->dxn),
+                                                             static_cast<const OT *>(dy), static_cast<OT *>(dx),
+                                                             b->inv_rms, eps, T, d);
+    // the partial buffer of the router's weight gradient is free again by now ([slices][E][d] >= [slices][d])
+    dgamma_partial_kernel<OT><<<dim3(ceil_div(d, 256), slices), 256, 0, s>>>(
+        static_cast<const OT *>(x), static_cast<const OT *>(b->dxn), b->inv_rms, b->dwr_part, T, d, slices);
+    dwr_reduce_kernel<<<ceil_div(d, 256), 256, 0, s>>>(b->dwr_part, dgamma, d, slices);
+    BW_TRY(cudaGetLastError());
+    *n += 3;
+    return cudaSuccess;
+}
+
+}  // namespace
+
+// Backward of y = x + MoE(rmsnorm(x) * gamma): the layer's backward on the normalised rows the forward kept,
+// then the RMSNorm backward, with the residual branch's dy added in the same pass.
+int bw_backward_block(omoe_handle *h, const void *x, const float *gamma, float eps, const void *dy, void *dx,
+                      float *dgamma, int T, int io_dtype, cudaStream_t s, int *launches) {
+    BwState *b = static_cast<BwState *>(h->bw);
+    if (!b || !b->training) {
+        snprintf(h->err, sizeof(h->err), "omoe_backward_block: call omoe_set_training(h, 1) and a forward first");
+        return OMOE_ERR_STATE;
+    }
+    if (!b->dxn) {
+        const size_t bytes = (size_t)h->cfg.t_max * h->cfg.d_model * 4;
+        if (cudaMalloc(&b->dxn, bytes) != cudaSuccess || cudaMalloc(&b->inv_rms, (size_t)h->cfg.t_max * 4) != cudaSuccess) {
+            cudaGetLastError();
+            snprintf(h->err, sizeof(h->err), "omoe_backward_block: device allocation failed");
+            return OMOE_ERR_NOMEM;
+        }
+    }
+    int rc = bw_backward(h, h->xn, true, dy, b->dxn, T, io_dtype, s, launches);
+    if (rc != OMOE_OK) return rc;
+    cudaError_t e = io_dtype == OMOE_BF16
+                        ? block_tail_t<__nv_bfloat16>(h, b, x, gamma, eps, dy, dx, dgamma, T, s, launches)
+                        : block_tail_t<float>(h, b, x, gamma, eps, dy, dx, dgamma, T, s, launches);
+    if (e != cudaSuccess) {
+        snprintf(h->err, sizeof(h->err), "omoe_backward_block: %s", cudaGetErrorString(e));
+        return OMOE_ERR_CUDA;
+    }
     return OMOE_OK;
 }
 

@@ -11,8 +11,11 @@ void bw_weights_changed(omoe_handle *h);
 void bw_forward_invalidate(omoe_handle *h);
 // Expert stage of a training-mode forward: g and u kept, then h = silu(g) * u, then the down product.
 cudaError_t bw_forward_experts(omoe_handle *h, int T, cudaStream_t s, int *n);
-int bw_backward(omoe_handle *h, const void *x, const void *dy, void *dx, int T, int io_dtype, cudaStream_t s,
-                int *launches);
+// x_is_compute: x has the layer's compute dtype (the normalised rows of the block form) instead of io_dtype
+int bw_backward(omoe_handle *h, const void *x, bool x_is_compute, const void *dy, void *dx, int T, int io_dtype,
+                cudaStream_t s, int *launches);
+int bw_backward_block(omoe_handle *h, const void *x, const float *gamma, float eps, const void *dy, void *dx,
+                      float *dgamma, int T, int io_dtype, cudaStream_t s, int *launches);
 int bw_get_grads(omoe_handle *h, float *d_router, float *d_bias, float *d_gate, float *d_up, float *d_down,
                  cudaStream_t s);
 int bw_set_aux(omoe_handle *h, float coef);

@@ -242,6 +242,16 @@ class MoELayer(Layer):
                                                _dt(x.dtype), s))
         return dx
 
+    def backward_block(self, x: torch.Tensor, gamma: torch.Tensor, dy: torch.Tensor, eps: float = 1e-5, stream=None):
+        """Backward of :meth:`forward_block`: returns (dx, dgamma); weight gradients via :meth:`weight_grads`."""
+        assert x.is_cuda and dy.is_cuda and x.is_contiguous() and dy.is_contiguous() and x.dtype == dy.dtype
+        dx = torch.empty_like(x)
+        dgamma = torch.empty(self.embedDim, dtype=torch.float32, device=x.device)
+        s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        check(self._h, self._lib.omoe_backward_block(self._h, x.data_ptr(), gamma.data_ptr(), eps, dy.data_ptr(),
+                                                     dx.data_ptr(), dgamma.data_ptr(), x.shape[0], _dt(x.dtype), s))
+        return dx, dgamma
+
     def set_aux_loss(self, coef: float):
         """Weight of the auxiliary load-balancing loss E * sum_e f_e * P_e in the objective :meth:`backward` differentiates."""
         check(self._h, self._lib.omoe_set_aux_loss(self._h, float(coef)))

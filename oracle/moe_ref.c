@@ -133,6 +133,38 @@ void ref_rmsnorm_rows(const float *x, const float *gamma, float eps, int64_t T, 
     }
 }
 
+/* RMSNorm backward, row by row, as rmsnorm_backward_kernel2 computes it
+ * (src/main/resources/cu/RMSKernel.cu:225-275): rms = sqrtf(sum(x^2)/C + eps) (same tree as the forward here),
+ * drms = sum_i(x_i * dout_i * w_i) * (-1 / (rms^3 * C)) in index order,
+ * dinp_i = dout_i * w_i / rms + drms * x_i,  dweight_i = sum over rows (in row order) of (x_i / rms) * dout_i.
+ * dweight is overwritten. */
+void ref_rmsnorm_backward_rows(const float *x, const float *gamma, float eps, const float *dout, int64_t T, int64_t d,
+                               float *dinp, float *dweight) {
+    for (int64_t i = 0; i < d; i++) dweight[i] = 0.0f;
+    for (int64_t t = 0; t < T; t++) {
+        const float *xr = x + t * d, *gr = dout + t * d;
+        float lane[32];
+        for (int l = 0; l < 32; l++) lane[l] = 0.0f;
+        for (int64_t i = 0; i < d; i++) {
+            int l = (int)((i >> 3) & 31);
+            lane[l] = fmaf(xr[i], xr[i], lane[l]);
+        }
+        for (int m = 16; m >= 1; m >>= 1) {
+            float nxt[32];
+            for (int l = 0; l < 32; l++) nxt[l] = lane[l] + lane[l ^ m];
+            for (int l = 0; l < 32; l++) lane[l] = nxt[l];
+        }
+        float rms = sqrtf(lane[0] / (float)d + eps);
+        float drms = 0.0f;
+        for (int64_t i = 0; i < d; i++) drms += xr[i] * gr[i] * gamma[i];
+        drms = drms * (-1.0f / (rms * rms * rms * (float)d));
+        for (int64_t i = 0; i < d; i++) {
+            dinp[t * d + i] = gr[i] * gamma[i] / rms + drms * xr[i];
+            dweight[i] += (xr[i] / rms) * gr[i];
+        }
+    }
+}
+
 /* ---- routing (no reference counterpart; rules fixed here) ---------------- */
 
 /* Router logits = x * W_r^T (+ bias), FullyLayer semantics as above, but with a

@@ -94,6 +94,10 @@ void ref_moe_forward(const ref_moe_shape *shape,
                      int32_t *counts, int32_t *offsets, int32_t *perm,
                      const int32_t *sel, int64_t n_sel, float *y, int nthreads);
 
+/* RMSNorm backward (rmsnorm_backward_kernel2, RMSKernel.cu:225-275); dweight [d] is overwritten. */
+void ref_rmsnorm_backward_rows(const float *x, const float *gamma, float eps, const float *dout, int64_t T, int64_t d,
+                               float *dinp, float *dweight);
+
 /* SiLU and softmax backward, element by element / row by row as the reference's kernels
  * silu_backward (activeFunction.cu:182-190) and softmax_back (SoftmaxKernel.cu:100-112) compute them. */
 void ref_silu_backward(const float *x, const float *delta, float *diff, int64_t n);

@@ -55,6 +55,7 @@ def lib():
         _lib.ref_moe_forward.argtypes = [
             C.POINTER(_Shape), fp, fp, fp, fp, fp, fp, fp, ip, fp, ip, ip, ip, ip, i64, fp, C.c_int,
         ]
+        _lib.ref_rmsnorm_backward_rows.argtypes = [fp, fp, C.c_float, fp, i64, i64, fp, fp]
         _lib.ref_silu_backward.argtypes = [fp, fp, fp, i64]
         _lib.ref_softmax_back_rows.argtypes = [fp, fp, fp, i64, i64]
         _lib.ref_moe_backward.argtypes = [C.POINTER(_Shape)] + [fp] * 7 + [C.c_float] + [fp] * 6 + [C.c_int]
@@ -266,3 +267,27 @@ def moe_backward(x, w_r, w_gate, w_up, w_down, k: int, dy, *, bias=None, renorm=
                            _f(g.dx), _f(g.d_w_r), _f(g.d_bias), _f(g.d_w_gate), _f(g.d_w_up), _f(g.d_w_down),
                            nthreads)
     return g
+
+
+def rmsnorm_backward(x, gamma, dout, eps: float = 1e-5):
+    """(dinp [T,d], dgamma [d]) of out = (x / rms(x)) * gamma for a given dout."""
+    x, gamma, dout = _cf(x), _cf(gamma), _cf(dout)
+    dinp, dgamma = np.empty_like(x), np.empty_like(gamma)
+    lib().ref_rmsnorm_backward_rows(_f(x), _f(gamma), eps, _f(dout), x.shape[0], x.shape[1], _f(dinp), _f(dgamma))
+    return dinp, dgamma
+
+
+def moe_block_backward(x, gamma, w_r, w_gate, w_up, w_down, k: int, dy, *, eps=1e-5, bias=None, renorm=True,
+                       bf16=False, out_bf16=None):
+    """Backward of y = x + MoE(rmsnorm(x) * gamma): (dx, dgamma, MoEGrads of the layer on the normalised rows).
+    bf16 mode rounds where the GPU path stores bf16: the normalised rows, and (with out_bf16) the gradient of
+    the normalised rows and dx."""
+    if out_bf16 is None:
+        out_bf16 = bf16
+    xn = rmsnorm(x, gamma, eps, bf16=bf16)
+    g = moe_backward(xn, w_r, w_gate, w_up, w_down, k, dy, bias=bias, renorm=renorm, bf16=bf16, out_bf16=out_bf16)
+    dinp, dgamma = rmsnorm_backward(x, gamma, g.dx, eps)
+    dx = (_cf(dy) + dinp).astype(np.float32)
+    if out_bf16:
+        dx = bf16_round(dx)
+    return dx, dgamma, g

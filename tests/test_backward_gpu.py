@@ -122,6 +122,46 @@ def test_aux_loss_value_and_gradient(oracle, compute):
     layer.close()
 
 
+@pytest.mark.parametrize("compute,io", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                        (torch.bfloat16, torch.float32)])
+def test_block_backward_matches_oracle(oracle, compute, io):
+    """y = x + MoE(rmsnorm(x) * gamma): dx, d gamma and the weight gradients of omoe_backward_block."""
+    from omega_ai_b200 import MoELayer
+    T, d, dff, E, k = 300, 256, 384, 8, 2
+    x, w_r, w_g, w_u, w_d, _ = make_layer(T, d, dff, E, k, seed=25)
+    bf = compute == torch.bfloat16
+    rb = oracle.bf16_round
+    x = (2.0 * x).astype(np.float32)
+    w_r, w_g, w_u, w_d = w_r * 10, w_g * 3, w_u * 3, w_d * 3
+    gamma = (1.0 + 0.2 * np.random.default_rng(3).standard_normal(d)).astype(np.float32)
+    dy = np.random.default_rng(4).standard_normal((T, d)).astype(np.float32)
+    if io == torch.bfloat16:
+        x, dy = rb(x), rb(dy)
+    if bf:
+        w_r, w_g, w_u, w_d = rb(w_r), rb(w_g), rb(w_u), rb(w_d)
+    out_bf16 = io == torch.bfloat16
+    dx_ref, dgamma_ref, g_ref = oracle.moe_block_backward(x, gamma, w_r, w_g, w_u, w_d, k, dy, bf16=bf, out_bf16=out_bf16)
+    layer = MoELayer(d, dff, E, k, t_max=T, compute_dtype=compute)
+    layer.setWeights(dev(w_r, compute), dev(w_g, compute), dev(w_u, compute), dev(w_d, compute))
+    layer.set_training(True)
+    xd, gd = dev(x, io), dev(gamma)
+    layer.forward_block(xd, gd)
+    dx, dgamma = layer.backward_block(xd, gd, dev(dy, io))
+    g = layer.weight_grads()
+    got = dict(dx=dx.float().cpu().numpy(), dgamma=dgamma.cpu().numpy(), d_w_r=g["d_router"].cpu().numpy(),
+               d_w_gate=g["d_gate"].cpu().numpy(), d_w_down=g["d_down"].cpu().numpy())
+    want = dict(dx=dx_ref, dgamma=dgamma_ref, d_w_r=g_ref.d_w_r, d_w_gate=g_ref.d_w_gate, d_w_down=g_ref.d_w_down)
+    for name in got:
+        if bf:
+            try:
+                assert_close_bf16(got[name], want[name])
+            except AssertionError as e:
+                raise AssertionError(f"{name}: {e}") from None
+        else:
+            close_scaled(got[name], want[name], name, 2e-4)
+    layer.close()
+
+
 def test_backward_call_order_and_modes(oracle):
     from omega_ai_b200 import MoELayer
     from omega_ai_b200.native import OmoeError

@@ -115,3 +115,17 @@ def test_aux_loss_value_and_gradient(oracle):
         close(getattr(g, name), ref[name], name)
     assert np.abs(g.d_w_r - g0.d_w_r).max() > 1e-4          # the term is there
     assert np.array_equal(g.d_w_down, g0.d_w_down)           # and touches the router's side only
+
+
+def test_rmsnorm_backward_matches_autograd(oracle):
+    rng = np.random.default_rng(8)
+    x = (2 * rng.standard_normal((9, 96))).astype(np.float32)
+    gamma = (1 + 0.2 * rng.standard_normal(96)).astype(np.float32)
+    dout = rng.standard_normal((9, 96)).astype(np.float32)
+    X = torch.tensor(x, dtype=torch.float64, requires_grad=True)
+    G = torch.tensor(gamma, dtype=torch.float64, requires_grad=True)
+    out = X / torch.sqrt((X * X).mean(dim=1, keepdim=True) + 1e-5) * G
+    out.backward(torch.tensor(dout, dtype=torch.float64))
+    dinp, dgamma = oracle.rmsnorm_backward(x, gamma, dout)
+    close(dinp, X.grad.numpy(), "dinp", rtol=1e-5)
+    close(dgamma, G.grad.numpy(), "dgamma", rtol=1e-5)
