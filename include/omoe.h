@@ -1,6 +1,7 @@
 /*
- * omoe.h — C ABI of libomoe.so: the mixture-of-experts FFN forward for
- * Omega-AI, built for NVIDIA B200 (sm_100a).
+ * omoe.h — C ABI of libomoe.so: the mixture-of-experts FFN layer for
+ * Omega-AI (forward, and the backward pass for training), built for NVIDIA
+ * B200 (sm_100a).
  *
  * The library takes the place of the JCuda "load a CUfunction by name and
  * cuLaunchKernel it" plumbing for this one layer.  A Java layer (or any other
