@@ -75,8 +75,6 @@ namespace {
 // ---- element access for fp32 and bf16 rows --------------------------------------------------------
 __device__ __forceinline__ float ldf(const float *p) { return *p; }
 __device__ __forceinline__ float ldf(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
-__device__ __forceinline__ void stf(float *p, float v) { *p = v; }
-__device__ __forceinline__ void stf(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
 
 __device__ __forceinline__ void load8(const float *p, float (&v)[8]) {
     float4 a = *reinterpret_cast<const float4 *>(p), b = *(reinterpret_cast<const float4 *>(p) + 1);
