@@ -104,7 +104,7 @@ int omoe_destroy(omoe_handle *h) {
     if (!h) return OMOE_OK;
     ep_destroy(h);
     bw_destroy(h);
-    void *ptrs[] = {h->w_router, h->router_bias, h->w_gate, h->w_up, h->w_down, h->logits, h->topk_idx,
+    void *ptrs[] = {h->w_router, h->w_router_bf16, h->router_bias, h->w_gate, h->w_up, h->w_down, h->logits, h->topk_idx,
                     h->topk_w, h->block_counts, h->block_base, h->counts, h->offsets, h->poffsets, h->tile_expert, h->pos, h->lrank,
                     h->perm_out, h->dev_err, h->xp, h->hbuf, h->yp, h->xn, h->x_stage, h->y_stage, h->d_row_table,
                     h->d_out_table, h->ticket, h->dst_base != h->poffsets ? h->dst_base : nullptr};
@@ -286,6 +286,15 @@ int omoe_set_weights(omoe_handle *h, const void *w_router, const void *router_bi
     const int64_t E = h->cfg.n_experts, d = h->cfg.d_model, dff = h->cfg.d_ff, El = h->e_local;
     const int64_t n_exp = El * dff * d;
     // router weights and bias are always held in fp32
+    if (src_dtype == OMOE_BF16 && E > 16) {
+        // bf16 values are exact in both copies; the router kernel stages the narrow one (half the L2 traffic)
+        if (!h->w_router_bf16) CU_TRY(h, cudaMalloc(reinterpret_cast<void **>(&h->w_router_bf16), E * d * 2));
+        CU_TRY(h, cudaMemcpyAsync(h->w_router_bf16, w_router, E * d * 2, cudaMemcpyDeviceToDevice, s));
+    } else if (h->w_router_bf16) {
+        CU_TRY(h, cudaStreamSynchronize(s));  // an earlier forward may still read it
+        cudaFree(h->w_router_bf16);
+        h->w_router_bf16 = nullptr;
+    }
     if (src_dtype == OMOE_F32) {
         CU_TRY(h, cudaMemcpyAsync(h->w_router, w_router, E * d * 4, cudaMemcpyDeviceToDevice, s));
         if (h->cfg.has_router_bias)

@@ -53,6 +53,7 @@ struct omoe_handle {
     // weights (device)
     float *w_router;      // [E, d] fp32
     float *router_bias;   // [E] fp32 or null
+    __nv_bfloat16 *w_router_bf16;  // [E, d] copy, only while the router weights were given as bf16 (exact)
     void *w_gate, *w_up;  // [E_local, dff, d] compute dtype
     void *w_down;         // [E_local, d, dff]
 

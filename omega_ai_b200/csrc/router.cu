@@ -23,6 +23,7 @@
 // warp holds TPW tokens x EPW experts of accumulators; with many experts ES
 // warps share one token group and split the experts, so every weight read from
 // shared memory feeds TPW tokens.
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -74,7 +75,11 @@ __device__ __forceinline__ void fma2(unsigned long long &acc, unsigned long long
     asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(x), "l"(w));
 }
 
-template <int EMAX, int ES, int TPW, typename XT>
+// WT: element type of the router weights staged in shared memory.  float always works; __nv_bfloat16 is used
+// when the weights were handed over as bf16 (every value is then exactly representable, so the logits keep
+// every bit) and halves the bytes a block pulls from L2 per step, which is what bounds the kernel when there
+// are many experts (a block re-reads all E rows for its 8 tokens).
+template <int EMAX, int ES, int TPW, typename XT, typename WT = float>
 struct RouterCfg {
     static constexpr int EPW = EMAX / ES;                 // experts per warp
     static constexpr int NG = kRouterWarps / ES;          // token groups per block
@@ -83,7 +88,7 @@ struct RouterCfg {
     static constexpr int NSUB = 1;
     static constexpr int CS = NSUB * kSub;                // columns per stage
     static constexpr int XBYTES = TB * CS * (int)sizeof(XT);
-    static constexpr int WBYTES = EMAX * CS * 4;
+    static constexpr int WBYTES = EMAX * CS * (int)sizeof(WT);
     static constexpr int STAGE = XBYTES + WBYTES;
     static constexpr int BUDGET = (EMAX <= 16) ? 100 * 1024 : 212 * 1024;  // two blocks per SM for few experts
     static constexpr int S0 = BUDGET / STAGE;
@@ -93,14 +98,15 @@ struct RouterCfg {
 
 // EMAX: experts padded to a power of two (>= E); ES: warps sharing a token
 // group; TPW: tokens per warp.
-template <int EMAX, int ES, int TPW, typename XT>
-__global__ void __launch_bounds__(kRouterWarps * 32, RouterCfg<EMAX, ES, TPW, XT>::MINB)
-router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const float *__restrict__ bias,
+template <int EMAX, int ES, int TPW, typename XT, typename WT = float>
+__global__ void __launch_bounds__(kRouterWarps * 32, RouterCfg<EMAX, ES, TPW, XT, WT>::MINB)
+router_kernel(const XT *__restrict__ x, const WT *__restrict__ w_r, const float *__restrict__ bias,
               int T, int d, int E, int k, int renorm,
               float *__restrict__ logits, int32_t *__restrict__ topk_idx, float *__restrict__ topk_w,
               int32_t *__restrict__ block_counts, int32_t *__restrict__ local_rank) {
-    using C = RouterCfg<EMAX, ES, TPW, XT>;
+    using C = RouterCfg<EMAX, ES, TPW, XT, WT>;
     constexpr int EPW = C::EPW, TB = C::TB, S = C::S, NSUB = C::NSUB, CS = C::CS;
+    constexpr bool WBF = sizeof(WT) == 2;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     // stage layout: x rows [TB][CS] XT, then weights [NSUB][2 halves][EMAX][32 lanes][4] fp32
     float *sl = reinterpret_cast<float *>(smem_raw + S * C::STAGE);  // [TB][EMAX] logits, later exp values
@@ -122,14 +128,18 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
     constexpr int PPR = kSub * (int)sizeof(XT) / 16;      // 16-byte pieces per token row (32 bf16 / 64 fp32)
     constexpr int XROWS_PER_IT = kRouterWarps * 32 / PPR;  // token rows covered per pass of the block
     constexpr int XIT = (TB + XROWS_PER_IT - 1) / XROWS_PER_IT;
-    constexpr int WIT = EMAX / 4;
+    // fp32 weights: 64 pieces per row, 4 rows per pass; bf16 weights: 32 pieces per row, 8 rows per pass, and a
+    // piece is exactly one lane's 8 elements
+    constexpr int WIT = WBF ? EMAX / 8 : EMAX / 4;
     const int x_row0 = tid / PPR, x_piece = tid % PPR;
     const int x_col = x_piece * (16 / (int)sizeof(XT));    // column inside the step
     const XT *x_src0 = x + (size_t)(t0 + x_row0) * d + x_col;
-    const int w_e0 = tid >> 6, w_q = tid & 63;
-    const int w_col = 4 * w_q;
-    const float *w_src0 = w_r + (size_t)w_e0 * d + w_col;
-    const uint32_t w_dst0 = C::XBYTES + (((w_q & 1) * EMAX + w_e0) * 32 + (w_q >> 1)) * 16;  // lane-split layout
+    const int w_e0 = WBF ? tid >> 5 : tid >> 6, w_q = WBF ? tid & 31 : tid & 63;
+    const int w_col = WBF ? 8 * w_q : 4 * w_q;
+    const WT *w_src0 = w_r + (size_t)w_e0 * d + w_col;
+    const uint32_t w_dst0 = WBF ? C::XBYTES + (w_e0 * 32 + w_q) * 16  // [expert][lane] 16-byte chunks
+                                : C::XBYTES + (((w_q & 1) * EMAX + w_e0) * 32 + (w_q >> 1)) * 16;  // lane-split layout
+    constexpr int W_ROWS_PER_IT = WBF ? 8 : 4;
     auto issue_stage = [&](int su) {
         const uint32_t st = smem_base + (su % S) * C::STAGE;
         const int c0 = su * CS;
@@ -146,9 +156,9 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
         const bool wcol_ok = c0 + w_col < d;
 #pragma unroll
         for (int it = 0; it < WIT; it++) {
-            const bool ok = wcol_ok && (w_e0 + 4 * it < E);
-            const float *src = ok ? w_src0 + (size_t)it * 4 * d + c0 : w_r;
-            cp_async16(st + w_dst0 + (uint32_t)it * (4 * 32 * 16), src, ok ? 16 : 0);
+            const bool ok = wcol_ok && (w_e0 + W_ROWS_PER_IT * it < E);
+            const WT *src = ok ? w_src0 + (size_t)it * W_ROWS_PER_IT * d + c0 : w_r;
+            cp_async16(st + w_dst0 + (uint32_t)it * (W_ROWS_PER_IT * 32 * 16), src, ok ? 16 : 0);
         }
     };
 
@@ -192,10 +202,15 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
             for (int e = 0; e < EPW; e++) {
                 const int eg = es * EPW + e;
                 unsigned long long wv[4];
-                const uint32_t wa = static_cast<uint32_t>(__cvta_generic_to_shared(ws + (eg * 32 + lane) * 4));
-                const uint32_t wb = static_cast<uint32_t>(__cvta_generic_to_shared(ws + ((EMAX + eg) * 32 + lane) * 4));
-                asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(wv[0]), "=l"(wv[1]) : "r"(wa));
-                asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(wv[2]), "=l"(wv[3]) : "r"(wb));
+                if constexpr (WBF) {
+                    lds_pairs(reinterpret_cast<const __nv_bfloat16 *>(wst) + (eg * 32 + lane) * 8, wv);
+                } else {
+                    const uint32_t wa = static_cast<uint32_t>(__cvta_generic_to_shared(ws + (eg * 32 + lane) * 4));
+                    const uint32_t wb =
+                        static_cast<uint32_t>(__cvta_generic_to_shared(ws + ((EMAX + eg) * 32 + lane) * 4));
+                    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(wv[0]), "=l"(wv[1]) : "r"(wa));
+                    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(wv[2]), "=l"(wv[3]) : "r"(wb));
+                }
 #pragma unroll
                 for (int i = 0; i < TPW; i++)
 #pragma unroll
@@ -275,18 +290,21 @@ router_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const flo
     RTRACE(4);
 }
 
-template <int EMAX, int ES, int TPW, typename XT>
+template <int EMAX, int ES, int TPW, typename XT, typename WT = float>
 cudaError_t launch_one(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
-    using C = RouterCfg<EMAX, ES, TPW, XT>;
+    using C = RouterCfg<EMAX, ES, TPW, XT, WT>;
     const int k = h->cfg.top_k;
     size_t smem = (size_t)C::S * C::STAGE + sizeof(float) * C::TB * EMAX + sizeof(int32_t) * C::TB * kMaxTopK +
                   sizeof(float) * EMAX;
-    auto kern = router_kernel<EMAX, ES, TPW, XT>;
+    auto kern = router_kernel<EMAX, ES, TPW, XT, WT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     h->tokens_per_block = C::TB;  // the scan and dispatch kernels walk the histogram with this granularity
     int blocks = ceil_div(T, C::TB);
-    kern<<<blocks, kRouterWarps * 32, smem, s>>>(x, h->w_router, h->router_bias, T, h->cfg.d_model,
+    const WT *w;
+    if constexpr (sizeof(WT) == 2) w = h->w_router_bf16;
+    else w = h->w_router;
+    kern<<<blocks, kRouterWarps * 32, smem, s>>>(x, w, h->router_bias, T, h->cfg.d_model,
                                                   h->cfg.n_experts, k, h->cfg.renormalize, h->logits,
                                                   h->topk_idx, h->topk_w, h->block_counts, h->lrank);
     return cudaGetLastError();
@@ -294,15 +312,15 @@ cudaError_t launch_one(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
 
 // More tokens per warp reuse every router weight read from shared memory more
 // often; fewer give more blocks.  Take the largest that still fills the GPU twice.
-template <int EMAX, int ES, typename XT>
+template <int EMAX, int ES, typename XT, typename WT = float>
 cudaError_t launch_tpw(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
     const int want_blocks = 2 * (h->sm_count > 0 ? h->sm_count : 148);
     constexpr int NG = kRouterWarps / ES;
     // accumulators take 2 registers per (token, expert): 4 tokens x 16 experts per warp is the most that fits
     if constexpr (EMAX / ES <= 16)
-        if (ceil_div(T, NG * 4) >= want_blocks) return launch_one<EMAX, ES, 4, XT>(h, x, T, s);
-    if (ceil_div(T, NG * 2) >= want_blocks) return launch_one<EMAX, ES, 2, XT>(h, x, T, s);
-    return launch_one<EMAX, ES, 1, XT>(h, x, T, s);
+        if (ceil_div(T, NG * 4) >= want_blocks) return launch_one<EMAX, ES, 4, XT, WT>(h, x, T, s);
+    if (ceil_div(T, NG * 2) >= want_blocks) return launch_one<EMAX, ES, 2, XT, WT>(h, x, T, s);
+    return launch_one<EMAX, ES, 1, XT, WT>(h, x, T, s);
 }
 
 template <typename XT>
@@ -311,6 +329,13 @@ cudaError_t launch_typed(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
     if (E <= 8) return launch_tpw<8, 1, XT>(h, x, T, s);
     // beyond 16 experts several warps share a token group, 16 experts each
     if (E <= 16) return launch_tpw<16, 1, XT>(h, x, T, s);
+    // many experts: the weight rows a block re-reads per step dominate its traffic; stage them as bf16 when exact
+    static const bool wbf_off = getenv("OMOE_ROUTER_W32") && atoi(getenv("OMOE_ROUTER_W32")) != 0;
+    if (h->w_router_bf16 != nullptr && !wbf_off) {
+        if (E <= 32) return launch_tpw<32, 2, XT, __nv_bfloat16>(h, x, T, s);
+        if (E <= 64) return launch_tpw<64, 4, XT, __nv_bfloat16>(h, x, T, s);
+        return launch_tpw<128, 8, XT, __nv_bfloat16>(h, x, T, s);
+    }
     if (E <= 32) return launch_tpw<32, 2, XT>(h, x, T, s);
     if (E <= 64) return launch_tpw<64, 4, XT>(h, x, T, s);
     return launch_tpw<128, 8, XT>(h, x, T, s);
