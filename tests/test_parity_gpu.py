@@ -125,6 +125,26 @@ def test_forward_host_matches_device(oracle):
     layer.close()
 
 
+@pytest.mark.parametrize("T", [8192 + 24, 16384 + 37, 40000])
+def test_forward_host_in_chunks_matches_device(T):
+    """Large host batches are cut into chunks whose copies overlap the kernels of their neighbours (2, 4 or 8 chunks;
+    with 4 the first and last are cut once more).  Tokens are independent: every output row keeps its bits."""
+    from omega_ai_b200 import MoELayer
+    d, dff, E, k = 128, 128, 8, 2
+    _, w_r, w_g, w_u, w_d, _ = make_layer(1, d, dff, E, k, seed=10)
+    layer = MoELayer(d, dff, E, k, t_max=T, compute_dtype=torch.bfloat16)
+    dev = lambda a: torch.from_numpy(a).cuda().to(torch.bfloat16).contiguous()
+    layer.setWeights(dev(w_r), dev(w_g), dev(w_u), dev(w_d))
+    g = torch.Generator(device="cuda").manual_seed(3)
+    xd = torch.randn(T, d, device="cuda", generator=g).to(torch.bfloat16)
+    yd = layer.forward_device(xd).clone()
+    xh = xd.cpu().pin_memory()
+    yh = torch.empty_like(xh).pin_memory()
+    layer.forward_host(xh, yh)
+    assert torch.equal(yd.cpu(), yh)
+    layer.close()
+
+
 def test_errors_are_reported_not_fatal():
     from omega_ai_b200 import MoELayer, OmoeError
     layer = MoELayer(128, 256, 8, 2, t_max=16, compute_dtype=torch.bfloat16)
