@@ -500,35 +500,22 @@ int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host, int32_t 
         CU_TRY(h, cudaStreamSynchronize(s));
         return check_dev_err(h);
     }
-    // Chunk boundaries.  Only the first chunk's copy in and the last chunk's copy out are not hidden behind
-    // kernels, so the first and the last chunk are cut once more (a quarter and three quarters of a chunk).
-    int bound[kHostChunksMax + 1];
-    int nb = 0;
     const int per = (T + chunks - 1) / chunks;
-    static const bool taper = !(getenv("OMOE_HOST_TAPER") && atoi(getenv("OMOE_HOST_TAPER")) == 0);
-    const bool cut_ends = taper && chunks >= 4 && chunks + 2 <= kHostChunksMax && per / 4 >= 512;
-    bound[nb++] = 0;
-    for (int i = 0; i < chunks; i++) {
-        const int t0 = i * per, t1 = (t0 + per <= T) ? t0 + per : T;
-        if (t1 <= t0) break;
-        if (cut_ends && i == 0) bound[nb++] = t0 + per / 4;
-        if (cut_ends && i == chunks - 1 && t1 - t0 > per / 4) bound[nb++] = t1 - per / 4;
-        bound[nb++] = t1;
-    }
-    const int pieces = nb - 1;
     // the copy streams must not run ahead of work already queued on the caller's stream
     CU_TRY(h, cudaEventRecord(h->ev_in[0], s));
     CU_TRY(h, cudaStreamWaitEvent(h->copy_in, h->ev_in[0], 0));
     CU_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev_in[0], 0));
-    for (int i = 0; i < pieces; i++) {
-        const int t0 = bound[i], n = bound[i + 1] - t0;
+    for (int i = 0; i < chunks; i++) {
+        const int t0 = i * per, n = (t0 + per <= T) ? per : T - t0;
+        if (n <= 0) break;
         const size_t off = (size_t)t0 * row_bytes;
         CU_TRY(h, cudaMemcpyAsync(static_cast<char *>(h->x_stage) + off, static_cast<const char *>(x_host) + off,
                                   (size_t)n * row_bytes, cudaMemcpyHostToDevice, h->copy_in));
         CU_TRY(h, cudaEventRecord(h->ev_in[i], h->copy_in));
     }
-    for (int i = 0; i < pieces; i++) {
-        const int t0 = bound[i], n = bound[i + 1] - t0;
+    for (int i = 0; i < chunks; i++) {
+        const int t0 = i * per, n = (t0 + per <= T) ? per : T - t0;
+        if (n <= 0) break;
         const size_t off = (size_t)t0 * row_bytes;
         CU_TRY(h, cudaStreamWaitEvent(s, h->ev_in[i], 0));
         int rc = omoe_forward(h, static_cast<char *>(h->x_stage) + off, static_cast<char *>(h->y_stage) + off, n,

@@ -127,8 +127,8 @@ def test_forward_host_matches_device(oracle):
 
 @pytest.mark.parametrize("T", [8192 + 24, 16384 + 37, 40000])
 def test_forward_host_in_chunks_matches_device(T):
-    """Large host batches are cut into chunks whose copies overlap the kernels of their neighbours (2, 4 or 8 chunks;
-    with 4 the first and last are cut once more).  Tokens are independent: every output row keeps its bits."""
+    """Large host batches are cut into 2, 4 or 8 chunks whose copies overlap the kernels of their neighbours.
+    Tokens are independent: every output row keeps its bits."""
     from omega_ai_b200 import MoELayer
     d, dff, E, k = 128, 128, 8, 2
     _, w_r, w_g, w_u, w_d, _ = make_layer(1, d, dff, E, k, seed=10)
