@@ -311,10 +311,14 @@ cudaError_t launch_one(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
 }
 
 // More tokens per warp reuse every router weight read from shared memory more
-// often; fewer give more blocks.  Take the largest that still fills the GPU twice.
+// often; fewer give more blocks.  Take the largest that still gives most SMs a block
+// (measured on 2048 to 8192 tokens: fatter blocks beat fuller grids, the per-block
+// prologue and epilogue being what they are).
 template <int EMAX, int ES, typename XT, typename WT = float>
 cudaError_t launch_tpw(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
-    const int want_blocks = 2 * (h->sm_count > 0 ? h->sm_count : 148);
+    // OMOE_ROUTER_FILL: blocks wanted per SM before a smaller tokens-per-warp is taken (tuning knob)
+    static const float fill = getenv("OMOE_ROUTER_FILL") ? (float)atof(getenv("OMOE_ROUTER_FILL")) : 0.8f;
+    const int want_blocks = (int)(fill * (float)(h->sm_count > 0 ? h->sm_count : 148));
     constexpr int NG = kRouterWarps / ES;
     // accumulators take 2 registers per (token, expert): 4 tokens x 16 experts per warp is the most that fits
     if constexpr (EMAX / ES <= 16)
