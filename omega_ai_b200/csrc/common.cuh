@@ -26,6 +26,19 @@ constexpr int kDevErrTimeout = 1;   // a bounded wait ran out
 constexpr int kDevErrBounds = 2;    // an index check failed
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Function attributes (the opt-in to more than 48 KB of dynamic shared memory) are per device: a launcher keeps
+// one "done" flag per device ordinal, so a process that drives several GPUs sets them on each.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+    bool done[kMaxDevices] = {};
+    // slot of the current device, or nullptr when it cannot be told (the caller then sets the attribute every time)
+    bool *slot() {
+        int dev = -1;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+        return &done[dev];
+    }
+};
 inline int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
 
 struct TensorMaps {

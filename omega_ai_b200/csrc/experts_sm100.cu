@@ -341,14 +341,15 @@ bool build_tensor_maps(omoe_handle *h) {
 
 namespace {
 cudaError_t set_smem_attrs() {
-    static bool attr_done = false;
-    if (attr_done) return cudaSuccess;
+    static PerDeviceOnce once;
+    bool *done = once.slot();
+    if (done && *done) return cudaSuccess;
     cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemBytes);
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    attr_done = true;
+    if (done) *done = true;
     return cudaSuccess;
 }
 }  // namespace

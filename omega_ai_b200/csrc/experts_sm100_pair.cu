@@ -334,14 +334,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 }  // namespace
 
 cudaError_t launch_experts_bf16_pair(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid) {
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce once;
+    bool *done = once.slot();
+    if (!done || !*done) {
         cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kSmemBytes2);
         if (e != cudaSuccess) return e;
         e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
         if (e != cudaSuccess) return e;
-        attr_done = true;
+        if (done) *done = true;
     }
     const int d = h->cfg.d_model, dff = h->cfg.d_ff;
     static int band_up = getenv("OMOE_BAND_UP") ? atoi(getenv("OMOE_BAND_UP")) : 16;

@@ -264,11 +264,12 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
 template <bool SWIGLU>
 cudaError_t prepare_splitk(omoe_handle *h, int S, cudaLaunchConfig_t *cfg, cudaLaunchAttribute *at, int *clusters) {
     auto kern = grouped_gemm_splitk_kernel<SWIGLU>;
-    static bool attr_done = false;  // one flag per instantiation
-    if (!attr_done) {
+    static PerDeviceOnce once;  // one per instantiation
+    bool *done = once.slot();
+    if (!done || !*done) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesK);
         if (e != cudaSuccess) return e;
-        attr_done = true;
+        if (done) *done = true;
     }
     *cfg = cudaLaunchConfig_t{};
     at->id = cudaLaunchAttributeClusterDimension;

@@ -258,12 +258,13 @@ wgrad_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
 template <bool MN_MAJOR>
 static cudaError_t launch_wgrad_t(omoe_handle *h, cudaStream_t s, const CUtensorMap &a, const CUtensorMap &b, int M,
                                   int N, int split, float *out0, float *out1) {
-    static bool attr_done = false;  // one per instantiation
-    if (!attr_done) {
+    static PerDeviceOnce once;  // one per instantiation
+    bool *done = once.slot();
+    if (!done || !*done) {
         cudaError_t e = cudaFuncSetAttribute(wgrad_kernel<MN_MAJOR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kSmemBytesW);
         if (e != cudaSuccess) return e;
-        attr_done = true;
+        if (done) *done = true;
     }
     wgrad_kernel<MN_MAJOR><<<dim3(h->sm_count), dim3(kThreadsW), kSmemBytesW, s>>>(
         a, b, out0, out1, M, N, split, h->ex_poffsets, h->ex_counts, h->e_local, h->dev_err);
