@@ -252,6 +252,18 @@ OMOE_API int omoe_ep_export(omoe_handle *h, void *blob /* [OMOE_EP_BLOB_BYTES] *
 OMOE_API int omoe_ep_import(omoe_handle *h, const void *all_blobs /* [world][OMOE_EP_BLOB_BYTES] */);
 
 /*
+ * The same set-up when ONE process drives every GPU, as the reference's own multi-GPU mode does (one thread
+ * per device in one JVM: src/main/java/com/omega/engine/parallel/dp/DP.java:68-94): handles[r] was created
+ * with (world, rank = r) while device r' was current, all in this process.  The call enables peer access
+ * between the handles' devices and hands every handle the others' buffers (no IPC).  It is the one entry
+ * point that switches the current device (and puts the caller's back before it returns).  Afterwards each
+ * rank's omoe_forward / omoe_backward is called with its own device current, from one thread per device or
+ * from one thread in turn: the calls only enqueue work, so issuing them one after the other cannot deadlock
+ * as long as every rank's call has been issued before the host waits for any of them.
+ */
+OMOE_API int omoe_ep_connect_local(omoe_handle **handles, int32_t world);
+
+/*
  * Routing only, with NO allocation.  This entry point has no counterpart in
  * the reference.  It exists for hosts that may not call cudaMalloc where they
  * need a routing decision (a serving loop whose memory pool owns all free

@@ -159,6 +159,7 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
     h->e_local = c.n_experts / c.world;
     h->e_first = c.rank * h->e_local;
     h->sm_count = sms;
+    h->device = dev;
     h->tokens_per_block = router_tokens_per_block(c.n_experts);
     h->n_blocks_max = ceil_div(c.t_max, h->tokens_per_block);
 
@@ -470,6 +471,13 @@ int omoe_set_aux_loss(omoe_handle *h, float coef) {
 int omoe_get_aux_loss(omoe_handle *h, float *loss_host) {
     if (!h || !loss_host) return OMOE_ERR_INVALID;
     return bw_aux_loss(h, loss_host, h->last_stream);
+}
+
+int omoe_ep_connect_local(omoe_handle **handles, int32_t world) {
+    if (!handles || world < 2 || world > kMaxWorld) return OMOE_ERR_INVALID;
+    for (int r = 0; r < world; r++)
+        if (!handles[r]) return OMOE_ERR_INVALID;
+    return ep_connect_local(handles, world);
 }
 
 int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host, int32_t T, int32_t io_dtype,

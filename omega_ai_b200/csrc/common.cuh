@@ -58,6 +58,7 @@ struct omoe_handle {
     int e_local;      // experts owned by this rank
     int e_first;      // first owned expert (global index)
     int sm_count;
+    int device;       // CUDA device ordinal the handle was created on
     int tokens_per_block;  // router block granularity
     int n_blocks_max;      // router blocks at t_max
     int64_t rows_cap;      // row capacity of xp / h / yp (padded)

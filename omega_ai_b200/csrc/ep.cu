@@ -279,6 +279,72 @@ int ep_import(omoe_handle *h, const void *all_blobs) {
     return OMOE_OK;
 }
 
+// One process drives every GPU (the reference's own multi-GPU mode: one thread per device in one JVM,
+// src/main/java/com/omega/engine/parallel/dp/DP.java:68-94).  IPC handles cannot be opened in the process that
+// made them, and need not be: with peer access enabled the other handles' buffers are addressed directly.
+int ep_connect_local(omoe_handle **hs, int world) {
+    int saved = 0;
+    cudaGetDevice(&saved);
+    auto fail_all = [&](omoe_handle *h, int code, const char *what, cudaError_t e) {
+        cudaSetDevice(saved);
+        return ep_fail(h, code, what, e);
+    };
+    for (int r = 0; r < world; r++) {
+        omoe_handle *h = hs[r];
+        EpState *st = static_cast<EpState *>(h->ep);
+        if (!st || h->cfg.world != world || h->cfg.rank != r || st->imported) {
+            cudaSetDevice(saved);
+            snprintf(h->err, sizeof(h->err),
+                     "omoe_ep_connect_local: handle %d must be created with world=%d, rank=%d and not be connected yet", r,
+                     world, r);
+            return OMOE_ERR_STATE;
+        }
+        for (int q = 0; q < r; q++)
+            if (hs[q]->device == h->device) {
+                cudaSetDevice(saved);
+                snprintf(h->err, sizeof(h->err), "omoe_ep_connect_local: ranks %d and %d are on the same device", q, r);
+                return OMOE_ERR_INVALID;
+            }
+    }
+    for (int r = 0; r < world; r++) {
+        omoe_handle *h = hs[r];
+        EpState *st = static_cast<EpState *>(h->ep);
+        cudaError_t e = cudaSetDevice(h->device);
+        if (e != cudaSuccess) return fail_all(h, OMOE_ERR_CUDA, "cudaSetDevice", e);
+        void *ctl[kMaxWorld], *xp[kMaxWorld], *yp[kMaxWorld], *dyp[kMaxWorld], *dxp[kMaxWorld];
+        uint32_t *rows_flags[kMaxWorld], *out_flags[kMaxWorld];
+        for (int q = 0; q < world; q++) {
+            if (q != r) {
+                e = cudaDeviceEnablePeerAccess(hs[q]->device, 0);
+                if (e == cudaErrorPeerAccessAlreadyEnabled) {
+                    cudaGetLastError();
+                } else if (e != cudaSuccess) {
+                    return fail_all(h, OMOE_ERR_COMM, "cudaDeviceEnablePeerAccess", e);
+                }
+            }
+            EpState *sq = static_cast<EpState *>(hs[q]->ep);
+            ctl[q] = sq->ctl;
+            xp[q] = hs[q]->xp;
+            yp[q] = hs[q]->yp;
+            dyp[q] = sq->dyp;
+            dxp[q] = sq->dxp;
+            rows_flags[q] = sq->ctl->flag_rows;  // address arithmetic only
+            out_flags[q] = sq->ctl->flag_out;
+        }
+        if ((e = cudaMemcpy(st->d_ctl_table, ctl, sizeof(void *) * world, cudaMemcpyHostToDevice)) != cudaSuccess ||
+            (e = cudaMemcpy(st->d_rows_flags, rows_flags, sizeof(void *) * world, cudaMemcpyHostToDevice)) != cudaSuccess ||
+            (e = cudaMemcpy(st->d_out_flags, out_flags, sizeof(void *) * world, cudaMemcpyHostToDevice)) != cudaSuccess ||
+            (e = cudaMemcpy(h->d_row_table, xp, sizeof(void *) * world, cudaMemcpyHostToDevice)) != cudaSuccess ||
+            (e = cudaMemcpy(h->d_out_table, yp, sizeof(void *) * world, cudaMemcpyHostToDevice)) != cudaSuccess ||
+            (e = cudaMemcpy(st->d_dyp_table, dyp, sizeof(void *) * world, cudaMemcpyHostToDevice)) != cudaSuccess ||
+            (e = cudaMemcpy(st->d_dxp_table, dxp, sizeof(void *) * world, cudaMemcpyHostToDevice)) != cudaSuccess)
+            return fail_all(h, OMOE_ERR_CUDA, "cudaMemcpy(peer tables)", e);
+        st->imported = true;
+    }
+    cudaSetDevice(saved);
+    return OMOE_OK;
+}
+
 int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype, const void *resid, int T,
                cudaStream_t s) {
     EpState *st = static_cast<EpState *>(h->ep);

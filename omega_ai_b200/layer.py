@@ -335,6 +335,18 @@ class MoELayer(Layer):
         torch.cuda.synchronize()
         dist.barrier(group=group)
 
+    @staticmethod
+    def ep_connect_local(layers):
+        """All ranks in this process, one layer per GPU in rank order (the reference's threads-per-device mode,
+        DP.java:68-94): peer access instead of IPC handles."""
+        arr = (C.c_void_p * len(layers))(*[l._h for l in layers])
+        rc = layers[0]._lib.omoe_ep_connect_local(arr, len(layers))
+        for l in layers:
+            if rc != 0 and l._lib.omoe_last_error(l._h):
+                check(l._h, rc)
+        if rc != 0:
+            raise native.OmoeError(rc, "omoe_ep_connect_local")
+
     def close(self):
         if self._h:
             self._lib.omoe_destroy(self._h)

@@ -32,7 +32,7 @@ SYMBOLS = (
     "omoe_forward_host", "omoe_forward_block", "omoe_get_routing", "omoe_get_logits", "omoe_last_launch_count",
     "omoe_set_profiling", "omoe_get_stage_ms", "omoe_ep_export", "omoe_ep_import",
     "omoe_route_noalloc", "omoe_route_noalloc_error",
-    "omoe_set_training", "omoe_backward", "omoe_backward_block", "omoe_get_weight_grads", "omoe_set_aux_loss", "omoe_get_aux_loss",
+    "omoe_ep_connect_local", "omoe_set_training", "omoe_backward", "omoe_backward_block", "omoe_get_weight_grads", "omoe_set_aux_loss", "omoe_get_aux_loss",
 )
 NOALLOC_MAX_TOKENS = 4096
 
@@ -101,6 +101,7 @@ def lib():
     L.omoe_ep_export.argtypes = [vp, vp]
     L.omoe_ep_import.argtypes = [vp, vp]
     L.omoe_route_noalloc.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]
+    L.omoe_ep_connect_local.argtypes = [C.POINTER(vp), i32]
     L.omoe_set_training.argtypes = [vp, i32]
     L.omoe_backward.argtypes = [vp, vp, vp, vp, i32, i32, vp]
     L.omoe_backward_block.argtypes = [vp, vp, vp, C.c_float, vp, vp, vp, i32, i32, vp]
