@@ -259,7 +259,10 @@ OMOE_API int omoe_ep_import(omoe_handle *h, const void *all_blobs /* [world][OMO
  * point that switches the current device (and puts the caller's back before it returns).  Afterwards each
  * rank's omoe_forward / omoe_backward is called with its own device current, from one thread per device or
  * from one thread in turn: the calls only enqueue work, so issuing them one after the other cannot deadlock
- * as long as every rank's call has been issued before the host waits for any of them.
+ * as long as every rank's call has been issued before the host waits for any of them.  Such a process must load
+ * its CUDA modules eagerly (CUDA_MODULE_LOADING=EAGER in its environment): with lazy loading the first use of a
+ * kernel on one device can wait for the kernel running on another device, which is itself waiting (bounded) for
+ * that rank.
  */
 OMOE_API int omoe_ep_connect_local(omoe_handle **handles, int32_t world);
 

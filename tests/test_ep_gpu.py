@@ -34,46 +34,12 @@ def test_expert_parallel_all_gpus():
 
 def test_expert_parallel_in_one_process():
     """One process drives two GPUs (the reference's threads-per-device mode): handles connected with
-    omoe_ep_connect_local, each rank's forward issued in turn from this thread, then both awaited."""
+    omoe_ep_connect_local, each rank's forward issued in turn from one thread, then both awaited.  The worker runs
+    with CUDA_MODULE_LOADING=EAGER (see its docstring)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    import numpy as np
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from helpers import assert_close_bf16, make_layer
-    from omega_ai_b200 import MoELayer
-    from oracle import ref
-    world, d, dff, E, k, T = 2, 256, 384, 8, 2, 200
-    El = E // world
-    _, w_r, w_g, w_u, w_d, _ = make_layer(1, d, dff, E, k, seed=80)
-    w_r = ref.bf16_round(w_r)
-    layers, xs, ys = [], [], []
-    for r in range(world):
-        torch.cuda.set_device(r)
-        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(f"cuda:{r}").to(torch.bfloat16).contiguous()
-        layer = MoELayer(d, dff, E, k, t_max=T, compute_dtype=torch.bfloat16, world=world, rank=r)
-        sl = slice(r * El, (r + 1) * El)
-        layer.setWeights(dev(w_r), dev(w_g[sl]), dev(w_u[sl]), dev(w_d[sl]))
-        layers.append(layer)
-        x = ref.bf16_round(np.random.Generator(np.random.Philox(key=900 + r)).standard_normal((T, d), dtype=np.float32))
-        xs.append(x)
-    for r in range(world):
-        torch.cuda.synchronize(r)
-    MoELayer.ep_connect_local(layers)
-    for step in range(2):
-        outs = []
-        for r in range(world):           # issue every rank's forward before waiting for any
-            torch.cuda.set_device(r)
-            xd = torch.from_numpy(xs[r]).to(f"cuda:{r}").to(torch.bfloat16)
-            outs.append(layers[r].forward_device(xd))
-        for r in range(world):
-            torch.cuda.synchronize(r)
-        for r in range(world):
-            torch.cuda.set_device(r)
-            want = ref.moe_forward(xs[r], w_r, w_g, w_u, w_d, k, bf16=True)
-            idx = layers[r].routing(T)[0]
-            assert np.array_equal(idx, want.topk_idx)
-            assert_close_bf16(outs[r].float().cpu().numpy(), want.y)
-    for r in range(world):
-        torch.cuda.set_device(r)
-        layers[r].close()
-    torch.cuda.set_device(0)
+    env = dict(os.environ, CUDA_MODULE_LOADING="EAGER", OMOE_EP_WAIT_MS="5000")
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "ep_local_worker.py")], capture_output=True,
+                       text=True, timeout=600, env=env)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    assert "single-process ep ok" in p.stdout
