@@ -52,6 +52,9 @@ public final class OmoeNative {
     /** omoe_get_weight_grads: fp32 device addresses (0 = skip): router [E,d], bias [E], gate/up [E,dff,d], down [E,d,dff]. */
     public static native int getWeightGrads(long handle, long dRouter, long dBias, long dGate, long dUp, long dDown);
 
+    /** omoe_ep_connect_local: all ranks' handles of this JVM, in rank order (one per device, DP.java:68-94). */
+    public static native int epConnectLocal(long[] handles);
+
     public static native int epExport(long handle, byte[] blob320);
 
     public static native int epImport(long handle, byte[] allBlobs);

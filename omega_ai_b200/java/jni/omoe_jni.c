@@ -87,6 +87,17 @@ JFN(jint, getWeightGrads)(JNIEnv *env, jclass c, jlong h, jlong dr, jlong db, jl
                                  (float *)(intptr_t)dg, (float *)(intptr_t)du, (float *)(intptr_t)dd, NULL);
 }
 
+JFN(jint, epConnectLocal)(JNIEnv *env, jclass c, jlongArray hs) {
+    jsize n = (*env)->GetArrayLength(env, hs);
+    jlong *p = (*env)->GetLongArrayElements(env, hs, NULL);
+    omoe_handle *arr[8];
+    if (n > 8) n = 8;
+    for (jsize i = 0; i < n; i++) arr[i] = (omoe_handle *)(intptr_t)p[i];
+    int rc = omoe_ep_connect_local(arr, (int32_t)n);
+    (*env)->ReleaseLongArrayElements(env, hs, p, JNI_ABORT);
+    return rc;
+}
+
 JFN(jint, epExport)(JNIEnv *env, jclass c, jlong h, jbyteArray blob) {
     jbyte *p = (*env)->GetByteArrayElements(env, blob, NULL);
     int rc = omoe_ep_export((omoe_handle *)(intptr_t)h, p);
