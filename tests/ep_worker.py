@@ -111,6 +111,32 @@ def run_backward_case(rank, world, compute):
         close(g["d_up"].cpu().numpy(), want.d_w_up[sl], "d_w_up")
         close(g["d_down"].cpu().numpy(), want.d_w_down[sl], "d_w_down")
         close(d_router.cpu().numpy(), want.d_w_r, "d_w_r")
+    # The auxiliary loss and the block form under expert parallelism: what they add depends on the rank's own
+    # tokens only (router side, RMSNorm, residual), so the oracle run on this rank's rows alone must agree.
+    T = t_cap
+    rng = np.random.Generator(np.random.Philox(key=3000 + rank))
+    x = rng.standard_normal((T, d), dtype=np.float32)
+    dy = (0.05 * rng.standard_normal((T, d))).astype(np.float32)
+    gamma = (1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+    if bf:
+        x, dy = ref.bf16_round(x), ref.bf16_round(dy)
+    close = (lambda a, b_, n: assert_close_bf16(a, b_)) if bf else (
+        lambda a, b_, n: np.testing.assert_allclose(a, b_, rtol=0, atol=2e-4 * (np.abs(b_).max() + 1e-30), err_msg=n))
+    layer.set_aux_loss(0.5)
+    xd, dyd = dev(x), dev(dy)
+    layer.forward_device(xd)
+    dx = layer.backward(xd, dyd).float().cpu().numpy()
+    g = layer.weight_grads()
+    want = ref.moe_backward(x, w_r, w_g, w_u, w_d, k, dy, bf16=bf, aux_coef=0.5)
+    close(dx, want.dx, "dx with aux loss")
+    close(g["d_router"].cpu().numpy(), want.d_w_r, "d_w_r with aux loss")
+    layer.set_aux_loss(0.0)
+    gd = torch.from_numpy(gamma).cuda()
+    layer.forward_block(xd, gd)
+    dxb, dgamma = layer.backward_block(xd, gd, dyd)
+    dx_ref, dgamma_ref, _ = ref.moe_block_backward(x, gamma, w_r, w_g, w_u, w_d, k, dy, bf16=bf)
+    close(dxb.float().cpu().numpy(), dx_ref, "block dx")
+    close(dgamma.cpu().numpy(), dgamma_ref, "dgamma")
     torch.cuda.synchronize()
     dist.barrier()
     layer.close()
