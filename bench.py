@@ -385,7 +385,9 @@ def run_ours(args, cfg):
 
     cpu = None
     if world == 1 and not args.no_cpu:
-        n_cpu = args.cpu_tokens or (256 if cfg["dtype"] == "bf16" and cfg["T"] >= 256 else cfg["T"])
+        # a bounded sample of the workload: about 12 s of CPU work at the ~150 GFLOP/s the port reaches on 16 cores
+        flops_per_token = 6.0 * k * d * dff + 2.0 * d * E
+        n_cpu = args.cpu_tokens or max(256, int(12.0 * 150e9 / flops_per_token) // 64 * 64)
         n_cpu = min(n_cpu, cfg["T"])
         tps, dt, cores, _ = cpu_sample(cfg, n_cpu)
         cpu = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
