@@ -9,6 +9,10 @@ this metric).  ``value`` is timed with CUDA events with x resident in HBM;
 ``e2e`` is the same forward through the host-buffer entry point
 (``omoe_forward_host``: pinned x -> H2D -> forward -> D2H y -> sync).
 Prints ONE JSON line on rank 0.
+
+Options beyond the contract: ``--tokens`` (decode sweep), ``--weak`` (weak scaling), ``--graph`` (time replays of
+one captured forward), ``--block`` (the RMSNorm + residual form), ``--train`` (adds the time of a training step:
+training-mode forward + backward, one GPU).
 """
 from __future__ import annotations
 
