@@ -27,8 +27,10 @@ import java.io.RandomAccessFile;
  * [out,in] layout of FullyLayer.  The native library keeps its own bf16 copies;
  * call syncWeights() after the weights change.
  *
- * Forward only: diff()/back() throw.  Not compiled in the repository that ships
- * it (no JDK in that build image).
+ * Training: setTraining(true) once, then back(delta) runs the native backward and
+ * hands every FullyLayer its diffW; update() lets their updaters change the weights
+ * and re-syncs the native copies.  Not compiled in the repository that ships it (no
+ * JDK in that build image).
  */
 public class MoELayer extends Layer {
 
