@@ -64,6 +64,16 @@ def test_bad_arguments_return_codes_without_a_gpu(native):
     cfg.world, cfg.rank = 3, 0  # 8 experts do not split over 3 ranks
     assert lib.omoe_create(C.byref(cfg), C.byref(h)) == -1
     assert lib.omoe_forward(None, None, None, 1, 0, None) == -1
+    # the training and multi-GPU entries refuse a null handle the same way
+    assert lib.omoe_set_training(None, 1) == -1
+    assert lib.omoe_backward(None, None, None, None, 1, 0, None) == -1
+    assert lib.omoe_backward_block(None, None, None, 1e-5, None, None, None, 1, 0, None) == -1
+    assert lib.omoe_get_weight_grads(None, None, None, None, None, None, None) == -1
+    assert lib.omoe_set_aux_loss(None, 0.5) == -1
+    assert lib.omoe_get_aux_loss(None, None) == -1
+    assert lib.omoe_ep_connect_local(None, 2) == -1
+    two = (C.c_void_p * 2)(None, None)
+    assert lib.omoe_ep_connect_local(two, 2) == -1 and lib.omoe_ep_connect_local(two, 9) == -1
     assert lib.omoe_destroy(None) == 0
 
 
