@@ -30,6 +30,11 @@ def main():
     r = ref.moe_forward(xb, w_rb, w_g, w_u, w_d, 3, bias=bb, bf16=True)
     out.update(bf16_logits=r.logits, bf16_idx=r.topk_idx, bf16_w=r.topk_w, bf16_counts=r.counts, bf16_perm=r.perm,
                bf16_y=r.y)
+    # backward of the fp32 case (with the auxiliary-loss term), for a fixed dy
+    x, w_r, w_g, w_u, w_d, _ = make_layer(24, 64, 96, 8, 2, seed=101)
+    dy = np.random.default_rng(103).standard_normal(x.shape).astype(np.float32)
+    g = ref.moe_backward(x, w_r * 10, w_g * 3, w_u * 3, w_d * 3, 2, dy, aux_coef=0.25)
+    out.update(bw_dx=g.dx, bw_d_w_r=g.d_w_r, bw_d_w_gate=g.d_w_gate, bw_d_w_up=g.d_w_up, bw_d_w_down=g.d_w_down)
     np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "moe_small.npz"), **out)
 
 

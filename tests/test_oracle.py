@@ -152,6 +152,13 @@ def test_golden_vectors(oracle):
     np.testing.assert_array_equal(r.counts, g["bf16_counts"])
     np.testing.assert_array_equal(r.perm, g["bf16_perm"])
     np.testing.assert_allclose(r.y, g["bf16_y"], rtol=1e-2, atol=1e-6)  # one bf16 ulp of slack for libm's expf
+    # backward of the fp32 case with the auxiliary-loss term
+    x, w_r, w_g, w_u, w_d, _ = make_layer(24, 64, 96, 8, 2, seed=101)
+    dy = np.random.default_rng(103).standard_normal(x.shape).astype(np.float32)
+    b = oracle.moe_backward(x, w_r * 10, w_g * 3, w_u * 3, w_d * 3, 2, dy, aux_coef=0.25)
+    for name in ("dx", "d_w_r", "d_w_gate", "d_w_up", "d_w_down"):
+        want = g["bw_" + name]
+        np.testing.assert_allclose(getattr(b, name), want, rtol=1e-5, atol=1e-6 * np.abs(want).max())
 
 
 def test_rmsnorm_matches_the_reference_formula(oracle):
