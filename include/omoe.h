@@ -138,9 +138,25 @@ OMOE_API int omoe_forward_block(omoe_handle *h, const void *x_dev, const float *
  * On one GPU a batch of 8192 tokens or more is cut into chunks of at least 4096 whose
  * copies overlap the kernels of their neighbours (tokens are independent, so
  * y is bit-identical); the routing read-outs then describe the last chunk.
+ * With world > 1 the call is collective like omoe_forward, and the batch is cut
+ * too: into as many chunks (at most 8, of at least 512 tokens) as t_max allows,
+ * the same number on every rank, each chunk one collective forward.
+ *
+ * omoe_forward_host_async is the same call without the final synchronise: it
+ * enqueues the copies and the forward(s) and returns; y_host is complete, and
+ * a device-side failure is reported, once omoe_wait(h) has returned.  Several
+ * calls may be enqueued before one omoe_wait: they run in order, and the
+ * copies of a call overlap the kernels of its neighbours (the host buffers of
+ * a call must stay untouched until the wait).  The reference splits the same
+ * work into Tensor.hostToDevice() and Tensor.syncHost()
+ * (src/main/java/com/omega/engine/tensor/Tensor.java:559-579), each of which
+ * synchronises the whole device.
  */
 OMOE_API int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host, int32_t T,
                       int32_t io_dtype, void *cuda_stream);
+OMOE_API int omoe_forward_host_async(omoe_handle *h, const void *x_host, void *y_host, int32_t T,
+                      int32_t io_dtype, void *cuda_stream);
+OMOE_API int omoe_wait(omoe_handle *h);
 
 /*
  * Training mode and the backward pass.
@@ -177,6 +193,10 @@ OMOE_API int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host,
  * ordered by the same device-side flags.  The expert weight gradients of a rank ([n_experts/world, ...]) are
  * complete; d W_router and d router_bias cover the rank's own tokens and must be summed over the ranks by the
  * caller (the router is replicated); the auxiliary loss term uses the rank's own tokens and counts.
+ * With world > 1 a forward takes ONE backward: a second omoe_backward without a new training-mode forward
+ * returns OMOE_ERR_STATE (on one GPU a backward may be repeated).
+ * All device pointers of the forward and backward entry points must be 16-byte aligned (rows move as
+ * 16-byte vectors); a misaligned one is refused with OMOE_ERR_INVALID before anything is launched.
  *
  * omoe_get_weight_grads copies the gradients of the last omoe_backward into the caller's DEVICE (or host)
  * fp32 buffers (any may be NULL) and synchronises the stream.
@@ -227,6 +247,10 @@ OMOE_API int omoe_last_launch_count(const omoe_handle *h);
 #define OMOE_N_STAGES 8
 OMOE_API int omoe_set_profiling(omoe_handle *h, int32_t enabled);
 OMOE_API int omoe_get_stage_ms(omoe_handle *h, float *ms /* [OMOE_N_STAGES] */);
+/* The same for an earlier forward: back = 0 is the last one, 1 the one before, ... up to the last 32 forwards
+ * made since profiling was switched on.  Lets a caller time a run of forwards back to back (no host
+ * synchronisation between them) and read every forward's stages afterwards.  No reference counterpart. */
+OMOE_API int omoe_get_stage_ms_at(omoe_handle *h, int32_t back, float *ms /* [OMOE_N_STAGES] */);
 
 /*
  * Expert-parallel transport.  The reference's only multi-GPU mechanism is
@@ -274,8 +298,13 @@ OMOE_API int omoe_ep_connect_local(omoe_handle **handles, int32_t world);
  * must avoid the device-wide synchronisation an allocation implies).  It runs
  * the same fused router kernel as omoe_forward; the kernel's scratch lives in
  * a fixed array inside the library image (about 4.3 MiB per GPU that loads
- * the library, held until the process exits) and nothing is allocated or
- * freed, by this call or by anything it calls.
+ * the library, held until the process exits) and the call itself makes no
+ * cudaMalloc, cudaFree or other allocating call.  One qualification: with
+ * CUDA's lazy module loading the driver brings this library's module -- the
+ * array included -- onto the device the first time one of its symbols is
+ * used in a context, so the FIRST call in a context may make the driver
+ * reserve those 4.3 MiB; later calls leave the device's free memory untouched.
+ * Make that first call early (at start-up, outside the request path).
  *
  *   x_dev [T, d_model] of io_dtype; w_router_dev [n_experts, d_model] fp32;
  *   router_bias_dev [n_experts] fp32 or NULL.
@@ -284,9 +313,12 @@ OMOE_API int omoe_ep_connect_local(omoe_handle **handles, int32_t world);
  *
  * Limits: T <= OMOE_NOALLOC_MAX_TOKENS, n_experts <= 128, top_k <= 16; a call
  * beyond them returns OMOE_ERR_TOO_LARGE and launches nothing.
- * The first call on each device looks up the array's device address; make that
- * first call before any stream capture begins on that device.
- * All calls on one device share the array: it keeps the previous call's
+ * x_dev and w_router_dev must be 16-byte aligned (OMOE_ERR_INVALID otherwise).
+ * The first call in each CUDA context (one per device for a runtime-API host; a
+ * host that creates its own driver-API contexts has one per context) looks up
+ * the array's device address in that context; make that first call before any
+ * stream capture begins there.
+ * All calls in one context share the array: it keeps the previous call's
  * contents (nothing in it needs clearing between calls), and two calls whose
  * kernels overlap on the GPU (different streams, no ordering) race on it.
  * Error text: omoe_route_noalloc_error().

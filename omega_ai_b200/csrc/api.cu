@@ -42,6 +42,8 @@ cudaError_t dev_alloc(T **p, size_t count) {
 
 size_t elt_size(int dtype) { return dtype == OMOE_BF16 ? 2 : 4; }
 
+bool misaligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
+
 __global__ void f32_to_bf16_kernel(const float *__restrict__ src, __nv_bfloat16 *__restrict__ dst, int64_t n) {
     int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x * 4;
@@ -110,12 +112,15 @@ int omoe_destroy(omoe_handle *h) {
                     h->d_out_table, h->ticket, h->dst_base != h->poffsets ? h->dst_base : nullptr};
     for (void *p : ptrs)
         if (p) cudaFree(p);
-    for (int i = 0; i <= OMOE_N_STAGES; i++)
-        if (h->ev[i]) cudaEventDestroy(h->ev[i]);
+    for (int r = 0; r < kProfSlots; r++)
+        for (int i = 0; i <= OMOE_N_STAGES; i++)
+            if (h->ev_ring[r][i]) cudaEventDestroy(h->ev_ring[r][i]);
     for (int i = 0; i < kHostChunksMax; i++) {
         if (h->ev_in[i]) cudaEventDestroy(h->ev_in[i]);
         if (h->ev_out[i]) cudaEventDestroy(h->ev_out[i]);
+        if (h->ev_d2h[i]) cudaEventDestroy(h->ev_d2h[i]);
     }
+    if (h->ev_fence) cudaEventDestroy(h->ev_fence);
     if (h->copy_in) cudaStreamDestroy(h->copy_in);
     if (h->copy_out) cudaStreamDestroy(h->copy_out);
     delete h;
@@ -242,6 +247,7 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
     // padding rows of the dispatch buffers are never read back, but start them
     // at zero so no stale NaN pattern ever enters a tensor-core tile
     cudaMemset(h->xp, 0, (size_t)h->rows_cap * d * cs);
+    h->ev = h->ev_ring[0];
     for (int i = 0; i <= OMOE_N_STAGES; i++)
         if (cudaEventCreate(&h->ev[i]) != cudaSuccess) {
             int rc = fail(nullptr, OMOE_ERR_CUDA, "omoe_create: cudaEventCreate failed");
@@ -250,12 +256,18 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
         }
     // copy streams of omoe_forward_host: non-blocking, so they can overlap kernels on the legacy default stream
     h->host_chunk_min = 4096;
-    if (const char *v = getenv("OMOE_HOST_CHUNK_MIN")) h->host_chunk_min = atoi(v) > 0 ? atoi(v) : 1 << 30;
+    h->host_chunk_min_ep = 512;  // expert parallel: the per-rank batch is small, and so are its chunks
+    if (const char *v = getenv("OMOE_HOST_CHUNK_MIN")) {
+        h->host_chunk_min = atoi(v) > 0 ? atoi(v) : 1 << 30;
+        h->host_chunk_min_ep = h->host_chunk_min;
+    }
     bool ok_streams = cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking) == cudaSuccess &&
-                      cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking) == cudaSuccess;
+                      cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking) == cudaSuccess &&
+                      cudaEventCreateWithFlags(&h->ev_fence, cudaEventDisableTiming) == cudaSuccess;
     for (int i = 0; ok_streams && i < kHostChunksMax; i++)
         ok_streams = cudaEventCreateWithFlags(&h->ev_in[i], cudaEventDisableTiming) == cudaSuccess &&
-                     cudaEventCreateWithFlags(&h->ev_out[i], cudaEventDisableTiming) == cudaSuccess;
+                     cudaEventCreateWithFlags(&h->ev_out[i], cudaEventDisableTiming) == cudaSuccess &&
+                     cudaEventCreateWithFlags(&h->ev_d2h[i], cudaEventDisableTiming) == cudaSuccess;
     if (!ok_streams) {
         int rc = fail(nullptr, OMOE_ERR_CUDA, "omoe_create: could not create the copy streams");
         omoe_destroy(h);
@@ -337,14 +349,19 @@ static int forward_impl(omoe_handle *h, const void *x_dev, int x_dtype, void *y_
     h->last_stream = s;
     h->last_launches = 0;
     h->ev_valid = false;
+    if (h->profiling) h->ev = h->ev_ring[h->prof_count % kProfSlots];
     h->last_resid = resid != nullptr;
     bw_forward_invalidate(h);  // the rows a backward pass would read are about to be overwritten
     if (h->cfg.world > 1) {
         int rc = ep_forward(h, x_dev, x_dtype, y_dev, y_dtype, resid, T, s);
         h->last_launches += pre;
+        if (rc == OMOE_OK && h->ev_valid) h->prof_count++;
         return rc;
     }
-    if (T == 0) return OMOE_OK;
+    if (T == 0) {
+        bw_forward_empty(h);
+        return OMOE_OK;
+    }
 
     int n = pre;
     const bool prof = h->profiling;
@@ -381,6 +398,7 @@ static int forward_impl(omoe_handle *h, const void *x_dev, int x_dtype, void *y_
     MARK(8);
 #undef MARK
     h->ev_valid = prof;
+    if (prof) h->prof_count++;
     h->last_launches = n;
     return OMOE_OK;
 }
@@ -394,6 +412,9 @@ static int check_forward_args(omoe_handle *h, const void *x_dev, void *y_dev, in
     if (h->cfg.compute_dtype == OMOE_F32 && io_dtype != OMOE_F32)
         return fail(h, OMOE_ERR_UNSUPPORTED, "%s: an fp32 layer takes fp32 rows", who);
     if (T > 0 && (!x_dev || !y_dev)) return fail(h, OMOE_ERR_INVALID, "%s: null buffer", who);
+    // rows move as 16-byte vectors; a misaligned address would raise a sticky device fault
+    if (T > 0 && (misaligned16(x_dev) || misaligned16(y_dev)))
+        return fail(h, OMOE_ERR_INVALID, "%s: device buffers must be 16-byte aligned", who);
     return OMOE_OK;
 }
 
@@ -410,6 +431,7 @@ int omoe_forward_block(omoe_handle *h, const void *x_dev, const float *gamma_dev
     int rc = check_forward_args(h, x_dev, y_dev, T, io_dtype, "omoe_forward_block");
     if (rc != OMOE_OK) return rc;
     if (!gamma_dev) return fail(h, OMOE_ERR_INVALID, "omoe_forward_block: null gamma");
+    if (misaligned16(gamma_dev)) return fail(h, OMOE_ERR_INVALID, "omoe_forward_block: gamma must be 16-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
     int pre = 0;
     if (T > 0) CU_TRY(h, launch_rmsnorm(h, x_dev, io_dtype, gamma_dev, eps, T, s, &pre));
@@ -427,6 +449,7 @@ int omoe_backward(omoe_handle *h, const void *x_dev, const void *dy_dev, void *d
     int rc = check_forward_args(h, x_dev, dx_dev, T, io_dtype, "omoe_backward");
     if (rc != OMOE_OK) return rc;
     if (T > 0 && !dy_dev) return fail(h, OMOE_ERR_INVALID, "omoe_backward: null buffer");
+    if (T > 0 && misaligned16(dy_dev)) return fail(h, OMOE_ERR_INVALID, "omoe_backward: device buffers must be 16-byte aligned");
     if (io_dtype != h->last_io_dtype && T > 0)
         return fail(h, OMOE_ERR_INVALID, "omoe_backward: io_dtype differs from the forward's");
     int n = 0;
@@ -444,6 +467,8 @@ int omoe_backward_block(omoe_handle *h, const void *x_dev, const float *gamma_de
     int rc = check_forward_args(h, x_dev, dx_dev, T, io_dtype, "omoe_backward_block");
     if (rc != OMOE_OK) return rc;
     if (!gamma_dev || !dgamma_dev || (T > 0 && !dy_dev)) return fail(h, OMOE_ERR_INVALID, "omoe_backward_block: null buffer");
+    if (T > 0 && (misaligned16(dy_dev) || misaligned16(gamma_dev) || misaligned16(dgamma_dev)))
+        return fail(h, OMOE_ERR_INVALID, "omoe_backward_block: device buffers must be 16-byte aligned");
     if (!h->last_resid)
         return fail(h, OMOE_ERR_STATE, "omoe_backward_block: the last forward was not omoe_forward_block");
     if (io_dtype != h->last_io_dtype && T > 0)
@@ -480,63 +505,112 @@ int omoe_ep_connect_local(omoe_handle **handles, int32_t world) {
     return ep_connect_local(handles, world);
 }
 
-int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host, int32_t T, int32_t io_dtype,
-                      void *cuda_stream) {
-    if (!h) return OMOE_ERR_INVALID;
-    if (T < 0 || T > h->cfg.t_max)
-        return fail(h, T < 0 ? OMOE_ERR_INVALID : OMOE_ERR_TOO_LARGE, "omoe_forward_host: T=%d outside [0, %d]", T,
-                    h->cfg.t_max);
-    if (io_dtype != OMOE_F32 && io_dtype != OMOE_BF16) return fail(h, OMOE_ERR_INVALID, "omoe_forward_host: bad io_dtype");
-    if (T > 0 && (!x_host || !y_host)) return fail(h, OMOE_ERR_INVALID, "omoe_forward_host: null buffer");
-    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+// Enqueues one host-buffer forward: H2D copies, the forward(s), D2H copies.  No host synchronisation.
+//
+// Tokens are independent, so a large batch is cut into chunks that run as separate forwards: the
+// host-to-device copy of chunk i+1 and the device-to-host copy of chunk i-1 overlap the kernels of chunk i (two
+// copy streams, ordered against the compute stream with events).  Every output row has the same bits as in
+// one big forward.  Successive calls pipeline as well: the staging area of chunk i is refilled as soon as the
+// previous call's forward of chunk i has consumed it, and its output area is rewritten only after the previous
+// call's device-to-host copy of it has finished.
+// With expert parallelism every forward is a collective step, so all ranks must cut their batches into the
+// SAME number of chunks: the count follows from t_max (identical on every rank), and a rank with fewer tokens
+// makes forwards of fewer (or zero) tokens.
+static int forward_host_enqueue(omoe_handle *h, const void *x_host, void *y_host, int32_t T, int32_t io_dtype,
+                                cudaStream_t s) {
     const size_t row_bytes = (size_t)h->cfg.d_model * elt_size(io_dtype);
-    // Tokens are independent, so a large batch is cut into chunks that run as
-    // separate forwards: the host-to-device copy of chunk i+1 and the
-    // device-to-host copy of chunk i-1 overlap the kernels of chunk i (two
-    // copy streams, ordered against the compute stream with events).  Every
-    // output row has the same bits as in one big forward.
     int chunks = 1;
-    if (h->cfg.world == 1 && h->copy_in != nullptr) {
-        while (chunks < kHostChunksMax && T / (chunks * 2) >= h->host_chunk_min) chunks *= 2;
-    }
-    if (chunks == 1) {
-        const size_t bytes = (size_t)T * row_bytes;
-        if (bytes) CU_TRY(h, cudaMemcpyAsync(h->x_stage, x_host, bytes, cudaMemcpyHostToDevice, s));
-        int rc = omoe_forward(h, h->x_stage, h->y_stage, T, io_dtype, s);
-        if (rc != OMOE_OK) return rc;
-        if (bytes) CU_TRY(h, cudaMemcpyAsync(y_host, h->y_stage, bytes, cudaMemcpyDeviceToHost, s));
-        CU_TRY(h, cudaStreamSynchronize(s));
-        return check_dev_err(h);
+    if (h->copy_in != nullptr) {
+        const int basis = h->cfg.world == 1 ? T : h->cfg.t_max;
+        const int cmin = h->cfg.world == 1 ? h->host_chunk_min : h->host_chunk_min_ep;
+        while (chunks < kHostChunksMax && basis / (chunks * 2) >= cmin) chunks *= 2;
     }
     const int per = (T + chunks - 1) / chunks;
     // the copy streams must not run ahead of work already queued on the caller's stream
-    CU_TRY(h, cudaEventRecord(h->ev_in[0], s));
-    CU_TRY(h, cudaStreamWaitEvent(h->copy_in, h->ev_in[0], 0));
-    CU_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev_in[0], 0));
+    CU_TRY(h, cudaEventRecord(h->ev_fence, s));
+    CU_TRY(h, cudaStreamWaitEvent(h->copy_in, h->ev_fence, 0));
+    CU_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev_fence, 0));
+    // Chunk i reuses the staging rows of the previous call's chunk i only when both calls cut the batch the same
+    // way; otherwise wait for all of the previous call (its last chunk's events: the streams run in order).
+    const size_t geom = (size_t)T * 16 + (size_t)chunks * 2 + (io_dtype == OMOE_BF16 ? 1 : 0);
+    if (h->host_prev_chunks > 0 && geom != h->host_prev_geom) {
+        CU_TRY(h, cudaStreamWaitEvent(h->copy_in, h->ev_out[h->host_prev_chunks - 1], 0));
+        CU_TRY(h, cudaStreamWaitEvent(s, h->ev_d2h[h->host_prev_chunks - 1], 0));
+    }
+    h->host_prev_geom = geom;
+    h->host_prev_chunks = chunks;
     for (int i = 0; i < chunks; i++) {
-        const int t0 = i * per, n = (t0 + per <= T) ? per : T - t0;
-        if (n <= 0) break;
+        const int t0 = i * per, n = t0 >= T ? 0 : ((t0 + per <= T) ? per : T - t0);
         const size_t off = (size_t)t0 * row_bytes;
-        CU_TRY(h, cudaMemcpyAsync(static_cast<char *>(h->x_stage) + off, static_cast<const char *>(x_host) + off,
-                                  (size_t)n * row_bytes, cudaMemcpyHostToDevice, h->copy_in));
+        // the previous call's forward of this chunk has read the staging rows about to be overwritten
+        CU_TRY(h, cudaStreamWaitEvent(h->copy_in, h->ev_out[i], 0));
+        if (n > 0)
+            CU_TRY(h, cudaMemcpyAsync(static_cast<char *>(h->x_stage) + off, static_cast<const char *>(x_host) + off,
+                                      (size_t)n * row_bytes, cudaMemcpyHostToDevice, h->copy_in));
         CU_TRY(h, cudaEventRecord(h->ev_in[i], h->copy_in));
     }
     for (int i = 0; i < chunks; i++) {
-        const int t0 = i * per, n = (t0 + per <= T) ? per : T - t0;
-        if (n <= 0) break;
-        const size_t off = (size_t)t0 * row_bytes;
+        const int t0 = i * per, n = t0 >= T ? 0 : ((t0 + per <= T) ? per : T - t0);
+        const size_t off = (size_t)(n > 0 ? t0 : 0) * row_bytes;
         CU_TRY(h, cudaStreamWaitEvent(s, h->ev_in[i], 0));
-        int rc = omoe_forward(h, static_cast<char *>(h->x_stage) + off, static_cast<char *>(h->y_stage) + off, n,
-                              io_dtype, s);
-        if (rc != OMOE_OK) return rc;
+        // the previous call's device-to-host copy of this chunk's output rows has finished
+        CU_TRY(h, cudaStreamWaitEvent(s, h->ev_d2h[i], 0));
+        if (n > 0 || h->cfg.world > 1) {
+            int rc = omoe_forward(h, static_cast<char *>(h->x_stage) + off, static_cast<char *>(h->y_stage) + off, n,
+                                  io_dtype, s);
+            if (rc != OMOE_OK) return rc;
+        }
         CU_TRY(h, cudaEventRecord(h->ev_out[i], s));
         CU_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev_out[i], 0));
-        CU_TRY(h, cudaMemcpyAsync(static_cast<char *>(y_host) + off, static_cast<char *>(h->y_stage) + off,
-                                  (size_t)n * row_bytes, cudaMemcpyDeviceToHost, h->copy_out));
+        if (n > 0)
+            CU_TRY(h, cudaMemcpyAsync(static_cast<char *>(y_host) + off, static_cast<char *>(h->y_stage) + off,
+                                      (size_t)n * row_bytes, cudaMemcpyDeviceToHost, h->copy_out));
+        CU_TRY(h, cudaEventRecord(h->ev_d2h[i], h->copy_out));
     }
-    CU_TRY(h, cudaStreamSynchronize(h->copy_out));
-    CU_TRY(h, cudaStreamSynchronize(s));
+    // work queued on the caller's stream after this call sees the finished copies too
+    CU_TRY(h, cudaStreamWaitEvent(s, h->ev_d2h[chunks - 1], 0));
+    h->host_pending = true;
+    return OMOE_OK;
+}
+
+static int check_host_args(omoe_handle *h, const void *x_host, void *y_host, int32_t T, int32_t io_dtype,
+                           const char *who) {
+    if (T < 0 || T > h->cfg.t_max)
+        return fail(h, T < 0 ? OMOE_ERR_INVALID : OMOE_ERR_TOO_LARGE, "%s: T=%d outside [0, %d]", who, T, h->cfg.t_max);
+    if (io_dtype != OMOE_F32 && io_dtype != OMOE_BF16) return fail(h, OMOE_ERR_INVALID, "%s: bad io_dtype", who);
+    if (T > 0 && (!x_host || !y_host)) return fail(h, OMOE_ERR_INVALID, "%s: null buffer", who);
+    if ((size_t)h->cfg.d_model * elt_size(io_dtype) % 16 != 0)
+        return fail(h, OMOE_ERR_UNSUPPORTED, "%s: a row must be a multiple of 16 bytes", who);
+    return OMOE_OK;
+}
+
+int omoe_forward_host_async(omoe_handle *h, const void *x_host, void *y_host, int32_t T, int32_t io_dtype,
+                            void *cuda_stream) {
+    if (!h) return OMOE_ERR_INVALID;
+    int rc = check_host_args(h, x_host, y_host, T, io_dtype, "omoe_forward_host_async");
+    if (rc != OMOE_OK) return rc;
+    return forward_host_enqueue(h, x_host, y_host, T, io_dtype, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int omoe_wait(omoe_handle *h) {
+    if (!h) return OMOE_ERR_INVALID;
+    if (h->host_pending) {
+        CU_TRY(h, cudaStreamSynchronize(h->copy_out));
+        h->host_pending = false;
+    }
+    CU_TRY(h, cudaStreamSynchronize(h->last_stream));
     return check_dev_err(h);
+}
+
+int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host, int32_t T, int32_t io_dtype,
+                      void *cuda_stream) {
+    if (!h) return OMOE_ERR_INVALID;
+    int rc = check_host_args(h, x_host, y_host, T, io_dtype, "omoe_forward_host");
+    if (rc != OMOE_OK) return rc;
+    rc = forward_host_enqueue(h, x_host, y_host, T, io_dtype, static_cast<cudaStream_t>(cuda_stream));
+    if (rc != OMOE_OK) return rc;
+    h->last_stream = static_cast<cudaStream_t>(cuda_stream);
+    return omoe_wait(h);
 }
 
 int omoe_get_routing(omoe_handle *h, int32_t *topk_idx, float *topk_w, int32_t *counts, int32_t *offsets,
@@ -574,17 +648,31 @@ int omoe_last_launch_count(const omoe_handle *h) { return h ? h->last_launches :
 
 int omoe_set_profiling(omoe_handle *h, int32_t enabled) {
     if (!h) return OMOE_ERR_INVALID;
+    if (enabled) {
+        for (int r = 0; r < kProfSlots; r++)
+            for (int i = 0; i <= OMOE_N_STAGES; i++)
+                if (!h->ev_ring[r][i]) CU_TRY(h, cudaEventCreate(&h->ev_ring[r][i]));
+    }
     h->profiling = enabled != 0;
+    h->prof_count = 0;
+    h->ev = h->ev_ring[0];
+    h->ev_valid = false;
     return OMOE_OK;
 }
 
-int omoe_get_stage_ms(omoe_handle *h, float *ms) {
+int omoe_get_stage_ms_at(omoe_handle *h, int32_t back, float *ms) {
     if (!h || !ms) return OMOE_ERR_INVALID;
     if (!h->ev_valid) return fail(h, OMOE_ERR_STATE, "omoe_get_stage_ms: profiling was off for the last forward");
-    CU_TRY(h, cudaEventSynchronize(h->ev[OMOE_N_STAGES]));
-    for (int i = 0; i < OMOE_N_STAGES; i++) CU_TRY(h, cudaEventElapsedTime(&ms[i], h->ev[i], h->ev[i + 1]));
-    return check_dev_err(h);
+    if (back < 0 || back >= kProfSlots || back >= h->prof_count)
+        return fail(h, OMOE_ERR_INVALID, "omoe_get_stage_ms_at: only the last %d profiled forwards are kept (%ld so far)",
+                    kProfSlots, h->prof_count);
+    cudaEvent_t *ev = h->ev_ring[(h->prof_count - 1 - back) % kProfSlots];
+    CU_TRY(h, cudaEventSynchronize(h->ev_ring[(h->prof_count - 1) % kProfSlots][OMOE_N_STAGES]));
+    for (int i = 0; i < OMOE_N_STAGES; i++) CU_TRY(h, cudaEventElapsedTime(&ms[i], ev[i], ev[i + 1]));
+    return back == 0 ? check_dev_err(h) : OMOE_OK;
 }
+
+int omoe_get_stage_ms(omoe_handle *h, float *ms) { return omoe_get_stage_ms_at(h, 0, ms); }
 
 int omoe_ep_export(omoe_handle *h, void *blob) {
     if (!h || !blob) return OMOE_ERR_INVALID;

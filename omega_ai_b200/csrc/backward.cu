@@ -174,7 +174,8 @@ combine_bwd_kernel(const OT *__restrict__ dy, void *const *__restrict__ yp_table
         YT *dyp = static_cast<YT *>(dyp_table[q]);
         const float w = topk_w[(size_t)t * k + j];
         float acc = 0.f;
-        for (int c = lane * 8; c < d; c += 256) {
+        // r < 0: the pick has no row (a refused expert-parallel step); nothing is read or written for it
+        for (int c = lane * 8; r >= 0 && c < d; c += 256) {
             float a[8], y[8], o[8];
             load8(dy + (size_t)t * d + c, a);
             load8(yp + (size_t)r * d + c, y);
@@ -288,9 +289,10 @@ dx_kernel(void *const *__restrict__ dxp_table, int e_local, const int32_t *__res
     for (int c = lane * 8; c < d; c += 256) {
         float acc[8];
         for (int j = 0; j < k; j++) {
-            float v[8];
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             const YT *dxp = static_cast<const YT *>(dxp_table[topk_idx[(size_t)t * k + j] / e_local]);
-            load8(dxp + (size_t)pos[(size_t)t * k + j] * d + c, v);
+            const int r = pos[(size_t)t * k + j];
+            if (r >= 0) load8(dxp + (size_t)r * d + c, v);  // r < 0: no row (a refused expert-parallel step)
 #pragma unroll
             for (int i = 0; i < 8; i++) acc[i] = (j == 0) ? v[i] : acc[i] + v[i];
         }
@@ -822,6 +824,14 @@ void bw_forward_invalidate(omoe_handle *h) {
     if (h->bw) static_cast<BwState *>(h->bw)->fwd_valid = false;
 }
 
+void bw_forward_empty(omoe_handle *h) {
+    BwState *b = static_cast<BwState *>(h->bw);
+    if (b && b->training) {
+        b->fwd_valid = true;
+        b->fwd_T = 0;
+    }
+}
+
 cudaError_t bw_forward_experts(omoe_handle *h, int T, cudaStream_t s, int *n) {
     BwState *b = static_cast<BwState *>(h->bw);
     cudaError_t e = h->cfg.compute_dtype == OMOE_BF16 ? forward_experts_t<__nv_bfloat16>(h, b, s, n)
@@ -865,6 +875,10 @@ int bw_backward(omoe_handle *h, const void *x, bool x_is_compute, const void *dy
         snprintf(h->err, sizeof(h->err), "omoe_backward: %s", cudaGetErrorString(e));
         return OMOE_ERR_CUDA;
     }
+    // Expert parallel: one backward per forward.  The owners raise "outputs ready" before their weight-gradient
+    // kernels, which still read the gradient rows; only the next forward's count exchange orders the peers
+    // behind those kernels, so a second backward could overwrite rows that are still being read.
+    if (h->cfg.world > 1) b->fwd_valid = false;
     return OMOE_OK;
 }
 

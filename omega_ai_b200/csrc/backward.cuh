@@ -9,6 +9,8 @@ int bw_set_training(omoe_handle *h, int on);
 bool bw_training(const omoe_handle *h);
 void bw_weights_changed(omoe_handle *h);
 void bw_forward_invalidate(omoe_handle *h);
+// A training-mode forward of no rows on one GPU launches nothing and still counts as the forward a backward follows.
+void bw_forward_empty(omoe_handle *h);
 // Expert stage of a training-mode forward: g and u kept, then h = silu(g) * u, then the down product.
 cudaError_t bw_forward_experts(omoe_handle *h, int T, cudaStream_t s, int *n);
 // x_is_compute: x has the layer's compute dtype (the normalised rows of the block form) instead of io_dtype

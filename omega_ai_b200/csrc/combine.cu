@@ -71,7 +71,8 @@ combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const OT
             int rj = __shfl_sync(0xffffffffu, r, j);
             int qj = __shfl_sync(0xffffffffu, q, j);
             w[j] = __shfl_sync(0xffffffffu, g, j);
-            src[j] = (j < k) ? static_cast<const YT *>(out_table[qj]) + (size_t)rj * d : nullptr;
+            // rj < 0: the pick has no row (an expert-parallel step that was refused); it contributes zeros
+            src[j] = (j < k && rj >= 0) ? static_cast<const YT *>(out_table[qj]) + (size_t)rj * d : nullptr;
         }
     }
     const int cw = ((d / (int)gridDim.y + 7) / 8) * 8;  // blockIdx.y walks one slice of the row
@@ -81,8 +82,9 @@ combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const OT
 #pragma unroll
         for (int j = 0; j < KR; j++) {
             if (j < k) {
-                float v[8];
-                if constexpr (sizeof(YT) == 2) {
+                float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                if (src[j] == nullptr) {
+                } else if constexpr (sizeof(YT) == 2) {
                     uint4 r = __ldcs(reinterpret_cast<const uint4 *>(src[j] + c));
                     unpack8(r, v);
                 } else {
@@ -128,8 +130,9 @@ combine_small_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, co
         const int q = __ldg(topk_idx + (size_t)t * k + j) / e_local;
         const float w = __ldg(topk_w + (size_t)t * k + j);
         const YT *src = static_cast<const YT *>(out_table[q]) + (size_t)r * d + c;
-        float v[8];
-        if constexpr (sizeof(YT) == 2) {
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (r < 0) {
+        } else if constexpr (sizeof(YT) == 2) {
             unpack8(__ldcs(reinterpret_cast<const uint4 *>(src)), v);
         } else {
             float4 a = __ldcs(reinterpret_cast<const float4 *>(src));

@@ -20,10 +20,15 @@ constexpr int kMaxExperts = 128;
 constexpr int kRouterWarps = 8;  // warps per router block
 constexpr int kHostChunksMax = 8;  // pieces a host-buffer forward is cut into to overlap copies and kernels
 constexpr int kMaxWorld = 8;     // expert-parallel ranks (GPUs of one NVSwitch node)
+constexpr int kProfSlots = 32;   // profiled forwards whose stage events are kept
 
 // Device-side error word bits (set by kernels instead of trapping).
 constexpr int kDevErrTimeout = 1;   // a bounded wait ran out
 constexpr int kDevErrBounds = 2;    // an index check failed
+
+// dst_base of every expert in a step that the count exchange refused (an owner's buffer would overflow): any
+// row position derived from it is negative, and kernels touch no row whose position is outside [0, rows_cap).
+constexpr int32_t kRefusedBase = -(1 << 30);
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
@@ -104,8 +109,14 @@ struct omoe_handle {
     void *x_stage, *y_stage;
     size_t stage_bytes;
     cudaStream_t copy_in, copy_out;
-    cudaEvent_t ev_in[omoe::kHostChunksMax], ev_out[omoe::kHostChunksMax];
-    int host_chunk_min;  // smallest chunk (tokens) worth its own forward
+    // per chunk: rows staged on the device / forward done (staging rows consumed, outputs written) / outputs
+    // copied back to the host; ev_fence orders the copy streams behind the caller's stream
+    cudaEvent_t ev_in[omoe::kHostChunksMax], ev_out[omoe::kHostChunksMax], ev_d2h[omoe::kHostChunksMax], ev_fence;
+    int host_chunk_min;     // smallest chunk (tokens) worth its own forward, one GPU
+    int host_chunk_min_ep;  // the same with expert parallelism
+    bool host_pending;      // an omoe_forward_host_async call has not been waited for yet
+    size_t host_prev_geom;  // how the previous host-buffer call cut its batch (tokens, chunks, dtype)
+    int host_prev_chunks;
 
     omoe::TensorMaps maps;
     bool maps_ready;
@@ -117,7 +128,12 @@ struct omoe_handle {
     cudaStream_t last_stream;
     int last_launches;
     bool profiling;
-    cudaEvent_t ev[OMOE_N_STAGES + 1];
+    // Stage events: a ring of event sets, one per profiled forward, so a caller can time many forwards back to
+    // back and read the stages afterwards without a host synchronisation in between.  `ev` points at the set
+    // the running forward records into; set 0 exists from creation, the others once profiling is switched on.
+    cudaEvent_t ev_ring[omoe::kProfSlots][OMOE_N_STAGES + 1];
+    cudaEvent_t *ev;
+    long prof_count;  // profiled forwards so far
     bool ev_valid;
 
     void *ep;  // expert-parallel state (ep.cu)

@@ -126,8 +126,9 @@ ep_exchange_kernel(EpCtl *self, EpCtl *const *__restrict__ peers, const int32_t 
     for (int e = tid; e < E; e += blockDim.x) {
         int before = 0;
         for (int s = 0; s < r; s++) before += s_cnt[s][e];
-        // a refused step parks every row in row 0 of the owner's buffer: harmless, and nothing is read back
-        dst_base[e] = bad ? 0 : s_rpoff[e] + before;
+        // a refused step moves no row: the base is far below zero, so every position the dispatch derives from
+        // it is negative, and the dispatch, combine and backward kernels skip rows with a negative position
+        dst_base[e] = bad ? kRefusedBase : s_rpoff[e] + before;
     }
     for (int le = tid; le < El; le += blockDim.x) {
         ex_counts[le] = bad ? 0 : s_tot[r * El + le];

@@ -223,6 +223,11 @@ cudaError_t launch_both(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid)
 }  // namespace
 
 cudaError_t launch_experts_decode(omoe_handle *h, int T, cudaStream_t s, int *n, cudaEvent_t mid) {
+    // the streaming kernels keep RP token rows of the longer reduction in shared memory; layers too wide for
+    // that take the tensor-core kernels, as steps with more tokens do
+    const int rp = T <= 1 ? 1 : (T <= 2 ? 2 : 4);
+    const int kmax = h->cfg.d_model > h->cfg.d_ff ? h->cfg.d_model : h->cfg.d_ff;
+    if ((size_t)rp * kmax * 2 > 200 * 1024) return launch_experts_bf16(h, s, n, mid, (long)T * h->cfg.top_k);
     if (T <= 1) return launch_both<1>(h, s, n, mid);
     if (T <= 2) return launch_both<2>(h, s, n, mid);
     return launch_both<4>(h, s, n, mid);

@@ -10,7 +10,7 @@
 // Both are the same mainloop: one CTA per SM walks a list of 128 x 256 output
 // tiles; a producer thread feeds a 4-stage shared-memory ring with TMA
 // (128-byte swizzle), one thread issues tcgen05.mma (M=128, N=256, K=16, bf16
-// in, fp32 accumulate in tensor memory), and four epilogue warps read the
+// in, fp32 accumulate in tensor memory), and eight epilogue warps read the
 // accumulator with tcgen05.ld while the next tile's mainloop already runs in
 // the other half of tensor memory.
 //
@@ -39,20 +39,6 @@ constexpr int kOutBytes = 2 * kOutSubBytes;         // 32 KB: 128 output columns
 constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 constexpr int kThreads = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 epilogue
 
-#ifdef OMOE_TRACE
-// Debug build only: per-CTA, per-tile timestamps (ns) of the MMA and epilogue
-// roles, written to a caller-provided buffer [ctas][kTraceTiles][4].
-constexpr int kTraceTiles = 256;
-__device__ unsigned long long *g_trace = nullptr;
-__device__ int g_trace_swiglu = 1;  // which of the two kernels records
-__device__ __forceinline__ void trace(int tile_i, int slot) {
-    if (g_trace && tile_i < kTraceTiles)
-        g_trace[((size_t)blockIdx.x * kTraceTiles + tile_i) * 4 + slot] = globaltimer_ns();
-}
-#define TRACE(i, s) do { if (SWIGLU == (g_trace_swiglu != 0)) trace(i, s); } while (0)
-#else
-#define TRACE(i, s) ((void)0)
-#endif
 
 struct TileCoord {
     int mt, nt;
@@ -162,11 +148,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int stage = 0, as = 0;
             uint32_t phase = 0, aphase = 0;
             bool ok = true;
-            int ti = 0;
-            for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x, ti++) {
+            for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
                 if (!mbar_wait(tempty_bar(as), aphase ^ 1u, abort_flag, dev_err)) { ok = false; break; }
                 tc_fence_after();
-                TRACE(ti, 0);
                 const uint32_t d_tmem = tmem_base + as * BLOCK_N;
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag, dev_err)) { ok = false; break; }
@@ -184,7 +168,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
                 if (!ok) break;
                 tc_commit(tfull_bar(as));  // accumulator complete
-                TRACE(ti, 1);
                 if (++as == kAccStages) { as = 0; aphase ^= 1u; }
             }
         }
@@ -203,14 +186,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         constexpr int kPasses = SWIGLU ? 1 : 2;
         int as = 0;
         uint32_t aphase = 0;
-        int ti = 0;
-        for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ti++) {
+        for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
             TileCoord tc = tile_coord(tile, num_m_tiles, n_tiles, kband);
             bool ok = mbar_wait(tfull_bar(as), aphase, abort_flag, dev_err);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            if (warp == 2 && lane == 0) TRACE(ti, 2);
             const uint32_t t_acc = tmem_base + as * BLOCK_N + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll
             for (int p = 0; p < kPasses; p++) {
@@ -270,7 +251,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
-            if (warp == 2 && lane == 0) TRACE(ti, 3);
             if (++as == kAccStages) { as = 0; aphase ^= 1u; }
         }
         if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -314,13 +294,6 @@ bool encode_map(EncodeTiledFn fn, CUtensorMap *m, void *ptr, uint64_t rows, uint
 
 }  // namespace
 
-#ifdef OMOE_TRACE
-extern "C" __attribute__((visibility("default"))) int omoe_debug_set_trace(void *dev_buf, int swiglu) {
-    unsigned long long *p = static_cast<unsigned long long *>(dev_buf);
-    if (cudaMemcpyToSymbol(g_trace_swiglu, &swiglu, sizeof(int)) != cudaSuccess) return -2;
-    return cudaMemcpyToSymbol(g_trace, &p, sizeof(p)) == cudaSuccess ? 0 : -2;
-}
-#endif
 
 bool build_tensor_maps(omoe_handle *h) {
     EncodeTiledFn fn = get_encode_fn();

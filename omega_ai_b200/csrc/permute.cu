@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(256)
 permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, const int32_t *__restrict__ topk_idx,
                const int32_t *__restrict__ lrank, int32_t *__restrict__ pos, const int32_t *__restrict__ block_base,
                const int32_t *__restrict__ dst_base, int T, int d, int n_blocks, int e_local, int k, int tokens_per_block,
-               EpSignal sig, int32_t *ticket) {
+               EpSignal sig, int32_t *ticket, int rows_cap, int32_t *dev_err) {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int my = 0, owner = 0;
@@ -108,6 +108,15 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
         int b = t / tokens_per_block;
         my = dst_base[e] + block_base[(size_t)e * n_blocks + b] + lrank[f];
         owner = e / e_local;
+        // No row outside the owner's buffer is ever touched: a step the count exchange refused gives negative
+        // positions (nothing moves, consumers skip the pick); a position beyond the capacity cannot follow
+        // from an accepted layout and is reported.
+        if (my >= rows_cap) {
+            atomicOr(dev_err, kDevErrBounds);
+            my = -1;
+        } else if (my < 0) {
+            my = -1;
+        }
         if (blockIdx.y == 0) pos[f] = my;
     }
     if (t < T) {
@@ -116,7 +125,7 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
     for (int j = 0; j < kMaxTopK; j++) {
         int row = __shfl_sync(0xffffffffu, my, j);
         int q = __shfl_sync(0xffffffffu, owner, j);
-        dst[j] = (j < k) ? static_cast<OT *>(row_table[q]) + (size_t)row * d : nullptr;
+        dst[j] = (j < k && row >= 0) ? static_cast<OT *>(row_table[q]) + (size_t)row * d : nullptr;
     }
 
     // blockIdx.y walks one slice of the row (more warps in flight when there are few tokens)
@@ -129,7 +138,7 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
             uint4 v = __ldg(reinterpret_cast<const uint4 *>(src + c));
 #pragma unroll
             for (int j = 0; j < kMaxTopK; j++)
-                if (j < k) *reinterpret_cast<uint4 *>(dst[j] + c) = v;
+                if (j < k && dst[j] != nullptr) *reinterpret_cast<uint4 *>(dst[j] + c) = v;
         }
     } else {
         // fp32 rows in, bf16 rows out: 8 elements per lane per step
@@ -143,7 +152,7 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
             v.w = pack_bf16(b.z, b.w);
 #pragma unroll
             for (int j = 0; j < kMaxTopK; j++)
-                if (j < k) *reinterpret_cast<uint4 *>(dst[j] + c) = v;
+                if (j < k && dst[j] != nullptr) *reinterpret_cast<uint4 *>(dst[j] + c) = v;
         }
     }
     }
@@ -170,6 +179,7 @@ __global__ void perm_readout_kernel(const int32_t *__restrict__ topk_idx, const 
     int f = blockIdx.x * blockDim.x + threadIdx.x;
     if (f >= n) return;
     int e = topk_idx[f];
+    if (pos[f] < 0) return;  // a refused expert-parallel step placed no row
     perm[offsets[e] + (pos[f] - poffsets[e])] = f;
 }
 
@@ -198,15 +208,15 @@ cudaError_t launch_permute(omoe_handle *h, const void *x, int io_dtype, int T, c
     if (io_dtype == OMOE_F32 && !cbf)
         permute_kernel<float, float><<<grid, block, 0, s>>>(
             static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->lrank, h->pos, h->block_base, h->dst_base, T, d,
-            nb, El, k, h->tokens_per_block, sg, h->ticket);
+            nb, El, k, h->tokens_per_block, sg, h->ticket, (int)h->rows_cap, h->dev_err);
     else if (io_dtype == OMOE_F32 && cbf)
         permute_kernel<float, __nv_bfloat16><<<grid, block, 0, s>>>(
             static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->lrank, h->pos, h->block_base, h->dst_base, T, d,
-            nb, El, k, h->tokens_per_block, sg, h->ticket);
+            nb, El, k, h->tokens_per_block, sg, h->ticket, (int)h->rows_cap, h->dev_err);
     else if (io_dtype == OMOE_BF16 && cbf)
         permute_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, block, 0, s>>>(
             static_cast<const __nv_bfloat16 *>(x), h->d_row_table, h->topk_idx, h->lrank, h->pos,
-            h->block_base, h->dst_base, T, d, nb, El, k, h->tokens_per_block, sg, h->ticket);
+            h->block_base, h->dst_base, T, d, nb, El, k, h->tokens_per_block, sg, h->ticket, (int)h->rows_cap, h->dev_err);
     else
         return cudaErrorInvalidValue;  // bf16 rows into an fp32 layer are rejected by the API
     (*n)++;

@@ -26,6 +26,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "router_common.cuh"
 
@@ -35,14 +37,6 @@ namespace {
 
 constexpr int kSub = 256;  // columns per step (32 lanes x 8)
 
-#ifdef OMOE_RTRACE
-// Debug build only (-DOMOE_RTRACE): per-block phase timestamps (SM clock) of the router kernel,
-// read back with omoe_debug_router_trace(long long out[2048][8]).
-__device__ long long g_rtrace[2048][8];
-#define RTRACE(slot) do { if (threadIdx.x == 0 && blockIdx.x < 2048) g_rtrace[blockIdx.x][slot] = clock64(); } while (0)
-#else
-#define RTRACE(slot) ((void)0)
-#endif
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -162,7 +156,6 @@ router_kernel(const XT *__restrict__ x, const WT *__restrict__ w_r, const float 
         }
     };
 
-    RTRACE(0);
     unsigned long long acc[TPW][EPW];  // (even chain, odd chain) of every token x expert
 #pragma unroll
     for (int i = 0; i < TPW; i++)
@@ -220,7 +213,6 @@ router_kernel(const XT *__restrict__ x, const WT *__restrict__ w_r, const float 
         if constexpr (S == 1) __syncthreads();
     }
 
-    RTRACE(1);
     // xor butterfly over all accumulators first (independent chains overlap), then lane (e % 32) publishes logit e
     float red[TPW][EPW];
 #pragma unroll
@@ -248,7 +240,6 @@ router_kernel(const XT *__restrict__ x, const WT *__restrict__ w_r, const float 
         }
     __syncthreads();
 
-    RTRACE(2);
     // Softmax statistics, top-k on the logits, gate weights: a group of GW lanes per token
     // (8 lanes for up to 8 experts, so a warp works on 4 tokens at once).
     constexpr int GW = EMAX <= 8 ? 8 : (EMAX <= 16 ? 16 : 32);
@@ -272,7 +263,6 @@ router_kernel(const XT *__restrict__ x, const WT *__restrict__ w_r, const float 
     }
     __syncthreads();
 
-    RTRACE(3);
     // Stable rank of every pick among the block's picks of the same expert, in
     // order of the flat index t*k+j; the last running count is the histogram.
     const int n_entries = TB * k;
@@ -287,7 +277,6 @@ router_kernel(const XT *__restrict__ x, const WT *__restrict__ w_r, const float 
         }
         if (lane == 0) block_counts[(size_t)e * gridDim.x + blockIdx.x] = base;  // expert-major
     }
-    RTRACE(4);
 }
 
 template <int EMAX, int ES, int TPW, typename XT, typename WT = float>
@@ -347,11 +336,6 @@ cudaError_t launch_typed(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
 
 }  // namespace
 
-#ifdef OMOE_RTRACE
-extern "C" __attribute__((visibility("default"))) int omoe_debug_router_trace(long long *host_out) {
-    return cudaMemcpyFromSymbol(host_out, g_rtrace, sizeof(long long) * 2048 * 8) == cudaSuccess ? 0 : -2;
-}
-#endif
 
 // Smallest number of tokens one router block may cover (sizes the per-block histogram arrays).
 int router_tokens_per_block(int E) { return E <= 16 ? kRouterWarps : (E <= 32 ? 4 : (E <= 64 ? 2 : 1)); }
@@ -383,8 +367,9 @@ cudaError_t launch_router(omoe_handle *h, const void *x, int io_dtype, int T, cu
 // caller's buffers.
 //
 // The array is a host-side stand-in when named from host code; its device
-// address is looked up once per device with cudaGetSymbolAddress, on the first
-// call made while that device is current.
+// address is looked up with cudaGetSymbolAddress on the first call made in a
+// CUDA context (one per device for runtime-API hosts; a host with its own
+// driver-API contexts gets one look-up per context), with that context current.
 // ---------------------------------------------------------------------------
 
 namespace omoe {
@@ -401,8 +386,60 @@ constexpr size_t kNaScratchBytes = kNaLogitsBytes + kNaBlocksBytes + kNaRankByte
 // held by each GPU that loads the library until the process exits).
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNaScratchBytes];
 
-constexpr int kNaMaxDevices = 64;
-unsigned char *g_na_ptr[kNaMaxDevices] = {};  // device address of the array, per device ordinal
+// Device address of the array, per CUDA context.  A __device__ symbol is instantiated once per context that
+// loads the module, not once per device ordinal: a host that created its own driver-API context (the
+// reference engine does, CUDAUtils.java:124-130) and the primary context of the same device each have their
+// own copy, so the cache is keyed by the context that is current at the call.
+constexpr int kNaMaxContexts = 64;
+struct NaSlot {
+    void *ctx;
+    unsigned char *ptr;
+};
+NaSlot g_na_slots[kNaMaxContexts] = {};
+int g_na_used = 0;
+std::mutex g_na_mutex;
+
+typedef CUresult (*CtxGetCurrentFn)(CUcontext *);
+CtxGetCurrentFn na_ctx_fn() {
+    static CtxGetCurrentFn fn = nullptr;
+    if (fn) return fn;
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuCtxGetCurrent", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<CtxGetCurrentFn>(p);
+    return fn;
+}
+
+// Address of the scratch array in the current context; looks it up (and, under lazy module loading, makes
+// the runtime load this library's module into the context) the first time a context is seen.
+cudaError_t na_scratch(unsigned char **out) {
+    *out = nullptr;
+    CtxGetCurrentFn get = na_ctx_fn();
+    CUcontext ctx = nullptr;
+    if (get && get(&ctx) == CUDA_SUCCESS && ctx != nullptr) {
+        std::lock_guard<std::mutex> lock(g_na_mutex);
+        for (int i = 0; i < g_na_used; i++)
+            if (g_na_slots[i].ctx == ctx) {
+                *out = g_na_slots[i].ptr;
+                return cudaSuccess;
+            }
+    }
+    void *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return e;
+    if (p == nullptr) return cudaErrorInvalidSymbol;
+    // the runtime call above binds the primary context when the thread had none; ask again
+    if (ctx == nullptr && get) get(&ctx);
+    if (ctx != nullptr) {
+        std::lock_guard<std::mutex> lock(g_na_mutex);
+        if (g_na_used < kNaMaxContexts) g_na_slots[g_na_used++] = NaSlot{ctx, static_cast<unsigned char *>(p)};
+        // table full: later calls from further contexts look the address up every time (still no allocation)
+    }
+    *out = static_cast<unsigned char *>(p);
+    return cudaSuccess;
+}
 
 // counts[e] = sum over router blocks of block_counts[b][e]; one warp per expert.
 __global__ void noalloc_counts_kernel(const int32_t *__restrict__ block_counts, int n_blocks, int E,
@@ -447,17 +484,19 @@ int omoe_route_noalloc(const void *x_dev, const float *w_router_dev, const float
     if (!counts_dev || (T > 0 && (!x_dev || !w_router_dev || !topk_idx_dev || !topk_w_dev)))
         return na_fail(OMOE_ERR_INVALID, "null buffer");
 
-    // set-up, once per device, with that device current
-    int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNaMaxDevices)
-        return na_fail(OMOE_ERR_CUDA, "cudaGetDevice failed or device ordinal out of range");
-    if (g_na_ptr[dev] == nullptr) {
-        void *p = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-        if (e != cudaSuccess || p == nullptr) return na_fail(OMOE_ERR_CUDA, "cudaGetSymbolAddress failed: ", cudaGetErrorString(e));
-        g_na_ptr[dev] = static_cast<unsigned char *>(p);
+    // rows and router weights move as 16-byte vectors; a misaligned address would raise a sticky device fault
+    if (T > 0 && (((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(w_router_dev)) & 15u) != 0))
+        return na_fail(OMOE_ERR_INVALID, "x_dev and w_router_dev must be 16-byte aligned");
+    if (((reinterpret_cast<uintptr_t>(topk_idx_dev) | reinterpret_cast<uintptr_t>(topk_w_dev) |
+          reinterpret_cast<uintptr_t>(counts_dev) | reinterpret_cast<uintptr_t>(router_bias_dev)) & 3u) != 0)
+        return na_fail(OMOE_ERR_INVALID, "output and bias buffers must be 4-byte aligned");
+
+    // set-up, once per context, with that context current
+    unsigned char *scratch = nullptr;
+    {
+        cudaError_t e = na_scratch(&scratch);
+        if (e != cudaSuccess) return na_fail(OMOE_ERR_CUDA, "cudaGetSymbolAddress failed: ", cudaGetErrorString(e));
     }
-    unsigned char *scratch = g_na_ptr[dev];
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
 
     // A stack handle that only carries what the router launcher reads; every

@@ -29,10 +29,30 @@ def owner_layout(counts_all: np.ndarray, q: int, e_local: int):
     return tot.astype(np.int32), poff.astype(np.int32)
 
 
-def dst_base(counts_all: np.ndarray, r: int, e_local: int) -> np.ndarray:
-    """First row, in the owner's buffer, of source rank r's picks of every expert."""
+REFUSED_BASE = -(1 << 30)  # dst_base of every expert in a refused step: every row position becomes negative
+
+
+def rows_capacity(rows_in: int, e_local: int) -> int:
+    """Row capacity of a rank's dispatch buffer: ``rows_in`` is ``recv_rows_max`` of the handle's configuration
+    (default ``t_max * top_k * world``); every local expert's segment may need rounding up to ROW_ALIGN."""
+    return (round_up(rows_in, ROW_ALIGN) // ROW_ALIGN + e_local) * ROW_ALIGN
+
+
+def step_refused(counts_all: np.ndarray, e_local: int, rows_cap: int) -> bool:
+    """A step is refused when the padded rows of ANY owner exceed the capacity.  Every rank evaluates this on the
+    same count matrix, so all of them refuse together; a refused step moves no row (dispatch, combine and the
+    backward kernels skip picks whose position is negative) and raises the bounds bit of the device error word."""
+    return rows_needed(counts_all, e_local) > rows_cap
+
+
+def dst_base(counts_all: np.ndarray, r: int, e_local: int, rows_cap: int | None = None) -> np.ndarray:
+    """First row, in the owner's buffer, of source rank r's picks of every expert (REFUSED_BASE everywhere when
+    ``rows_cap`` is given and the step does not fit it)."""
     W, E = counts_all.shape
     out = np.zeros(E, np.int32)
+    if rows_cap is not None and step_refused(counts_all, e_local, rows_cap):
+        out[:] = REFUSED_BASE
+        return out
     for q in range(W):
         _, poff = owner_layout(counts_all, q, e_local)
         for le in range(e_local):

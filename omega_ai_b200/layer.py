@@ -284,6 +284,18 @@ class MoELayer(Layer):
         check(self._h, self._lib.omoe_forward_host(self._h, x.data_ptr(), y.data_ptr(), x.shape[0], _dt(x.dtype), s))
         return y
 
+    def forward_host_async(self, x: torch.Tensor, y: torch.Tensor, stream=None) -> None:
+        """:meth:`forward_host` without the final synchronise: enqueue, return; ``y`` is complete once
+        :meth:`wait` has returned.  Calls made before the wait run in order with their copies overlapped."""
+        assert not x.is_cuda and not y.is_cuda and x.is_contiguous() and y.is_contiguous()
+        s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        check(self._h, self._lib.omoe_forward_host_async(self._h, x.data_ptr(), y.data_ptr(), x.shape[0],
+                                                         _dt(x.dtype), s))
+
+    def wait(self) -> None:
+        """Host waits for everything enqueued on this layer and raises if a kernel reported a failure."""
+        check(self._h, self._lib.omoe_wait(self._h))
+
     # ---- read-outs -------------------------------------------------------
     def routing(self, T: int):
         """(topk_idx [T,k], topk_w [T,k], counts [E], offsets [E+1], perm [T*k]) of the last forward."""
@@ -308,9 +320,11 @@ class MoELayer(Layer):
     def set_profiling(self, on: bool):
         check(self._h, self._lib.omoe_set_profiling(self._h, int(on)))
 
-    def stage_ms(self) -> dict:
+    def stage_ms(self, back: int = 0) -> dict:
+        """Device time of every stage of a profiled forward: the last one (``back`` = 0) or one of the 31 before
+        it, so a run of forwards can be timed back to back and read afterwards."""
         ms = (C.c_float * native.N_STAGES)()
-        check(self._h, self._lib.omoe_get_stage_ms(self._h, ms))
+        check(self._h, self._lib.omoe_get_stage_ms_at(self._h, back, ms))
         return dict(zip(native.STAGE_NAMES, [float(v) for v in ms]))
 
     def ep_export(self) -> bytes:
@@ -324,16 +338,42 @@ class MoELayer(Layer):
         assert len(blobs) == self.world and all(len(b) == native.EP_BLOB_BYTES for b in blobs)
         check(self._h, self._lib.omoe_ep_import(self._h, b"".join(blobs)))
 
-    def ep_connect(self, group=None):
-        """Exchange the handles over torch.distributed and open the peers' buffers.
-        Ends with a barrier, after which forward may be called (collectively)."""
+    def ep_connect(self, group=None, store=None, timeout_s: float = 60.0, tag: str = "0"):
+        """Exchange the handles and open the peers' buffers; returns once every rank has done so, after which
+        forward may be called (collectively).
+
+        Default: over torch.distributed (``all_gather_object`` + ``barrier`` on ``group``).  With ``store`` (any
+        torch.distributed store, e.g. a ``TCPStore``) the exchange is a rendezvous with a deadline instead: every
+        rank posts its blob under ``omoe_ep/<tag>/<rank>`` and waits at most ``timeout_s`` seconds for the
+        others; a rank that never posts makes the others raise ``OmoeError(OMOE_ERR_COMM)`` naming it, rather
+        than wait forever (the reference's CyclicBarrier, DP.java:74, does wait forever on a dead thread)."""
         import torch.distributed as dist
 
-        blobs = [None] * self.world
-        dist.all_gather_object(blobs, self.ep_export(), group=group)
-        self.ep_import(blobs)
+        if store is None:
+            blobs = [None] * self.world
+            dist.all_gather_object(blobs, self.ep_export(), group=group)
+            self.ep_import(blobs)
+            torch.cuda.synchronize()
+            dist.barrier(group=group)
+            return
+        import datetime
+
+        def rendezvous(phase, payload):
+            store.set(f"omoe_ep/{tag}/{phase}/{self.rank}", payload)
+            got = []
+            for q in range(self.world):
+                key = f"omoe_ep/{tag}/{phase}/{q}"
+                try:
+                    store.wait([key], datetime.timedelta(seconds=timeout_s))
+                except Exception as e:  # the store raises its own error types on a deadline
+                    raise OmoeError(-7, f"ep_connect: rank {q} did not post its {phase} within {timeout_s} s ({type(e).__name__})")
+                got.append(store.get(key))
+            return got
+
+        blobs = rendezvous("handles", self.ep_export())
+        self.ep_import([bytes(b) for b in blobs])
         torch.cuda.synchronize()
-        dist.barrier(group=group)
+        rendezvous("opened", b"1")
 
     @staticmethod
     def ep_connect_local(layers):

@@ -29,8 +29,8 @@ ERRORS = {
 # every symbol include/omoe.h declares
 SYMBOLS = (
     "omoe_create", "omoe_destroy", "omoe_last_error", "omoe_set_weights", "omoe_forward",
-    "omoe_forward_host", "omoe_forward_block", "omoe_get_routing", "omoe_get_logits", "omoe_last_launch_count",
-    "omoe_set_profiling", "omoe_get_stage_ms", "omoe_ep_export", "omoe_ep_import",
+    "omoe_forward_host", "omoe_forward_host_async", "omoe_wait", "omoe_forward_block", "omoe_get_routing", "omoe_get_logits", "omoe_last_launch_count",
+    "omoe_set_profiling", "omoe_get_stage_ms", "omoe_get_stage_ms_at", "omoe_ep_export", "omoe_ep_import",
     "omoe_route_noalloc", "omoe_route_noalloc_error",
     "omoe_ep_connect_local", "omoe_set_training", "omoe_backward", "omoe_backward_block", "omoe_get_weight_grads", "omoe_set_aux_loss", "omoe_get_aux_loss",
 )
@@ -92,12 +92,15 @@ def lib():
     L.omoe_set_weights.argtypes = [vp, vp, vp, vp, vp, vp, i32, vp]
     L.omoe_forward.argtypes = [vp, vp, vp, i32, i32, vp]
     L.omoe_forward_host.argtypes = [vp, vp, vp, i32, i32, vp]
+    L.omoe_forward_host_async.argtypes = [vp, vp, vp, i32, i32, vp]
+    L.omoe_wait.argtypes = [vp]
     L.omoe_forward_block.argtypes = [vp, vp, vp, C.c_float, vp, i32, i32, vp]
     L.omoe_get_routing.argtypes = [vp, vp, vp, vp, vp, vp]
     L.omoe_get_logits.argtypes = [vp, vp]
     L.omoe_last_launch_count.argtypes = [vp]
     L.omoe_set_profiling.argtypes = [vp, i32]
     L.omoe_get_stage_ms.argtypes = [vp, vp]
+    L.omoe_get_stage_ms_at.argtypes = [vp, i32, vp]
     L.omoe_ep_export.argtypes = [vp, vp]
     L.omoe_ep_import.argtypes = [vp, vp]
     L.omoe_route_noalloc.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]

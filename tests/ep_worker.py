@@ -178,6 +178,78 @@ def run_graph_case(rank, world):
     layer.close()
 
 
+def run_refused_case(rank, world):
+    """A step that does not fit an owner's buffer (recv_rows_max far below what the picks need) is refused by every
+    rank alike: no row moves (nothing outside any buffer is touched), the output is zeros, the next synchronising
+    call reports the device error, and the step after it -- one that fits -- is correct again."""
+    from omega_ai_b200 import OmoeError
+    d, dff, E, k, T = 128, 256, 8, 2, 512
+    El = E // world
+    _, w_r, w_g, w_u, w_d, _ = make_layer(1, d, dff, E, k, seed=81)
+    w_r = ref.bf16_round(w_r)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda().to(torch.bfloat16).contiguous()
+    # capacity: (ceil(64/128) + El) * 128 rows per owner; every expert receives world * 128 rows on average,
+    # which padded to 128 per expert is more than that for every world size
+    layer = MoELayer(d, dff, E, k, t_max=T, compute_dtype=torch.bfloat16, world=world, rank=rank, recv_rows_max=64)
+    sl = slice(rank * El, (rank + 1) * El)
+    layer.setWeights(dev(w_r), dev(w_g[sl]), dev(w_u[sl]), dev(w_d[sl]))
+    layer.ep_connect()
+    rng = np.random.Generator(np.random.Philox(key=4000 + rank))
+    x = ref.bf16_round(rng.standard_normal((T, d), dtype=np.float32))
+    y = torch.full((T, d), 7.0, device="cuda", dtype=torch.bfloat16)
+    layer.forward_device(dev(x), y)
+    torch.cuda.synchronize()
+    try:
+        layer.routing(T)
+        raise AssertionError("a refused step must report OMOE_ERR_DEVICE")
+    except OmoeError as e:
+        assert e.code == -6 and "index check" in str(e), str(e)
+    assert float(y.float().abs().max()) == 0.0, "a refused step combines nothing"
+    dist.barrier()
+    # a step small enough to fit: few tokens, so every owner receives at most 2 * 8 * world rows
+    Ts = 8
+    xs = ref.bf16_round(rng.standard_normal((Ts, d), dtype=np.float32))
+    ys = layer.forward_device(dev(xs)).float().cpu().numpy()
+    idx = layer.routing(Ts)[0]
+    r = ref.moe_forward(xs, w_r, w_g, w_u, w_d, k, bf16=True)
+    np.testing.assert_array_equal(idx, r.topk_idx)
+    assert_close_bf16(ys, r.y)
+    torch.cuda.synchronize()
+    dist.barrier()
+    layer.close()
+
+
+def run_host_chunks_case(rank, world):
+    """Host-buffer forwards under expert parallelism are cut into the same number of chunks on every rank (from
+    t_max), also when the ranks hold different numbers of tokens; rows are bit-identical to the device path, and
+    calls enqueued back to back with omoe_forward_host_async give the same rows after one omoe_wait."""
+    d, dff, E, k = 256, 384, 8, 2
+    El = E // world
+    t_max = 2048   # four chunks of at least 512 tokens
+    _, w_r, w_g, w_u, w_d, _ = make_layer(1, d, dff, E, k, seed=83)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda().to(torch.bfloat16).contiguous()
+    layer = MoELayer(d, dff, E, k, t_max=t_max, compute_dtype=torch.bfloat16, world=world, rank=rank)
+    sl = slice(rank * El, (rank + 1) * El)
+    layer.setWeights(dev(ref.bf16_round(w_r)), dev(w_g[sl]), dev(w_u[sl]), dev(w_d[sl]))
+    layer.ep_connect()
+    for step, T in enumerate([2048 if rank % 2 == 0 else 700, 1500, 0 if rank == world - 1 else 2048]):
+        rng = np.random.Generator(np.random.Philox(key=5000 + 10 * step + rank))
+        x = torch.from_numpy(rng.standard_normal((T, d), dtype=np.float32)).to(torch.bfloat16)
+        xd = x.cuda()
+        want = layer.forward_device(xd).cpu()
+        xh, yh = x.pin_memory(), torch.empty(T, d, dtype=torch.bfloat16).pin_memory()
+        layer.forward_host(xh, yh)
+        assert torch.equal(yh, want), f"host chunks differ from the device path (step {step}, rank {rank})"
+        yh2 = [torch.empty(T, d, dtype=torch.bfloat16).pin_memory() for _ in range(3)]
+        for i in range(3):
+            layer.forward_host_async(xh, yh2[i])
+        layer.wait()
+        for i in range(3):
+            assert torch.equal(yh2[i], want), f"pipelined host call {i} differs (step {step}, rank {rank})"
+        dist.barrier()
+    layer.close()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
@@ -187,6 +259,8 @@ def main():
     run_case(rank, world, [256, 128], 256, 256, 64, 6, torch.bfloat16, True, steps=2)
     run_case(rank, world, [64, 40], 128, 256, 8, 2, torch.float32, False, steps=2)
     run_graph_case(rank, world)
+    run_host_chunks_case(rank, world)
+    run_refused_case(rank, world)
     run_backward_case(rank, world, torch.float32)
     run_backward_case(rank, world, torch.bfloat16)
     dist.destroy_process_group()

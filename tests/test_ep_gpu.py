@@ -43,3 +43,17 @@ def test_expert_parallel_in_one_process():
                        text=True, timeout=600, env=env)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     assert "single-process ep ok" in p.stdout
+
+
+def test_skipped_collective_call_is_detected():
+    """Failure detection on 2 GPUs without a fault: one rank skips one forward between steps; the other's bounded
+    device waits (300 ms here) run out, its next synchronising call reports OMOE_ERR_DEVICE and its context keeps
+    working.  NVLS off, plain peer loads/stores only."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMOE_EP_WAIT_MS="300")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29519", os.path.join(ROOT, "tests", "ep_skipped_call_worker.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    assert "skipped-call detection ok" in p.stdout

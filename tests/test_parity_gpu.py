@@ -145,6 +145,29 @@ def test_forward_host_in_chunks_matches_device(T):
     layer.close()
 
 
+def test_forward_host_async_pipelines_calls():
+    """Calls enqueued with omoe_forward_host_async before one omoe_wait run in order with their copies overlapped;
+    batches of different sizes (different chunking) in a row keep every row's bits."""
+    from omega_ai_b200 import MoELayer
+    d, dff, E, k = 128, 128, 8, 2
+    _, w_r, w_g, w_u, w_d, _ = make_layer(1, d, dff, E, k, seed=11)
+    layer = MoELayer(d, dff, E, k, t_max=20000, compute_dtype=torch.bfloat16)
+    dev = lambda a: torch.from_numpy(a).cuda().to(torch.bfloat16).contiguous()
+    layer.setWeights(dev(w_r), dev(w_g), dev(w_u), dev(w_d))
+    g = torch.Generator(device="cuda").manual_seed(4)
+    cases = []
+    for T in (20000, 300, 9000, 9000, 17000, 0, 20000):
+        xd = torch.randn(T, d, device="cuda", generator=g).to(torch.bfloat16)
+        want = layer.forward_device(xd).cpu()
+        cases.append((xd.cpu().pin_memory(), torch.full((T, d), 3.0, dtype=torch.bfloat16).pin_memory(), want))
+    for xh, yh, _ in cases:
+        layer.forward_host_async(xh, yh)
+    layer.wait()
+    for i, (_, yh, want) in enumerate(cases):
+        assert torch.equal(yh, want), f"call {i} differs"
+    layer.close()
+
+
 def test_errors_are_reported_not_fatal():
     from omega_ai_b200 import MoELayer, OmoeError
     layer = MoELayer(128, 256, 8, 2, t_max=16, compute_dtype=torch.bfloat16)
@@ -158,6 +181,17 @@ def test_errors_are_reported_not_fatal():
     assert e.value.code == -3
     y = layer.forward_device(x[:0].contiguous())  # empty batch is a no-op
     assert y.shape[0] == 0
+    # a view that starts 4 bytes into an allocation: refused before any launch (rows move as 16-byte vectors)
+    import ctypes as C
+    from omega_ai_b200 import native
+    L = native.lib()
+    flat = torch.zeros(8 * 128 + 8, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros(8 * 128 + 8, device="cuda", dtype=torch.bfloat16)
+    for xo, yo in ((4, 0), (0, 4)):
+        rc = L.omoe_forward(layer._h, flat.data_ptr() + xo, out.data_ptr() + yo, 8, native.OMOE_BF16, None)
+        assert rc == -1 and b"16-byte aligned" in L.omoe_last_error(layer._h)
+    layer.forward_device(x[:8].contiguous())  # and the handle still works
+    torch.cuda.synchronize()
     layer.close()
     with pytest.raises(OmoeError):
         MoELayer(130, 256, 8, 2)  # d_model not a multiple of 8

@@ -71,6 +71,51 @@ def test_noalloc_matches_regular_twice(E, k, zipf):
         assert counts.sum() == T * k
 
 
+@pytest.mark.parametrize("T,d,E,k,xdt,zipf", [
+    (700, 256, 8, 2, torch.bfloat16, False),
+    (4096, 512, 128, 16, torch.float32, False),   # the largest footprint the fixed array allows, fp32 rows
+    (4096, 256, 64, 6, torch.bfloat16, True),
+])
+def test_noalloc_matches_oracle_and_allocates_nothing(oracle, T, d, E, k, xdt, zipf):
+    """Against the CPU oracle (logits -> top-k and gate weights -> counts), not only against the library itself;
+    and the device's free memory is the same before and after a call once the first call in the context (which
+    may make the driver load the library's module, the array included) has been made."""
+    x, w_r, _, _, _, bias = make_layer(T, d, 8, E, k, seed=31, zipf=zipf)
+    if xdt == torch.bfloat16:
+        x = oracle.bf16_round(x)
+    w_r = oracle.bf16_round(w_r)
+    bias = None if bias is None else oracle.bf16_round(bias)
+    xd = torch.from_numpy(x).cuda().to(xdt).contiguous()
+    wd = torch.from_numpy(w_r).cuda().contiguous()
+    bd = None if bias is None else torch.from_numpy(bias).cuda().contiguous()
+    _route_noalloc(xd, wd, bd, k)           # first call in this context: set-up
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    idx, w, counts = _route_noalloc(xd, wd, bd, k)
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, f"device free memory changed across the call: {free0} -> {free1}"
+    logits = oracle.router_logits(x, w_r, bias)
+    ref_idx, ref_w = oracle.topk_gate(logits, k)
+    np.testing.assert_array_equal(idx, ref_idx)
+    np.testing.assert_allclose(w, ref_w, rtol=1e-5, atol=1e-7)
+    np.testing.assert_array_equal(counts, np.bincount(ref_idx.reshape(-1), minlength=E))
+
+
+def test_noalloc_rejects_misaligned_buffers():
+    from omega_ai_b200 import native
+
+    L = native.lib()
+    x = torch.zeros(8 * 64 + 8, device="cuda")
+    w = torch.zeros(8 * 64 + 8, device="cuda")
+    out_i = torch.zeros(8, 2, dtype=torch.int32, device="cuda")
+    out_w = torch.zeros(8, 2, device="cuda")
+    counts = torch.zeros(8, dtype=torch.int32, device="cuda")
+    for xo, wo in ((4, 0), (0, 4)):   # a view that starts 4 bytes into an allocation
+        rc = L.omoe_route_noalloc(x.data_ptr() + xo, w.data_ptr() + wo, None, 8, 64, 8, 2, 1, native.OMOE_F32,
+                                  out_i.data_ptr(), out_w.data_ptr(), counts.data_ptr(), None)
+        assert rc == -1 and b"16-byte aligned" in L.omoe_route_noalloc_error()
+
+
 def test_noalloc_rejects_sizes_beyond_its_scratch():
     from omega_ai_b200 import native
 
