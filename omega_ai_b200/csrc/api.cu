@@ -68,7 +68,8 @@ int check_dev_err(omoe_handle *h) {
     CU_TRY(h, cudaMemcpy(&v, h->dev_err, sizeof(v), cudaMemcpyDeviceToHost));
     if (v != 0) {
         cudaMemset(h->dev_err, 0, sizeof(int32_t));
-    cudaMemset(h->ticket, 0, sizeof(int32_t));
+        cudaMemset(h->ticket, 0, sizeof(int32_t));
+        cudaMemset(h->ticket2, 0, sizeof(int32_t));
         return fail(h, OMOE_ERR_DEVICE, "device error word = %d (%s%s)", v,
                     (v & kDevErrTimeout) ? "a bounded wait ran out " : "",
                     (v & kDevErrBounds) ? "an index check failed" : "");
@@ -109,7 +110,7 @@ int omoe_destroy(omoe_handle *h) {
     void *ptrs[] = {h->w_router, h->w_router_bf16, h->router_bias, h->w_gate, h->w_up, h->w_down, h->logits, h->topk_idx,
                     h->topk_w, h->block_counts, h->block_base, h->counts, h->offsets, h->poffsets, h->tile_expert, h->pos, h->lrank,
                     h->perm_out, h->dev_err, h->xp, h->hbuf, h->yp, h->xn, h->x_stage, h->y_stage, h->d_row_table,
-                    h->d_out_table, h->ticket, h->dst_base != h->poffsets ? h->dst_base : nullptr};
+                    h->d_out_table, h->ticket, h->ticket2, h->dst_base != h->poffsets ? h->dst_base : nullptr};
     for (void *p : ptrs)
         if (p) cudaFree(p);
     for (int r = 0; r < kProfSlots; r++)
@@ -223,6 +224,7 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
     ALLOC(perm_out, tm * k);
     ALLOC(dev_err, 1);
     ALLOC(ticket, 1);
+    ALLOC(ticket2, 1);
     ALLOC(d_row_table, c.world);
     ALLOC(d_out_table, c.world);
     if (c.world > 1) ALLOC(dst_base, E);
@@ -244,6 +246,7 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
     }
     cudaMemset(h->dev_err, 0, sizeof(int32_t));
     cudaMemset(h->ticket, 0, sizeof(int32_t));
+    cudaMemset(h->ticket2, 0, sizeof(int32_t));
     // padding rows of the dispatch buffers are never read back, but start them
     // at zero so no stale NaN pattern ever enters a tensor-core tile
     cudaMemset(h->xp, 0, (size_t)h->rows_cap * d * cs);

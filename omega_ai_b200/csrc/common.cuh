@@ -99,6 +99,7 @@ struct omoe_handle {
     // and expert-output buffer (yp); entry `rank` is this GPU's own buffer.
     void **d_row_table, **d_out_table;
     int32_t *ticket;      // blocks of the dispatch kernel that have finished (EP)
+    int32_t *ticket2;     // CTAs of the down product that have finished (EP: the last one raises "outputs ready")
     int32_t *perm_out;    // [t_max*k] scratch for omoe_get_routing
     int32_t *dev_err;     // device error word
 
@@ -170,15 +171,19 @@ cudaError_t launch_rmsnorm(omoe_handle *h, const void *x, int x_dtype, const flo
 cudaError_t launch_experts_f32(omoe_handle *h, cudaStream_t s, int *n);
 // rows_ub: upper bound on the rows (token, expert picks) this GPU's experts hold in the step, -1 if unknown; a small
 // bound sends a product with few tiles to the split-K kernels
-cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid, long rows_ub = -1);
+// gate: expert parallel only -- the up/gate product waits for the dispatched rows, the down product raises
+// "outputs ready" (see EpGate); null on one GPU
+struct EpGate;
+cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid, long rows_ub = -1,
+                                const EpGate *gate = nullptr);
 // The same two products on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles per pair).
 // split-K over a thread-block cluster of S CTAs (experts_sm100_splitk.cu); splitk_ways_*() pick S, 0 = use the
 // persistent kernels of experts_sm100.cu
 // m_tiles_ub: bound on the step's 128-row tiles, -1 if unknown
 int splitk_ways_up_gate(omoe_handle *h, long m_tiles_ub);
 int splitk_ways_down(omoe_handle *h, long m_tiles_ub);
-cudaError_t launch_up_gate_splitk(omoe_handle *h, cudaStream_t s, int S);
-cudaError_t launch_down_splitk(omoe_handle *h, cudaStream_t s, int S);
+cudaError_t launch_up_gate_splitk(omoe_handle *h, cudaStream_t s, int S, const EpGate *gate);
+cudaError_t launch_down_splitk(omoe_handle *h, cudaStream_t s, int S, const EpGate *gate);
 cudaError_t launch_experts_bf16_pair(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid);
 // Weight-streaming expert products for decode steps (T <= decode_tokens_threshold(), bf16).
 cudaError_t launch_experts_decode(omoe_handle *h, int T, cudaStream_t s, int *n, cudaEvent_t mid);
@@ -207,6 +212,21 @@ struct EpWait {
     unsigned long long timeout_ns;
 };
 
+// What ties an expert product to the expert-parallel exchange without launches of its own.  Wait side (the
+// up/gate product): the rows of source rank s have landed once wait_flags[s] >= *seq; tile_src_mask[mt], when
+// given, names the sources whose rows 128-row tile mt holds, so a tile starts as soon as ITS sources are in
+// (otherwise all sources are awaited before the first tile).  Signal side (the down product): the CTA that
+// finishes last stores *seq into slot `rank` of every rank's signal_flags array ("outputs ready").
+struct EpGate {
+    const uint32_t *wait_flags;      // this rank's flag_rows[world]; null = no wait
+    const uint32_t *tile_src_mask;   // [m tiles] bit s set = the tile holds rows of source rank s; may be null
+    uint32_t *const *signal_flags;   // device table [world] of the ranks' flag_out arrays; null = no signal
+    int32_t *ticket;                 // CTAs of the signalling kernel that have finished (left at 0)
+    const uint32_t *seq;             // device: sequence number of the running step
+    unsigned long long timeout_ns;
+    int world, rank;
+};
+
 // Bounded spin until *flag >= seq (acquire, system scope).  Returns false on
 // time-out or when the device error word is already set.
 __device__ __forceinline__ bool ep_wait_flag(const uint32_t *flag, uint32_t seq, unsigned long long timeout_ns,
@@ -226,6 +246,36 @@ __device__ __forceinline__ bool ep_wait_flag(const uint32_t *flag, uint32_t seq,
                 return false;
             }
         }
+    }
+}
+
+// Producer side of an EpGate: wait (bounded) until every source in `need` that has not been seen yet has
+// landed its rows, then order the tensor-memory-accelerator reads that follow behind the peers' stores.
+__device__ __forceinline__ bool ep_gate_wait(const EpGate &g, uint32_t need, uint32_t &seen, int32_t *dev_err) {
+    need &= ~seen;
+    if (need == 0) return true;
+    const uint32_t seq = *g.seq;
+    while (need) {
+        const int s = __ffs(need) - 1;
+        if (!ep_wait_flag(g.wait_flags + s, seq, g.timeout_ns, dev_err)) return false;
+        seen |= 1u << s;
+        need &= need - 1;
+    }
+    asm volatile("fence.proxy.async;" ::: "memory");
+    return true;
+}
+
+// Signal side of an EpGate, called by ONE thread per CTA after that CTA's output stores are complete (for
+// stores issued by other threads: after a __syncthreads() that follows their __threadfence_system()).
+__device__ __forceinline__ void ep_gate_signal(const EpGate &g, int n_ctas) {
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __threadfence_system();
+    if (atomicAdd(g.ticket, 1) == n_ctas - 1) {
+        __threadfence_system();
+        *g.ticket = 0;  // every CTA has arrived; ready for the next step
+        const uint32_t seq = *g.seq;
+        for (int q = 0; q < g.world; q++)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(g.signal_flags[q] + g.rank), "r"(seq) : "memory");
     }
 }
 

@@ -10,15 +10,19 @@
 // synchronisation happens inside a forward, and no collective library is used.
 //
 // One forward (sequence number seq) on every rank:
-//   1. router, scan                          (local)
-//   2. exchange kernel: publish my per-expert counts to every rank, wait for
-//      all rows of the count matrix, derive where my picks go on each owner
-//      (dst_base) and how the rows I receive are laid out (ex_* arrays)
+//   1. router                                 (local)
+//   2. scan + count exchange (one kernel): publish my per-expert counts to
+//      every rank, wait for all rows of the count matrix, derive where my picks
+//      go on each owner (dst_base) and how the rows I receive are laid out
+//      (ex_* arrays, and for every 128-row tile the set of ranks its rows come from)
 //   3. dispatch: rows -> owners' buffers, then "rows landed" flag to every rank
-//   4. wait kernel: all ranks' rows have landed here
-//   5. grouped expert products                (local)
-//   6. signal kernel: "outputs ready" flag to every rank
-//   7. combine: wait for all owners' flags, gather rows over NVLink
+//      (a decode step of <= 8 tokens does 1-3 in ONE launch)
+//   4. up/gate product: its producer thread waits, tile by tile, only for the
+//      ranks whose rows the tile holds, so tiles start while other rows are
+//      still in flight; no separate wait launch
+//   5. down product; the CTA that finishes last raises "outputs ready" on
+//      every rank; no separate signal launch
+//   6. combine: wait for all owners' flags, gather rows over NVLink
 // Flags carry the sequence number, so nothing is reset between forwards; the
 // count matrix is double-buffered by the parity of seq.  Every wait is bounded
 // and reports through the device error word instead of hanging.
@@ -27,18 +31,12 @@
 
 #include "ep.cuh"
 #include "backward.cuh"
+#include "route_small.cuh"
+#include "scan.cuh"
 
 namespace omoe {
 
 namespace {
-
-// Control block of one rank, written by its peers.  Lives in IPC-shared memory.
-struct EpCtl {
-    int32_t cnt[2][kMaxWorld][kMaxExperts];  // [parity][source rank][expert]
-    uint32_t flag_cnt[2][kMaxWorld];         // seq once source's count row is complete
-    uint32_t flag_rows[kMaxWorld];           // seq once source's rows have landed in my dispatch buffer
-    uint32_t flag_out[kMaxWorld];            // seq once owner's expert outputs are readable
-};
 
 struct EpState {
     EpCtl *ctl;                 // this rank's control block (device)
@@ -46,6 +44,7 @@ struct EpState {
     uint32_t **d_rows_flags;    // device [world]: &peer_ctl[q]->flag_rows[0]
     uint32_t **d_out_flags;     // device [world]: &peer_ctl[q]->flag_out[0]
     int32_t *ex_counts, *ex_poffsets, *ex_tile_expert;  // layout of the rows this rank receives
+    uint32_t *ex_tile_mask;     // [m tiles] bit s: the tile holds rows that source rank s sent
     void *peer_ptrs[kMaxWorld][5];  // opened IPC mappings (ctl, xp, yp, dyp, dxp), null for self
     void *dyp, *dxp;            // [rows_cap, d] gradient rows of the backward pass (peers write dyp, read dxp)
     void **d_dyp_table, **d_dxp_table;  // device [world]
@@ -63,87 +62,217 @@ __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// One block of 256 threads.
-__global__ void __launch_bounds__(256)
-ep_exchange_kernel(EpCtl *self, EpCtl *const *__restrict__ peers, const int32_t *__restrict__ counts, int W, int r,
-                   int E, int El, uint32_t *seq_ptr, int rows_cap, int32_t *__restrict__ dst_base,
-                   int32_t *__restrict__ ex_counts, int32_t *__restrict__ ex_poffsets,
-                   int32_t *__restrict__ ex_tile_expert, int max_tiles, int32_t *ticket, int32_t *dev_err,
-                   unsigned long long timeout_ns) {
-    __shared__ int32_t s_cnt[kMaxWorld][kMaxExperts];
-    __shared__ int32_t s_tot[kMaxExperts];
-    __shared__ int32_t s_rpoff[kMaxExperts + kMaxWorld];  // padded start of expert e in its owner's buffer
-    __shared__ int32_t s_mypoff[kMaxExperts + 1];
-    __shared__ int s_bad;
-    __shared__ uint32_t s_seq;
-    const int tid = threadIdx.x;
-    // a new step begins: this kernel is the first of the step to need the number, the later ones read it
-    if (tid == 0) { s_seq = *seq_ptr + 1u; *seq_ptr = s_seq; *ticket = 0; s_bad = 0; }
+// Shared memory of the count exchange.
+struct ExSmem {
+    int32_t cnt[kMaxWorld][kMaxExperts];
+    int32_t tot[kMaxExperts];
+    int32_t rpoff[kMaxExperts + kMaxWorld];  // padded start of expert e in its owner's buffer
+    int32_t mypoff[kMaxExperts + 1];
+    int32_t base[kMaxExperts];               // dst_base of this rank
+    int bad;
+    uint32_t seq;
+};
+
+// Arguments of the count exchange that do not change from step to step.
+struct ExArgs {
+    EpCtl *self;
+    EpCtl *const *peers;
+    int W, r, E, El;
+    uint32_t *seq_ptr;
+    int rows_cap;
+    int32_t *dst_base, *ex_counts, *ex_poffsets, *ex_tile_expert;
+    uint32_t *ex_tile_mask;
+    int max_tiles;
+    int32_t *ticket, *dev_err;
+    unsigned long long timeout_ns;
+};
+
+// The count exchange, by one block (any number of threads >= world).  A new step begins here: the sequence
+// number advances (this is the first piece of a step to need it, the later kernels read it).  Publishes this
+// rank's per-expert counts to every rank, waits (bounded) for all rows of the count matrix, and derives: where
+// this rank's picks of every expert start in the owner's buffer (dst_base; sm.base keeps a copy), and how the
+// rows this rank receives are laid out (ex_counts, ex_poffsets, ex_tile_expert, ex_tile_mask).  A step that
+// does not fit some owner's buffer is refused by every rank alike.  counts: this rank's counts [E] (global or
+// shared memory, complete and visible to the whole block on entry).
+__device__ void exchange_body(ExSmem &sm, const ExArgs &a, const int32_t *counts) {
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int W = a.W, r = a.r, E = a.E, El = a.El;
+    if (tid == 0) { sm.seq = *a.seq_ptr + 1u; *a.seq_ptr = sm.seq; *a.ticket = 0; sm.bad = 0; }
     __syncthreads();
-    const uint32_t seq = s_seq;
+    const uint32_t seq = sm.seq;
     const int par = seq & 1u;
     // publish my counts to every rank (my own included)
-    for (int i = tid; i < W * E; i += blockDim.x) {
+    for (int i = tid; i < W * E; i += nt) {
         int q = i / E, e = i % E;
-        peers[q]->cnt[par][r][e] = counts[e];
+        a.peers[q]->cnt[par][r][e] = counts[e];
     }
     __threadfence_system();
     __syncthreads();
-    if (tid < W) st_release_sys(&peers[tid]->flag_cnt[par][r], seq);
+    if (tid < W) st_release_sys(&a.peers[tid]->flag_cnt[par][r], seq);
     // wait for every source's row
     if (tid < W) {
-        if (!ep_wait_flag(&self->flag_cnt[par][tid], seq, timeout_ns, dev_err)) s_bad = 1;
+        if (!ep_wait_flag(&a.self->flag_cnt[par][tid], seq, a.timeout_ns, a.dev_err)) sm.bad = 1;
     }
     __syncthreads();
     __threadfence_system();
-    for (int i = tid; i < W * E; i += blockDim.x) {
+    for (int i = tid; i < W * E; i += nt) {
         int s = i / E, e = i % E;
-        s_cnt[s][e] = *(volatile int32_t *)&self->cnt[par][s][e];
+        sm.cnt[s][e] = *(volatile int32_t *)&a.self->cnt[par][s][e];
     }
     __syncthreads();
-    for (int e = tid; e < E; e += blockDim.x) {
+    for (int e = tid; e < E; e += nt) {
         int t = 0;
-        for (int s = 0; s < W; s++) t += s_cnt[s][e];
-        s_tot[e] = t;
+        for (int s = 0; s < W; s++) t += sm.cnt[s][e];
+        sm.tot[e] = t;
     }
     __syncthreads();
     if (tid < W) {  // thread q lays out owner q's buffer
         int q = tid, off = 0;
         for (int le = 0; le < El; le++) {
             int e = q * El + le;
-            s_rpoff[e] = off;
-            off += (s_tot[e] + kRowAlign - 1) / kRowAlign * kRowAlign;
+            sm.rpoff[e] = off;
+            off += (sm.tot[e] + kRowAlign - 1) / kRowAlign * kRowAlign;
         }
-        if (off > rows_cap) s_bad = 1;  // every rank sees the same matrix, so all of them refuse together
+        if (off > a.rows_cap) sm.bad = 1;  // every rank sees the same matrix, so all of them refuse together
         if (q == r) {
-            for (int le = 0; le < El; le++) s_mypoff[le] = s_rpoff[q * El + le];
-            s_mypoff[El] = off;
+            for (int le = 0; le < El; le++) sm.mypoff[le] = sm.rpoff[q * El + le];
+            sm.mypoff[El] = off;
         }
     }
     __syncthreads();
-    const bool bad = s_bad != 0;
-    if (bad && tid == 0) atomicOr(dev_err, kDevErrBounds);
-    for (int e = tid; e < E; e += blockDim.x) {
+    const bool bad = sm.bad != 0;
+    if (bad && tid == 0) atomicOr(a.dev_err, kDevErrBounds);
+    for (int e = tid; e < E; e += nt) {
         int before = 0;
-        for (int s = 0; s < r; s++) before += s_cnt[s][e];
+        for (int s = 0; s < r; s++) before += sm.cnt[s][e];
         // a refused step moves no row: the base is far below zero, so every position the dispatch derives from
         // it is negative, and the dispatch, combine and backward kernels skip rows with a negative position
-        dst_base[e] = bad ? kRefusedBase : s_rpoff[e] + before;
+        const int b = bad ? kRefusedBase : sm.rpoff[e] + before;
+        sm.base[e] = b;
+        a.dst_base[e] = b;
     }
-    for (int le = tid; le < El; le += blockDim.x) {
-        ex_counts[le] = bad ? 0 : s_tot[r * El + le];
-        ex_poffsets[le] = bad ? 0 : s_mypoff[le];
+    for (int le = tid; le < El; le += nt) {
+        a.ex_counts[le] = bad ? 0 : sm.tot[r * El + le];
+        a.ex_poffsets[le] = bad ? 0 : sm.mypoff[le];
     }
-    if (tid == 0) ex_poffsets[El] = bad ? 0 : s_mypoff[El];
-    const int n_tiles = bad ? 0 : s_mypoff[El] / kRowAlign;
-    for (int i = tid; i < max_tiles; i += blockDim.x) {
+    if (tid == 0) a.ex_poffsets[El] = bad ? 0 : sm.mypoff[El];
+    const int n_tiles = bad ? 0 : sm.mypoff[El] / kRowAlign;
+    for (int i = tid; i < a.max_tiles; i += nt) {
         int ex = -1;
+        uint32_t mask = 0;
         if (i < n_tiles) {
-            int row = i * kRowAlign;
+            const int row = i * kRowAlign;
             ex = 0;
-            while (ex + 1 < El && s_mypoff[ex + 1] <= row) ex++;
+            while (ex + 1 < El && sm.mypoff[ex + 1] <= row) ex++;
+            // rows [lo, lo + 128) of the expert's segment; source s holds [before_s, before_s + cnt_s) of it
+            const int lo = row - sm.mypoff[ex], hi = lo + kRowAlign;
+            int before = 0;
+            for (int s = 0; s < W; s++) {
+                const int c = sm.cnt[s][r * El + ex];
+                if (c > 0 && before < hi && before + c > lo) mask |= 1u << s;
+                before += c;
+            }
         }
-        ex_tile_expert[i] = ex;
+        a.ex_tile_expert[i] = ex;
+        a.ex_tile_mask[i] = mask;
+    }
+    __syncthreads();
+}
+
+// Scan of the router's per-block histograms and the count exchange in one launch (one block of 1024 threads).
+__global__ void __launch_bounds__(1024)
+ep_scan_exchange_kernel(const int32_t *__restrict__ block_counts, int32_t *__restrict__ block_base, int n_blocks,
+                        int32_t *__restrict__ counts, int32_t *__restrict__ offsets, int32_t *__restrict__ poffsets,
+                        int32_t *__restrict__ tile_expert, const ExArgs a) {
+    __shared__ ExSmem sm;
+    __shared__ int32_t s_cnt[kMaxExperts];
+    __shared__ int32_t s_poff[kMaxExperts + 1];
+    // the local tile table is not used with expert parallelism (the expert kernels read the ex_* arrays)
+    scan_body(block_counts, block_base, n_blocks, a.E, counts, offsets, poffsets, tile_expert, 0, s_cnt, s_poff);
+    __syncthreads();
+    exchange_body(sm, a, s_cnt);
+}
+
+// A decode step under expert parallelism in ONE launch: block t computes token t's logits and picks (as the
+// one-GPU route_small_kernel does); the block that finishes last ranks the picks, runs the count exchange,
+// stores every token row straight into the dispatch buffer of the rank that owns the pick's expert (peer
+// stores) and raises "rows have landed" on every rank.  T <= 8 tokens on this rank (0 is allowed: the grid is
+// one block that only takes part in the exchange).
+template <int PL, typename XT>
+__global__ void __launch_bounds__(256)
+route_small_ep_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, const float *__restrict__ bias, int T,
+                      int d, int k, int renorm, float *__restrict__ logits, int32_t *__restrict__ topk_idx,
+                      float *__restrict__ topk_w, int32_t *__restrict__ counts, int32_t *__restrict__ offsets,
+                      int32_t *__restrict__ pos, void *const *__restrict__ row_table, uint32_t *const *rows_flags,
+                      int32_t *ticket_blocks, const ExArgs a) {
+    using namespace small;
+    __shared__ ExSmem sm;
+    __shared__ float sl[kMaxExperts];
+    __shared__ int32_t s_idx[kSmallMaxPicks], s_rank[kSmallMaxPicks], s_pos[kSmallMaxPicks];
+    __shared__ int32_t s_cnt[kMaxExperts];
+    __shared__ int s_last;
+    const int tid = threadIdx.x;
+    const int t = blockIdx.x;
+    const int E = a.E;
+    if (t < T) token_logits_topk<PL, XT>(x, w_r, bias, t, d, E, k, renorm, logits, topk_idx, topk_w, sl);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(ticket_blocks, 1) == (int)gridDim.x - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (tid == 0) *ticket_blocks = 0;  // ready for the next step
+    const int n = T * k;
+    if (tid < n) s_idx[tid] = __ldcg(topk_idx + tid);
+    __syncthreads();
+    rank_picks(n, E, s_idx, s_rank, s_cnt);
+    __syncthreads();
+    if (tid == 0) {
+        int off = 0;
+        for (int e = 0; e < E; e++) {
+            counts[e] = s_cnt[e];
+            offsets[e] = off;
+            off += s_cnt[e];
+        }
+        offsets[E] = off;
+    }
+    exchange_body(sm, a, s_cnt);
+    if (tid < n) {
+        int p = sm.base[s_idx[tid]] + s_rank[tid];
+        if (p >= a.rows_cap) {  // cannot follow from an accepted layout; reported, and the row is not moved
+            atomicOr(a.dev_err, kDevErrBounds);
+            p = -1;
+        } else if (p < 0) {
+            p = -1;  // refused step
+        }
+        s_pos[tid] = p;
+        pos[tid] = p;
+    }
+    __syncthreads();
+    // copy the token rows to their k places in the owners' buffers (bf16 rows out; fp32 rows are converted)
+    const int vec = d / 8;
+    for (int i = tid; i < T * vec; i += blockDim.x) {
+        const int tt = i / vec, c = (i % vec) * 8;
+        float v[8];
+        ldx8(x + (size_t)tt * d + c, v);
+        uint4 o;
+        o.x = pack_bf16(v[0], v[1]);
+        o.y = pack_bf16(v[2], v[3]);
+        o.z = pack_bf16(v[4], v[5]);
+        o.w = pack_bf16(v[6], v[7]);
+        for (int j = 0; j < k; j++) {
+            const int p = s_pos[tt * k + j];
+            if (p < 0) continue;
+            __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(row_table[s_idx[tt * k + j] / a.El]);
+            *reinterpret_cast<uint4 *>(dst + (size_t)p * d + c) = o;
+        }
+    }
+    // the rows are visible system-wide before the flag is
+    __threadfence_system();
+    __syncthreads();
+    if (tid < a.W) {
+        __threadfence_system();
+        st_release_sys(rows_flags[tid] + a.r, sm.seq);
     }
 }
 
@@ -183,7 +312,8 @@ int ep_create(omoe_handle *h) {
         (e = cudaMalloc(&st->dyp, grad_bytes)) != cudaSuccess || (e = cudaMalloc(&st->dxp, grad_bytes)) != cudaSuccess ||
         (e = cudaMalloc(&st->ex_counts, sizeof(int32_t) * El)) != cudaSuccess ||
         (e = cudaMalloc(&st->ex_poffsets, sizeof(int32_t) * (El + 1))) != cudaSuccess ||
-        (e = cudaMalloc(&st->ex_tile_expert, sizeof(int32_t) * (h->rows_cap / kRowAlign))) != cudaSuccess)
+        (e = cudaMalloc(&st->ex_tile_expert, sizeof(int32_t) * (h->rows_cap / kRowAlign))) != cudaSuccess ||
+        (e = cudaMalloc(&st->ex_tile_mask, sizeof(uint32_t) * (h->rows_cap / kRowAlign))) != cudaSuccess)
         return ep_fail(h, OMOE_ERR_NOMEM, "cudaMalloc(expert-parallel state)", e);
     cudaMemset(st->d_seq, 0, sizeof(uint32_t));
     cudaMemset(st->dyp, 0, grad_bytes);
@@ -207,7 +337,7 @@ void ep_destroy(omoe_handle *h) {
             if (st->peer_ptrs[q][i]) cudaIpcCloseMemHandle(st->peer_ptrs[q][i]);
     void *ptrs[] = {st->ctl, st->d_ctl_table, st->d_rows_flags, st->d_out_flags, st->d_seq, st->d_dyp_table,
                     st->d_dxp_table, st->dyp, st->dxp, st->ex_counts, st->ex_poffsets,
-                    st->ex_tile_expert};
+                    st->ex_tile_expert, st->ex_tile_mask};
     for (void *p : ptrs)
         if (p) cudaFree(p);
     free(st);
@@ -346,6 +476,53 @@ int ep_connect_local(omoe_handle **hs, int world) {
     return OMOE_OK;
 }
 
+namespace {
+
+ExArgs exchange_args(omoe_handle *h, EpState *st) {
+    ExArgs a;
+    a.self = st->ctl;
+    a.peers = st->d_ctl_table;
+    a.W = h->cfg.world;
+    a.r = h->cfg.rank;
+    a.E = h->cfg.n_experts;
+    a.El = h->e_local;
+    a.seq_ptr = st->d_seq;
+    a.rows_cap = (int)h->rows_cap;
+    a.dst_base = h->dst_base;
+    a.ex_counts = st->ex_counts;
+    a.ex_poffsets = st->ex_poffsets;
+    a.ex_tile_expert = st->ex_tile_expert;
+    a.ex_tile_mask = st->ex_tile_mask;
+    a.max_tiles = (int)(h->rows_cap / kRowAlign);
+    a.ticket = h->ticket;
+    a.dev_err = h->dev_err;
+    a.timeout_ns = st->timeout_ns;
+    return a;
+}
+
+template <typename XT>
+cudaError_t launch_route_small_ep(omoe_handle *h, EpState *st, const XT *x, int T, cudaStream_t s) {
+    const ExArgs a = exchange_args(h, st);
+    const int E = h->cfg.n_experts;
+    const int blocks = T > 0 ? T : 1;
+#define OMOE_RSE(PLV)                                                                                              \
+    route_small_ep_kernel<PLV, XT><<<blocks, 256, 0, s>>>(x, h->w_router, h->router_bias, T, h->cfg.d_model,       \
+                                                          h->cfg.top_k, h->cfg.renormalize, h->logits, h->topk_idx, \
+                                                          h->topk_w, h->counts, h->offsets, h->pos, h->d_row_table, \
+                                                          st->d_rows_flags, h->ticket, a)
+    if (E <= 32) OMOE_RSE(1);
+    else if (E <= 64) OMOE_RSE(2);
+    else OMOE_RSE(4);
+#undef OMOE_RSE
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// One forward of this rank.  Launches (bf16 layer, inference): router, scan + count exchange, dispatch (raises
+// "rows landed"), up/gate product (its producer waits for the rows, tile by tile), down product (its last CTA
+// raises "outputs ready"), combine (waits for the owners' flags) -- six; a decode step of at most 8 tokens
+// takes one launch for everything before the products -- four.
 int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype, const void *resid, int T,
                cudaStream_t s) {
     EpState *st = static_cast<EpState *>(h->ep);
@@ -353,11 +530,14 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
         snprintf(h->err, sizeof(h->err), "omoe_forward: call omoe_ep_export / omoe_ep_import on every rank first");
         return OMOE_ERR_STATE;
     }
-    const int W = h->cfg.world, r = h->cfg.rank, E = h->cfg.n_experts, El = h->e_local;
+    const int W = h->cfg.world, r = h->cfg.rank;
     uint32_t *const seq = st->d_seq;  // advanced on the device by the count exchange
     int n = 0;
     cudaError_t e = cudaSuccess;
     const bool prof = h->profiling;
+    const bool bf16 = h->cfg.compute_dtype == OMOE_BF16;
+    // OMOE_EP_UNFUSED=1: separate wait / signal launches around the products and no one-launch decode routing
+    static const bool unfused = getenv("OMOE_EP_UNFUSED") && atoi(getenv("OMOE_EP_UNFUSED")) != 0;
 #define MARK(i) do { if (prof) cudaEventRecord(h->ev[i], s); } while (0)
 #define TRY(expr)                                                                      \
     do {                                                                               \
@@ -365,44 +545,66 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
         if (e != cudaSuccess) return ep_fail(h, OMOE_ERR_CUDA, #expr, e);              \
     } while (0)
     MARK(0);
-    if (T > 0) {
-        TRY(launch_router(h, x, x_dtype, T, s, &n));
-    }
-    MARK(1);
-    TRY(launch_scan(h, T, s, &n));  // T == 0: zero blocks, all counts zero
-    MARK(2);
-    ep_exchange_kernel<<<1, 256, 0, s>>>(st->ctl, st->d_ctl_table, h->counts, W, r, E, El, seq, (int)h->rows_cap,
-                                         h->dst_base, st->ex_counts, st->ex_poffsets, st->ex_tile_expert,
-                                         (int)(h->rows_cap / kRowAlign), h->ticket, h->dev_err, st->timeout_ns);
-    TRY(cudaGetLastError());
-    n++;
-    EpSignal sig{st->d_rows_flags, W, r, seq};
-    if (T > 0) {
-        TRY(launch_permute(h, x, x_dtype, T, s, &n, &sig));
+    if (bf16 && !unfused && T <= route_small_max_tokens()) {
+        if (T > 0 && (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return ep_fail(h, OMOE_ERR_CUDA, "x", cudaErrorMisalignedAddress);
+        if (x_dtype == OMOE_F32) TRY(launch_route_small_ep<float>(h, st, static_cast<const float *>(x), T, s));
+        else TRY(launch_route_small_ep<__nv_bfloat16>(h, st, static_cast<const __nv_bfloat16 *>(x), T, s));
+        n++;
+        MARK(1);
+        MARK(2);
     } else {
-        ep_signal_kernel<<<1, 32, 0, s>>>(st->d_rows_flags, W, r, seq);
+        if (T > 0) TRY(launch_router(h, x, x_dtype, T, s, &n));
+        MARK(1);
+        // T == 0: zero router blocks, all counts zero
+        ep_scan_exchange_kernel<<<1, 1024, 0, s>>>(h->block_counts, h->block_base, ceil_div(T, h->tokens_per_block),
+                                                   h->counts, h->offsets, h->poffsets, h->tile_expert,
+                                                   exchange_args(h, st));
+        TRY(cudaGetLastError());
+        n++;
+        MARK(2);
+        EpSignal sig{st->d_rows_flags, W, r, seq};
+        if (T > 0) {
+            TRY(launch_permute(h, x, x_dtype, T, s, &n, &sig));
+        } else {
+            ep_signal_kernel<<<1, 32, 0, s>>>(st->d_rows_flags, W, r, seq);
+            TRY(cudaGetLastError());
+            n++;
+        }
+    }
+    MARK(3);
+    const bool gated = bf16 && !bw_training(h) && !unfused;
+    if (!gated) {
+        ep_wait_kernel<<<1, 32, 0, s>>>(st->ctl->flag_rows, W, seq, h->dev_err, st->timeout_ns);
         TRY(cudaGetLastError());
         n++;
     }
-    MARK(3);
-    ep_wait_kernel<<<1, 32, 0, s>>>(st->ctl->flag_rows, W, seq, h->dev_err, st->timeout_ns);
-    TRY(cudaGetLastError());
-    n++;
     MARK(4);
     if (bw_training(h)) {
         TRY(bw_forward_experts(h, T, s, &n));  // keeps g and u for the backward pass
         MARK(5);
-    } else if (h->cfg.compute_dtype == OMOE_BF16) {
+    } else if (bf16) {
+        EpGate gate{};
+        gate.wait_flags = st->ctl->flag_rows;
+        gate.tile_src_mask = st->ex_tile_mask;
+        gate.signal_flags = st->d_out_flags;
+        gate.ticket = h->ticket2;
+        gate.seq = seq;
+        gate.timeout_ns = st->timeout_ns;
+        gate.world = W;
+        gate.rank = r;
         // rows can come from every rank's tokens; a rank's step holds at most t_max of them
-        TRY(launch_experts_bf16(h, s, &n, prof ? h->ev[5] : nullptr, (long)h->cfg.t_max * W * h->cfg.top_k));
+        TRY(launch_experts_bf16(h, s, &n, prof ? h->ev[5] : nullptr, (long)h->cfg.t_max * W * h->cfg.top_k,
+                                gated ? &gate : nullptr));
     } else {
         TRY(launch_experts_f32(h, s, &n));
         MARK(5);
     }
     MARK(6);
-    ep_signal_kernel<<<1, 32, 0, s>>>(st->d_out_flags, W, r, seq);
-    TRY(cudaGetLastError());
-    n++;
+    if (!gated) {
+        ep_signal_kernel<<<1, 32, 0, s>>>(st->d_out_flags, W, r, seq);
+        TRY(cudaGetLastError());
+        n++;
+    }
     MARK(7);
     EpWait wt{st->ctl->flag_out, W, seq, st->timeout_ns};
     if (T > 0) {

@@ -5,6 +5,14 @@
 
 namespace omoe {
 
+// Control block of one rank, written by its peers.  Lives in memory the other ranks have mapped.
+struct EpCtl {
+    int32_t cnt[2][kMaxWorld][kMaxExperts];  // [parity][source rank][expert]
+    uint32_t flag_cnt[2][kMaxWorld];         // seq once source's count row is complete
+    uint32_t flag_rows[kMaxWorld];           // seq once source's rows have landed in my dispatch buffer
+    uint32_t flag_out[kMaxWorld];            // seq once owner's expert outputs are readable
+};
+
 int ep_create(omoe_handle *h);   // allocates the control block and receive-side layout arrays
 int ep_export(omoe_handle *h, void *blob);
 int ep_import(omoe_handle *h, const void *all_blobs);

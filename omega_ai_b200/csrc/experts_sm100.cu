@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                     const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_out, int n_out,
                     int K, const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ poffsets,
-                    int E, int kband, int32_t *dev_err) {
+                    int E, int kband, int32_t *dev_err, const EpGate gate) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;  // stages need 1024-byte alignment for the swizzle
@@ -118,9 +118,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             // the expert of the next tile is fetched while the current tile streams
             int e_next = (int)blockIdx.x < total ? tile_expert[tile_coord(blockIdx.x, num_m_tiles, n_tiles, kband).mt] : 0;
+            uint32_t seen = 0;  // expert parallel: sources whose rows are known to have landed
             for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
                 TileCoord tc = tile_coord(tile, num_m_tiles, n_tiles, kband);
                 const int e = e_next;
+                if (gate.wait_flags != nullptr) {
+                    // the rows of this tile come from the ranks named in its mask; wait for those only
+                    const uint32_t need = gate.tile_src_mask ? gate.tile_src_mask[tc.mt] : ((1u << gate.world) - 1u);
+                    if (!ep_gate_wait(gate, need, seen, dev_err)) { *abort_flag = 1; ok = false; break; }
+                }
                 if (tile + (int)gridDim.x < total)
                     e_next = tile_expert[tile_coord(tile + gridDim.x, num_m_tiles, n_tiles, kband).mt];
                 const int row_a = tc.mt * BLOCK_M;
@@ -136,6 +142,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
+            // Expert parallel: the product that follows overwrites the output rows of the previous step, which a
+            // rank may still be gathering until it has sent this step's rows -- so this kernel does not end
+            // before EVERY rank has raised its flag, also those that sent this GPU nothing.
+            if (ok && gate.wait_flags != nullptr) ep_gate_wait(gate, (1u << gate.world) - 1u, seen, dev_err);
             if (!ok) {
                 // let copies that were already issued land before the CTA retires
                 unsigned long long t0 = globaltimer_ns();
@@ -253,7 +263,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             if (++as == kAccStages) { as = 0; aphase ^= 1u; }
         }
-        if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            // expert parallel: this CTA's output rows are complete; the last CTA tells every rank
+            if (gate.signal_flags != nullptr) ep_gate_signal(gate, (int)gridDim.x);
+        }
     }
 
     tc_fence_before();
@@ -345,13 +359,23 @@ cudaError_t launch_grouped_plain(omoe_handle *h, cudaStream_t s, const CUtensorM
     if (e != cudaSuccess) return e;
     static int band = getenv("OMOE_BAND_DOWN") ? atoi(getenv("OMOE_BAND_DOWN")) : 16;
     grouped_gemm_kernel<false><<<dim3(h->sm_count), dim3(kThreads), kSmemBytes, s>>>(
-        a, b, b, c, n_out, K, h->ex_tile_expert, h->ex_poffsets, h->e_local, band, h->dev_err);
+        a, b, b, c, n_out, K, h->ex_tile_expert, h->ex_poffsets, h->e_local, band, h->dev_err, EpGate{});
     return cudaGetLastError();
 }
 
-cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid, long rows_ub) {
+cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid, long rows_ub,
+                                const EpGate *gate) {
     static int use_pair = getenv("OMOE_PAIR") ? atoi(getenv("OMOE_PAIR")) : 0;
-    if (use_pair) return launch_experts_bf16_pair(h, s, n, mid);
+    if (use_pair && gate == nullptr) return launch_experts_bf16_pair(h, s, n, mid);
+    // the up/gate product takes the wait side of the gate, the down product the signal side
+    EpGate g_up{}, g_dn{};
+    if (gate != nullptr) {
+        g_up = *gate;
+        g_up.signal_flags = nullptr;
+        g_dn = *gate;
+        g_dn.wait_flags = nullptr;
+        g_dn.tile_src_mask = nullptr;
+    }
     {
         cudaError_t e0 = set_smem_attrs();
         if (e0 != cudaSuccess) return e0;
@@ -371,24 +395,24 @@ cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEven
     const int s_up = splitk_ways_up_gate(h, m_tiles_ub), s_dn = splitk_ways_down(h, m_tiles_ub);
     cudaError_t e;
     if (s_up > 0) {
-        e = launch_up_gate_splitk(h, s, s_up);
+        e = launch_up_gate_splitk(h, s, s_up, gate ? &g_up : nullptr);
     } else {
         grouped_gemm_kernel<true><<<grid, block, kSmemBytes, s>>>(
             h->maps.a_x, h->maps.b_gate, h->maps.b_up, h->maps.a_h, dff, d,
-            h->ex_tile_expert, h->ex_poffsets, h->e_local, band_up, h->dev_err);
+            h->ex_tile_expert, h->ex_poffsets, h->e_local, band_up, h->dev_err, g_up);
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) return e;
     (*n)++;
     if (mid) cudaEventRecord(mid, s);
     if (s_dn > 0) {
-        e = launch_down_splitk(h, s, s_dn);
+        e = launch_down_splitk(h, s, s_dn, gate ? &g_dn : nullptr);
         if (e == cudaSuccess) (*n)++;
         return e;
     }
     grouped_gemm_kernel<false><<<grid, block, kSmemBytes, s>>>(
         h->maps.a_h, h->maps.b_down, h->maps.b_down, h->maps.c_y, d, dff,
-        h->ex_tile_expert, h->ex_poffsets, h->e_local, band_dn, h->dev_err);
+        h->ex_tile_expert, h->ex_poffsets, h->e_local, band_dn, h->dev_err, g_dn);
     e = cudaGetLastError();
     if (e == cudaSuccess) (*n)++;
     return e;

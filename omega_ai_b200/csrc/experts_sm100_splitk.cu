@@ -87,7 +87,7 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
                            const __grid_constant__ CUtensorMap map_b0,
                            const __grid_constant__ CUtensorMap map_b1, __nv_bfloat16 *__restrict__ out, int n_out,
                            int K, const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ poffsets,
-                           const int32_t *__restrict__ counts, int E, int32_t *dev_err) {
+                           const int32_t *__restrict__ counts, int E, int32_t *dev_err, const EpGate gate) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;  // stages need 1024-byte alignment for the swizzle
@@ -147,6 +147,7 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     int stage = 0;
     uint32_t phase = 0, tphase = 0;
     bool ok = true;
+    uint32_t seen = 0;  // expert parallel: sources whose rows are known to have landed (producer thread)
 
     for (int tile = cid; tile < total; tile += ncl) {
         const int mt = tile % num_m_tiles, nt = tile / num_m_tiles;  // row tiles fastest: a weight tile is fetched once
@@ -163,7 +164,11 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
                 const int row_a = mt * BLOCK_M;
                 const int row_b0 = e * n_out + nt * n_tile_w;
                 const int row_b1 = SWIGLU ? row_b0 : row_b0 + 128;
-                for (int kb = kb0; kb < kb1; kb++) {
+                if (gate.wait_flags != nullptr) {
+                    const uint32_t need = gate.tile_src_mask ? gate.tile_src_mask[mt] : ((1u << gate.world) - 1u);
+                    if (!ep_gate_wait(gate, need, seen, dev_err)) { *abort_flag = 1; ok = false; }
+                }
+                for (int kb = kb0; ok && kb < kb1; kb++) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, dev_err)) { ok = false; break; }
                     const uint32_t sa = base + stage * stage_bytes;
                     mbar_expect_tx(full_bar(stage), stage_bytes);
@@ -252,6 +257,13 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
         cluster_barrier();  // nobody reads this CTA's partial tile or accumulator any more
     }
 
+    // Expert parallel, wait side: the product that follows overwrites the output rows of the previous step, which
+    // a rank may still be gathering until it has sent this step's rows -- so this kernel does not end before
+    // EVERY rank has raised its flag, also those that sent this GPU nothing.
+    if (gate.wait_flags != nullptr && warp == 0 && lane == 0 && ok)
+        ep_gate_wait(gate, (1u << gate.world) - 1u, seen, dev_err);
+    // signal side: every thread's output stores are ordered system-wide before the CTA reports in
+    if (gate.signal_flags != nullptr) __threadfence_system();
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -259,6 +271,7 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColsK)
                      : "memory");
     }
+    if (gate.signal_flags != nullptr && threadIdx.x == 0) ep_gate_signal(gate, (int)gridDim.x);
 }
 
 template <bool SWIGLU>
@@ -297,7 +310,8 @@ cudaError_t prepare_splitk(omoe_handle *h, int S, cudaLaunchConfig_t *cfg, cudaL
 
 template <bool SWIGLU>
 cudaError_t launch_splitk(omoe_handle *h, cudaStream_t s, int S, const CUtensorMap &a, const CUtensorMap &a32,
-                          const CUtensorMap &b0, const CUtensorMap &b1, void *out, int n_out, int K) {
+                          const CUtensorMap &b0, const CUtensorMap &b1, void *out, int n_out, int K,
+                          const EpGate *gate) {
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute at;
     int clusters = 0;
@@ -306,7 +320,8 @@ cudaError_t launch_splitk(omoe_handle *h, cudaStream_t s, int S, const CUtensorM
     cfg.stream = s;
     return cudaLaunchKernelEx(&cfg, grouped_gemm_splitk_kernel<SWIGLU>, a, a32, b0, b1,
                               static_cast<__nv_bfloat16 *>(out), n_out, K, (const int32_t *)h->ex_tile_expert,
-                              (const int32_t *)h->ex_poffsets, (const int32_t *)h->ex_counts, h->e_local, h->dev_err);
+                              (const int32_t *)h->ex_poffsets, (const int32_t *)h->ex_counts, h->e_local, h->dev_err,
+                              gate ? *gate : EpGate{});
 }
 
 // Number of CTAs to share one tile of a product with `tiles_ub` tiles at most and `num_kb` blocks of K:
@@ -344,14 +359,14 @@ int splitk_ways_down(omoe_handle *h, long m_tiles_ub) {
                               (h->cfg.d_ff + BLOCK_K - 1) / BLOCK_K);
 }
 
-cudaError_t launch_up_gate_splitk(omoe_handle *h, cudaStream_t s, int S) {
+cudaError_t launch_up_gate_splitk(omoe_handle *h, cudaStream_t s, int S, const EpGate *gate) {
     return launch_splitk<true>(h, s, S, h->maps.a_x, h->maps.a_x32, h->maps.b_gate, h->maps.b_up, h->hbuf,
-                               h->cfg.d_ff, h->cfg.d_model);
+                               h->cfg.d_ff, h->cfg.d_model, gate);
 }
 
-cudaError_t launch_down_splitk(omoe_handle *h, cudaStream_t s, int S) {
+cudaError_t launch_down_splitk(omoe_handle *h, cudaStream_t s, int S, const EpGate *gate) {
     return launch_splitk<false>(h, s, S, h->maps.a_h, h->maps.a_h32, h->maps.b_down, h->maps.b_down, h->yp,
-                                h->cfg.d_model, h->cfg.d_ff);
+                                h->cfg.d_model, h->cfg.d_ff, gate);
 }
 
 }  // namespace omoe

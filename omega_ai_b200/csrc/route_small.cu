@@ -9,37 +9,13 @@
 // three-kernel path; the logits follow the same fixed reduction tree, so the
 // routing stays bit-exact.  Single GPU only (expert-parallel steps need the
 // count exchange between the two halves).
-#include "common.cuh"
-#include "router_common.cuh"
+#include "route_small.cuh"
 
 namespace omoe {
 
 namespace {
 
-constexpr int kSmallMaxTokens = 8;
-constexpr int kSmallMaxPicks = kSmallMaxTokens * kMaxTopK;  // 128
-
-__device__ __forceinline__ void ldx8(const float *p, float (&v)[8]) {
-    float4 a = __ldg(reinterpret_cast<const float4 *>(p));
-    float4 b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-
-__device__ __forceinline__ void ldx8(const __nv_bfloat16 *p, float (&v)[8]) {
-    uint4 r = __ldg(reinterpret_cast<const uint4 *>(p));
-    uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t *>(&v);
-}
+using namespace small;
 
 template <int PL, typename XT>
 __global__ void __launch_bounds__(256)
@@ -55,52 +31,7 @@ route_small_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, cons
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int t = blockIdx.x;
 
-    // ---- logits of token t: warp w takes experts w, w+8, ...; reduction tree as in router.cu ----
-    const XT *xr = x + (size_t)t * d;
-    for (int e = warp; e < E; e += 8) {
-        const float *wr = w_r + (size_t)e * d;
-        float acc_even = 0.f, acc_odd = 0.f;  // the two chains of the reduction rule
-        for (int i0 = lane * 8; i0 < d; i0 += 4 * 256) {
-            float xv[4][8], wv[4][8];
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int i = i0 + u * 256;
-                if (i < d) {
-                    ldx8(xr + i, xv[u]);
-                    ldx8(wr + i, wv[u]);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                if (i0 + u * 256 < d) {
-#pragma unroll
-                    for (int j = 0; j < 8; j += 2) {
-                        acc_even = fmaf(xv[u][j], wv[u][j], acc_even);
-                        acc_odd = fmaf(xv[u][j + 1], wv[u][j + 1], acc_odd);
-                    }
-                }
-            }
-        }
-        float acc = acc_even + acc_odd;
-#pragma unroll
-        for (int m = 16; m >= 1; m >>= 1) acc = acc + __shfl_xor_sync(0xffffffffu, acc, m);
-        if (lane == 0) {
-            float v = acc;
-            if (bias != nullptr) v = v + __ldg(bias + e);
-            sl[e] = v;
-            logits[(size_t)t * E + e] = v;
-        }
-    }
-    __syncthreads();
-    if (warp == 0) {
-        int my_e;
-        float my_w;
-        warp_softmax_topk<PL>(sl, E, k, renorm, lane, my_e, my_w);
-        if (lane < k) {
-            topk_idx[(size_t)t * k + lane] = my_e;
-            topk_w[(size_t)t * k + lane] = my_w;
-        }
-    }
+    token_logits_topk<PL, XT>(x, w_r, bias, t, d, E, k, renorm, logits, topk_idx, topk_w, sl);
     // ---- the block that finishes last does the scan and the dispatch ----
     __threadfence();
     __syncthreads();
@@ -111,17 +42,7 @@ route_small_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, cons
     const int n = T * k;
     if (tid < n) s_idx[tid] = __ldcg(topk_idx + tid);
     __syncthreads();
-    for (int e = warp; e < E; e += 8) {
-        int base = 0;
-        for (int c = 0; c < n; c += 32) {
-            const int f = c + lane;
-            const int v = (f < n) ? s_idx[f] : -1;
-            const uint32_t m = __ballot_sync(0xffffffffu, v == e);
-            if (v == e) s_rank[f] = base + __popc(m & ((1u << lane) - 1u));
-            base += __popc(m);
-        }
-        if (lane == 0) s_cnt[e] = base;
-    }
+    rank_picks(n, E, s_idx, s_rank, s_cnt);
     __syncthreads();
     if (tid == 0) {
         int off = 0, poff = 0;
