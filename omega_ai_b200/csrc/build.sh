@@ -8,7 +8,7 @@ NVCC=${NVCC:-/usr/local/cuda/bin/nvcc}
 OUT=${OMOE_OUT:-../libomoe.so}
 OBJDIR=${OMOE_OBJDIR:-build}
 FLAGS="-gencode arch=compute_100a,code=sm_100a -O3 -lineinfo -std=c++17 -Xcompiler -fPIC -Xcompiler -fvisibility=hidden ${OMOE_NVCC_EXTRA}"
-SRCS="api.cu rmsnorm.cu router.cu route_small.cu permute.cu combine.cu experts_f32.cu experts_sm100.cu experts_sm100_pair.cu experts_sm100_splitk.cu experts_sm100_wgrad.cu backward.cu experts_decode.cu ep.cu"
+SRCS="api.cu rmsnorm.cu router.cu route_small.cu permute.cu combine.cu experts_f32.cu experts_sm100.cu experts_sm100_splitk.cu experts_sm100_wgrad.cu backward.cu experts_decode.cu ep.cu"
 mkdir -p "$OBJDIR"
 # a changed flag set rebuilds everything
 echo "$FLAGS" > "$OBJDIR/flags.new"

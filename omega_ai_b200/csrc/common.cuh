@@ -176,7 +176,6 @@ cudaError_t launch_experts_f32(omoe_handle *h, cudaStream_t s, int *n);
 struct EpGate;
 cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid, long rows_ub = -1,
                                 const EpGate *gate = nullptr);
-// The same two products on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles per pair).
 // split-K over a thread-block cluster of S CTAs (experts_sm100_splitk.cu); splitk_ways_*() pick S, 0 = use the
 // persistent kernels of experts_sm100.cu
 // m_tiles_ub: bound on the step's 128-row tiles, -1 if unknown
@@ -184,7 +183,6 @@ int splitk_ways_up_gate(omoe_handle *h, long m_tiles_ub);
 int splitk_ways_down(omoe_handle *h, long m_tiles_ub);
 cudaError_t launch_up_gate_splitk(omoe_handle *h, cudaStream_t s, int S, const EpGate *gate);
 cudaError_t launch_down_splitk(omoe_handle *h, cudaStream_t s, int S, const EpGate *gate);
-cudaError_t launch_experts_bf16_pair(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid);
 // Weight-streaming expert products for decode steps (T <= decode_tokens_threshold(), bf16).
 cudaError_t launch_experts_decode(omoe_handle *h, int T, cudaStream_t s, int *n, cudaEvent_t mid);
 int decode_tokens_threshold();

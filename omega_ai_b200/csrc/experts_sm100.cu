@@ -365,8 +365,6 @@ cudaError_t launch_grouped_plain(omoe_handle *h, cudaStream_t s, const CUtensorM
 
 cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid, long rows_ub,
                                 const EpGate *gate) {
-    static int use_pair = getenv("OMOE_PAIR") ? atoi(getenv("OMOE_PAIR")) : 0;
-    if (use_pair && gate == nullptr) return launch_experts_bf16_pair(h, s, n, mid);
     // the up/gate product takes the wait side of the gate, the down product the signal side
     EpGate g_up{}, g_dn{};
     if (gate != nullptr) {

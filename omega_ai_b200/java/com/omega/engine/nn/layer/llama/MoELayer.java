@@ -50,6 +50,10 @@ public class MoELayer extends Layer {
     private long handle;
     // experts packed contiguously for omoe_set_weights: [E,dff,d], [E,dff,d], [E,d,dff]
     private Tensor packedGate, packedUp, packedDown;
+    // network.train_time at the last syncWeights(): an optimizer that walks the network's parameter list
+    // (putParamters below) changes the FullyLayer weights without calling update() here, so the native copies
+    // are refreshed at the start of the first forward after the network's step counter has moved
+    private int syncedTrainTime = -1;
 
     public MoELayer(int embedDim, int dff, int numExperts, int topK, boolean bias, Network network) {
         this(embedDim, dff, numExperts, topK, bias, network, 16384, OmoeNative.BF16);
@@ -118,6 +122,36 @@ public class MoELayer extends Layer {
         check(OmoeNative.setWeights(handle, addr(router.weight.getGpuData()),
                 bias ? addr(router.bias.getGpuData()) : 0L, addr(packedGate.getGpuData()),
                 addr(packedUp.getGpuData()), addr(packedDown.getGpuData()), OmoeNative.F32));
+        syncedTrainTime = network != null ? network.train_time : 0;
+    }
+
+    /** Re-syncs the native weight copies when the network has taken a training step since the last sync. */
+    private void syncWeightsIfStale() {
+        if (network != null && network.train_time != syncedTrainTime) {
+            syncWeights();
+        }
+    }
+
+    /** Registers every weight with the network's parameter list, as LlamaMLPLayer.putParamters() does for its
+     *  three linears (LlamaMLPLayer.java:285-289; FullyLayer.java:868-873); LlamaTransformerBlock.putParamters()
+     *  calls this on its mlp (LlamaTransformerBlock.java:281). */
+    public void putParamters() {
+        router.putParamters();
+        for (int e = 0; e < numExperts; e++) {
+            gate[e].putParamters();
+            up[e].putParamters();
+            down[e].putParamters();
+        }
+    }
+
+    /** The gradients in the same order (LlamaMLPLayer.java:291-295; FullyLayer.java:875-880). */
+    public void putParamterGrads() {
+        router.putParamterGrads();
+        for (int e = 0; e < numExperts; e++) {
+            gate[e].putParamterGrads();
+            up[e].putParamterGrads();
+            down[e].putParamterGrads();
+        }
     }
 
     private void check(int rc) {
@@ -136,6 +170,7 @@ public class MoELayer extends Layer {
 
     @Override
     public void output() {
+        syncWeightsIfStale();
         // one native call; it enqueues on the legacy default stream and does not synchronise
         check(OmoeNative.forward(handle, addr(input.getGpuData()), addr(output.getGpuData()), number, OmoeNative.F32));
     }

@@ -40,6 +40,17 @@ public final class OmoeNative {
     /** Host arrays in and out: H2D, forward, D2H, synchronise. */
     public static native int forwardHost(long handle, float[] x, float[] y, int tokens);
 
+    /** omoe_forward_host_async: the same without the final synchronise; the arrays are pinned by the JVM until
+     *  waitDone() has returned, so they must stay reachable and untouched until then. */
+    public static native int forwardHostAsync(long handle, float[] x, float[] y, int tokens);
+
+    /** omoe_wait: host waits for everything enqueued on the handle; reports a device-side failure. */
+    public static native int waitDone(long handle);
+
+    /** omoe_forward_block: y = x + MoE(rmsnorm(x) * gamma); gammaDev is the fp32 device address of RMSLayer's gamma. */
+    public static native int forwardBlock(long handle, long xDev, long gammaDev, float eps, long yDev, int tokens,
+                                          int ioDtype);
+
     public static native int getRouting(long handle, int[] topkIdx, float[] topkW, int[] counts, int[] offsets,
                                         int[] perm);
 

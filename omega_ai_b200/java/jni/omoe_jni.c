@@ -57,6 +57,46 @@ JFN(jint, forwardHost)(JNIEnv *env, jclass c, jlong h, jfloatArray x, jfloatArra
     return rc;
 }
 
+/* The arrays of an asynchronous call stay pinned (GetFloatArrayElements) until waitDone releases them. */
+static jfloatArray g_async_x, g_async_y;
+static jfloat *g_async_xp, *g_async_yp;
+
+static void release_async(JNIEnv *env) {
+    if (g_async_x) {
+        (*env)->ReleaseFloatArrayElements(env, g_async_x, g_async_xp, JNI_ABORT);
+        (*env)->ReleaseFloatArrayElements(env, g_async_y, g_async_yp, 0);
+        (*env)->DeleteGlobalRef(env, g_async_x);
+        (*env)->DeleteGlobalRef(env, g_async_y);
+        g_async_x = g_async_y = NULL;
+    }
+}
+
+JFN(jint, forwardHostAsync)(JNIEnv *env, jclass c, jlong h, jfloatArray x, jfloatArray y, jint T) {
+    if (g_async_x) {  /* one call in flight per process through this shim: finish the previous one first */
+        int rc0 = omoe_wait((omoe_handle *)(intptr_t)h);
+        release_async(env);
+        if (rc0 != OMOE_OK) return rc0;
+    }
+    g_async_x = (jfloatArray)(*env)->NewGlobalRef(env, x);
+    g_async_y = (jfloatArray)(*env)->NewGlobalRef(env, y);
+    g_async_xp = (*env)->GetFloatArrayElements(env, g_async_x, NULL);
+    g_async_yp = (*env)->GetFloatArrayElements(env, g_async_y, NULL);
+    int rc = omoe_forward_host_async((omoe_handle *)(intptr_t)h, g_async_xp, g_async_yp, T, OMOE_F32, NULL);
+    if (rc != OMOE_OK) release_async(env);
+    return rc;
+}
+
+JFN(jint, waitDone)(JNIEnv *env, jclass c, jlong h) {
+    int rc = omoe_wait((omoe_handle *)(intptr_t)h);
+    release_async(env);
+    return rc;
+}
+
+JFN(jint, forwardBlock)(JNIEnv *env, jclass c, jlong h, jlong x, jlong gamma, jfloat eps, jlong y, jint T, jint io) {
+    return omoe_forward_block((omoe_handle *)(intptr_t)h, (const void *)(intptr_t)x, (const float *)(intptr_t)gamma, eps,
+                              (void *)(intptr_t)y, T, io, NULL);
+}
+
 JFN(jint, getRouting)(JNIEnv *env, jclass c, jlong h, jintArray idx, jfloatArray w, jintArray counts,
                       jintArray offsets, jintArray perm) {
     jint *pi = idx ? (*env)->GetIntArrayElements(env, idx, NULL) : NULL;

@@ -372,20 +372,6 @@ def test_config5_full_size_decode(oracle, decode_layer, T):
     assert_close_bf16(y[sel], r.y)
 
 
-def test_cta_pair_kernels_in_a_subprocess():
-    """The cta_group::2 variant of the grouped GEMMs is selected by OMOE_PAIR=1, read once per process:
-    run two parity cases (odd tile counts per expert included) in a child process with it set."""
-    import os
-    import subprocess
-    import sys
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, OMOE_PAIR="1")
-    cmd = [sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_parity_gpu.py"), "-x", "-q", "-m", "gpu",
-           "-k", "small_bf16 or config4_skewed or odd_shapes"]
-    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=root)
-    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
-
-
 @pytest.mark.parametrize("knob", ["OMOE_SPLITK=0", "OMOE_SPLITK=1", "OMOE_SPLITK=2", "OMOE_SPLITK=4", "OMOE_SPLITK=8"])
 def test_few_row_variants_forced_in_a_subprocess(knob):
     """Steps with few row tiles run the expert products with K split over a cluster of 1, 2, 4 or 8 CTAs (picked
