@@ -369,6 +369,9 @@ static int forward_impl(omoe_handle *h, const void *x_dev, int x_dtype, void *y_
     int n = pre;
     const bool prof = h->profiling;
 #define MARK(i) do { if (prof) cudaEventRecord(h->ev[i], s); } while (0)
+#ifdef OMOE_BOUNDS_CHECK
+    CU_TRY(h, check_fill(h, s));  // self-checking build: a row the step never wrote reads as NaN
+#endif
     MARK(0);
     if (h->cfg.compute_dtype == OMOE_BF16 && T <= route_small_max_tokens()) {
         CU_TRY(h, launch_route_small(h, x_dev, x_dtype, T, s, &n));
@@ -381,6 +384,9 @@ static int forward_impl(omoe_handle *h, const void *x_dev, int x_dtype, void *y_
         MARK(2);
         CU_TRY(h, launch_permute(h, x_dev, x_dtype, T, s, &n, nullptr));
     }
+#ifdef OMOE_BOUNDS_CHECK
+    CU_TRY(h, check_after_dispatch(h, T, s));  // routing indices in bounds, padding rows untouched
+#endif
     MARK(3);
     MARK(4);
     if (bw_training(h)) {

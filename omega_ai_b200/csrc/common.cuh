@@ -195,6 +195,13 @@ bool build_tensor_maps(omoe_handle *h);
 
 int router_tokens_per_block(int E);
 
+#ifdef OMOE_BOUNDS_CHECK
+// Self-checking build (check.cu): fill the row buffers with NaN patterns before a step; validate the routing
+// arrays and the padding rows after the dispatch.
+cudaError_t check_fill(omoe_handle *h, cudaStream_t s);
+cudaError_t check_after_dispatch(omoe_handle *h, int T, cudaStream_t s);
+#endif
+
 // Flag words the expert-parallel kernels exchange through peer-mapped memory.
 // The step's sequence number lives in device memory (the count-exchange kernel, first of a step, advances
 // it): no kernel argument changes from step to step, so a captured forward replays correctly.

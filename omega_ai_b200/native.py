@@ -11,7 +11,9 @@ import os
 import subprocess
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libomoe.so")
+# OMOE_LIB selects another build of the same ABI, e.g. the self-checking one (libomoe_check.so, csrc/check.cu)
+LIB_PATH = os.environ.get("OMOE_LIB") or os.path.join(_PKG, "libomoe.so")
+CHECK_LIB_PATH = os.path.join(_PKG, "libomoe_check.so")
 CSRC = os.path.join(_PKG, "csrc")
 
 OMOE_F32 = 0
@@ -61,14 +63,14 @@ def sources():
     ]
 
 
-def build(force: bool = False) -> str:
-    """Compile ``libomoe.so`` for sm_100a with nvcc (cross-compiles without a GPU)."""
-    stale = (not os.path.exists(LIB_PATH)) or any(
-        os.path.getmtime(s) > os.path.getmtime(LIB_PATH) for s in sources()
-    )
+def build(force: bool = False, check: bool = False) -> str:
+    """Compile ``libomoe.so`` for sm_100a with nvcc (cross-compiles without a GPU); with ``check`` the
+    self-checking variant ``libomoe_check.so`` (-DOMOE_BOUNDS_CHECK)."""
+    path = CHECK_LIB_PATH if check else os.path.join(_PKG, "libomoe.so")
+    stale = (not os.path.exists(path)) or any(os.path.getmtime(s) > os.path.getmtime(path) for s in sources())
     if force or stale:
-        subprocess.check_call(["sh", os.path.join(CSRC, "build.sh")])
-    return LIB_PATH
+        subprocess.check_call(["sh", os.path.join(CSRC, "build.sh")] + (["check"] if check else []))
+    return path
 
 
 _lib = None
