@@ -626,14 +626,17 @@ def run_ours(args, cfg):
             n_active = max(int((c_all[r * El:(r + 1) * El] > 0).sum()) for r in range(world))
             wbytes = n_active * 3.0 * d * dff * 2
             kern_s = (st["up_gate"] + st["down"]) * 1e-3
-            ent = {"tokens": Td, "ms_per_step": ms_d, "n_active": n_active, "weight_bytes": wbytes,
+            # A decode step is a handful of short launches, so a serving loop replays it from a CUDA graph: that
+            # is the step time reported (one GPU); the same step issued as direct calls is given beside it.
+            step_ms = graph_ms if graph_ms is not None else ms_d
+            ent = {"tokens": Td, "ms_per_step": step_ms,
+                   "launch": "cuda graph replay" if graph_ms is not None else "direct calls",
+                   "direct_ms_per_step": ms_d, "n_active": n_active, "weight_bytes": wbytes,
                    "expert_kernels_ms": kern_s * 1e3, "expert_kernels_gbs": wbytes / kern_s / 1e9,
                    "frac": wbytes / kern_s / 1e9 / peaks["hbm"],
-                   "whole_step_frac": wbytes / (ms_d * 1e-3) / 1e9 / peaks["hbm"], "launches": n_launch,
+                   "whole_step_frac": wbytes / (step_ms * 1e-3) / 1e9 / peaks["hbm"],
+                   "direct_whole_step_frac": wbytes / (ms_d * 1e-3) / 1e9 / peaks["hbm"], "launches": n_launch,
                    "stage_ms": st}
-            if graph_ms is not None:
-                ent["graph_ms_per_step"] = graph_ms
-                ent["graph_whole_step_frac"] = wbytes / (graph_ms * 1e-3) / 1e9 / peaks["hbm"]
             decode.append(ent)
         decode_layer.close()
         decode = {"workload": CONFIGS["c5"]["name"], "bound": "hbm", "peak_gbs": peaks["hbm"],

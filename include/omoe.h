@@ -145,9 +145,11 @@ OMOE_API int omoe_forward_block(omoe_handle *h, const void *x_dev, const float *
  * omoe_forward_host_async is the same call without the final synchronise: it
  * enqueues the copies and the forward(s) and returns; y_host is complete, and
  * a device-side failure is reported, once omoe_wait(h) has returned.  Several
- * calls may be enqueued before one omoe_wait: they run in order, and the
- * copies of a call overlap the kernels of its neighbours (the host buffers of
- * a call must stay untouched until the wait).  The reference splits the same
+ * calls may be enqueued before one omoe_wait: they run in order, each as one
+ * forward (no chunks), and two staging sets alternate between them so that the
+ * copy-in of the next call and the copy-out of the previous one run while the
+ * kernels of the current one do (the host buffers of a call must stay
+ * untouched until the wait).  The reference splits the same
  * work into Tensor.hostToDevice() and Tensor.syncHost()
  * (src/main/java/com/omega/engine/tensor/Tensor.java:559-579), each of which
  * synchronises the whole device.

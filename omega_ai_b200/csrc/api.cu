@@ -109,7 +109,7 @@ int omoe_destroy(omoe_handle *h) {
     bw_destroy(h);
     void *ptrs[] = {h->w_router, h->w_router_bf16, h->router_bias, h->w_gate, h->w_up, h->w_down, h->logits, h->topk_idx,
                     h->topk_w, h->block_counts, h->block_base, h->counts, h->offsets, h->poffsets, h->tile_expert, h->pos, h->lrank,
-                    h->perm_out, h->dev_err, h->xp, h->hbuf, h->yp, h->xn, h->x_stage, h->y_stage, h->d_row_table,
+                    h->perm_out, h->dev_err, h->xp, h->hbuf, h->yp, h->xn, h->x_stage[0], h->y_stage[0], h->x_stage[1], h->y_stage[1], h->d_row_table,
                     h->d_out_table, h->ticket, h->ticket2, h->dst_base != h->poffsets ? h->dst_base : nullptr};
     for (void *p : ptrs)
         if (p) cudaFree(p);
@@ -119,7 +119,10 @@ int omoe_destroy(omoe_handle *h) {
     for (int i = 0; i < kHostChunksMax; i++) {
         if (h->ev_in[i]) cudaEventDestroy(h->ev_in[i]);
         if (h->ev_out[i]) cudaEventDestroy(h->ev_out[i]);
-        if (h->ev_d2h[i]) cudaEventDestroy(h->ev_d2h[i]);
+    }
+    for (int i = 0; i < 2; i++) {
+        if (h->ev_set_fwd[i]) cudaEventDestroy(h->ev_set_fwd[i]);
+        if (h->ev_set_d2h[i]) cudaEventDestroy(h->ev_set_d2h[i]);
     }
     if (h->ev_fence) cudaEventDestroy(h->ev_fence);
     if (h->copy_in) cudaStreamDestroy(h->copy_in);
@@ -196,7 +199,8 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
             {&h->w_gate, (size_t)h->e_local * dff * d * cs}, {&h->w_up, (size_t)h->e_local * dff * d * cs},
             {&h->w_down, (size_t)h->e_local * dff * d * cs}, {&h->xp, (size_t)h->rows_cap * d * cs},
             {&h->hbuf, (size_t)h->rows_cap * dff * cs},      {&h->yp, (size_t)h->rows_cap * d * cs},
-            {&h->x_stage, (size_t)tm * d * 4},               {&h->y_stage, (size_t)tm * d * 4},
+            {&h->x_stage[0], (size_t)tm * d * 4},            {&h->y_stage[0], (size_t)tm * d * 4},
+            {&h->x_stage[1], (size_t)tm * d * 4},            {&h->y_stage[1], (size_t)tm * d * 4},
             {&h->xn, (size_t)tm * d * cs}};
         h->stage_bytes = (size_t)tm * d * 4;
         for (auto &b : bufs) {
@@ -269,8 +273,10 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
                       cudaEventCreateWithFlags(&h->ev_fence, cudaEventDisableTiming) == cudaSuccess;
     for (int i = 0; ok_streams && i < kHostChunksMax; i++)
         ok_streams = cudaEventCreateWithFlags(&h->ev_in[i], cudaEventDisableTiming) == cudaSuccess &&
-                     cudaEventCreateWithFlags(&h->ev_out[i], cudaEventDisableTiming) == cudaSuccess &&
-                     cudaEventCreateWithFlags(&h->ev_d2h[i], cudaEventDisableTiming) == cudaSuccess;
+                     cudaEventCreateWithFlags(&h->ev_out[i], cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; ok_streams && i < 2; i++)
+        ok_streams = cudaEventCreateWithFlags(&h->ev_set_fwd[i], cudaEventDisableTiming) == cudaSuccess &&
+                     cudaEventCreateWithFlags(&h->ev_set_d2h[i], cudaEventDisableTiming) == cudaSuccess;
     if (!ok_streams) {
         int rc = fail(nullptr, OMOE_ERR_CUDA, "omoe_create: could not create the copy streams");
         omoe_destroy(h);
@@ -516,68 +522,62 @@ int omoe_ep_connect_local(omoe_handle **handles, int32_t world) {
 
 // Enqueues one host-buffer forward: H2D copies, the forward(s), D2H copies.  No host synchronisation.
 //
-// Tokens are independent, so a large batch is cut into chunks that run as separate forwards: the
-// host-to-device copy of chunk i+1 and the device-to-host copy of chunk i-1 overlap the kernels of chunk i (two
-// copy streams, ordered against the compute stream with events).  Every output row has the same bits as in
-// one big forward.  Successive calls pipeline as well: the staging area of chunk i is refilled as soon as the
-// previous call's forward of chunk i has consumed it, and its output area is rewritten only after the previous
-// call's device-to-host copy of it has finished.
-// With expert parallelism every forward is a collective step, so all ranks must cut their batches into the
-// SAME number of chunks: the count follows from t_max (identical on every rank), and a rank with fewer tokens
-// makes forwards of fewer (or zero) tokens.
+// Two staging sets alternate from call to call, so the copy-in of call n+1 and the copy-out of call n-1 run
+// while the kernels of call n do: calls enqueued back to back (omoe_forward_host_async) cost the longer of
+// their copies and their kernels.  A set is reused by the call two later, which waits (on the device) for the
+// earlier call's forward to have consumed the staged rows and for its copy-out to have left the output rows.
+//
+// `chunked` (the synchronous entry point, where nothing else overlaps the call): tokens are independent, so a
+// large batch is cut into chunks that run as separate forwards and the copy-in of chunk i+1 and the copy-out of
+// chunk i-1 overlap the kernels of chunk i.  Every output row has the same bits as in one big forward.  With
+// expert parallelism every forward is a collective step, so all ranks must cut their batches into the SAME
+// number of chunks: the count follows from t_max (identical on every rank), and a rank with fewer tokens makes
+// forwards of fewer (or zero) tokens.
 static int forward_host_enqueue(omoe_handle *h, const void *x_host, void *y_host, int32_t T, int32_t io_dtype,
-                                cudaStream_t s) {
+                                cudaStream_t s, bool chunked) {
     const size_t row_bytes = (size_t)h->cfg.d_model * elt_size(io_dtype);
     int chunks = 1;
-    if (h->copy_in != nullptr) {
+    if (chunked) {
         const int basis = h->cfg.world == 1 ? T : h->cfg.t_max;
         const int cmin = h->cfg.world == 1 ? h->host_chunk_min : h->host_chunk_min_ep;
         while (chunks < kHostChunksMax && basis / (chunks * 2) >= cmin) chunks *= 2;
     }
     const int per = (T + chunks - 1) / chunks;
+    const int set = h->stage_next;
+    h->stage_next ^= 1;
+    char *xs = static_cast<char *>(h->x_stage[set]), *ys = static_cast<char *>(h->y_stage[set]);
     // the copy streams must not run ahead of work already queued on the caller's stream
     CU_TRY(h, cudaEventRecord(h->ev_fence, s));
     CU_TRY(h, cudaStreamWaitEvent(h->copy_in, h->ev_fence, 0));
     CU_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev_fence, 0));
-    // Chunk i reuses the staging rows of the previous call's chunk i only when both calls cut the batch the same
-    // way; otherwise wait for all of the previous call (its last chunk's events: the streams run in order).
-    const size_t geom = (size_t)T * 16 + (size_t)chunks * 2 + (io_dtype == OMOE_BF16 ? 1 : 0);
-    if (h->host_prev_chunks > 0 && geom != h->host_prev_geom) {
-        CU_TRY(h, cudaStreamWaitEvent(h->copy_in, h->ev_out[h->host_prev_chunks - 1], 0));
-        CU_TRY(h, cudaStreamWaitEvent(s, h->ev_d2h[h->host_prev_chunks - 1], 0));
-    }
-    h->host_prev_geom = geom;
-    h->host_prev_chunks = chunks;
+    // the call two before this one used the same staging set
+    CU_TRY(h, cudaStreamWaitEvent(h->copy_in, h->ev_set_fwd[set], 0));
+    CU_TRY(h, cudaStreamWaitEvent(s, h->ev_set_d2h[set], 0));
     for (int i = 0; i < chunks; i++) {
         const int t0 = i * per, n = t0 >= T ? 0 : ((t0 + per <= T) ? per : T - t0);
         const size_t off = (size_t)t0 * row_bytes;
-        // the previous call's forward of this chunk has read the staging rows about to be overwritten
-        CU_TRY(h, cudaStreamWaitEvent(h->copy_in, h->ev_out[i], 0));
         if (n > 0)
-            CU_TRY(h, cudaMemcpyAsync(static_cast<char *>(h->x_stage) + off, static_cast<const char *>(x_host) + off,
-                                      (size_t)n * row_bytes, cudaMemcpyHostToDevice, h->copy_in));
+            CU_TRY(h, cudaMemcpyAsync(xs + off, static_cast<const char *>(x_host) + off, (size_t)n * row_bytes,
+                                      cudaMemcpyHostToDevice, h->copy_in));
         CU_TRY(h, cudaEventRecord(h->ev_in[i], h->copy_in));
     }
     for (int i = 0; i < chunks; i++) {
         const int t0 = i * per, n = t0 >= T ? 0 : ((t0 + per <= T) ? per : T - t0);
         const size_t off = (size_t)(n > 0 ? t0 : 0) * row_bytes;
         CU_TRY(h, cudaStreamWaitEvent(s, h->ev_in[i], 0));
-        // the previous call's device-to-host copy of this chunk's output rows has finished
-        CU_TRY(h, cudaStreamWaitEvent(s, h->ev_d2h[i], 0));
         if (n > 0 || h->cfg.world > 1) {
-            int rc = omoe_forward(h, static_cast<char *>(h->x_stage) + off, static_cast<char *>(h->y_stage) + off, n,
-                                  io_dtype, s);
+            int rc = omoe_forward(h, xs + off, ys + off, n, io_dtype, s);
             if (rc != OMOE_OK) return rc;
         }
         CU_TRY(h, cudaEventRecord(h->ev_out[i], s));
         CU_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev_out[i], 0));
         if (n > 0)
-            CU_TRY(h, cudaMemcpyAsync(static_cast<char *>(y_host) + off, static_cast<char *>(h->y_stage) + off,
-                                      (size_t)n * row_bytes, cudaMemcpyDeviceToHost, h->copy_out));
-        CU_TRY(h, cudaEventRecord(h->ev_d2h[i], h->copy_out));
+            CU_TRY(h, cudaMemcpyAsync(static_cast<char *>(y_host) + off, ys + off, (size_t)n * row_bytes,
+                                      cudaMemcpyDeviceToHost, h->copy_out));
     }
-    // work queued on the caller's stream after this call sees the finished copies too
-    CU_TRY(h, cudaStreamWaitEvent(s, h->ev_d2h[chunks - 1], 0));
+    CU_TRY(h, cudaEventRecord(h->ev_set_fwd[set], s));
+    CU_TRY(h, cudaEventRecord(h->ev_set_d2h[set], h->copy_out));
+    h->last_stream = s;
     h->host_pending = true;
     return OMOE_OK;
 }
@@ -598,7 +598,7 @@ int omoe_forward_host_async(omoe_handle *h, const void *x_host, void *y_host, in
     if (!h) return OMOE_ERR_INVALID;
     int rc = check_host_args(h, x_host, y_host, T, io_dtype, "omoe_forward_host_async");
     if (rc != OMOE_OK) return rc;
-    return forward_host_enqueue(h, x_host, y_host, T, io_dtype, static_cast<cudaStream_t>(cuda_stream));
+    return forward_host_enqueue(h, x_host, y_host, T, io_dtype, static_cast<cudaStream_t>(cuda_stream), false);
 }
 
 int omoe_wait(omoe_handle *h) {
@@ -616,9 +616,8 @@ int omoe_forward_host(omoe_handle *h, const void *x_host, void *y_host, int32_t 
     if (!h) return OMOE_ERR_INVALID;
     int rc = check_host_args(h, x_host, y_host, T, io_dtype, "omoe_forward_host");
     if (rc != OMOE_OK) return rc;
-    rc = forward_host_enqueue(h, x_host, y_host, T, io_dtype, static_cast<cudaStream_t>(cuda_stream));
+    rc = forward_host_enqueue(h, x_host, y_host, T, io_dtype, static_cast<cudaStream_t>(cuda_stream), true);
     if (rc != OMOE_OK) return rc;
-    h->last_stream = static_cast<cudaStream_t>(cuda_stream);
     return omoe_wait(h);
 }
 

@@ -106,18 +106,18 @@ struct omoe_handle {
     // activations (device, compute dtype)
     void *xp, *hbuf, *yp;
     void *xn;  // [t_max, d] normalised rows of omoe_forward_block (compute dtype)
-    // staging for omoe_forward_host
-    void *x_stage, *y_stage;
+    // staging for the host-buffer entry points: two sets that alternate from call to call
+    void *x_stage[2], *y_stage[2];
+    int stage_next;
     size_t stage_bytes;
     cudaStream_t copy_in, copy_out;
-    // per chunk: rows staged on the device / forward done (staging rows consumed, outputs written) / outputs
-    // copied back to the host; ev_fence orders the copy streams behind the caller's stream
-    cudaEvent_t ev_in[omoe::kHostChunksMax], ev_out[omoe::kHostChunksMax], ev_d2h[omoe::kHostChunksMax], ev_fence;
+    // per chunk of a call: rows staged on the device / forward done; per staging set: the last call that used it
+    // has consumed the staged rows / has copied its outputs back; ev_fence orders the copy streams behind the
+    // caller's stream
+    cudaEvent_t ev_in[omoe::kHostChunksMax], ev_out[omoe::kHostChunksMax], ev_set_fwd[2], ev_set_d2h[2], ev_fence;
     int host_chunk_min;     // smallest chunk (tokens) worth its own forward, one GPU
     int host_chunk_min_ep;  // the same with expert parallelism
     bool host_pending;      // an omoe_forward_host_async call has not been waited for yet
-    size_t host_prev_geom;  // how the previous host-buffer call cut its batch (tokens, chunks, dtype)
-    int host_prev_chunks;
 
     omoe::TensorMaps maps;
     bool maps_ready;

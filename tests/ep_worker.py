@@ -15,7 +15,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-from helpers import assert_close_bf16, assert_close_f32, make_layer  # noqa: E402
+from helpers import assert_close_bf16, assert_close_bf16_grad, assert_close_f32, make_layer  # noqa: E402
 from omega_ai_b200 import MoELayer  # noqa: E402
 from oracle import ref  # noqa: E402
 
@@ -103,7 +103,7 @@ def run_backward_case(rank, world, compute):
         dist.all_reduce(d_router)
         want = ref.moe_backward(np.concatenate(xs), w_r, w_g, w_u, w_d, k, np.concatenate(dys), bf16=bf)
         lo = sum(counts_t[:rank])
-        close = (lambda a, b_, n: assert_close_bf16(a, b_)) if bf else (
+        close = (lambda a, b_, n: assert_close_bf16_grad(a, b_)) if bf else (
             lambda a, b_, n: np.testing.assert_allclose(a, b_, rtol=0, atol=2e-4 * (np.abs(b_).max() + 1e-30), err_msg=n))
         if T:
             close(dx, want.dx[lo:lo + T], "dx")
@@ -120,7 +120,7 @@ def run_backward_case(rank, world, compute):
     gamma = (1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32)
     if bf:
         x, dy = ref.bf16_round(x), ref.bf16_round(dy)
-    close = (lambda a, b_, n: assert_close_bf16(a, b_)) if bf else (
+    close = (lambda a, b_, n: assert_close_bf16_grad(a, b_)) if bf else (
         lambda a, b_, n: np.testing.assert_allclose(a, b_, rtol=0, atol=2e-4 * (np.abs(b_).max() + 1e-30), err_msg=n))
     layer.set_aux_loss(0.5)
     xd, dyd = dev(x), dev(dy)

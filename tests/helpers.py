@@ -51,7 +51,12 @@ def assert_close_f32(got, ref):
     assert (err <= bound).all(), f"fp32 parity: max err {err.max():.3e} (max |ref| {np.abs(ref).max():.3e})"
 
 
-def bf16_margins(got, ref):
+# Gradients of a bf16 layer pass through two chained bf16 products (dh = dyp * W_down, dxp = [dg | du] * W) with bf16
+# rows in between, where the forward has one: their per-element bound is twice the forward's relative term.
+BF16_GRAD_RTOL = 4e-2
+
+
+def bf16_margins(got, ref, rtol=BF16_RTOL):
     """(worst err/bound over all elements with the floor, worst err/(rel*|ref|) over elements with |ref| >= rms,
     rms of ref, the floor the worst small element would need)."""
     if ref.size == 0:
@@ -59,11 +64,11 @@ def bf16_margins(got, ref):
     err = np.abs(got.astype(np.float64) - ref.astype(np.float64))
     mag = np.abs(ref.astype(np.float64))
     rms = float(np.sqrt(np.mean(mag ** 2)))
-    worst_all = float((err / (BF16_RTOL * mag + BF16_FLOOR * rms + 1e-300)).max())
+    worst_all = float((err / (rtol * mag + BF16_FLOOR * rms + 1e-300)).max())
     big = mag >= rms
-    worst_big = float((err[big] / (BF16_RTOL * mag[big])).max()) if big.any() and rms > 0 else 0.0
+    worst_big = float((err[big] / (rtol * mag[big])).max()) if big.any() and rms > 0 else 0.0
     # what the floor would have to be for the worst small element to sit exactly on the bound
-    need = float(((err - BF16_RTOL * mag) / (rms + 1e-300)).max())
+    need = float(((err - rtol * mag) / (rms + 1e-300)).max())
     return worst_all, worst_big, rms, need
 
 
@@ -74,3 +79,11 @@ def assert_close_bf16(got, ref):
     _log_margin("bf16", worst_all=worst_all, worst_big=worst_big, rms=rms, floor_needed=need, n=int(ref.size))
     assert worst_big <= 1.0, f"bf16 parity (|ref| >= rms, pure rel {BF16_RTOL}): worst err/bound {worst_big:.2f}"
     assert worst_all <= 1.0, f"bf16 parity: worst err/bound {worst_all:.2f} with floor {BF16_FLOOR}*rms, rms {rms:.3e}"
+
+
+def assert_close_bf16_grad(got, ref):
+    """The same two-part bound for gradients of a bf16 layer, with rel 4e-2 (see BF16_GRAD_RTOL)."""
+    worst_all, worst_big, rms, need = bf16_margins(got, ref, BF16_GRAD_RTOL)
+    _log_margin("bf16_grad", worst_all=worst_all, worst_big=worst_big, rms=rms, floor_needed=need, n=int(ref.size))
+    assert worst_big <= 1.0, f"bf16 gradient parity (|ref| >= rms, pure rel {BF16_GRAD_RTOL}): worst err/bound {worst_big:.2f}"
+    assert worst_all <= 1.0, f"bf16 gradient parity: worst err/bound {worst_all:.2f} with floor {BF16_FLOOR}*rms, rms {rms:.3e}"

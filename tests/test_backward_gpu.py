@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import assert_close_bf16, assert_close_f32, make_layer
+from helpers import assert_close_bf16, assert_close_bf16_grad, assert_close_f32, make_layer
 
 pytestmark = pytest.mark.gpu
 
@@ -83,7 +83,7 @@ def test_bf16_backward_matches_oracle(oracle, T, d, dff, E, k, io):
     ref = oracle.moe_backward(x, w_r, w_g, w_u, w_d, k, dy, bf16=True, out_bf16=out_bf16)
     for name in NAMES:
         try:
-            assert_close_bf16(got[name], getattr(ref, name))
+            assert_close_bf16_grad(got[name], getattr(ref, name))
         except AssertionError as e:
             raise AssertionError(f"{name}: {e}") from None
     for e in np.nonzero(r.counts == 0)[0]:
@@ -114,8 +114,8 @@ def test_aux_loss_value_and_gradient(oracle, compute):
     ref0 = oracle.moe_backward(x, w_r, w_g, w_u, w_d, k, dy, bf16=bf)
     assert np.abs(ref.d_w_r - ref0.d_w_r).max() > 10 * np.abs(ref0.d_w_r).max() * 1e-3   # the term matters here
     if bf:
-        assert_close_bf16(g["d_router"].cpu().numpy(), ref.d_w_r)
-        assert_close_bf16(dx, ref.dx)
+        assert_close_bf16_grad(g["d_router"].cpu().numpy(), ref.d_w_r)
+        assert_close_bf16_grad(dx, ref.dx)
     else:
         close_scaled(g["d_router"].cpu().numpy(), ref.d_w_r, "d_w_r", 2e-4)
         close_scaled(dx, ref.dx, "dx", 2e-4)
@@ -154,7 +154,7 @@ def test_block_backward_matches_oracle(oracle, compute, io):
     for name in got:
         if bf:
             try:
-                assert_close_bf16(got[name], want[name])
+                assert_close_bf16_grad(got[name], want[name])
             except AssertionError as e:
                 raise AssertionError(f"{name}: {e}") from None
         else:
