@@ -76,34 +76,6 @@ namespace {
 __device__ __forceinline__ float ldf(const float *p) { return *p; }
 __device__ __forceinline__ float ldf(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
 
-__device__ __forceinline__ void load8(const float *p, float (&v)[8]) {
-    float4 a = *reinterpret_cast<const float4 *>(p), b = *(reinterpret_cast<const float4 *>(p) + 1);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-__device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&v)[8]) {
-    uint4 r = *reinterpret_cast<const uint4 *>(p);
-    uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-}
-__device__ __forceinline__ void store8(float *p, const float (&v)[8]) {
-    float4 *o = reinterpret_cast<float4 *>(p);
-    o[0] = make_float4(v[0], v[1], v[2], v[3]);
-    o[1] = make_float4(v[4], v[5], v[6], v[7]);
-}
-__device__ __forceinline__ void store8(__nv_bfloat16 *p, const float (&v)[8]) {
-    uint4 o;
-    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
-    __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), e = __floats2bfloat162_rn(v[6], v[7]);
-    o.x = *reinterpret_cast<uint32_t *>(&a);
-    o.y = *reinterpret_cast<uint32_t *>(&b);
-    o.z = *reinterpret_cast<uint32_t *>(&c);
-    o.w = *reinterpret_cast<uint32_t *>(&e);
-    *reinterpret_cast<uint4 *>(p) = o;
-}
 
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
 __device__ __forceinline__ float silu_grad_f32(float x) {
@@ -241,6 +213,7 @@ combine_bwd_kernel(const OT *__restrict__ dy, void *const *__restrict__ yp_table
             uint32_t *f = sig.flags[threadIdx.x] + sig.rank;
             asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(*sig.seq) : "memory");
         }
+        if (s_last && threadIdx.x == 0) *ticket = 0;  // every block has arrived: zero for the next user
     }
 }
 

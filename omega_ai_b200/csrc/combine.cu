@@ -11,20 +11,6 @@ namespace omoe {
 
 namespace {
 
-__device__ __forceinline__ void unpack8(const uint4 &r, float (&v)[8]) {
-    uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-}
-
-__device__ __forceinline__ uint32_t pack2(float a, float b) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t *>(&v);
-}
-
 // y = residual + combined rows: the residual add of the transformer block
 // (LlamaTransformerBlock.java:136) folded into this pass; fp32 add, one rounding.
 __device__ __forceinline__ void add_residual(const float *r, float (&acc)[8]) {
@@ -100,10 +86,10 @@ combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const OT
         if (resid != nullptr) add_residual(resid + (size_t)t * d + c, acc);
         if constexpr (sizeof(OT) == 2) {
             uint4 o;
-            o.x = pack2(acc[0], acc[1]);
-            o.y = pack2(acc[2], acc[3]);
-            o.z = pack2(acc[4], acc[5]);
-            o.w = pack2(acc[6], acc[7]);
+            o.x = pack_bf16(acc[0], acc[1]);
+            o.y = pack_bf16(acc[2], acc[3]);
+            o.z = pack_bf16(acc[4], acc[5]);
+            o.w = pack_bf16(acc[6], acc[7]);
             *reinterpret_cast<uint4 *>(y + (size_t)t * d + c) = o;
         } else {
             float4 *o = reinterpret_cast<float4 *>(y + (size_t)t * d + c);
@@ -146,10 +132,10 @@ combine_small_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, co
     if (resid != nullptr) add_residual(resid + (size_t)t * d + c, acc);
     if constexpr (sizeof(OT) == 2) {
         uint4 o;
-        o.x = pack2(acc[0], acc[1]);
-        o.y = pack2(acc[2], acc[3]);
-        o.z = pack2(acc[4], acc[5]);
-        o.w = pack2(acc[6], acc[7]);
+        o.x = pack_bf16(acc[0], acc[1]);
+        o.y = pack_bf16(acc[2], acc[3]);
+        o.z = pack_bf16(acc[4], acc[5]);
+        o.w = pack_bf16(acc[6], acc[7]);
         *reinterpret_cast<uint4 *>(y + (size_t)t * d + c) = o;
     } else {
         float4 *o = reinterpret_cast<float4 *>(y + (size_t)t * d + c);

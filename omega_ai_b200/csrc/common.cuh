@@ -9,6 +9,7 @@
 #include <stdio.h>
 
 #include "../../include/omoe.h"
+#include "vec8.cuh"
 
 namespace omoe {
 

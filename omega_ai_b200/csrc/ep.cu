@@ -254,7 +254,7 @@ route_small_ep_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, c
     for (int i = tid; i < T * vec; i += blockDim.x) {
         const int tt = i / vec, c = (i % vec) * 8;
         float v[8];
-        ldx8(x + (size_t)tt * d + c, v);
+        ldg8(x + (size_t)tt * d + c, v);
         uint4 o;
         o.x = pack_bf16(v[0], v[1]);
         o.y = pack_bf16(v[2], v[3]);

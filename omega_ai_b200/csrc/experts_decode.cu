@@ -19,15 +19,6 @@ namespace {
 constexpr int kDecThreads = 256;
 constexpr int kPairs = kDecThreads / 64;
 
-__device__ __forceinline__ void unpack8(const uint4 &r, float (&v)[8]) {
-    uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-}
-
 // 64-thread barrier of one warp pair; the id is a literal so the kernel reserves only the barriers it uses
 __device__ __forceinline__ void pair_sync(int pair) {
     switch (pair) {

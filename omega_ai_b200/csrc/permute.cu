@@ -32,11 +32,6 @@ struct Vec16<float> { static constexpr int n = 4; };
 template <>
 struct Vec16<__nv_bfloat16> { static constexpr int n = 8; };
 
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t *>(&v);
-}
-
 // One warp per token: finalise the k row positions, read the token's row once
 // and write it to its k places with 16-byte stores.
 // Rows go to the dispatch buffer of the rank that owns the expert: row_table[q]
@@ -119,6 +114,9 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
             uint32_t *f = sig.flags[threadIdx.x] + sig.rank;
             asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(*sig.seq) : "memory");
         }
+        // every block has arrived: leave the counter at zero for whichever kernel uses it next (a decode step's
+        // one-launch routing counts its blocks with it and does not pass through the count-exchange kernel)
+        if (s_last && threadIdx.x == 0) *ticket = 0;
     }
 }
 

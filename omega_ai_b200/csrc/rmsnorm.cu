@@ -16,34 +16,6 @@ namespace omoe {
 
 namespace {
 
-__device__ __forceinline__ void ld8(const float *p, float (&v)[8]) {
-    float4 a = __ldg(reinterpret_cast<const float4 *>(p)), b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-__device__ __forceinline__ void ld8(const __nv_bfloat16 *p, float (&v)[8]) {
-    uint4 r = __ldg(reinterpret_cast<const uint4 *>(p));
-    uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-}
-__device__ __forceinline__ void st8(float *p, const float (&v)[8]) {
-    reinterpret_cast<float4 *>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
-    reinterpret_cast<float4 *>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
-}
-__device__ __forceinline__ void st8(__nv_bfloat16 *p, const float (&v)[8]) {
-    uint4 o;
-    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
-    __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
-    o.x = *reinterpret_cast<uint32_t *>(&a);
-    o.y = *reinterpret_cast<uint32_t *>(&b);
-    o.z = *reinterpret_cast<uint32_t *>(&c);
-    o.w = *reinterpret_cast<uint32_t *>(&d);
-    *reinterpret_cast<uint4 *>(p) = o;
-}
 
 template <typename XT, typename OT>
 __global__ void __launch_bounds__(256)
@@ -55,7 +27,7 @@ rmsnorm_kernel(const XT *__restrict__ x, const float *__restrict__ gamma, OT *__
     float ss = 0.f;
     for (int c = lane * 8; c < d; c += 256) {
         float v[8];
-        ld8(row + c, v);
+        ldg8(row + c, v);
 #pragma unroll
         for (int j = 0; j < 8; j++) ss = fmaf(v[j], v[j], ss);
     }
@@ -65,11 +37,11 @@ rmsnorm_kernel(const XT *__restrict__ x, const float *__restrict__ gamma, OT *__
     OT *o = out + (size_t)t * d;
     for (int c = lane * 8; c < d; c += 256) {
         float v[8], g[8];
-        ld8(row + c, v);
-        ld8(gamma + c, g);
+        ldg8(row + c, v);
+        ldg8(gamma + c, g);
 #pragma unroll
         for (int j = 0; j < 8; j++) v[j] = (v[j] / rms) * g[j];
-        st8(o + c, v);
+        store8(o + c, v);
     }
 }
 

@@ -12,28 +12,6 @@ namespace small {
 constexpr int kSmallMaxTokens = 8;
 constexpr int kSmallMaxPicks = kSmallMaxTokens * kMaxTopK;  // 128
 
-__device__ __forceinline__ void ldx8(const float *p, float (&v)[8]) {
-    float4 a = __ldg(reinterpret_cast<const float4 *>(p));
-    float4 b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-
-__device__ __forceinline__ void ldx8(const __nv_bfloat16 *p, float (&v)[8]) {
-    uint4 r = __ldg(reinterpret_cast<const uint4 *>(p));
-    uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t *>(&v);
-}
-
 // Logits of token t (eight warps split the experts; reduction tree as in router.cu), then softmax statistics,
 // top-k and gate weights by warp 0.  sl: kMaxExperts floats of shared memory.  All 256 threads call this.
 template <int PL, typename XT>
@@ -52,8 +30,8 @@ __device__ __forceinline__ void token_logits_topk(const XT *__restrict__ x, cons
             for (int u = 0; u < 4; u++) {
                 const int i = i0 + u * 256;
                 if (i < d) {
-                    ldx8(xr + i, xv[u]);
-                    ldx8(wr + i, wv[u]);
+                    ldg8(xr + i, xv[u]);
+                    ldg8(wr + i, wv[u]);
                 }
             }
 #pragma unroll

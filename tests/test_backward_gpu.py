@@ -79,7 +79,9 @@ def test_bf16_backward_matches_oracle(oracle, T, d, dff, E, k, io):
     out_bf16 = io == torch.bfloat16
     r = oracle.moe_forward(x, w_r, w_g, w_u, w_d, k, bf16=True, out_bf16=out_bf16)
     assert np.array_equal(routing[0], r.topk_idx)
-    assert_close_bf16(got["y"], r.y)
+    # a training-mode forward rounds g and u to bf16 before SiLU (they are kept for the backward), one rounding
+    # more than the inference forward the oracle's moe_forward states: held to the two-rounding bound
+    assert_close_bf16_grad(got["y"], r.y)
     ref = oracle.moe_backward(x, w_r, w_g, w_u, w_d, k, dy, bf16=True, out_bf16=out_bf16)
     for name in NAMES:
         try:
