@@ -157,8 +157,10 @@ int route_small_max_tokens();
 // sig != nullptr: after the last block has written its rows, raise the
 // "rows have landed" flag on every rank (expert-parallel dispatch).
 struct EpSignal;
+// pass (expert parallel): 0 = all picks; 1 = only the picks whose expert this rank owns (tells this rank alone);
+// 2 = only the picks other ranks own (tells them), in blocks small enough to run beside the up/gate product
 cudaError_t launch_permute(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n,
-                           const EpSignal *sig);
+                           const EpSignal *sig, int pass = 0);
 cudaError_t launch_perm_readout(omoe_handle *h, int T, cudaStream_t s);
 // wait != nullptr: every block first waits (bounded) until all ranks have
 // published their expert outputs (expert-parallel return).
@@ -226,6 +228,8 @@ struct EpWait {
 struct EpGate {
     const uint32_t *wait_flags;      // this rank's flag_rows[world]; null = no wait
     const uint32_t *tile_src_mask;   // [m tiles] bit s set = the tile holds rows of source rank s; may be null
+    const int32_t *tile_order;       // [m tiles] order in which the 128-row tiles are walked (this rank's own rows
+                                     // first: they are here before anything crosses NVLink); null = as they lie
     uint32_t *const *signal_flags;   // device table [world] of the ranks' flag_out arrays; null = no signal
     int32_t *ticket;                 // CTAs of the signalling kernel that have finished (left at 0)
     const uint32_t *seq;             // device: sequence number of the running step

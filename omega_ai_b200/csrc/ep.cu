@@ -45,6 +45,10 @@ struct EpState {
     uint32_t **d_out_flags;     // device [world]: &peer_ctl[q]->flag_out[0]
     int32_t *ex_counts, *ex_poffsets, *ex_tile_expert;  // layout of the rows this rank receives
     uint32_t *ex_tile_mask;     // [m tiles] bit s: the tile holds rows that source rank s sent
+    int32_t *ex_tile_order;     // [m tiles] walk order of the tiles: this rank's own rows first
+    cudaStream_t comm;          // side stream of the remote pass of the dispatch
+    cudaEvent_t ev_fork, ev_join;
+    long overlap_min_bytes;     // smallest dispatch (bytes of rows) worth a remote pass of its own
     void *peer_ptrs[kMaxWorld][5];  // opened IPC mappings (ctl, xp, yp, dyp, dxp), null for self
     void *dyp, *dxp;            // [rows_cap, d] gradient rows of the backward pass (peers write dyp, read dxp)
     void **d_dyp_table, **d_dxp_table;  // device [world]
@@ -69,6 +73,10 @@ struct ExSmem {
     int32_t rpoff[kMaxExperts + kMaxWorld];  // padded start of expert e in its owner's buffer
     int32_t mypoff[kMaxExperts + 1];
     int32_t base[kMaxExperts];               // dst_base of this rank
+    // tiles that hold nothing but this rank's own rows, per local expert: how many, the first one, and the
+    // running sums that place them (and the other tiles) in the walk order
+    int32_t nloc[kMaxExperts], afirst[kMaxExperts], loc_pre[kMaxExperts], rem_pre[kMaxExperts];
+    int n_loc_total;
     int bad;
     uint32_t seq;
 };
@@ -82,6 +90,7 @@ struct ExArgs {
     int rows_cap;
     int32_t *dst_base, *ex_counts, *ex_poffsets, *ex_tile_expert;
     uint32_t *ex_tile_mask;
+    int32_t *ex_tile_order;
     int max_tiles;
     int32_t *ticket, *dev_err;
     unsigned long long timeout_ns;
@@ -157,6 +166,11 @@ __device__ void exchange_body(ExSmem &sm, const ExArgs &a, const int32_t *counts
     }
     if (tid == 0) a.ex_poffsets[El] = bad ? 0 : sm.mypoff[El];
     const int n_tiles = bad ? 0 : sm.mypoff[El] / kRowAlign;
+    for (int le = tid; le < El; le += nt) {
+        sm.nloc[le] = 0;
+        sm.afirst[le] = 0x7fffffff;
+    }
+    __syncthreads();
     for (int i = tid; i < a.max_tiles; i += nt) {
         int ex = -1;
         uint32_t mask = 0;
@@ -175,6 +189,37 @@ __device__ void exchange_body(ExSmem &sm, const ExArgs &a, const int32_t *counts
         }
         a.ex_tile_expert[i] = ex;
         a.ex_tile_mask[i] = mask;
+        if (mask == (1u << r)) {  // only this rank's own rows (a contiguous run of tiles inside the expert)
+            atomicAdd(&sm.nloc[ex], 1);
+            atomicMin(&sm.afirst[ex], i);
+        }
+    }
+    __syncthreads();
+    // Walk order of the tiles: first the tiles that hold only this rank's own rows (they are complete as soon as
+    // the local pass of the dispatch is, before anything has crossed NVLink), expert by expert, then the others
+    // in buffer order.  Tiles of one expert stay together, so a band of tiles still shares its weight tiles.
+    if (tid == 0) {
+        int L = 0, R = 0;
+        for (int le = 0; le < El; le++) {
+            sm.loc_pre[le] = L;
+            sm.rem_pre[le] = R;
+            L += sm.nloc[le];
+            R += (sm.mypoff[le + 1] - sm.mypoff[le]) / kRowAlign - sm.nloc[le];
+        }
+        sm.n_loc_total = L;
+    }
+    __syncthreads();
+    for (int i = tid; i < n_tiles; i += nt) {
+        const int ex = a.ex_tile_expert[i];  // written above by this same thread
+        int p;
+        if (a.ex_tile_mask[i] == (1u << r)) {
+            p = sm.loc_pre[ex] + (i - sm.afirst[ex]);
+        } else {
+            int j = i - sm.mypoff[ex] / kRowAlign;
+            if (sm.nloc[ex] > 0 && i > sm.afirst[ex]) j -= sm.nloc[ex];
+            p = sm.n_loc_total + sm.rem_pre[ex] + j;
+        }
+        a.ex_tile_order[p] = i;
     }
     __syncthreads();
 }
@@ -313,7 +358,8 @@ int ep_create(omoe_handle *h) {
         (e = cudaMalloc(&st->ex_counts, sizeof(int32_t) * El)) != cudaSuccess ||
         (e = cudaMalloc(&st->ex_poffsets, sizeof(int32_t) * (El + 1))) != cudaSuccess ||
         (e = cudaMalloc(&st->ex_tile_expert, sizeof(int32_t) * (h->rows_cap / kRowAlign))) != cudaSuccess ||
-        (e = cudaMalloc(&st->ex_tile_mask, sizeof(uint32_t) * (h->rows_cap / kRowAlign))) != cudaSuccess)
+        (e = cudaMalloc(&st->ex_tile_mask, sizeof(uint32_t) * (h->rows_cap / kRowAlign))) != cudaSuccess ||
+        (e = cudaMalloc(&st->ex_tile_order, sizeof(int32_t) * (h->rows_cap / kRowAlign))) != cudaSuccess)
         return ep_fail(h, OMOE_ERR_NOMEM, "cudaMalloc(expert-parallel state)", e);
     cudaMemset(st->d_seq, 0, sizeof(uint32_t));
     cudaMemset(st->dyp, 0, grad_bytes);
@@ -321,6 +367,12 @@ int ep_create(omoe_handle *h) {
     h->ex_counts = st->ex_counts;
     h->ex_poffsets = st->ex_poffsets;
     h->ex_tile_expert = st->ex_tile_expert;
+    if ((e = cudaStreamCreateWithFlags(&st->comm, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&st->ev_fork, cudaEventDisableTiming)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&st->ev_join, cudaEventDisableTiming)) != cudaSuccess)
+        return ep_fail(h, OMOE_ERR_CUDA, "cudaStreamCreate / cudaEventCreate (expert-parallel state)", e);
+    st->overlap_min_bytes = 8l << 20;
+    if (const char *v = getenv("OMOE_EP_OVERLAP_MIN_MB")) st->overlap_min_bytes = atol(v) < 0 ? (1l << 60) : (atol(v) << 20);
     st->timeout_ns = 10ull * 1000 * 1000 * 1000;
     if (const char *v = getenv("OMOE_EP_WAIT_MS")) {
         long ms = atol(v);
@@ -337,9 +389,12 @@ void ep_destroy(omoe_handle *h) {
             if (st->peer_ptrs[q][i]) cudaIpcCloseMemHandle(st->peer_ptrs[q][i]);
     void *ptrs[] = {st->ctl, st->d_ctl_table, st->d_rows_flags, st->d_out_flags, st->d_seq, st->d_dyp_table,
                     st->d_dxp_table, st->dyp, st->dxp, st->ex_counts, st->ex_poffsets,
-                    st->ex_tile_expert, st->ex_tile_mask};
+                    st->ex_tile_expert, st->ex_tile_mask, st->ex_tile_order};
     for (void *p : ptrs)
         if (p) cudaFree(p);
+    if (st->comm) cudaStreamDestroy(st->comm);
+    if (st->ev_fork) cudaEventDestroy(st->ev_fork);
+    if (st->ev_join) cudaEventDestroy(st->ev_join);
     free(st);
     h->ep = nullptr;
 }
@@ -493,6 +548,7 @@ ExArgs exchange_args(omoe_handle *h, EpState *st) {
     a.ex_poffsets = st->ex_poffsets;
     a.ex_tile_expert = st->ex_tile_expert;
     a.ex_tile_mask = st->ex_tile_mask;
+    a.ex_tile_order = st->ex_tile_order;
     a.max_tiles = (int)(h->rows_cap / kRowAlign);
     a.ticket = h->ticket;
     a.dev_err = h->dev_err;
@@ -536,8 +592,11 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
     cudaError_t e = cudaSuccess;
     const bool prof = h->profiling;
     const bool bf16 = h->cfg.compute_dtype == OMOE_BF16;
+    bool overlapped = false;
     // OMOE_EP_UNFUSED=1: separate wait / signal launches around the products and no one-launch decode routing
     static const bool unfused = getenv("OMOE_EP_UNFUSED") && atoi(getenv("OMOE_EP_UNFUSED")) != 0;
+    // the products take the wait and the signal themselves (no launches of their own around them)
+    const bool gated_step = bf16 && !bw_training(h) && !unfused;
 #define MARK(i) do { if (prof) cudaEventRecord(h->ev[i], s); } while (0)
 #define TRY(expr)                                                                      \
     do {                                                                               \
@@ -563,7 +622,19 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
         n++;
         MARK(2);
         EpSignal sig{st->d_rows_flags, W, r, seq};
-        if (T > 0) {
+        // Large steps: the rows this rank keeps go first (local pass), then the rows for the other ranks travel on
+        // a side stream WHILE the up/gate product already multiplies the tiles that hold only local rows (its
+        // producer waits, tile by tile, for exactly the ranks a tile's rows come from).  The side stream rejoins
+        // before the combine.
+        overlapped = gated_step && T > 0 &&
+                     (long)T * h->cfg.top_k * h->cfg.d_model * (bf16 ? 2 : 4) >= st->overlap_min_bytes;
+        if (overlapped) {
+            TRY(launch_permute(h, x, x_dtype, T, s, &n, &sig, 1));
+            TRY(cudaEventRecord(st->ev_fork, s));
+            TRY(cudaStreamWaitEvent(st->comm, st->ev_fork, 0));
+            TRY(launch_permute(h, x, x_dtype, T, st->comm, &n, &sig, 2));
+            TRY(cudaEventRecord(st->ev_join, st->comm));
+        } else if (T > 0) {
             TRY(launch_permute(h, x, x_dtype, T, s, &n, &sig));
         } else {
             ep_signal_kernel<<<1, 32, 0, s>>>(st->d_rows_flags, W, r, seq);
@@ -572,7 +643,7 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
         }
     }
     MARK(3);
-    const bool gated = bf16 && !bw_training(h) && !unfused;
+    const bool gated = gated_step;
     if (!gated) {
         ep_wait_kernel<<<1, 32, 0, s>>>(st->ctl->flag_rows, W, seq, h->dev_err, st->timeout_ns);
         TRY(cudaGetLastError());
@@ -586,6 +657,7 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
         EpGate gate{};
         gate.wait_flags = st->ctl->flag_rows;
         gate.tile_src_mask = st->ex_tile_mask;
+        gate.tile_order = st->ex_tile_order;
         gate.signal_flags = st->d_out_flags;
         gate.ticket = h->ticket2;
         gate.seq = seq;
@@ -606,6 +678,8 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
         n++;
     }
     MARK(7);
+    // the remote pass of the dispatch reads the routing arrays the next step overwrites: rejoin before going on
+    if (overlapped) TRY(cudaStreamWaitEvent(s, st->ev_join, 0));
     EpWait wt{st->ctl->flag_out, W, seq, st->timeout_ns};
     if (T > 0) {
         TRY(launch_combine(h, y, y_dtype, T, s, &n, &wt, resid));

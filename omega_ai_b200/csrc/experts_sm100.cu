@@ -46,13 +46,16 @@ struct TileCoord {
 
 // Tiles are walked in bands of `band` m-tiles x all n-tiles, m fastest, so the
 // rows of a band stay in L2 while the weight tiles stream past them.
-__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m_tiles, int n_tiles, int kband) {
+// order (may be null): the m-tiles are walked in this order instead of as they lie in the buffer.
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m_tiles, int n_tiles, int kband,
+                                                const int32_t *__restrict__ order) {
     int per_band = kband * n_tiles;
     int band = tile / per_band, r = tile % per_band;
     int m0 = band * kband;
     int bm = min(kband, num_m_tiles - m0);
     TileCoord c;
     c.mt = m0 + r % bm;
+    if (order != nullptr) c.mt = order[c.mt];
     c.nt = r / bm;
     return c;
 }
@@ -117,10 +120,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t phase = 0;
             bool ok = true;
             // the expert of the next tile is fetched while the current tile streams
-            int e_next = (int)blockIdx.x < total ? tile_expert[tile_coord(blockIdx.x, num_m_tiles, n_tiles, kband).mt] : 0;
+            int e_next = (int)blockIdx.x < total ? tile_expert[tile_coord(blockIdx.x, num_m_tiles, n_tiles, kband, gate.tile_order).mt] : 0;
             uint32_t seen = 0;  // expert parallel: sources whose rows are known to have landed
             for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
-                TileCoord tc = tile_coord(tile, num_m_tiles, n_tiles, kband);
+                TileCoord tc = tile_coord(tile, num_m_tiles, n_tiles, kband, gate.tile_order);
                 const int e = e_next;
                 if (gate.wait_flags != nullptr) {
                     // the rows of this tile come from the ranks named in its mask; wait for those only
@@ -128,7 +131,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (!ep_gate_wait(gate, need, seen, dev_err)) { *abort_flag = 1; ok = false; break; }
                 }
                 if (tile + (int)gridDim.x < total)
-                    e_next = tile_expert[tile_coord(tile + gridDim.x, num_m_tiles, n_tiles, kband).mt];
+                    e_next = tile_expert[tile_coord(tile + gridDim.x, num_m_tiles, n_tiles, kband, gate.tile_order).mt];
                 const int row_a = tc.mt * BLOCK_M;
                 const int row_b0 = e * n_out + tc.nt * n_tile_w;
                 const int row_b1 = SWIGLU ? row_b0 : row_b0 + 128;
@@ -197,7 +200,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int as = 0;
         uint32_t aphase = 0;
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
-            TileCoord tc = tile_coord(tile, num_m_tiles, n_tiles, kband);
+            TileCoord tc = tile_coord(tile, num_m_tiles, n_tiles, kband, gate.tile_order);
             bool ok = mbar_wait(tfull_bar(as), aphase, abort_flag, dev_err);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -373,6 +376,7 @@ cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEven
         g_dn = *gate;
         g_dn.wait_flags = nullptr;
         g_dn.tile_src_mask = nullptr;
+        g_dn.tile_order = nullptr;
     }
     {
         cudaError_t e0 = set_smem_attrs();

@@ -150,7 +150,9 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     uint32_t seen = 0;  // expert parallel: sources whose rows are known to have landed (producer thread)
 
     for (int tile = cid; tile < total; tile += ncl) {
-        const int mt = tile % num_m_tiles, nt = tile / num_m_tiles;  // row tiles fastest: a weight tile is fetched once
+        int mt = tile % num_m_tiles;  // row tiles fastest: a weight tile is fetched once
+        const int nt = tile / num_m_tiles;
+        if (gate.tile_order != nullptr) mt = gate.tile_order[mt];
         const int e = tile_expert[mt];
         const int m_valid = min(BLOCK_M, counts[e] - (mt * BLOCK_M - poffsets[e]));
         // all lanes are converged here; a role that gave up (or whose CTA did) sits out the remaining tiles

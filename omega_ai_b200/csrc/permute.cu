@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(256)
 permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, const int32_t *__restrict__ topk_idx,
                const int32_t *__restrict__ lrank, int32_t *__restrict__ pos, const int32_t *__restrict__ block_base,
                const int32_t *__restrict__ dst_base, int T, int d, int n_blocks, int e_local, int k, int tokens_per_block,
-               EpSignal sig, int32_t *ticket, int rows_cap, int32_t *dev_err) {
+               EpSignal sig, int32_t *ticket, int rows_cap, int32_t *dev_err, int pass) {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int my = 0, owner = 0;
@@ -62,16 +62,21 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
         } else if (my < 0) {
             my = -1;
         }
-        if (blockIdx.y == 0) pos[f] = my;
+        if (blockIdx.y == 0 && pass != 2) pos[f] = my;
     }
     if (t < T) {
     OT *dst[kMaxTopK];
+    bool any = false;  // a token none of whose picks belongs to this pass is not read at all
 #pragma unroll
     for (int j = 0; j < kMaxTopK; j++) {
         int row = __shfl_sync(0xffffffffu, my, j);
         int q = __shfl_sync(0xffffffffu, owner, j);
-        dst[j] = (j < k && row >= 0) ? static_cast<OT *>(row_table[q]) + (size_t)row * d : nullptr;
+        // pass 1 moves only the picks whose expert this rank owns, pass 2 only the others (0: all of them)
+        const bool mine = pass == 0 || ((pass == 1) == (q == sig.rank));
+        dst[j] = (j < k && row >= 0 && mine) ? static_cast<OT *>(row_table[q]) + (size_t)row * d : nullptr;
+        any = any || dst[j] != nullptr;
     }
+    if (any) {
 
     // blockIdx.y walks one slice of the row (more warps in flight when there are few tokens)
     const int cw = ((d / (int)gridDim.y + 7) / 8) * 8;
@@ -100,6 +105,7 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
                 if (j < k && dst[j] != nullptr) *reinterpret_cast<uint4 *>(dst[j] + c) = v;
         }
     }
+    }  // any
     }
     if (sig.flags != nullptr) {
         // Expert parallel: make this block's rows visible system-wide, take a
@@ -109,7 +115,9 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
         __shared__ int s_last;
         if (threadIdx.x == 0) s_last = (atomicAdd(ticket, 1) == (int)(gridDim.x * gridDim.y) - 1);
         __syncthreads();
-        if (s_last && (int)threadIdx.x < sig.world) {
+        // pass 1 has completed this rank's own rows only: it tells this rank alone; pass 2 tells the others
+        if (s_last && (int)threadIdx.x < sig.world &&
+            (pass == 0 || ((pass == 1) == ((int)threadIdx.x == sig.rank)))) {
             __threadfence_system();
             uint32_t *f = sig.flags[threadIdx.x] + sig.rank;
             asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(*sig.seq) : "memory");
@@ -143,10 +151,11 @@ cudaError_t launch_scan(omoe_handle *h, int T, cudaStream_t s, int *n) {
 }
 
 cudaError_t launch_permute(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n,
-                           const EpSignal *sig) {
+                           const EpSignal *sig, int pass) {
     const int d = h->cfg.d_model, k = h->cfg.top_k, El = h->e_local;
     const int nb = ceil_div(T, h->tokens_per_block);
-    const int wpb = 8;
+    // pass 2 runs beside the up/gate product, whose CTAs leave room for one block of four warps per SM
+    const int wpb = pass == 2 ? 4 : 8;
     // enough warps to keep every SM's memory pipes busy: split rows when there are few tokens
     int split = 1;
     while (split < 8 && (long long)T * split < 32LL * h->sm_count && d / (split * 2) >= 512) split *= 2;
@@ -156,15 +165,15 @@ cudaError_t launch_permute(omoe_handle *h, const void *x, int io_dtype, int T, c
     if (io_dtype == OMOE_F32 && !cbf)
         permute_kernel<float, float><<<grid, block, 0, s>>>(
             static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->lrank, h->pos, h->block_base, h->dst_base, T, d,
-            nb, El, k, h->tokens_per_block, sg, h->ticket, (int)h->rows_cap, h->dev_err);
+            nb, El, k, h->tokens_per_block, sg, h->ticket, (int)h->rows_cap, h->dev_err, pass);
     else if (io_dtype == OMOE_F32 && cbf)
         permute_kernel<float, __nv_bfloat16><<<grid, block, 0, s>>>(
             static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->lrank, h->pos, h->block_base, h->dst_base, T, d,
-            nb, El, k, h->tokens_per_block, sg, h->ticket, (int)h->rows_cap, h->dev_err);
+            nb, El, k, h->tokens_per_block, sg, h->ticket, (int)h->rows_cap, h->dev_err, pass);
     else if (io_dtype == OMOE_BF16 && cbf)
         permute_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, block, 0, s>>>(
             static_cast<const __nv_bfloat16 *>(x), h->d_row_table, h->topk_idx, h->lrank, h->pos,
-            h->block_base, h->dst_base, T, d, nb, El, k, h->tokens_per_block, sg, h->ticket, (int)h->rows_cap, h->dev_err);
+            h->block_base, h->dst_base, T, d, nb, El, k, h->tokens_per_block, sg, h->ticket, (int)h->rows_cap, h->dev_err, pass);
     else
         return cudaErrorInvalidValue;  // bf16 rows into an fp32 layer are rejected by the API
     (*n)++;

@@ -10,8 +10,8 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(n):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMOE_EP_WAIT_MS="5000")
+def _run(n, **extra):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMOE_EP_WAIT_MS="5000", **extra)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", "29517", os.path.join(ROOT, "tests", "ep_worker.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
@@ -25,11 +25,28 @@ def test_expert_parallel_two_gpus():
     _run(2)
 
 
+def test_expert_parallel_two_gpus_overlapped_dispatch():
+    """Large steps send the rows for other ranks on a side stream while the up/gate product already works on the
+    tiles that hold only local rows.  The parity cases are small, so the threshold is set to zero here: every
+    step takes that path (local pass, remote pass beside the product, tiles walked local-first)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _run(2, OMOE_EP_OVERLAP_MIN_MB="0")
+
+
+def test_expert_parallel_two_gpus_separate_wait_and_signal_launches():
+    """The same cases with the wait and signal as launches of their own around the products (OMOE_EP_UNFUSED=1)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _run(2, OMOE_EP_UNFUSED="1")
+
+
 def test_expert_parallel_all_gpus():
     n = torch.cuda.device_count()
     if n < 4:
         pytest.skip("needs 4 or more GPUs")
     _run(8 if n >= 8 else 4)
+    _run(8 if n >= 8 else 4, OMOE_EP_OVERLAP_MIN_MB="0")
 
 
 def test_expert_parallel_in_one_process():
