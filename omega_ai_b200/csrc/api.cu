@@ -70,6 +70,7 @@ int check_dev_err(omoe_handle *h) {
         cudaMemset(h->dev_err, 0, sizeof(int32_t));
         cudaMemset(h->ticket, 0, sizeof(int32_t));
         cudaMemset(h->ticket2, 0, sizeof(int32_t));
+        cudaMemset(h->ticket3, 0, sizeof(int32_t));
         return fail(h, OMOE_ERR_DEVICE, "device error word = %d (%s%s)", v,
                     (v & kDevErrTimeout) ? "a bounded wait ran out " : "",
                     (v & kDevErrBounds) ? "an index check failed" : "");
@@ -110,7 +111,7 @@ int omoe_destroy(omoe_handle *h) {
     void *ptrs[] = {h->w_router, h->w_router_bf16, h->router_bias, h->w_gate, h->w_up, h->w_down, h->logits, h->topk_idx,
                     h->topk_w, h->block_counts, h->block_base, h->counts, h->offsets, h->poffsets, h->tile_expert, h->pos, h->lrank,
                     h->perm_out, h->dev_err, h->xp, h->hbuf, h->yp, h->xn, h->x_stage[0], h->y_stage[0], h->x_stage[1], h->y_stage[1], h->d_row_table,
-                    h->d_out_table, h->ticket, h->ticket2, h->dst_base != h->poffsets ? h->dst_base : nullptr};
+                    h->d_out_table, h->ticket, h->ticket2, h->ticket3, h->dst_base != h->poffsets ? h->dst_base : nullptr};
     for (void *p : ptrs)
         if (p) cudaFree(p);
     for (int r = 0; r < kProfSlots; r++)
@@ -229,6 +230,7 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
     ALLOC(dev_err, 1);
     ALLOC(ticket, 1);
     ALLOC(ticket2, 1);
+    ALLOC(ticket3, 1);
     ALLOC(d_row_table, c.world);
     ALLOC(d_out_table, c.world);
     if (c.world > 1) ALLOC(dst_base, E);
@@ -251,6 +253,7 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
     cudaMemset(h->dev_err, 0, sizeof(int32_t));
     cudaMemset(h->ticket, 0, sizeof(int32_t));
     cudaMemset(h->ticket2, 0, sizeof(int32_t));
+    cudaMemset(h->ticket3, 0, sizeof(int32_t));
     // padding rows of the dispatch buffers are never read back, but start them
     // at zero so no stale NaN pattern ever enters a tensor-core tile
     cudaMemset(h->xp, 0, (size_t)h->rows_cap * d * cs);
@@ -262,6 +265,7 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
             return rc;
         }
     // copy streams of omoe_forward_host: non-blocking, so they can overlap kernels on the legacy default stream
+    h->pdl = !(getenv("OMOE_PDL") && atoi(getenv("OMOE_PDL")) == 0);
     h->host_chunk_min = 4096;
     h->host_chunk_min_ep = 512;  // expert parallel: the per-rank batch is small, and so are its chunks
     if (const char *v = getenv("OMOE_HOST_CHUNK_MIN")) {

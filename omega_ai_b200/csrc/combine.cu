@@ -33,6 +33,8 @@ combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const OT
                const float *__restrict__ topk_w, int T, int d, int k_rt, int e_local, EpWait wait, int32_t *dev_err) {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    pdl_trigger();
+    pdl_wait();
     if (wait.flags != nullptr) {
         // expert-parallel return: rows are read from the owners' output buffers
         // over NVLink once every rank has published them
@@ -108,6 +110,8 @@ combine_small_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, co
                      const float *__restrict__ topk_w, int T, int d, int k, int e_local) {
     const int vec = d / 8;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
     if (idx >= T * vec) return;
     const int t = idx / vec, c = (idx % vec) * 8;
     float acc[8];
@@ -154,14 +158,14 @@ cudaError_t launch_k(omoe_handle *h, void *y, const void *resid_v, int T, cudaSt
     const OT *resid = static_cast<const OT *>(resid_v);
     if (wait == nullptr && (long long)T * (d / 8) <= 65536) {
         const int threads = T * (d / 8);
-        combine_small_kernel<YT, OT><<<ceil_div(threads, 256), 256, 0, s>>>(h->d_out_table, out, resid, h->pos, h->topk_idx,
-                                                                           h->topk_w, T, d, k, El);
-        return cudaGetLastError();
+        return launch_ex(combine_small_kernel<YT, OT>, dim3(ceil_div(threads, 256)), dim3(256), 0, s, h->pdl,
+                         h->d_out_table, out, resid, h->pos, h->topk_idx, h->topk_w, T, d, k, El);
     }
     EpWait wt = wait ? *wait : EpWait{nullptr, 1, 0, 0};
+    cudaError_t e;
 #define OMOE_COMBINE(KK)                                                                                         \
-    combine_kernel<YT, OT, KK><<<grid, block, 0, s>>>(h->d_out_table, out, resid, h->pos, h->topk_idx, h->topk_w, T, d, k, \
-                                                      El, wt, h->dev_err)
+    e = launch_ex(combine_kernel<YT, OT, KK>, grid, block, 0, s, h->pdl, h->d_out_table, out, resid, h->pos,      \
+                  h->topk_idx, h->topk_w, T, d, k, El, wt, h->dev_err)
     switch (k) {
         case 1: OMOE_COMBINE(1); break;
         case 2: OMOE_COMBINE(2); break;
@@ -171,7 +175,7 @@ cudaError_t launch_k(omoe_handle *h, void *y, const void *resid_v, int T, cudaSt
         default: OMOE_COMBINE(0); break;
     }
 #undef OMOE_COMBINE
-    return cudaGetLastError();
+    return e;
 }
 
 }  // namespace

@@ -9,6 +9,7 @@
 #include <stdio.h>
 
 #include "../../include/omoe.h"
+#include "pdl.cuh"
 #include "vec8.cuh"
 
 namespace omoe {
@@ -101,8 +102,10 @@ struct omoe_handle {
     void **d_row_table, **d_out_table;
     int32_t *ticket;      // blocks of the dispatch kernel that have finished (EP)
     int32_t *ticket2;     // CTAs of the down product that have finished (EP: the last one raises "outputs ready")
+    int32_t *ticket3;     // dispatch warps of the up/gate product that have finished (EP)
     int32_t *perm_out;    // [t_max*k] scratch for omoe_get_routing
     int32_t *dev_err;     // device error word
+    bool pdl;             // launch the forward's kernels with programmatic dependent launch (pdl.cuh)
 
     // activations (device, compute dtype)
     void *xp, *hbuf, *yp;
@@ -157,8 +160,8 @@ int route_small_max_tokens();
 // sig != nullptr: after the last block has written its rows, raise the
 // "rows have landed" flag on every rank (expert-parallel dispatch).
 struct EpSignal;
-// pass (expert parallel): 0 = all picks; 1 = only the picks whose expert this rank owns (tells this rank alone);
-// 2 = only the picks other ranks own (tells them), in blocks small enough to run beside the up/gate product
+// pass (expert parallel): 0 = all picks; 1 = only the picks whose expert this rank owns (tells this rank alone;
+// the others travel inside the up/gate product, see EpDispatch); 2 = only the picks other ranks own (tells them)
 cudaError_t launch_permute(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n,
                            const EpSignal *sig, int pass = 0);
 cudaError_t launch_perm_readout(omoe_handle *h, int T, cudaStream_t s);
@@ -183,6 +186,9 @@ cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEven
 // persistent kernels of experts_sm100.cu
 // m_tiles_ub: bound on the step's 128-row tiles, -1 if unknown
 int splitk_ways_up_gate(omoe_handle *h, long m_tiles_ub);
+// true when launch_experts_bf16 with this row bound runs the up/gate product on the persistent kernel (the one
+// that can carry the remote half of the dispatch)
+bool experts_up_is_persistent(omoe_handle *h, long rows_ub);
 int splitk_ways_down(omoe_handle *h, long m_tiles_ub);
 cudaError_t launch_up_gate_splitk(omoe_handle *h, cudaStream_t s, int S, const EpGate *gate);
 cudaError_t launch_down_splitk(omoe_handle *h, cudaStream_t s, int S, const EpGate *gate);
@@ -225,7 +231,22 @@ struct EpWait {
 // given, names the sources whose rows 128-row tile mt holds, so a tile starts as soon as ITS sources are in
 // (otherwise all sources are awaited before the first tile).  Signal side (the down product): the CTA that
 // finishes last stores *seq into slot `rank` of every rank's signal_flags array ("outputs ready").
+// The remote half of the dispatch, carried out by two extra warps of every CTA of the up/gate product while its
+// other warps multiply the tiles that are already complete: token rows whose expert lives on another rank are
+// stored into that rank's dispatch buffer (peer stores), and the warp that finishes last raises "rows landed"
+// on those ranks.  Inside the product's kernel the transfer can never wait for a place on the GPU.
+struct EpDispatch {
+    const void *x;                   // [T, d] token rows; null = nothing to dispatch
+    int x_is_f32;                    // rows are fp32 (converted to bf16 on the way) or bf16
+    void *const *row_table;          // device table [world]: every rank's dispatch buffer
+    const int32_t *topk_idx, *lrank, *block_base, *dst_base;
+    int T, d, n_blocks, e_local, k, tokens_per_block, rows_cap;
+    uint32_t *const *rows_flags;     // device table [world]: every rank's flag_rows array
+    int32_t *ticket;                 // dispatch warps that have finished (left at 0)
+};
+
 struct EpGate {
+    EpDispatch disp;
     const uint32_t *wait_flags;      // this rank's flag_rows[world]; null = no wait
     const uint32_t *tile_src_mask;   // [m tiles] bit s set = the tile holds rows of source rank s; may be null
     const int32_t *tile_order;       // [m tiles] order in which the 128-row tiles are walked (this rank's own rows

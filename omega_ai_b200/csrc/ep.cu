@@ -16,10 +16,13 @@
 //      go on each owner (dst_base) and how the rows I receive are laid out
 //      (ex_* arrays, and for every 128-row tile the set of ranks its rows come from)
 //   3. dispatch: rows -> owners' buffers, then "rows landed" flag to every rank
-//      (a decode step of <= 8 tokens does 1-3 in ONE launch)
+//      (a decode step of <= 8 tokens does 1-3 in ONE launch; a large step
+//      moves only the rows this rank keeps here and leaves the rest to 4)
 //   4. up/gate product: its producer thread waits, tile by tile, only for the
-//      ranks whose rows the tile holds, so tiles start while other rows are
-//      still in flight; no separate wait launch
+//      ranks whose rows the tile holds, and walks the tiles that hold only local
+//      rows first; in a large step two extra warps of every CTA carry this
+//      rank's rows for the OTHER ranks across NVLink meanwhile (peer stores
+//      in the same kernel as the tensor-core tiles); no separate wait launch
 //   5. down product; the CTA that finishes last raises "outputs ready" on
 //      every rank; no separate signal launch
 //   6. combine: wait for all owners' flags, gather rows over NVLink
@@ -46,9 +49,7 @@ struct EpState {
     int32_t *ex_counts, *ex_poffsets, *ex_tile_expert;  // layout of the rows this rank receives
     uint32_t *ex_tile_mask;     // [m tiles] bit s: the tile holds rows that source rank s sent
     int32_t *ex_tile_order;     // [m tiles] walk order of the tiles: this rank's own rows first
-    cudaStream_t comm;          // side stream of the remote pass of the dispatch
-    cudaEvent_t ev_fork, ev_join;
-    long overlap_min_bytes;     // smallest dispatch (bytes of rows) worth a remote pass of its own
+    long overlap_min_bytes;     // smallest dispatch (bytes of rows) whose remote half travels inside the product
     void *peer_ptrs[kMaxWorld][5];  // opened IPC mappings (ctl, xp, yp, dyp, dxp), null for self
     void *dyp, *dxp;            // [rows_cap, d] gradient rows of the backward pass (peers write dyp, read dxp)
     void **d_dyp_table, **d_dxp_table;  // device [world]
@@ -259,6 +260,8 @@ route_small_ep_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, c
     const int tid = threadIdx.x;
     const int t = blockIdx.x;
     const int E = a.E;
+    pdl_trigger();
+    pdl_wait();  // the step before may still be reading the routing arrays this kernel overwrites
     if (t < T) token_logits_topk<PL, XT>(x, w_r, bias, t, d, E, k, renorm, logits, topk_idx, topk_w, sl);
     __threadfence();
     __syncthreads();
@@ -367,10 +370,6 @@ int ep_create(omoe_handle *h) {
     h->ex_counts = st->ex_counts;
     h->ex_poffsets = st->ex_poffsets;
     h->ex_tile_expert = st->ex_tile_expert;
-    if ((e = cudaStreamCreateWithFlags(&st->comm, cudaStreamNonBlocking)) != cudaSuccess ||
-        (e = cudaEventCreateWithFlags(&st->ev_fork, cudaEventDisableTiming)) != cudaSuccess ||
-        (e = cudaEventCreateWithFlags(&st->ev_join, cudaEventDisableTiming)) != cudaSuccess)
-        return ep_fail(h, OMOE_ERR_CUDA, "cudaStreamCreate / cudaEventCreate (expert-parallel state)", e);
     st->overlap_min_bytes = 8l << 20;
     if (const char *v = getenv("OMOE_EP_OVERLAP_MIN_MB")) st->overlap_min_bytes = atol(v) < 0 ? (1l << 60) : (atol(v) << 20);
     st->timeout_ns = 10ull * 1000 * 1000 * 1000;
@@ -392,9 +391,6 @@ void ep_destroy(omoe_handle *h) {
                     st->ex_tile_expert, st->ex_tile_mask, st->ex_tile_order};
     for (void *p : ptrs)
         if (p) cudaFree(p);
-    if (st->comm) cudaStreamDestroy(st->comm);
-    if (st->ev_fork) cudaEventDestroy(st->ev_fork);
-    if (st->ev_join) cudaEventDestroy(st->ev_join);
     free(st);
     h->ep = nullptr;
 }
@@ -561,16 +557,16 @@ cudaError_t launch_route_small_ep(omoe_handle *h, EpState *st, const XT *x, int 
     const ExArgs a = exchange_args(h, st);
     const int E = h->cfg.n_experts;
     const int blocks = T > 0 ? T : 1;
+    cudaError_t e;
 #define OMOE_RSE(PLV)                                                                                              \
-    route_small_ep_kernel<PLV, XT><<<blocks, 256, 0, s>>>(x, h->w_router, h->router_bias, T, h->cfg.d_model,       \
-                                                          h->cfg.top_k, h->cfg.renormalize, h->logits, h->topk_idx, \
-                                                          h->topk_w, h->counts, h->offsets, h->pos, h->d_row_table, \
-                                                          st->d_rows_flags, h->ticket, a)
+    e = launch_ex(route_small_ep_kernel<PLV, XT>, dim3(blocks), dim3(256), 0, s, h->pdl, x, h->w_router,           \
+                  h->router_bias, T, h->cfg.d_model, h->cfg.top_k, h->cfg.renormalize, h->logits, h->topk_idx,     \
+                  h->topk_w, h->counts, h->offsets, h->pos, h->d_row_table, st->d_rows_flags, h->ticket, a)
     if (E <= 32) OMOE_RSE(1);
     else if (E <= 64) OMOE_RSE(2);
     else OMOE_RSE(4);
 #undef OMOE_RSE
-    return cudaGetLastError();
+    return e;
 }
 
 }  // namespace
@@ -603,8 +599,16 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
         e = (expr);                                                                    \
         if (e != cudaSuccess) return ep_fail(h, OMOE_ERR_CUDA, #expr, e);              \
     } while (0)
+    // Programmatic dependent launch along the decode chain only (one-launch routing, products, combine).
+    const bool small_path = bf16 && !unfused && T <= route_small_max_tokens();
+    struct PdlScope {
+        omoe_handle *h;
+        bool saved;
+        ~PdlScope() { h->pdl = saved; }
+    } pdl_scope{h, h->pdl};
+    h->pdl = h->pdl && small_path && gated_step;
     MARK(0);
-    if (bf16 && !unfused && T <= route_small_max_tokens()) {
+    if (small_path) {
         if (T > 0 && (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return ep_fail(h, OMOE_ERR_CUDA, "x", cudaErrorMisalignedAddress);
         if (x_dtype == OMOE_F32) TRY(launch_route_small_ep<float>(h, st, static_cast<const float *>(x), T, s));
         else TRY(launch_route_small_ep<__nv_bfloat16>(h, st, static_cast<const __nv_bfloat16 *>(x), T, s));
@@ -622,18 +626,15 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
         n++;
         MARK(2);
         EpSignal sig{st->d_rows_flags, W, r, seq};
-        // Large steps: the rows this rank keeps go first (local pass), then the rows for the other ranks travel on
-        // a side stream WHILE the up/gate product already multiplies the tiles that hold only local rows (its
-        // producer waits, tile by tile, for exactly the ranks a tile's rows come from).  The side stream rejoins
-        // before the combine.
-        overlapped = gated_step && T > 0 &&
-                     (long)T * h->cfg.top_k * h->cfg.d_model * (bf16 ? 2 : 4) >= st->overlap_min_bytes;
+        // Large steps: the rows this rank keeps go first (local pass, tells this rank alone); the rows for the
+        // other ranks travel INSIDE the up/gate product (two extra warps per CTA, peer stores) while its other
+        // warps already multiply the tiles that hold only local rows -- the producer waits, tile by tile, for
+        // exactly the ranks a tile's rows come from, and the tiles are walked local-first.
+        const long rows_ub = (long)h->cfg.t_max * W * h->cfg.top_k;
+        overlapped = gated_step && T > 0 && experts_up_is_persistent(h, rows_ub) &&
+                     (long)T * h->cfg.top_k * h->cfg.d_model * 2 >= st->overlap_min_bytes;
         if (overlapped) {
             TRY(launch_permute(h, x, x_dtype, T, s, &n, &sig, 1));
-            TRY(cudaEventRecord(st->ev_fork, s));
-            TRY(cudaStreamWaitEvent(st->comm, st->ev_fork, 0));
-            TRY(launch_permute(h, x, x_dtype, T, st->comm, &n, &sig, 2));
-            TRY(cudaEventRecord(st->ev_join, st->comm));
         } else if (T > 0) {
             TRY(launch_permute(h, x, x_dtype, T, s, &n, &sig));
         } else {
@@ -658,6 +659,25 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
         gate.wait_flags = st->ctl->flag_rows;
         gate.tile_src_mask = st->ex_tile_mask;
         gate.tile_order = st->ex_tile_order;
+        if (overlapped) {
+            EpDispatch &dp = gate.disp;
+            dp.x = x;
+            dp.x_is_f32 = x_dtype == OMOE_F32;
+            dp.row_table = h->d_row_table;
+            dp.topk_idx = h->topk_idx;
+            dp.lrank = h->lrank;
+            dp.block_base = h->block_base;
+            dp.dst_base = h->dst_base;
+            dp.T = T;
+            dp.d = h->cfg.d_model;
+            dp.n_blocks = ceil_div(T, h->tokens_per_block);
+            dp.e_local = h->e_local;
+            dp.k = h->cfg.top_k;
+            dp.tokens_per_block = h->tokens_per_block;
+            dp.rows_cap = (int)h->rows_cap;
+            dp.rows_flags = st->d_rows_flags;
+            dp.ticket = h->ticket3;
+        }
         gate.signal_flags = st->d_out_flags;
         gate.ticket = h->ticket2;
         gate.seq = seq;
@@ -678,8 +698,6 @@ int ep_forward(omoe_handle *h, const void *x, int x_dtype, void *y, int y_dtype,
         n++;
     }
     MARK(7);
-    // the remote pass of the dispatch reads the routing arrays the next step overwrites: rejoin before going on
-    if (overlapped) TRY(cudaStreamWaitEvent(s, st->ev_join, 0));
     EpWait wt{st->ctl->flag_out, W, seq, st->timeout_ns};
     if (T > 0) {
         TRY(launch_combine(h, y, y_dtype, T, s, &n, &wt, resid));

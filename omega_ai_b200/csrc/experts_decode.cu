@@ -55,6 +55,8 @@ decode_gemv_kernel(const __nv_bfloat16 *__restrict__ A, const __nv_bfloat16 *__r
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int pair = warp >> 1, half = warp & 1;
+    pdl_trigger();
+    pdl_wait();
     if (tid == 0) {
         int n = 0;
         for (int e = 0; e < El; e++)
@@ -191,12 +193,10 @@ cudaError_t launch_gemv(omoe_handle *h, const void *A, const void *W0, const voi
     if (per_sm < 1) per_sm = 1;
     if (per_sm > 4) per_sm = 4;
     const int sms = h->sm_count > 0 ? h->sm_count : 148;
-    kern<<<sms * per_sm, kDecThreads, smem, s>>>(static_cast<const __nv_bfloat16 *>(A),
-                                                static_cast<const __nv_bfloat16 *>(W0),
-                                                static_cast<const __nv_bfloat16 *>(W1),
-                                                static_cast<__nv_bfloat16 *>(out), K, N, h->ex_counts, h->ex_poffsets,
-                                                h->e_local);
-    return cudaGetLastError();
+    return launch_ex(kern, dim3(sms * per_sm), dim3(kDecThreads), smem, s, h->pdl,
+                     static_cast<const __nv_bfloat16 *>(A), static_cast<const __nv_bfloat16 *>(W0),
+                     static_cast<const __nv_bfloat16 *>(W1), static_cast<__nv_bfloat16 *>(out), K, N, h->ex_counts,
+                     h->ex_poffsets, h->e_local);
 }
 
 template <int RP>

@@ -37,7 +37,8 @@ constexpr int kStageBytes = kABytes + 2 * kBHalfBytes;  // 48 KB
 constexpr int kOutSubBytes = 128 * 64 * 2;          // one [128 x 64] bf16 sub-tile of the output staging
 constexpr int kOutBytes = 2 * kOutSubBytes;         // 32 KB: 128 output columns per pass
 constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + 1024 /*align slack*/ + 256 /*barriers*/;
-constexpr int kThreads = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 epilogue
+constexpr int kThreads = 384;  // warp 0 producer, warp 1 MMA, warps 2-9 epilogue, warps 10-11 dispatch (expert parallel)
+constexpr int kDispatchWarps = 2;
 
 
 struct TileCoord {
@@ -84,6 +85,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    pdl_trigger();
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; s++) {
             mbar_init(full_bar(s), 1);
@@ -107,6 +109,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // barriers and tensor memory are set up; everything from here on reads what earlier kernels wrote
+    pdl_wait();
     const int num_m_tiles = poffsets[E] / kRowAlign;
     const int n_tile_w = SWIGLU ? 128 : 256;
     const int n_tiles = (n_out + n_tile_w - 1) / n_tile_w;
@@ -182,6 +186,68 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (!ok) break;
                 tc_commit(tfull_bar(as));  // accumulator complete
                 if (++as == kAccStages) { as = 0; aphase ^= 1u; }
+            }
+        }
+    } else if (warp >= 10) {
+        // ---------------- dispatch warps (expert parallel, up/gate product only) ----------------
+        // The rows this rank's tokens send to experts on OTHER ranks cross NVLink here, while the warps above
+        // already multiply the tiles whose rows are in place (this rank's own rows went first, in a kernel of
+        // their own).  One warp per token; nothing in here waits for anything.
+        if constexpr (SWIGLU) {
+            const EpDispatch &dp = gate.disp;
+            if (dp.x != nullptr) {
+                const int n_warps = (int)gridDim.x * kDispatchWarps;
+                for (int t = (int)blockIdx.x * kDispatchWarps + (warp - 10); t < dp.T; t += n_warps) {
+                    int my = -1, owner = 0;
+                    if (lane < dp.k) {
+                        const int f = t * dp.k + lane;
+                        const int e = dp.topk_idx[f];
+                        const int b = t / dp.tokens_per_block;
+                        my = dp.dst_base[e] + dp.block_base[(size_t)e * dp.n_blocks + b] + dp.lrank[f];
+                        owner = e / dp.e_local;
+                        if (my < 0 || my >= dp.rows_cap || owner == gate.rank) my = -1;  // refused step / local pick
+                    }
+                    __nv_bfloat16 *dst[kMaxTopK];
+                    bool any = false;
+#pragma unroll
+                    for (int j = 0; j < kMaxTopK; j++) {
+                        const int row = __shfl_sync(0xffffffffu, my, j);
+                        const int q = __shfl_sync(0xffffffffu, owner, j);
+                        dst[j] = (j < dp.k && row >= 0)
+                                     ? static_cast<__nv_bfloat16 *>(dp.row_table[q]) + (size_t)row * dp.d
+                                     : nullptr;
+                        any = any || dst[j] != nullptr;
+                    }
+                    if (!any) continue;
+                    for (int c = lane * 8; c < dp.d; c += 256) {
+                        uint4 v;
+                        if (dp.x_is_f32) {
+                            float r[8];
+                            ldg8(static_cast<const float *>(dp.x) + (size_t)t * dp.d + c, r);
+                            v = pack8(r);
+                        } else {
+                            v = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(dp.x) +
+                                                                      (size_t)t * dp.d + c));
+                        }
+#pragma unroll
+                        for (int j = 0; j < kMaxTopK; j++)
+                            if (dst[j] != nullptr) *reinterpret_cast<uint4 *>(dst[j] + c) = v;
+                    }
+                }
+                // rows before flag, system-wide; the warp that finishes last tells the other ranks
+                __threadfence_system();
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) last = atomicAdd(dp.ticket, 1) == (int)gridDim.x * kDispatchWarps - 1;
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence_system();
+                    const uint32_t seq = *gate.seq;
+                    if (lane < gate.world && lane != gate.rank)
+                        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dp.rows_flags[lane] + gate.rank), "r"(seq)
+                                     : "memory");
+                    if (lane == 0) *dp.ticket = 0;
+                }
             }
         }
     } else {
@@ -361,9 +427,19 @@ cudaError_t launch_grouped_plain(omoe_handle *h, cudaStream_t s, const CUtensorM
     cudaError_t e = set_smem_attrs();
     if (e != cudaSuccess) return e;
     static int band = getenv("OMOE_BAND_DOWN") ? atoi(getenv("OMOE_BAND_DOWN")) : 16;
-    grouped_gemm_kernel<false><<<dim3(h->sm_count), dim3(kThreads), kSmemBytes, s>>>(
-        a, b, b, c, n_out, K, h->ex_tile_expert, h->ex_poffsets, h->e_local, band, h->dev_err, EpGate{});
-    return cudaGetLastError();
+    return launch_ex(grouped_gemm_kernel<false>, dim3(h->sm_count), dim3(kThreads), kSmemBytes, s, false, a, b, b, c,
+                     n_out, K, h->ex_tile_expert, h->ex_poffsets, h->e_local, band, h->dev_err, EpGate{});
+}
+
+// most 128-row tiles any placement of rows_ub rows on the local experts can give (-1: unknown)
+static long m_tiles_bound(omoe_handle *h, long rows_ub) {
+    if (rows_ub < 0) return -1;
+    const long act = rows_ub < h->e_local ? rows_ub : h->e_local;
+    return act + (rows_ub - act) / kRowAlign;
+}
+
+bool experts_up_is_persistent(omoe_handle *h, long rows_ub) {
+    return splitk_ways_up_gate(h, m_tiles_bound(h, rows_ub)) == 0;
 }
 
 cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEvent_t mid, long rows_ub,
@@ -377,6 +453,7 @@ cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEven
         g_dn.wait_flags = nullptr;
         g_dn.tile_src_mask = nullptr;
         g_dn.tile_order = nullptr;
+        g_dn.disp = EpDispatch{};
     }
     {
         cudaError_t e0 = set_smem_attrs();
@@ -388,21 +465,15 @@ cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEven
     dim3 grid(h->sm_count), block(kThreads);
     // With very few row tiles, whole tiles per CTA would leave most SMs (and their share of the memory
     // system) idle: split K over a cluster instead (experts_sm100_splitk.cu).
-    long m_tiles_ub = -1;
-    if (rows_ub >= 0) {
-        // most tiles any placement of rows_ub rows on e_local experts can give
-        const long act = rows_ub < h->e_local ? rows_ub : h->e_local;
-        m_tiles_ub = act + (rows_ub - act) / kRowAlign;
-    }
+    const long m_tiles_ub = m_tiles_bound(h, rows_ub);
     const int s_up = splitk_ways_up_gate(h, m_tiles_ub), s_dn = splitk_ways_down(h, m_tiles_ub);
     cudaError_t e;
     if (s_up > 0) {
         e = launch_up_gate_splitk(h, s, s_up, gate ? &g_up : nullptr);
     } else {
-        grouped_gemm_kernel<true><<<grid, block, kSmemBytes, s>>>(
-            h->maps.a_x, h->maps.b_gate, h->maps.b_up, h->maps.a_h, dff, d,
-            h->ex_tile_expert, h->ex_poffsets, h->e_local, band_up, h->dev_err, g_up);
-        e = cudaGetLastError();
+        e = launch_ex(grouped_gemm_kernel<true>, grid, block, kSmemBytes, s, h->pdl, h->maps.a_x, h->maps.b_gate,
+                      h->maps.b_up, h->maps.a_h, dff, d, h->ex_tile_expert, h->ex_poffsets, h->e_local, band_up,
+                      h->dev_err, g_up);
     }
     if (e != cudaSuccess) return e;
     (*n)++;
@@ -412,10 +483,9 @@ cudaError_t launch_experts_bf16(omoe_handle *h, cudaStream_t s, int *n, cudaEven
         if (e == cudaSuccess) (*n)++;
         return e;
     }
-    grouped_gemm_kernel<false><<<grid, block, kSmemBytes, s>>>(
-        h->maps.a_h, h->maps.b_down, h->maps.b_down, h->maps.c_y, d, dff,
-        h->ex_tile_expert, h->ex_poffsets, h->e_local, band_dn, h->dev_err, g_dn);
-    e = cudaGetLastError();
+    e = launch_ex(grouped_gemm_kernel<false>, grid, block, kSmemBytes, s, h->pdl, h->maps.a_h, h->maps.b_down,
+                  h->maps.b_down, h->maps.c_y, d, dff, h->ex_tile_expert, h->ex_poffsets, h->e_local, band_dn,
+                  h->dev_err, g_dn);
     if (e == cudaSuccess) (*n)++;
     return e;
 }

@@ -106,6 +106,7 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     const uint32_t rank = sreg_cluster_ctarank(), S = sreg_cluster_nctarank();
     const int cid = (int)sreg_clusterid(), ncl = (int)sreg_nclusterid();
 
+    pdl_trigger();
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStagesMax; s++) {
             mbar_init(full_bar(s), 1);
@@ -116,6 +117,7 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 2) {  // does any expert hold more than 32 tokens?
+        pdl_wait();   // the counts come from the kernel before this one
         int mx = 0;
         for (int e = lane; e < E; e += 32) mx = max(mx, counts[e]);
         mx = __reduce_max_sync(0xffffffffu, mx);
@@ -131,6 +133,8 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // barriers and tensor memory are set up; everything from here on reads what earlier kernels wrote
+    pdl_wait();
     const bool small = *small_flag != 0;
     const int n_stages = small ? kStagesSmall : kStagesBig;
     const uint32_t stage_bytes = small ? kStageBytesSmall : kStageBytesBig;
@@ -287,14 +291,16 @@ cudaError_t prepare_splitk(omoe_handle *h, int S, cudaLaunchConfig_t *cfg, cudaL
         if (done) *done = true;
     }
     *cfg = cudaLaunchConfig_t{};
-    at->id = cudaLaunchAttributeClusterDimension;
-    at->val.clusterDim.x = S;
-    at->val.clusterDim.y = 1;
-    at->val.clusterDim.z = 1;
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = S;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg->blockDim = dim3(kThreadsK);
     cfg->dynamicSmemBytes = kSmemBytesK;
     cfg->attrs = at;
-    cfg->numAttrs = 1;
+    cfg->numAttrs = h->pdl ? 2 : 1;  // [0] cluster shape, [1] programmatic dependent launch
     // as many clusters as can be resident at once (a cluster lives inside one GPC)
     static int max_clusters[9] = {0};
     if (max_clusters[S] == 0) {
@@ -315,9 +321,9 @@ cudaError_t launch_splitk(omoe_handle *h, cudaStream_t s, int S, const CUtensorM
                           const CUtensorMap &b0, const CUtensorMap &b1, void *out, int n_out, int K,
                           const EpGate *gate) {
     cudaLaunchConfig_t cfg;
-    cudaLaunchAttribute at;
+    cudaLaunchAttribute at[2];
     int clusters = 0;
-    cudaError_t e = prepare_splitk<SWIGLU>(h, S, &cfg, &at, &clusters);
+    cudaError_t e = prepare_splitk<SWIGLU>(h, S, &cfg, at, &clusters);
     if (e != cudaSuccess) return e;
     cfg.stream = s;
     return cudaLaunchKernelEx(&cfg, grouped_gemm_splitk_kernel<SWIGLU>, a, a32, b0, b1,
@@ -338,9 +344,9 @@ int splitk_ways(omoe_handle *h, long tiles_ub, int num_kb) {
     for (int S = 8; S >= 1; S /= 2) {
         if (S > 1 && num_kb < 8 * S) continue;
         cudaLaunchConfig_t cfg;
-        cudaLaunchAttribute at;
+        cudaLaunchAttribute at[2];
         int clusters = 0;
-        if (prepare_splitk<SWIGLU>(h, S, &cfg, &at, &clusters) != cudaSuccess) {
+        if (prepare_splitk<SWIGLU>(h, S, &cfg, at, &clusters) != cudaSuccess) {
             cudaGetLastError();
             continue;
         }

@@ -22,6 +22,8 @@ scan_kernel(const int32_t *__restrict__ block_counts, int32_t *__restrict__ bloc
             int32_t *__restrict__ poffsets, int32_t *__restrict__ tile_expert, int max_tiles) {
     __shared__ int32_t s_cnt[kMaxExperts];
     __shared__ int32_t s_poff[kMaxExperts + 1];
+    pdl_trigger();
+    pdl_wait();
     scan_body(block_counts, block_base, n_blocks, E, counts, offsets, poffsets, tile_expert, max_tiles, s_cnt, s_poff);
 }
 
@@ -46,6 +48,8 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
                EpSignal sig, int32_t *ticket, int rows_cap, int32_t *dev_err, int pass) {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    pdl_trigger();
+    pdl_wait();
     int my = 0, owner = 0;
     if (t < T && lane < k) {
         int f = t * k + lane;
@@ -144,40 +148,35 @@ __global__ void perm_readout_kernel(const int32_t *__restrict__ topk_idx, const 
 cudaError_t launch_scan(omoe_handle *h, int T, cudaStream_t s, int *n) {
     int n_blocks = ceil_div(T, h->tokens_per_block);
     int max_tiles = (int)(h->rows_cap / kRowAlign);
-    scan_kernel<<<1, 1024, 0, s>>>(h->block_counts, h->block_base, n_blocks, h->cfg.n_experts, h->counts, h->offsets,
-                                   h->poffsets, h->tile_expert, max_tiles);
     (*n)++;
-    return cudaGetLastError();
+    return launch_ex(scan_kernel, dim3(1), dim3(1024), 0, s, h->pdl, h->block_counts, h->block_base, n_blocks,
+                     h->cfg.n_experts, h->counts, h->offsets, h->poffsets, h->tile_expert, max_tiles);
 }
 
 cudaError_t launch_permute(omoe_handle *h, const void *x, int io_dtype, int T, cudaStream_t s, int *n,
                            const EpSignal *sig, int pass) {
     const int d = h->cfg.d_model, k = h->cfg.top_k, El = h->e_local;
     const int nb = ceil_div(T, h->tokens_per_block);
-    // pass 2 runs beside the up/gate product, whose CTAs leave room for one block of four warps per SM
-    const int wpb = pass == 2 ? 4 : 8;
+    const int wpb = 8;
     // enough warps to keep every SM's memory pipes busy: split rows when there are few tokens
     int split = 1;
     while (split < 8 && (long long)T * split < 32LL * h->sm_count && d / (split * 2) >= 512) split *= 2;
     dim3 grid(ceil_div(T, wpb), split), block(wpb * 32);
     const bool cbf = h->cfg.compute_dtype == OMOE_BF16;
     EpSignal sg = sig ? *sig : EpSignal{nullptr, 1, 0, 0};
-    if (io_dtype == OMOE_F32 && !cbf)
-        permute_kernel<float, float><<<grid, block, 0, s>>>(
-            static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->lrank, h->pos, h->block_base, h->dst_base, T, d,
-            nb, El, k, h->tokens_per_block, sg, h->ticket, (int)h->rows_cap, h->dev_err, pass);
-    else if (io_dtype == OMOE_F32 && cbf)
-        permute_kernel<float, __nv_bfloat16><<<grid, block, 0, s>>>(
-            static_cast<const float *>(x), h->d_row_table, h->topk_idx, h->lrank, h->pos, h->block_base, h->dst_base, T, d,
-            nb, El, k, h->tokens_per_block, sg, h->ticket, (int)h->rows_cap, h->dev_err, pass);
-    else if (io_dtype == OMOE_BF16 && cbf)
-        permute_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, block, 0, s>>>(
-            static_cast<const __nv_bfloat16 *>(x), h->d_row_table, h->topk_idx, h->lrank, h->pos,
-            h->block_base, h->dst_base, T, d, nb, El, k, h->tokens_per_block, sg, h->ticket, (int)h->rows_cap, h->dev_err, pass);
-    else
-        return cudaErrorInvalidValue;  // bf16 rows into an fp32 layer are rejected by the API
-    (*n)++;
-    return cudaGetLastError();
+    const bool pdl = h->pdl;
+    cudaError_t e;
+#define OMOE_PERMUTE(XT, OT)                                                                                        \
+    e = launch_ex(permute_kernel<XT, OT>, grid, block, 0, s, pdl, static_cast<const XT *>(x), h->d_row_table,       \
+                  h->topk_idx, h->lrank, h->pos, h->block_base, h->dst_base, T, d, nb, El, k, h->tokens_per_block,  \
+                  sg, h->ticket, (int)h->rows_cap, h->dev_err, pass)
+    if (io_dtype == OMOE_F32 && !cbf) OMOE_PERMUTE(float, float);
+    else if (io_dtype == OMOE_F32 && cbf) OMOE_PERMUTE(float, __nv_bfloat16);
+    else if (io_dtype == OMOE_BF16 && cbf) OMOE_PERMUTE(__nv_bfloat16, __nv_bfloat16);
+    else return cudaErrorInvalidValue;  // bf16 rows into an fp32 layer are rejected by the API
+#undef OMOE_PERMUTE
+    if (e == cudaSuccess) (*n)++;
+    return e;
 }
 
 cudaError_t launch_perm_readout(omoe_handle *h, int T, cudaStream_t s) {

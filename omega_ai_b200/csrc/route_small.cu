@@ -28,8 +28,10 @@ route_small_kernel(const XT *__restrict__ x, const float *__restrict__ w_r, cons
     __shared__ int32_t s_idx[kSmallMaxPicks], s_rank[kSmallMaxPicks], s_pos[kSmallMaxPicks];
     __shared__ int32_t s_cnt[kMaxExperts], s_poff[kMaxExperts + 1];
     __shared__ int s_last;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
     const int t = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();  // the step before may still be reading the routing arrays this kernel overwrites
 
     token_logits_topk<PL, XT>(x, w_r, bias, t, d, E, k, renorm, logits, topk_idx, topk_w, sl);
     // ---- the block that finishes last does the scan and the dispatch ----
@@ -97,16 +99,17 @@ template <typename XT>
 cudaError_t launch_typed(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
     const int E = h->cfg.n_experts;
     const int max_tiles = (int)(h->rows_cap / kRowAlign);
+    cudaError_t e;
 #define OMOE_RS(PLV)                                                                                             \
-    route_small_kernel<PLV, XT><<<T, 256, 0, s>>>(x, h->w_router, h->router_bias, T, h->cfg.d_model, E, h->cfg.top_k, \
-                                                  h->cfg.renormalize, h->logits, h->topk_idx, h->topk_w, h->counts,  \
-                                                  h->offsets, h->poffsets, h->tile_expert, max_tiles, h->pos,        \
-                                                  static_cast<__nv_bfloat16 *>(h->xp), h->ticket)
+    e = launch_ex(route_small_kernel<PLV, XT>, dim3(T), dim3(256), 0, s, h->pdl, x, h->w_router, h->router_bias, T, \
+                  h->cfg.d_model, E, h->cfg.top_k, h->cfg.renormalize, h->logits, h->topk_idx, h->topk_w, h->counts, \
+                  h->offsets, h->poffsets, h->tile_expert, max_tiles, h->pos, static_cast<__nv_bfloat16 *>(h->xp),  \
+                  h->ticket)
     if (E <= 32) OMOE_RS(1);
     else if (E <= 64) OMOE_RS(2);
     else OMOE_RS(4);
 #undef OMOE_RS
-    return cudaGetLastError();
+    return e;
 }
 
 }  // namespace

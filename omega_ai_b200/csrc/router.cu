@@ -106,6 +106,8 @@ router_kernel(const XT *__restrict__ x, const WT *__restrict__ w_r, const float 
     float *sl = reinterpret_cast<float *>(smem_raw + S * C::STAGE);  // [TB][EMAX] logits, later exp values
     int32_t *sidx = reinterpret_cast<int32_t *>(sl + TB * EMAX);      // [TB][k]
     const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw));
+    pdl_trigger();
+    pdl_wait();  // the step before may still be reading the routing arrays this kernel overwrites
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int grp = warp / ES, es = warp % ES;
@@ -293,10 +295,9 @@ cudaError_t launch_one(omoe_handle *h, const XT *x, int T, cudaStream_t s) {
     const WT *w;
     if constexpr (sizeof(WT) == 2) w = h->w_router_bf16;
     else w = h->w_router;
-    kern<<<blocks, kRouterWarps * 32, smem, s>>>(x, w, h->router_bias, T, h->cfg.d_model,
-                                                  h->cfg.n_experts, k, h->cfg.renormalize, h->logits,
-                                                  h->topk_idx, h->topk_w, h->block_counts, h->lrank);
-    return cudaGetLastError();
+    return launch_ex(kern, dim3(blocks), dim3(kRouterWarps * 32), smem, s, h->pdl, x, w, h->router_bias, T,
+                     h->cfg.d_model, h->cfg.n_experts, k, h->cfg.renormalize, h->logits, h->topk_idx, h->topk_w,
+                     h->block_counts, h->lrank);
 }
 
 // More tokens per warp reuse every router weight read from shared memory more

@@ -26,12 +26,13 @@ def test_expert_parallel_two_gpus():
 
 
 def test_expert_parallel_two_gpus_overlapped_dispatch():
-    """Large steps send the rows for other ranks on a side stream while the up/gate product already works on the
-    tiles that hold only local rows.  The parity cases are small, so the threshold is set to zero here: every
-    step takes that path (local pass, remote pass beside the product, tiles walked local-first)."""
+    """Large steps keep only the local rows in the dispatch kernel; the rows for other ranks are stored into the
+    owners' buffers by two extra warps of every CTA of the up/gate product, while its other warps already work on
+    the tiles that hold only local rows (walked first).  The parity cases are small, so the threshold is set to
+    zero and the persistent product kernel is forced (OMOE_SPLITK=0): every step takes that path."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    _run(2, OMOE_EP_OVERLAP_MIN_MB="0")
+    _run(2, OMOE_EP_OVERLAP_MIN_MB="0", OMOE_SPLITK="0")
 
 
 def test_expert_parallel_two_gpus_separate_wait_and_signal_launches():
@@ -46,7 +47,7 @@ def test_expert_parallel_all_gpus():
     if n < 4:
         pytest.skip("needs 4 or more GPUs")
     _run(8 if n >= 8 else 4)
-    _run(8 if n >= 8 else 4, OMOE_EP_OVERLAP_MIN_MB="0")
+    _run(8 if n >= 8 else 4, OMOE_EP_OVERLAP_MIN_MB="0", OMOE_SPLITK="0")
 
 
 def test_expert_parallel_in_one_process():
