@@ -149,7 +149,8 @@ OMOE_API int omoe_forward_block(omoe_handle *h, const void *x_dev, const float *
  * forward (no chunks), and two staging sets alternate between them so that the
  * copy-in of the next call and the copy-out of the previous one run while the
  * kernels of the current one do (the host buffers of a call must stay
- * untouched until the wait).  The reference splits the same
+ * untouched until the wait).  x_host must hold the rows when the call is made:
+ * the copy-in is not ordered behind work queued earlier on cuda_stream.  The reference splits the same
  * work into Tensor.hostToDevice() and Tensor.syncHost()
  * (src/main/java/com/omega/engine/tensor/Tensor.java:559-579), each of which
  * synchronises the whole device.

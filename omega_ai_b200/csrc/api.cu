@@ -550,10 +550,9 @@ static int forward_host_enqueue(omoe_handle *h, const void *x_host, void *y_host
     const int set = h->stage_next;
     h->stage_next ^= 1;
     char *xs = static_cast<char *>(h->x_stage[set]), *ys = static_cast<char *>(h->y_stage[set]);
-    // the copy streams must not run ahead of work already queued on the caller's stream
-    CU_TRY(h, cudaEventRecord(h->ev_fence, s));
-    CU_TRY(h, cudaStreamWaitEvent(h->copy_in, h->ev_fence, 0));
-    CU_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev_fence, 0));
+    // The copy-in does NOT wait for work already queued on the caller's stream (that is what lets it run under
+    // the previous call's kernels): x_host must hold the rows when the call is made.  The copy-out only ever
+    // follows this call's own forward.
     // the call two before this one used the same staging set
     CU_TRY(h, cudaStreamWaitEvent(h->copy_in, h->ev_set_fwd[set], 0));
     CU_TRY(h, cudaStreamWaitEvent(s, h->ev_set_d2h[set], 0));

@@ -219,19 +219,31 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         any = any || dst[j] != nullptr;
                     }
                     if (!any) continue;
-                    for (int c = lane * 8; c < dp.d; c += 256) {
-                        uint4 v;
-                        if (dp.x_is_f32) {
-                            float r[8];
-                            ldg8(static_cast<const float *>(dp.x) + (size_t)t * dp.d + c, r);
-                            v = pack8(r);
-                        } else {
-                            v = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(dp.x) +
-                                                                      (size_t)t * dp.d + c));
+                    // four 16-byte loads in flight per lane before the first store: the warp is alone with the
+                    // memory latency here
+                    for (int c0 = lane * 8; c0 < dp.d; c0 += 4 * 256) {
+                        uint4 v[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int c = c0 + u * 256;
+                            if (c >= dp.d) break;
+                            if (dp.x_is_f32) {
+                                float r[8];
+                                ldg8(static_cast<const float *>(dp.x) + (size_t)t * dp.d + c, r);
+                                v[u] = pack8(r);
+                            } else {
+                                v[u] = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(dp.x) +
+                                                                             (size_t)t * dp.d + c));
+                            }
                         }
 #pragma unroll
-                        for (int j = 0; j < kMaxTopK; j++)
-                            if (dst[j] != nullptr) *reinterpret_cast<uint4 *>(dst[j] + c) = v;
+                        for (int u = 0; u < 4; u++) {
+                            const int c = c0 + u * 256;
+                            if (c >= dp.d) break;
+#pragma unroll
+                            for (int j = 0; j < kMaxTopK; j++)
+                                if (dst[j] != nullptr) *reinterpret_cast<uint4 *>(dst[j] + c) = v[u];
+                        }
                     }
                 }
                 // rows before flag, system-wide; the warp that finishes last tells the other ranks
