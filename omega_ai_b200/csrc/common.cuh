@@ -296,17 +296,26 @@ __device__ __forceinline__ bool ep_gate_wait(const EpGate &g, uint32_t need, uin
     return true;
 }
 
-// Signal side of an EpGate, called by ONE thread per CTA after that CTA's output stores are complete (for
-// stores issued by other threads: after a __syncthreads() that follows their __threadfence_system()).
+// Signal side of an EpGate, called by ONE WARP per CTA (all 32 lanes, converged) after that CTA's output stores
+// are complete: either lane 0 of the calling warp issued them itself and has waited for them (the TMA stores of
+// the persistent kernel), or the call follows a __syncthreads() that follows the storing threads'
+// __threadfence_system().  The last CTA's lanes raise the flags on all ranks at once: one release store per
+// lane, so the round trips to the other GPUs overlap instead of queueing behind one another.
 __device__ __forceinline__ void ep_gate_signal(const EpGate &g, int n_ctas) {
-    asm volatile("fence.proxy.async;" ::: "memory");
-    __threadfence_system();
-    if (atomicAdd(g.ticket, 1) == n_ctas - 1) {
+    const int lane = threadIdx.x & 31;
+    int last = 0;
+    if (lane == 0) {
+        asm volatile("fence.proxy.async;" ::: "memory");
         __threadfence_system();
-        *g.ticket = 0;  // every CTA has arrived; ready for the next step
+        last = atomicAdd(g.ticket, 1) == n_ctas - 1;
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+        __threadfence_system();
+        if (lane == 0) *g.ticket = 0;  // every CTA has arrived; ready for the next step
         const uint32_t seq = *g.seq;
-        for (int q = 0; q < g.world; q++)
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(g.signal_flags[q] + g.rank), "r"(seq) : "memory");
+        if (lane < g.world)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(g.signal_flags[lane] + g.rank), "r"(seq) : "memory");
     }
 }
 

@@ -344,8 +344,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             if (++as == kAccStages) { as = 0; aphase ^= 1u; }
         }
-        if (warp == 2 && lane == 0) {
-            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (warp == 2) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            __syncwarp();
             // expert parallel: this CTA's output rows are complete; the last CTA tells every rank
             if (gate.signal_flags != nullptr) ep_gate_signal(gate, (int)gridDim.x);
         }

@@ -277,7 +277,7 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColsK)
                      : "memory");
     }
-    if (gate.signal_flags != nullptr && threadIdx.x == 0) ep_gate_signal(gate, (int)gridDim.x);
+    if (gate.signal_flags != nullptr && warp == 0) ep_gate_signal(gate, (int)gridDim.x);
 }
 
 template <bool SWIGLU>
