@@ -229,6 +229,21 @@ def test_odd_shapes_bf16(oracle, T, d, dff, E, k):
     assert_close_bf16(y, r.y)
 
 
+@pytest.mark.parametrize("T", [5, 16, 40])
+def test_single_expert_layer_bf16(oracle, T):
+    """One expert, top-1: what a GPU of an 8-way expert-parallel Mixtral-shaped layer holds.  Few rows, so the
+    products run with K split over a cluster, and (one local expert) their weights are prefetched to L2 before
+    the routing is known."""
+    d, dff = 512, 1024
+    x, w_r, w_g, w_u, w_d, _ = make_layer(T, d, dff, 1, 1, seed=44)
+    rb = oracle.bf16_round
+    xb, w_rb = rb(x), rb(w_r)
+    r = oracle.moe_forward(xb, w_rb, w_g, w_u, w_d, 1, bf16=True)
+    y, routing, logits, n = run_gpu(xb, w_rb, rb(w_g), rb(w_u), rb(w_d), None, 1, torch.bfloat16, torch.bfloat16)
+    check_routing(routing, logits, r)
+    assert_close_bf16(y, r.y)
+
+
 def test_router_bias_and_raw_gate_weights(oracle):
     """A router bias and renormalize=0 (gate weights are the softmax values themselves)."""
     x, w_r, w_g, w_u, w_d, bias = make_layer(260, 256, 256, 16, 4, seed=32, bias_scale=0.5)
