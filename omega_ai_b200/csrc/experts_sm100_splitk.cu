@@ -87,8 +87,7 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
                            const __grid_constant__ CUtensorMap map_b0,
                            const __grid_constant__ CUtensorMap map_b1, __nv_bfloat16 *__restrict__ out, int n_out,
                            int K, const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ poffsets,
-                           const int32_t *__restrict__ counts, int E, int32_t *dev_err, const EpGate gate,
-                           int prefetch_kb) {
+                           const int32_t *__restrict__ counts, int E, int32_t *dev_err, const EpGate gate) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;  // stages need 1024-byte alignment for the swizzle
@@ -116,24 +115,6 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
         mbar_init(tfull_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    // A GPU that owns ONE expert knows which weights a decode step will stream before the routing is known: if
-    // the expert gets any token at all, its first row tile is tile `cid` of this cluster.  Launched with
-    // programmatic dependent launch this CTA is resident while the routing kernel (count exchange over NVLink,
-    // a few blocks) still runs, so the first prefetch_kb blocks of its slice of K go to L2 meanwhile; a step
-    // that gives the expert no token wasted the prefetch and nothing else.
-    if (prefetch_kb > 0 && E == 1 && warp == 0 && lane == 0) {
-        constexpr int ntw = SWIGLU ? 128 : 256;
-        const int n_tiles_p = (n_out + ntw - 1) / ntw;
-        const int nkb = (K + BLOCK_K - 1) / BLOCK_K;
-        const int p0 = (int)(((long long)nkb * rank) / S), p1 = (int)(((long long)nkb * (rank + 1)) / S);
-        if (cid < n_tiles_p) {
-            const int row0 = cid * ntw, row1 = SWIGLU ? row0 : row0 + 128;
-            for (int kb = p0; kb < p1 && kb < p0 + prefetch_kb; kb++) {
-                tma_prefetch_l2_2d(&map_b0, kb * BLOCK_K, row0);
-                tma_prefetch_l2_2d(&map_b1, kb * BLOCK_K, row1);
-            }
-        }
     }
     if (warp == 2) {  // does any expert hold more than 32 tokens?
         pdl_wait();   // the counts come from the kernel before this one
@@ -345,20 +326,10 @@ cudaError_t launch_splitk(omoe_handle *h, cudaStream_t s, int S, const CUtensorM
     cudaError_t e = prepare_splitk<SWIGLU>(h, S, &cfg, at, &clusters);
     if (e != cudaSuccess) return e;
     cfg.stream = s;
-    // Weight prefetch to L2 ahead of the routing (see the kernel): only the up/gate product, which comes right
-    // after the routing kernel, only with programmatic dependent launch, and at most 96 MB over all CTAs so the
-    // prefetched blocks are still in L2 (126 MB) when the main loop asks for them.
-    int prefetch_kb = 0;
-    static const bool prefetch_off = getenv("OMOE_PREFETCH") && atoi(getenv("OMOE_PREFETCH")) == 0;
-    if (SWIGLU && h->pdl && h->e_local == 1 && !prefetch_off) {
-        const long tiles = (n_out + 127) / 128;
-        const long per_kb = 2L * 128 * BLOCK_K * 2 * tiles;   // bytes one k-block of every tile takes
-        prefetch_kb = (int)((96L << 20) / per_kb);
-    }
     return cudaLaunchKernelEx(&cfg, grouped_gemm_splitk_kernel<SWIGLU>, a, a32, b0, b1,
                               static_cast<__nv_bfloat16 *>(out), n_out, K, (const int32_t *)h->ex_tile_expert,
                               (const int32_t *)h->ex_poffsets, (const int32_t *)h->ex_counts, h->e_local, h->dev_err,
-                              gate ? *gate : EpGate{}, prefetch_kb);
+                              gate ? *gate : EpGate{});
 }
 
 // Number of CTAs to share one tile of a product with `tiles_ub` tiles at most and `num_kb` blocks of K:

@@ -232,8 +232,7 @@ def test_odd_shapes_bf16(oracle, T, d, dff, E, k):
 @pytest.mark.parametrize("T", [5, 16, 40])
 def test_single_expert_layer_bf16(oracle, T):
     """One expert, top-1: what a GPU of an 8-way expert-parallel Mixtral-shaped layer holds.  Few rows, so the
-    products run with K split over a cluster, and (one local expert) their weights are prefetched to L2 before
-    the routing is known."""
+    products run with K split over a cluster."""
     d, dff = 512, 1024
     x, w_r, w_g, w_u, w_d, _ = make_layer(T, d, dff, 1, 1, seed=44)
     rb = oracle.bf16_round
