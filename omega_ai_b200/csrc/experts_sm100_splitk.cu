@@ -250,10 +250,23 @@ grouped_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
                 const int row = i % mv, j = (int)rank * w + i / mv;  // j: output column inside the tile
                 const int oc = nt * kOutCols + j;
                 if (row >= m_valid || oc >= n_out) continue;
+                // all S partials are requested before the first is used (the loads are the latency here); they are
+                // then added in rank order, so the sum keeps its one fixed order
+                float gv[8], uv[8];
+#pragma unroll
+                for (uint32_t s = 0; s < 8; s++) {
+                    if (s < S) {
+                        gv[s] = ld_peer_f32(p0 + 4u * (uint32_t)(j * BLOCK_M + row), s);
+                        if (SWIGLU) uv[s] = ld_peer_f32(p0 + 4u * (uint32_t)((128 + j) * BLOCK_M + row), s);
+                    }
+                }
                 float g = 0.f, u = 0.f;
-                for (uint32_t s = 0; s < S; s++) {
-                    g += ld_peer_f32(p0 + 4u * (uint32_t)(j * BLOCK_M + row), s);
-                    if (SWIGLU) u += ld_peer_f32(p0 + 4u * (uint32_t)((128 + j) * BLOCK_M + row), s);
+#pragma unroll
+                for (uint32_t s = 0; s < 8; s++) {
+                    if (s < S) {
+                        g += gv[s];
+                        if (SWIGLU) u += uv[s];
+                    }
                 }
                 const float v = SWIGLU ? silu_f(g) * u : g;
                 out[(size_t)(mt * BLOCK_M + row) * n_out + oc] = __float2bfloat16_rn(v);
