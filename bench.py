@@ -363,6 +363,28 @@ def mean_stage_ms(layer, n):
     return {a: v / n for a, v in acc.items()}
 
 
+def gpu_local_cpus(torch, local_rank):
+    """CPUs of the NUMA node the GPU hangs off (sysfs), or None when it cannot be told."""
+    try:
+        p = torch.cuda.get_device_properties(local_rank)
+        bdf = "%04x:%02x:%02x.0" % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            spec = f.read().strip()
+        cpus = set()
+        for part in spec.split(","):
+            a, _, b = part.partition("-")
+            cpus.update(range(int(a), int(b or a) + 1))
+        allowed = os.sched_getaffinity(0)
+        cpus &= allowed
+        return cpus or None
+    except Exception:
+        return None
+
+
 def small_case(torch, dist, world, rank, dev, layer, x, steps, barrier, graph=False):
     """Times a short step (decode sweep, extras): 3 regions of `steps` steps, median; then 32 profiled forwards
     back to back for the stage times."""
@@ -577,6 +599,19 @@ def run_ours(args, cfg):
     # are enqueued with omoe_forward_host_async and awaited once with omoe_wait, so the copies of a step overlap
     # the kernels of its neighbours.  `sync_value` is the same loop with a host wait after every step.
     layer.forward_device(x, y)   # y of an inference forward (a training step above may have rounded differently)
+    # Several GPUs copying at once load the host's memory fabric: each rank runs on the CPUs of its GPU's NUMA
+    # node while it allocates and fills its pinned buffers and drives the copies, as a host process feeding one GPU
+    # of a multi-socket box would (the affinity is put back afterwards; nothing on the GPU is set).
+    saved_affinity, numa_bound = None, False
+    if world > 1:
+        cpus = gpu_local_cpus(torch, local_rank)
+        if cpus:
+            try:
+                saved_affinity = os.sched_getaffinity(0)
+                os.sched_setaffinity(0, cpus)
+                numa_bound = True
+            except OSError:
+                saved_affinity = None
     xh = torch.empty((T_local, d), dtype=cdt).pin_memory()
     xh.copy_(x.cpu())
     yh = torch.empty((T_local, d), dtype=cdt).pin_memory()
@@ -607,6 +642,8 @@ def run_ours(args, cfg):
     e2e_sync_ms = statistics.median(e2e_region(False) for _ in range(3))
     e2e_ms = statistics.median(e2e_region(True) for _ in range(3)) if not args.block else e2e_sync_ms
     e2e_value = T / (e2e_ms / e2e_steps * 1e-3)
+    if saved_affinity is not None:
+        os.sched_setaffinity(0, saved_affinity)
 
     # ---- decode sweep (config 5) on the same weights -------------------------------------------------------
     decode = None
@@ -758,7 +795,8 @@ def run_ours(args, cfg):
                 "d2h_bytes_per_step": T_local * d * bpe, "steps": e2e_steps,
                 "how": "omoe_forward_host_async per step + one omoe_wait: each step's H2D and D2H are inside the "
                        "timed region and overlap neighbouring steps' kernels",
-                "sync_value": T / (e2e_sync_ms / e2e_steps * 1e-3), "matches_device_path": e2e_ok},
+                "sync_value": T / (e2e_sync_ms / e2e_steps * 1e-3), "matches_device_path": e2e_ok,
+                "host_threads_on_gpu_numa_node": numa_bound},
         "gpu_launches": launches_per_step * args.steps, "timed_regions": len(ms_all),
     }
     if decode is not None:
