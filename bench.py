@@ -642,6 +642,33 @@ def run_ours(args, cfg):
     e2e_sync_ms = statistics.median(e2e_region(False) for _ in range(3))
     e2e_ms = statistics.median(e2e_region(True) for _ in range(3)) if not args.block else e2e_sync_ms
     e2e_value = T / (e2e_ms / e2e_steps * 1e-3)
+    # What the box's host<->device copies alone cost per step (all ranks copying at once, both directions, no
+    # kernels): the end-to-end step cannot be shorter than this, whatever the library does.
+    copy_floor_ms = None
+    try:
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        x_tmp = torch.empty_like(x)
+        def copies():
+            with torch.cuda.stream(s_in):
+                x_tmp.copy_(xh, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                yh.copy_(y, non_blocking=True)
+        for _ in range(2):
+            copies()
+        barrier()
+        t0c = time.perf_counter()
+        for _ in range(10):
+            copies()
+        torch.cuda.synchronize()
+        dtc = (time.perf_counter() - t0c) * 1e3 / 10
+        if world > 1:
+            t = torch.tensor([dtc], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dtc = float(t.item())
+        copy_floor_ms = dtc
+        del x_tmp
+    except Exception:
+        copy_floor_ms = None
     if saved_affinity is not None:
         os.sched_setaffinity(0, saved_affinity)
 
@@ -796,7 +823,10 @@ def run_ours(args, cfg):
                 "how": "omoe_forward_host_async per step + one omoe_wait: each step's H2D and D2H are inside the "
                        "timed region and overlap neighbouring steps' kernels",
                 "sync_value": T / (e2e_sync_ms / e2e_steps * 1e-3), "matches_device_path": e2e_ok,
-                "host_threads_on_gpu_numa_node": numa_bound},
+                "host_threads_on_gpu_numa_node": numa_bound, "ms_per_step": e2e_ms / e2e_steps,
+                "copies_alone_ms_per_step": copy_floor_ms,
+                "copies_alone": "the same H2D + D2H per step on all ranks at once with no kernels running: a floor "
+                                "the host's copy fabric sets for the end-to-end step"},
         "gpu_launches": launches_per_step * args.steps, "timed_regions": len(ms_all),
     }
     if decode is not None:
