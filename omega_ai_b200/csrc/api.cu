@@ -125,7 +125,6 @@ int omoe_destroy(omoe_handle *h) {
         if (h->ev_set_fwd[i]) cudaEventDestroy(h->ev_set_fwd[i]);
         if (h->ev_set_d2h[i]) cudaEventDestroy(h->ev_set_d2h[i]);
     }
-    if (h->ev_fence) cudaEventDestroy(h->ev_fence);
     if (h->copy_in) cudaStreamDestroy(h->copy_in);
     if (h->copy_out) cudaStreamDestroy(h->copy_out);
     delete h;
@@ -273,8 +272,7 @@ int omoe_create(const omoe_config *cfg, omoe_handle **out) {
         h->host_chunk_min_ep = h->host_chunk_min;
     }
     bool ok_streams = cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking) == cudaSuccess &&
-                      cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking) == cudaSuccess &&
-                      cudaEventCreateWithFlags(&h->ev_fence, cudaEventDisableTiming) == cudaSuccess;
+                      cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking) == cudaSuccess;
     for (int i = 0; ok_streams && i < kHostChunksMax; i++)
         ok_streams = cudaEventCreateWithFlags(&h->ev_in[i], cudaEventDisableTiming) == cudaSuccess &&
                      cudaEventCreateWithFlags(&h->ev_out[i], cudaEventDisableTiming) == cudaSuccess;

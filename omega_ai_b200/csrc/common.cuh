@@ -116,9 +116,8 @@ struct omoe_handle {
     size_t stage_bytes;
     cudaStream_t copy_in, copy_out;
     // per chunk of a call: rows staged on the device / forward done; per staging set: the last call that used it
-    // has consumed the staged rows / has copied its outputs back; ev_fence orders the copy streams behind the
-    // caller's stream
-    cudaEvent_t ev_in[omoe::kHostChunksMax], ev_out[omoe::kHostChunksMax], ev_set_fwd[2], ev_set_d2h[2], ev_fence;
+    // has consumed the staged rows / has copied its outputs back
+    cudaEvent_t ev_in[omoe::kHostChunksMax], ev_out[omoe::kHostChunksMax], ev_set_fwd[2], ev_set_d2h[2];
     int host_chunk_min;     // smallest chunk (tokens) worth its own forward, one GPU
     int host_chunk_min_ep;  // the same with expert parallelism
     bool host_pending;      // an omoe_forward_host_async call has not been waited for yet
