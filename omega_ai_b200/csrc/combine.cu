@@ -65,13 +65,31 @@ combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const OT
     }
     const int cw = ((d / (int)gridDim.y + 7) / 8) * 8;  // blockIdx.y walks one slice of the row
     const int c_lo = blockIdx.y * cw, c_hi = min(d, c_lo + cw);
-    for (int c = c_lo + lane * 8; c < c_hi; c += 256) {
+    // bf16 rows with few picks: the loads of two column chunks are requested before the first is used (the loads,
+    // over NVLink for remote rows, are the latency here); the arithmetic and its order are the same either way
+    constexpr int U = (K > 0 && K <= 4 && sizeof(YT) == 2) ? 2 : 1;
+    for (int c0 = c_lo + lane * 8; c0 < c_hi; c0 += 256 * U) {
+        uint4 raw[U][KR];
+        if constexpr (U == 2) {
+#pragma unroll
+            for (int u = 0; u < U; u++)
+#pragma unroll
+                for (int j = 0; j < KR; j++)
+                    if (j < k && src[j] != nullptr && c0 + u * 256 < c_hi)
+                        raw[u][j] = __ldcs(reinterpret_cast<const uint4 *>(src[j] + c0 + u * 256));
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+        const int c = c0 + u * 256;
+        if (c >= c_hi) break;
         float acc[8];
 #pragma unroll
         for (int j = 0; j < KR; j++) {
             if (j < k) {
                 float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                 if (src[j] == nullptr) {
+                } else if constexpr (U == 2) {
+                    unpack8(raw[u][j], v);
                 } else if constexpr (sizeof(YT) == 2) {
                     uint4 r = __ldcs(reinterpret_cast<const uint4 *>(src[j] + c));
                     unpack8(r, v);
@@ -98,6 +116,7 @@ combine_kernel(void *const *__restrict__ out_table, OT *__restrict__ y, const OT
             o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
             o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
         }
+        }  // u
     }
 }
 

@@ -88,11 +88,21 @@ permute_kernel(const XT *__restrict__ x, void *const *__restrict__ row_table, co
     const XT *src = x + (size_t)t * d;
     if constexpr (sizeof(XT) == sizeof(OT)) {
         constexpr int V = 16 / sizeof(XT);
-        for (int c = c_lo + lane * V; c < c_hi; c += 32 * V) {
-            uint4 v = __ldg(reinterpret_cast<const uint4 *>(src + c));
+        // four 16-byte loads in flight per lane before the first store (the loads are the latency here)
+        for (int c0 = c_lo + lane * V; c0 < c_hi; c0 += 4 * 32 * V) {
+            uint4 v[4];
 #pragma unroll
-            for (int j = 0; j < kMaxTopK; j++)
-                if (j < k && dst[j] != nullptr) *reinterpret_cast<uint4 *>(dst[j] + c) = v;
+            for (int u = 0; u < 4; u++)
+                if (c0 + u * 32 * V < c_hi) v[u] = __ldg(reinterpret_cast<const uint4 *>(src + c0 + u * 32 * V));
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int c = c0 + u * 32 * V;
+                if (c < c_hi) {
+#pragma unroll
+                    for (int j = 0; j < kMaxTopK; j++)
+                        if (j < k && dst[j] != nullptr) *reinterpret_cast<uint4 *>(dst[j] + c) = v[u];
+                }
+            }
         }
     } else {
         // fp32 rows in, bf16 rows out: 8 elements per lane per step
