@@ -6,6 +6,8 @@
 
 #include <new>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "backward.cuh"
 #include "common.cuh"
 #include "ep.cuh"
@@ -41,6 +43,13 @@ cudaError_t dev_alloc(T **p, size_t count) {
 }
 
 size_t elt_size(int dtype) { return dtype == OMOE_BF16 ? 2 : 4; }
+
+// NVTX range over the host side of one entry point (header-only NVTX: a no-op unless a tool is attached), so a
+// timeline shows which launches belong to which call of the layer.
+struct NvtxRange {
+    explicit NvtxRange(const char *name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+};
 
 bool misaligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
 
@@ -355,6 +364,7 @@ int omoe_set_weights(omoe_handle *h, const void *w_router, const void *router_bi
 // forward (the block entry point's RMSNorm).
 static int forward_impl(omoe_handle *h, const void *x_dev, int x_dtype, void *y_dev, int y_dtype, const void *resid,
                         int32_t T, cudaStream_t s, int pre) {
+    NvtxRange range("omoe_forward");
     h->last_T = T;
     h->last_io_dtype = y_dtype;
     h->last_stream = s;
@@ -470,6 +480,7 @@ int omoe_backward(omoe_handle *h, const void *x_dev, const void *dy_dev, void *d
     if (io_dtype != h->last_io_dtype && T > 0)
         return fail(h, OMOE_ERR_INVALID, "omoe_backward: io_dtype differs from the forward's");
     int n = 0;
+    NvtxRange range("omoe_backward");
     if (h->last_resid)
         return fail(h, OMOE_ERR_STATE,
                     "omoe_backward: the last forward was omoe_forward_block; its backward is omoe_backward_block");
@@ -537,6 +548,7 @@ int omoe_ep_connect_local(omoe_handle **handles, int32_t world) {
 // forwards of fewer (or zero) tokens.
 static int forward_host_enqueue(omoe_handle *h, const void *x_host, void *y_host, int32_t T, int32_t io_dtype,
                                 cudaStream_t s, bool chunked) {
+    NvtxRange range("omoe_forward_host");
     const size_t row_bytes = (size_t)h->cfg.d_model * elt_size(io_dtype);
     int chunks = 1;
     if (chunked) {
