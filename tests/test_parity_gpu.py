@@ -403,6 +403,23 @@ def test_few_row_variants_forced_in_a_subprocess(knob):
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
 
 
+@pytest.mark.parametrize("knobs", ["OMOE_DECODE_MMA=0", "OMOE_DECODE_MAX_T=8", "OMOE_DECODE_MAX_T=8 OMOE_DECODE_MMA=0"])
+def test_decode_kernel_variants_forced_in_a_subprocess(knobs):
+    """The weight-streaming products exist twice: staged through per-warp rings of bulk copies (the default) and
+    loaded straight into registers.  By default they serve steps of one or two tokens; raised to 8 tokens, experts
+    hold more rows than one pass folds, so the weights are streamed in several passes.  Every combination must
+    pass the decode cases (odd K: the last chunk of a weight row is short)."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, **dict(kv.split("=") for kv in knobs.split()))
+    cmd = [sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_parity_gpu.py"), "-x", "-q", "-m", "gpu",
+           "-k", "decode_streaming_path or decode_shapes"]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=root)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+
+
 @pytest.mark.parametrize("compute,io", [(torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32),
                                         (torch.float32, torch.float32)])
 @pytest.mark.parametrize("T", [3, 300])
