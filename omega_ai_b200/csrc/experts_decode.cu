@@ -2,16 +2,15 @@
 // kernels.  With one or two rows per expert the tensor-core tiles of
 // experts_sm100.cu would be 99 % padding and, worse, there are too few tiles to
 // keep every SM's share of HBM busy.  Here the work item is one output column
-// (one weight row, or a gate/up pair of rows): a pair of warps streams it once
-// with 16-byte loads, 512 contiguous bytes per warp and load, and folds it
-// against the expert's token rows held in shared memory, so the items spread
-// evenly over all SMs and the kernels run at HBM speed.  Two kernels: one that
-// folds on the CUDA cores (any K, 1-4 token rows per pass) and one that folds
-// with warp-level MMAs and keeps requesting memory while a column is reduced
-// (K a multiple of 512, one or two rows; the default where it applies).  Same
-// arithmetic points as the tensor-core path (bf16 operands, fp32 accumulate, h
-// and yp rounded to bf16); they replace the same reference calls
-// (LlamaMLPLayer.java:117-123).
+// (one weight row, or a gate/up pair of rows), streamed once in 512-byte
+// pieces and folded against the expert's token rows held in shared memory, so
+// the items spread evenly over all SMs and the kernels run at HBM speed.  Two
+// kernels: one that loads into registers and folds on the CUDA cores (1-4
+// token rows per pass) and one that stages the weights through shared-memory
+// rings with bulk copies and folds with warp-level MMAs (one or two rows; the
+// default where it applies).  Same arithmetic points as the tensor-core path
+// (bf16 operands, fp32 accumulate, h and yp rounded to bf16); they replace the
+// same reference calls (LlamaMLPLayer.java:117-123).
 #include <stdlib.h>
 
 #include "common.cuh"
@@ -171,26 +170,31 @@ decode_gemv_kernel(const __nv_bfloat16 *__restrict__ A, const __nv_bfloat16 *__r
 //
 // The kernel above spends 26 (one token row) to 43 (two) instructions per 16 bytes of weights, unpacking bf16
 // pairs and issuing one FMA per element, which makes it issue-bound from two rows on; and after every output
-// column its warps stop requesting memory while they reduce.  This kernel keeps its access pattern (a warp reads
-// 512 contiguous bytes of ONE weight row per load, full 128-byte lines) and hands the arithmetic to
-// `mma.sync.m16n8k16`: lane (g, t) (g = lane/4, t = lane%4) holds 8 consecutive k of the row, which the MMA takes
-// as the B operand's k slots {2t, 2t+1, 2t+8, 2t+9} of "column" g (two MMAs per 16 bytes); the same lane supplies
-// the token's values at the same k as row g (first token) and row g+8 (second token) of the A operand.  Then
-// D[g][g] is the lane group's share of the first token's dot product and D[g+8][g] of the second: the diagonal is
-// what is kept, summed over g at the end of a weight row.  The products off the diagonal are wasted work on a
-// pipe that has nothing else to do.  One load, one or two shared-memory loads and two MMAs per 16 bytes.
+// column its warps stop requesting memory while they reduce.  This kernel keeps the access pattern (512
+// contiguous bytes of ONE weight row at a time) but stages the weights through shared memory with bulk copies
+// and hands the arithmetic to `mma.sync.m16n8k16`.
+//
+// Staging: each of the eight warps owns a ring of three 4 KB stages; lane 0 keeps one `cp.async.bulk` copy
+// (completion on the stage's mbarrier, bounded waits) in flight per stage, the warp folds a stage as soon as it
+// has landed and re-arms it at once, so the next columns' weights are already requested while a column is
+// reduced and stored.  Three stages (96 KB per SM in flight) measured best; deeper rings were slower.
+//
+// Fold: lane (g, t) (g = lane/4, t = lane%4) reads 16 bytes = 8 consecutive k of the weight row, which the MMA
+// takes as the B operand's k slots {2t, 2t+1, 2t+8, 2t+9} of "column" g (two MMAs per 16 bytes); the same lane
+// supplies the token's values at the same k as row g (first token) and row g+8 (second token) of the A operand.
+// Then D[g][g] is the lane group's share of the first token's dot product and D[g+8][g] of the second: the
+// diagonal is what is kept, summed over the lanes at the end of a weight row.  The products off the diagonal
+// are wasted work on a pipe that has nothing else to do.
 //
 // Work split: a block works for ONE expert (the blocks are dealt evenly over the experts that have rows), so the
-// expert's token rows stay in shared memory for the whole launch.  Its 8 warp pairs take the output columns
-// round-robin, each warp of a pair one half of K, and every warp runs a register ring of loads that continues
-// across columns: the next columns' weights are already requested while a column is reduced.  The second warp of
-// a pair leaves its partial sums in one of four shared-memory slots (full/empty mbarriers, bounded waits); the
-// first adds them to its own one column late, applies SiLU·mul and stores.
-constexpr int kMmaWarps = 16;
-constexpr int kMmaThreads = kMmaWarps * 32;
-constexpr int kMmaPairs = kMmaWarps / 2;
-constexpr int kMmaSlots = 4;
-constexpr int kMmaHeader = 4096;  // mbarriers: [pairs][slots] full, then empty (512 B); partial sums from 1024
+// expert's token rows stay in shared memory for the whole launch; its warps take the output columns round-robin
+// and own them whole, so nothing is handed between warps and nothing synchronises once the rows are staged.
+// Any K that is a multiple of 8: a short last piece of a weight row is masked.
+constexpr int kRingWarps = 8;
+constexpr int kRingThreads = kRingWarps * 32;
+constexpr int kRingStageBytes = 4096;
+constexpr int kRingStages = 3;
+constexpr int kRingHeader = 1024;  // mbarriers: kRingWarps * kRingStages * 8 bytes
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 r;
@@ -208,36 +212,38 @@ __device__ __forceinline__ void mma_diag(float (&d)[4], uint32_t a_lo, uint32_t 
         : "r"(a_lo), "r"(b_lo), "r"(a_hi), "r"(b_hi), "r"(w_lo), "r"(w_hi));
 }
 
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 // NT: token rows folded (1 or 2); an expert never holds more when the step has at most NT tokens
 template <bool SWIGLU, int NT>
-__global__ void __launch_bounds__(kMmaThreads, 1)
+__global__ void __launch_bounds__(kRingThreads, 1)
 decode_mma_kernel(const __nv_bfloat16 *__restrict__ A, const __nv_bfloat16 *__restrict__ W0,
-                  const __nv_bfloat16 *__restrict__ W1, __nv_bfloat16 *__restrict__ out, int K, int N,
-                  const int32_t *__restrict__ counts, const int32_t *__restrict__ poffsets, int El,
-                  int32_t *dev_err) {
+                   const __nv_bfloat16 *__restrict__ W1, __nv_bfloat16 *__restrict__ out, int K, int N,
+                   const int32_t *__restrict__ counts, const int32_t *__restrict__ poffsets, int El, int stages,
+                   int32_t *dev_err) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int s_active[kMaxExperts];
     __shared__ int s_n_active;
     __shared__ int s_abort;
     constexpr int CH = SWIGLU ? 2 : 1;
-    constexpr int U = SWIGLU ? 6 : 12;  // 512-byte pieces per operand in flight per warp
+    constexpr int CE = SWIGLU ? kRingStageBytes / 4 : kRingStageBytes / 2;  // elements of K per stage and operand
+    constexpr int UNITS = CE / 256;                                          // 512-byte pieces per stage and operand
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int pair = warp >> 1, half = warp & 1;
     const uint32_t smem0 = sm100::smem_u32(smem_raw);
-    const uint32_t bar_full = smem0 + pair * kMmaSlots * 8;
-    const uint32_t bar_empty = smem0 + 256 + pair * kMmaSlots * 8;
-    // partial sums: [pair][slot][half][CH][NT]
-    float *part = reinterpret_cast<float *>(smem_raw + 1024) + (size_t)pair * kMmaSlots * 2 * CH * NT;
-    __nv_bfloat16 *rows_p = reinterpret_cast<__nv_bfloat16 *>(smem_raw + kMmaHeader);  // [NT][K]
-    const uint32_t rows = smem0 + kMmaHeader;
-
+    const uint32_t bars = smem0 + warp * kRingStages * 8;
+    const uint32_t ring = smem0 + kRingHeader + warp * stages * kRingStageBytes;
+    const uint32_t rows = smem0 + kRingHeader + kRingWarps * stages * kRingStageBytes;  // [NT][K] bf16
+    __nv_bfloat16 *rows_p = reinterpret_cast<__nv_bfloat16 *>(smem_raw + kRingHeader +
+                                                               (size_t)kRingWarps * stages * kRingStageBytes);
     pdl_trigger();
-    if (tid < kMmaPairs * kMmaSlots) {
-        sm100::mbar_init(smem0 + tid * 8, 1);
-        sm100::mbar_init(smem0 + 256 + tid * 8, 1);
-    }
+    if (lane == 0)
+        for (int s = 0; s < stages; s++) sm100::mbar_init(bars + s * 8, 1);
     if (tid == 0) s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     pdl_wait();
@@ -262,14 +268,41 @@ decode_mma_kernel(const __nv_bfloat16 *__restrict__ A, const __nv_bfloat16 *__re
     const int m = counts[e];
     const int mr = m < NT ? m : NT;
     const int row0 = poffsets[e];
-    const int nu = K / 512;                                       // 512-byte pieces of half a weight row
-    const int cnt = n1 - n0 > pair ? (n1 - n0 - pair + kMmaPairs - 1) / kMmaPairs : 0;  // this pair's columns
-    const int total = cnt * nu;
-    const size_t first = ((size_t)e * N + n0 + pair) * K + (size_t)half * (K / 2) + lane * 8;
-    const uint4 *lp0 = reinterpret_cast<const uint4 *>(W0 + first);
-    const uint4 *lp1 = SWIGLU ? reinterpret_cast<const uint4 *>(W1 + first) : nullptr;
-    const int row_jump = (kMmaPairs * K * 2 - K) / 16;             // from the end of a half row to the next column's
-    uint32_t xaddr = rows + (uint32_t)(half * (K / 2) + lane * 8) * 2;
+
+    const int nch = (K + CE - 1) / CE;  // stages per column
+    const int cnt = n1 - n0 > warp ? (n1 - n0 - warp + kRingWarps - 1) / kRingWarps : 0;  // this warp's columns
+    const int total = cnt * nch;
+    const __nv_bfloat16 *w0 = W0 + ((size_t)e * N + n0 + warp) * K;
+    const __nv_bfloat16 *w1 = SWIGLU ? W1 + ((size_t)e * N + n0 + warp) * K : nullptr;
+
+    // lane 0's issue cursor: chunk i_ch of the column at w0/w1 goes into stage i_stage
+    int i_ch = 0, i_stage = 0, issued = 0;
+    auto issue_one = [&]() {
+        const int k0 = i_ch * CE;
+        const uint32_t bytes = (uint32_t)((K - k0 < CE ? K - k0 : CE) * 2);
+        const uint32_t bar = bars + i_stage * 8;
+        const uint32_t dst = ring + i_stage * kRingStageBytes;
+        sm100::mbar_expect_tx(bar, SWIGLU ? 2 * bytes : bytes);
+        bulk_load(dst, w0 + k0, bytes, bar);
+        if (SWIGLU) bulk_load(dst + kRingStageBytes / 2, w1 + k0, bytes, bar);
+        if (++i_ch == nch) {
+            i_ch = 0;
+            w0 += (size_t)kRingWarps * K;
+            if (SWIGLU) w1 += (size_t)kRingWarps * K;
+        }
+        if (++i_stage == stages) i_stage = 0;
+        issued++;
+    };
+    if (lane == 0)
+        while (issued < total && issued < stages) issue_one();
+    // the token rows come in while the first weights are on their way
+    for (int i = tid; i < NT * (K / 8); i += kRingThreads) {
+        int r = i / (K / 8), c = i % (K / 8);
+        // a missing second row is read as zeros
+        reinterpret_cast<uint4 *>(rows_p + (size_t)r * K)[c] =
+            r < mr ? reinterpret_cast<const uint4 *>(A + (size_t)(row0 + r) * K)[c] : make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();
 
     float acc[CH][2][4];
 #pragma unroll
@@ -278,123 +311,79 @@ decode_mma_kernel(const __nv_bfloat16 *__restrict__ A, const __nv_bfloat16 *__re
         for (int s = 0; s < 2; s++)
 #pragma unroll
             for (int j = 0; j < 4; j++) acc[c][s][j] = 0.f;
-
-    // first warp of the pair: column j of this pair is complete in slot j % kMmaSlots; finish and store it
-    auto combine = [&](int j) -> bool {
-        const int b = j & (kMmaSlots - 1);
-        if (!__all_sync(0xffffffffu, sm100::mbar_wait(bar_full + b * 8, (uint32_t)(j / kMmaSlots) & 1u, &s_abort, dev_err)))
-            return false;
-        __syncwarp();
-        if (lane < mr) {
-            const float *p0 = part + (size_t)(b * 2 + 0) * CH * NT, *p1 = part + (size_t)(b * 2 + 1) * CH * NT;
-            float v = p0[lane] + p1[lane];
-            if (SWIGLU) v = __fdividef(v, 1.0f + __expf(-v)) * (p0[NT + lane] + p1[NT + lane]);
-            out[(size_t)(row0 + lane) * N + n0 + pair + j * kMmaPairs] = __float2bfloat16_rn(v);
-        }
-        __syncwarp();
-        if (lane == 0) sm100::mbar_arrive(bar_empty + b * 8);
-        return true;
-    };
-    // this warp's half of column i is folded: pick the diagonal, sum it over the lanes, leave it in the slot
-    auto row_end = [&](int i) -> bool {
-        const int b = i & (kMmaSlots - 1);
-        float v[CH][NT];
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    int c_stage = 0, ch = 0, col = 0;
+    uint32_t c_parity = 0;
+    int c = 0;
+    for (; c < total; c++) {
+        // one verdict for the whole warp: the lanes poll on their own and must not part ways here
+        if (!__all_sync(0xffffffffu, sm100::mbar_wait(bars + c_stage * 8, c_parity, &s_abort, dev_err))) break;
+        const int k0 = ch * CE;
+        const int left8 = (K - k0) / 8 - lane;  // 16-byte pieces of the row from this lane's first one on
+        const uint32_t st = ring + c_stage * kRingStageBytes + lane * 16;
+        const uint32_t xa = rows + (uint32_t)(k0 + lane * 8) * 2;
 #pragma unroll
-        for (int c = 0; c < CH; c++) {
-            const bool mine = t == (g >> 1);
-            const bool odd = g & 1;
-            const float d0 = acc[c][0][0] + acc[c][1][0], d1 = acc[c][0][1] + acc[c][1][1];
-            v[c][0] = mine ? (odd ? d1 : d0) : 0.f;
-            if (NT > 1) {
-                const float d2 = acc[c][0][2] + acc[c][1][2], d3 = acc[c][0][3] + acc[c][1][3];
-                v[c][NT - 1] = mine ? (odd ? d3 : d2) : 0.f;
+        for (int u = 0; u < UNITS; u++) {
+            const bool in = u * 32 < left8;
+            const uint4 q0 = in ? lds128(st + u * 512) : zero4;
+            const uint4 x0 = in ? lds128(xa + u * 512) : zero4;
+            uint4 x1 = zero4;
+            if (NT > 1 && in) x1 = lds128(xa + u * 512 + (uint32_t)K * 2);
+            mma_diag(acc[0][0], x0.x, x1.x, x0.y, x1.y, q0.x, q0.y);
+            mma_diag(acc[0][1], x0.z, x1.z, x0.w, x1.w, q0.z, q0.w);
+            if (SWIGLU) {
+                const uint4 q1 = in ? lds128(st + kRingStageBytes / 2 + u * 512) : zero4;
+                mma_diag(acc[CH - 1][0], x0.x, x1.x, x0.y, x1.y, q1.x, q1.y);
+                mma_diag(acc[CH - 1][1], x0.z, x1.z, x0.w, x1.w, q1.z, q1.w);
             }
-#pragma unroll
-            for (int s = 0; s < 2; s++)
-#pragma unroll
-                for (int j = 0; j < 4; j++) acc[c][s][j] = 0.f;
-#pragma unroll
-            for (int r = 0; r < NT; r++)
-#pragma unroll
-                for (int o = 16; o >= 1; o >>= 1) v[c][r] += __shfl_xor_sync(0xffffffffu, v[c][r], o);
         }
-        if (half == 1 && i >= kMmaSlots &&
-            !__all_sync(0xffffffffu, sm100::mbar_wait(bar_empty + b * 8, (uint32_t)(i / kMmaSlots - 1) & 1u, &s_abort, dev_err)))
-            return false;
-        if (lane == 0) {
-            float *p = part + (size_t)(b * 2 + half) * CH * NT;
-#pragma unroll
-            for (int c = 0; c < CH; c++)
-#pragma unroll
-                for (int r = 0; r < NT; r++) p[c * NT + r] = v[c][r];
-            if (half == 1) sm100::mbar_arrive(bar_full + b * 8);
+        __syncwarp();
+        if (lane == 0 && issued < total) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the stage was read; a copy overwrites it
+            issue_one();
         }
-        if (half == 0 && i >= 1) return combine(i - 1);
-        return true;
-    };
-
-    int l_left = nu, c_left = nu, c_row = 0, loaded = 0, done = 0;
-    uint4 q0[U], q1[SWIGLU ? U : 1];
-    auto load_unit = [&](uint4 &a, uint4 &b) {
-        a = ld_stream(lp0);
-        lp0 += 32;
-        if (SWIGLU) { b = ld_stream(lp1); lp1 += 32; }
-        if (--l_left == 0) {
-            l_left = nu;
-            lp0 += row_jump;
-            if (SWIGLU) lp1 += row_jump;
-        }
-        loaded++;
-    };
-    auto fold_unit = [&](const uint4 &a, const uint4 &b) -> bool {
-        const uint4 x0 = lds128(xaddr);
-        uint4 x1 = make_uint4(0u, 0u, 0u, 0u);
-        if (NT > 1) x1 = lds128(xaddr + (uint32_t)K * 2);
-        xaddr += 512;
-        mma_diag(acc[0][0], x0.x, x1.x, x0.y, x1.y, a.x, a.y);
-        mma_diag(acc[0][1], x0.z, x1.z, x0.w, x1.w, a.z, a.w);
-        if (SWIGLU) {
-            mma_diag(acc[CH - 1][0], x0.x, x1.x, x0.y, x1.y, b.x, b.y);
-            mma_diag(acc[CH - 1][1], x0.z, x1.z, x0.w, x1.w, b.z, b.w);
-        }
-        done++;
-        if (--c_left == 0) {
-            c_left = nu;
-            xaddr -= (uint32_t)nu * 512;
-            return row_end(c_row++);
-        }
-        return true;
-    };
-
+        if (++c_stage == stages) { c_stage = 0; c_parity ^= 1u; }
+        if (++ch == nch) {
+            ch = 0;
+            // the column is folded: pick the diagonal, sum it over the lanes, finish and store
+            float v[CH][NT];
 #pragma unroll
-    for (int u = 0; u < U; u++)
-        if (u < total) load_unit(q0[u], q1[SWIGLU ? u : 0]);
-    // the token rows come in while the first weights are on their way
-    for (int i = tid; i < NT * (K / 8); i += kMmaThreads) {
-        int r = i / (K / 8), c = i % (K / 8);
-        // a missing second row is read as zeros
-        reinterpret_cast<uint4 *>(rows_p + (size_t)r * K)[c] =
-            r < mr ? reinterpret_cast<const uint4 *>(A + (size_t)(row0 + r) * K)[c] : make_uint4(0u, 0u, 0u, 0u);
-    }
-    __syncthreads();
-    while (loaded + U <= total) {  // whole rounds of the ring: no bounds to check
+            for (int cc = 0; cc < CH; cc++) {
+                const bool mine = t == (g >> 1);
+                const bool odd = g & 1;
+                const float d0 = acc[cc][0][0] + acc[cc][1][0], d1 = acc[cc][0][1] + acc[cc][1][1];
+                v[cc][0] = mine ? (odd ? d1 : d0) : 0.f;
+                if (NT > 1) {
+                    const float d2 = acc[cc][0][2] + acc[cc][1][2], d3 = acc[cc][0][3] + acc[cc][1][3];
+                    v[cc][NT - 1] = mine ? (odd ? d3 : d2) : 0.f;
+                }
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            if (!fold_unit(q0[u], q1[SWIGLU ? u : 0])) return;
-            load_unit(q0[u], q1[SWIGLU ? u : 0]);
+                for (int s = 0; s < 2; s++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc[cc][s][j] = 0.f;
+#pragma unroll
+                for (int r = 0; r < NT; r++)
+#pragma unroll
+                    for (int o = 16; o >= 1; o >>= 1) v[cc][r] += __shfl_xor_sync(0xffffffffu, v[cc][r], o);
+            }
+            if (lane < mr) {
+                float a = lane == 0 ? v[0][0] : v[0][NT - 1];
+                if (SWIGLU) a = __fdividef(a, 1.0f + __expf(-a)) * (lane == 0 ? v[CH - 1][0] : v[CH - 1][NT - 1]);
+                out[(size_t)(row0 + lane) * N + n0 + warp + col * kRingWarps] = __float2bfloat16_rn(a);
+            }
+            col++;
         }
     }
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-        if (done < total) {
-            if (!fold_unit(q0[u], q1[SWIGLU ? u : 0])) return;
-            if (loaded < total) load_unit(q0[u], q1[SWIGLU ? u : 0]);
+    if (c < total) {
+        // a wait ran out (the error word is set): let this warp's copies in flight land, each wait bounded again,
+        // before the block's shared memory can go to another block
+        int pending = __shfl_sync(0xffffffffu, issued, 0) - c;
+        for (; pending > 0; pending--) {
+            const unsigned long long t0 = sm100::globaltimer_ns();
+            while (!sm100::mbar_try_wait(bars + c_stage * 8, c_parity) && sm100::globaltimer_ns() - t0 < sm100::kWaitNs) {}
+            if (++c_stage == stages) { c_stage = 0; c_parity ^= 1u; }
         }
     }
-#pragma unroll
-    for (int u = 0; u < U; u++)
-        if (done < total && !fold_unit(q0[u], q1[SWIGLU ? u : 0])) return;
-    if (half == 0 && cnt > 0) combine(cnt - 1);
 }
 
 }  // namespace
@@ -434,23 +423,28 @@ cudaError_t launch_gemv(omoe_handle *h, const void *A, const void *W0, const voi
                      h->ex_poffsets, h->e_local);
 }
 
-// Shared memory of decode_mma_kernel for `nt` token rows of length K; 0 when it does not fit.
-size_t mma_smem(int nt, int K) {
-    const size_t need = kMmaHeader + (size_t)nt * K * 2;
-    return need <= 224 * 1024 ? need : 0;
+// Stages per warp of decode_mma_kernel beside `nt` token rows of length K: kRingStages, or 2 when the rows leave
+// less room; 0 when not even two fit.
+int mma_stages(int nt, int K) {
+    const long budget = 224 * 1024 - kRingHeader - (long)nt * K * 2;
+    long st = budget / ((long)kRingWarps * kRingStageBytes);
+    if (st > kRingStages) st = kRingStages;
+    return st < 2 ? 0 : (int)st;
 }
 
 template <bool SWIGLU, int NT>
 cudaError_t launch_mma(omoe_handle *h, const void *A, const void *W0, const void *W1, void *out, int K, int N,
                        cudaStream_t s) {
     auto kern = decode_mma_kernel<SWIGLU, NT>;
-    const size_t smem = mma_smem(NT, K);
+    const int stages = mma_stages(NT, K);
+    const size_t smem = kRingHeader + (size_t)kRingWarps * stages * kRingStageBytes + (size_t)NT * K * 2;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int sms = h->sm_count > 0 ? h->sm_count : 148;
-    return launch_ex(kern, dim3(sms), dim3(kMmaThreads), smem, s, h->pdl, static_cast<const __nv_bfloat16 *>(A),
+    return launch_ex(kern, dim3(sms), dim3(kRingThreads), smem, s, h->pdl, static_cast<const __nv_bfloat16 *>(A),
                      static_cast<const __nv_bfloat16 *>(W0), static_cast<const __nv_bfloat16 *>(W1),
-                     static_cast<__nv_bfloat16 *>(out), K, N, h->ex_counts, h->ex_poffsets, h->e_local, h->dev_err);
+                     static_cast<__nv_bfloat16 *>(out), K, N, h->ex_counts, h->ex_poffsets, h->e_local, stages,
+                     h->dev_err);
 }
 
 // OMOE_DECODE_MMA=0 keeps the CUDA-core kernels (decode_gemv_kernel)
@@ -467,11 +461,9 @@ template <int RP>
 cudaError_t launch_both(omoe_handle *h, int T, cudaStream_t s, int *n, cudaEvent_t mid) {
     const int d = h->cfg.d_model, dff = h->cfg.d_ff;
     const int sms = h->sm_count > 0 ? h->sm_count : 148;
-    // decode_mma_kernel: one or two token rows, every expert with rows gets blocks of its own, and a warp walks
-    // half a weight row in 512-byte pieces
+    // decode_mma_kernel: one or two token rows, and every expert with rows gets blocks of its own
     constexpr int NT = RP <= 1 ? 1 : 2;
-    const bool mma = mma_enabled() && RP <= 2 && (long)T * h->cfg.top_k <= sms && d % 512 == 0 && dff % 512 == 0 &&
-                     mma_smem(NT, d) && mma_smem(NT, dff);
+    const bool mma = mma_enabled() && RP <= 2 && (long)T * h->cfg.top_k <= sms && mma_stages(NT, d) && mma_stages(NT, dff);
     cudaError_t e = mma ? launch_mma<true, NT>(h, h->xp, h->w_gate, h->w_up, h->hbuf, d, dff, s)
                         : launch_gemv<true, RP>(h, h->xp, h->w_gate, h->w_up, h->hbuf, d, dff, s);
     if (e != cudaSuccess) return e;
