@@ -212,6 +212,24 @@ def test_decode_streaming_path_bf16(oracle, T, E, k):
     assert_close_bf16(y, r.y)
 
 
+@pytest.mark.parametrize("T,d,dff", [
+    (2, 36864, 64),    # two token rows of this width leave room for two ring stages per warp, not three
+    (1, 36864, 64),
+    (2, 45056, 64),    # and of this width for none: the register-streaming kernel serves the step
+    (2, 64, 36864),    # the wide side is the down product's K
+])
+def test_decode_wide_layers_bf16(oracle, T, d, dff):
+    """Streaming products on very wide layers: fewer ring stages, or the other kernel; K of 64 is one short piece."""
+    x, w_r, w_g, w_u, w_d, _ = make_layer(T, d, dff, 4, 2, seed=17)
+    rb = oracle.bf16_round
+    xb, w_rb = rb(x), rb(w_r)
+    r = oracle.moe_forward(xb, w_rb, w_g, w_u, w_d, 2, bf16=True)
+    y, routing, logits, n = run_gpu(xb, w_rb, rb(w_g), rb(w_u), rb(w_d), None, 2, torch.bfloat16, torch.bfloat16,
+                                    t_max=8)
+    check_routing(routing, logits, r)
+    assert_close_bf16(y, r.y)
+
+
 @pytest.mark.parametrize("T,d,dff,E,k", [
     (200, 328, 200, 8, 2),     # K and N not multiples of the 64/128/256 tile sizes (tails come from TMA bounds)
     (77, 64, 64, 4, 1),        # smallest bf16 shapes, top-1
