@@ -199,7 +199,7 @@ def test_errors_are_reported_not_fatal():
         MoELayer(128, 256, 8, 9)  # top_k > experts
 
 
-@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (2, 8, 2), (5, 8, 2), (8, 8, 2), (7, 64, 6)])
+@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (2, 8, 2), (3, 8, 2), (4, 8, 2), (5, 8, 2), (8, 8, 2), (7, 64, 6), (4, 64, 6)])
 def test_decode_streaming_path_bf16(oracle, T, E, k):
     """T <= 8 takes the weight-streaming expert kernels; odd sizes exercise the K split and row passes."""
     x, w_r, w_g, w_u, w_d, _ = make_layer(T, 520, 1096, E, k, seed=13)
