@@ -18,7 +18,7 @@ What the line carries beyond the contract:
   * ``parity``: checksums of the bit patterns of y and of the routing indices in global token order, reduced
     over the ranks (the rows are drawn from the global token index, so every GPU count must print the same
     sums), and ``oracle_ok``: rank 0 checks a few of its tokens against the CPU oracle;
-  * ``decode``: the small-token sweep (T = 1, 8, 64, 256 on one GPU; T = 64 expert-parallel) on the same
+  * ``decode``: the small-token sweep (T = 1, 2, 8, 64, 256 on one GPU; T = 64 expert-parallel) on the same
     weights, against the HBM roofline; ``extras``: the mid-size and the 64-expert configurations.
 
 Options beyond the contract: ``--tokens`` (override T), ``--weak`` (weak scaling), ``--graph`` (time replays of
@@ -676,7 +676,7 @@ def run_ours(args, cfg):
     decode = None
     if decode_layer is not None:
         decode = []
-        for Td in ((1, 8, 64, 256) if world == 1 else (64,)):
+        for Td in ((1, 2, 8, 64, 256) if world == 1 else (64,)):
             dlo, dhi = shard_tokens(Td, world, rank)
             xd = global_rows(torch, dev, dlo, dhi, d, cdt, SEED + 1000 + Td)
             ms_d, st, n_launch, graph_ms = small_case(torch, dist, world, rank, dev, decode_layer, xd, 200, barrier,

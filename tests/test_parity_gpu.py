@@ -391,7 +391,7 @@ def decode_layer():
 
 
 @pytest.mark.slow
-@pytest.mark.parametrize("T", [1, 8, 64, 256])
+@pytest.mark.parametrize("T", [1, 2, 8, 64, 256])
 def test_config5_full_size_decode(oracle, decode_layer, T):
     layer, (w_r, w_g, w_u, w_d) = decode_layer
     g = torch.Generator(device="cuda").manual_seed(100 + T)
