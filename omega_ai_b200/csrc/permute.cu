@@ -27,13 +27,6 @@ scan_kernel(const int32_t *__restrict__ block_counts, int32_t *__restrict__ bloc
     scan_body(block_counts, block_base, n_blocks, E, counts, offsets, poffsets, tile_expert, max_tiles, s_cnt, s_poff);
 }
 
-template <typename T>
-struct Vec16 {};
-template <>
-struct Vec16<float> { static constexpr int n = 4; };
-template <>
-struct Vec16<__nv_bfloat16> { static constexpr int n = 8; };
-
 // One warp per token: finalise the k row positions, read the token's row once
 // and write it to its k places with 16-byte stores.
 // Rows go to the dispatch buffer of the rank that owns the expert: row_table[q]
