@@ -316,7 +316,7 @@ decode_mma_kernel(const __nv_bfloat16 *__restrict__ A, const __nv_bfloat16 *__re
     uint32_t c_parity = 0;
     int c = 0;
     for (; c < total; c++) {
-        // one verdict for the whole warp: the lanes poll on their own and must not part ways here
+        // one answer for the whole warp: the lanes poll on their own and must not part ways here
         if (!__all_sync(0xffffffffu, sm100::mbar_wait(bars + c_stage * 8, c_parity, &s_abort, dev_err))) break;
         const int k0 = ch * CE;
         const int left8 = (K - k0) / 8 - lane;  // 16-byte pieces of the row from this lane's first one on
